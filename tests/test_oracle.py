@@ -1,0 +1,90 @@
+"""Pins the CPU oracle to vectors produced by the reference's own fastmax_function."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, case_kwargs, load_small_cases
+from oracle.fastmax_oracle import fastmax_dense, fastmax_fwd_bwd, fastmax_moments, rel_err
+
+CASES = load_small_cases()
+
+
+def tol64(c):
+    """fp64 agreement bound.  The reference builds the a0*count term of the
+    denominator from a float32 ``torch.ones`` (reference example.py:132,155), so
+    for an a0 that float32 cannot hold exactly (the ``_b`` cases use 0.7) its
+    fp64 run carries a ~1e-8 relative rounding that the oracle does not copy."""
+    return 1e-11 if c["a0"] == 1.0 else 1e-6
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_moments_oracle_matches_reference_fp64(c):
+    q, k, v, go = [c[x].double() for x in ("q", "k", "v", "go")]
+    out, dq, dk, dv = fastmax_fwd_bwd(q, k, v, go, **case_kwargs(c))
+    for got, name in ((out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert rel_err(got, c[name + "64"]) < tol64(c), name
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_blocked_scan_equals_full_cumsum(c):
+    if not c["mask"]:
+        pytest.skip("unmasked has no scan")
+    q, k, v, go = [c[x].double() for x in ("q", "k", "v", "go")]
+    res = fastmax_fwd_bwd(q, k, v, go, block=7, **case_kwargs(c))
+    for got, name in zip(res, ("out", "dq", "dk", "dv")):
+        assert rel_err(got, c[name + "64"]) < tol64(c), name
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_dense_oracle_matches_reference_fp64(c):
+    q, k, v, go = [c[x].double() for x in ("q", "k", "v", "go")]
+    res = fastmax_fwd_bwd(q, k, v, go, dense=True, **case_kwargs(c))
+    for got, name in zip(res, ("out", "dq", "dk", "dv")):
+        assert rel_err(got, c[name + "64"]) < max(1e-9, tol64(c)), name
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_oracle_fp32_close_to_reference_fp32(c):
+    res = fastmax_fwd_bwd(c["q"], c["k"], c["v"], c["go"], **case_kwargs(c))
+    for got, name in zip(res, ("out", "dq", "dk", "dv")):
+        # both sides are fp32 evaluations of the same formula; they agree to rounding
+        assert rel_err(got, c[name + "32"]) < 2e-4, name
+        assert rel_err(got, c[name + "64"]) < 2e-4, name
+
+
+def test_c1_configuration_sampled_rows():
+    z = np.load(os.path.join(GOLDEN, "c1_sampled.npz"))
+    b, h, n, d = [int(x) for x in z["cfg"][:4]]
+    g = torch.Generator().manual_seed(int(z["seed"]))
+    q, k, v, go = [torch.randn(b, h, n, d, generator=g) for _ in range(4)]
+    chk = np.array([float(t.double().sum()) for t in (q, k, v, go)])
+    if not np.allclose(chk, z["input_checksum"], rtol=0, atol=1e-6):
+        pytest.skip("torch RNG stream differs from the one the fixture was made with")
+    res = fastmax_fwd_bwd(q.double(), k.double(), v.double(), go.double(),
+                          mask=0, normalize=1, p=2)
+    st = int(z["row_stride"])
+    for got, name in zip(res, ("out", "dq", "dk", "dv")):
+        pick = torch.stack([got[bb, hh, ::st] for bb, hh in z["heads"]])
+        ref = torch.from_numpy(z[name + "64"])
+        assert float((pick - ref).abs().max()) < 1e-11 * float(z[name + "64_absmax"]), name
+
+
+def test_temperature_is_ignored_and_bad_p_raises():
+    c = CASES[0]
+    a = fastmax_moments(c["q"], c["k"], c["v"], temperature=1.0, p=2)
+    b = fastmax_moments(c["q"], c["k"], c["v"], temperature=7.5, p=2)
+    assert torch.equal(a, b)
+    with pytest.raises(ValueError):
+        fastmax_moments(c["q"], c["k"], c["v"], p=3)
+    with pytest.raises(ValueError):
+        fastmax_dense(c["q"], c["k"], c["v"], p=0)
+
+
+def test_dense_rows_subset():
+    c = [x for x in CASES if x["tag"] == "m1p2n1_d32"][0]
+    q, k, v = [c[x].double() for x in ("q", "k", "v")]
+    rows = [0, 3, 69]
+    part = fastmax_dense(q, k, v, rows=rows, **case_kwargs(c))
+    assert rel_err(part, c["out64"][:, :, rows]) < 1e-10
