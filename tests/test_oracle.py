@@ -50,8 +50,10 @@ def test_oracle_fp32_close_to_reference_fp32(c):
     res = fastmax_fwd_bwd(c["q"], c["k"], c["v"], c["go"], **case_kwargs(c))
     for got, name in zip(res, ("out", "dq", "dk", "dv")):
         # both sides are fp32 evaluations of the same formula; they agree to rounding
-        assert rel_err(got, c[name + "32"]) < 2e-4, name
-        assert rel_err(got, c[name + "64"]) < 2e-4, name
+        for ref in (c[name + "32"], c[name + "64"]):
+            diff = float((got.double() - ref.double()).abs().max())
+            # absolute floor: the n=1 gradients of q and k are exactly zero
+            assert diff <= 2e-4 * float(ref.abs().max()) + 1e-6, name
 
 
 def test_c1_configuration_sampled_rows():
