@@ -1,0 +1,321 @@
+"""Fastmax forward+backward throughput on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one forward + backward pass of Fastmax attention over one batch of
+synthetic N(0,1) inputs.  The workload is the configuration the headline target
+is quoted on: causal, bf16, p=2, B=64, H=16, N=10000, D=64, normalize=True,
+lim=1, a=(1,1,0.5).  With N GPUs every rank runs that workload on its own shard
+of an N-times larger batch (batch*head units are independent; no collective on
+the data path), so `value` is total tokens of all ranks over the slowest rank's
+device time ("weak" scaling); `--scaling strong` splits the single batch's
+batch*head units over the ranks instead.
+
+Rank 0 prints one JSON line.  `value` is measured with the inputs resident in
+HBM; `e2e` is the same metric through the public module with pinned host
+buffers, host<->device copies inside the timed region.  `--impl reference` times
+the CPU restatement of the reference's PyTorch path (oracle/) on the host
+cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, N, D, dtype, mask, p, normalize)
+    "c3": (64, 16, 10000, 64, "bf16", 1, 2, 1),
+    "c2": (64, 8, 1000, 32, "fp32", 1, 2, 1),
+    "c4p2": (32, 32, 16384, 128, "bf16", 0, 2, 0),
+    "c4p1": (32, 32, 16384, 128, "bf16", 0, 1, 0),
+    "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
+}
+A = dict(a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+
+
+def describe(name):
+    B, H, N, D, dt, mask, p, norm = WORKLOADS[name]
+    return (f"{name}: {'causal' if mask else 'unmasked'} {dt} p={p} B={B} H={H} N={N} D={D} "
+            f"normalize={bool(norm)} lim=1 a=(1,1,0.5)")
+
+
+def alg_flops_per_token_head(D, p):
+    """Algorithmic FLOPs of the factorised evaluation, per token and head:
+    (forward, grad_q pass, grad_k+grad_v pass) = (4, 4, 6) * F * (D+1), F = D + [p=2] D^2."""
+    F = D + (D * D if p == 2 else 0)
+    u = F * (D + 1)
+    return 4 * u, 4 * u, 6 * u
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        z = json.load(open(path))
+        return {"hbm_gbs": z["hbm_gbs"], "bf16_tflops": z["bf16_tflops"],
+                "bf16_tflops_sustained": z.get("bf16_tflops_sustained", z["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_sample(name, steps, warmup):
+    """Time the oracle (CPU restatement of the reference's PyTorch path) on one
+    head of the workload at a sequence length it can hold in memory; the
+    factorised evaluation is linear in n, so tokens/s per head carries over."""
+    import torch
+
+    from oracle.fastmax_oracle import fastmax_moments
+
+    B, H, N, D, dt, mask, p, norm = WORKLOADS[name]
+    n = min(N, 1024 if D >= 64 else 2048)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(1234)
+    q, k, v, go = [torch.randn(1, 1, n, D, generator=g) for _ in range(4)]
+    if dt == "bf16":
+        q, k, v, go = [t.bfloat16().float() for t in (q, k, v, go)]
+    times = []
+    for it in range(warmup + steps):
+        qq, kk, vv = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        t0 = time.perf_counter()
+        out = fastmax_moments(qq, kk, vv, mask=mask, normalize=norm, p=p, **A)
+        out.backward(go)
+        dtm = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dtm)
+    t = statistics.median(times)
+    # whole-job tokens/s: a token counts once for all H heads
+    value = (n / t) / H
+    return {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"1 of {B * H} batch*head units, first {n} of {N} tokens, fp32 math, "
+                      f"median of {steps} fwd+bwd ({t:.2f} s each), scaled by 1/H"}, t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb, t = cpu_sample(args.workload, max(1, min(args.steps, 5)), max(1, min(args.warmup, 1)))
+    line = {"impl": "reference", "metric": "fastmax_fwd_bwd_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": describe(args.workload)},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import fastmax_b200
+    from fastmax_b200 import _cabi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, H, N, D, dt, mask, p, norm = WORKLOADS[args.workload]
+    dtype = torch.bfloat16 if dt == "bf16" else torch.float32
+    bh_total = B * H
+    if args.scaling == "strong":
+        bh = bh_total // world + (1 if rank < bh_total % world else 0)
+        tokens_job = B * N
+    else:
+        bh = bh_total
+        tokens_job = B * N * world
+    kw = dict(mask=bool(mask), normalize=bool(norm), p=p, **A)
+
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v, go = [torch.randn(bh, N, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4)]
+
+    def step():
+        out, den, stats = _cabi.forward(q, k, v, **kw)
+        return out, _cabi.backward(q, k, v, out, den, stats, go, **kw)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    _cabi.profile(True)
+    n0 = _cabi.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        res = step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = _cabi.launch_count() - n0
+    recs = _cabi.profile_records()
+    _cabi.profile(False)
+    clocks = sampler.stop() if rank == 0 else None
+    tms = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    value = tokens_job * args.steps / (ms * 1e-3)
+
+    # ---- end to end through the public module, host buffers ----------------------
+    mod = fastmax_b200.FASTMultiHeadAttention()
+    del res
+    host_in = [t.cpu().pin_memory() for t in (q, k, v, go)]
+    host_out = [torch.empty_like(h) for h in host_in]
+    del q, k, v, go
+    torch.cuda.empty_cache()
+
+    def e2e_step():
+        qd, kd, vd, gd = [h.to(dev, non_blocking=True) for h in host_in]
+        qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+        out = mod(qd, kd, vd, None, bool(mask), 0.0, bool(norm), 1.0, A["a0"], A["a1"], A["a2"], A["lim"], p)
+        out.backward(gd)
+        for h, t in zip(host_out, (out.detach(), qd.grad, kd.grad, vd.grad)):
+            h.copy_(t, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    e2e_ms = float(tms.item()) / e2e_steps
+    nbytes = sum(h.numel() * h.element_size() for h in host_in)
+
+    if rank == 0:
+        per = {}
+        for name, t in recs:
+            c, s = per.get(name, (0, 0.0))
+            per[name] = (c + 1, s + t)
+        dom = max(per, key=lambda n: per[n][1]) if per else None
+        peaks = load_peaks()
+        ff, fq, fkv = alg_flops_per_token_head(D, p)
+        flops_of = {"fwd": ff, "dq": fq, "dkdv": fkv}
+        roof = None
+        if dom is not None:
+            cnt, tot = per[dom]
+            kind = dom.rsplit("_", 1)[-1]
+            if kind in flops_of:
+                achieved = flops_of[kind] * bh * N / (tot / cnt * 1e-3) / 1e12
+                roof = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
+                        "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
+                        "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "ms_per_launch": tot / cnt,
+                        "alg_flops_per_launch": flops_of[kind] * bh * N}
+            else:
+                nb = 2 * bh * N * D * (2 if dt == "bf16" else 4)
+                achieved = nb / (tot / cnt * 1e-3) / 1e9
+                roof = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
+        total_alg = (ff + fq + fkv) * bh * N * args.steps * (world if args.scaling != "strong" else 1)
+        line = {
+            "metric": "fastmax_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": describe(args.workload), "global_batch": B * (world if args.scaling != "strong" else 1),
+                       "batch_heads_per_gpu": bh, "parallelism": f"batch*head sharded x{world}, no collective",
+                       "l2": "inputs (4 x %.2f GB per GPU) larger than the 126 MB L2" % (bh * N * D * (2 if dt == "bf16" else 4) / 1e9)},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "alg_tflops_whole_step": total_alg / world / (ms * 1e-3) / 1e12,
+            "kernels": {n: {"launches": c, "ms_total": round(s, 3), "share": round(s / sum(x[1] for x in per.values()), 4)}
+                        for n, (c, s) in sorted(per.items(), key=lambda kv: -kv[1][1])},
+            "roofline": roof,
+            "e2e": {"value": tokens_job / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
+                    "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms},
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_sample(args.workload, 2, 1)[0]
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

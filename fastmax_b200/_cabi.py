@@ -1,0 +1,188 @@
+"""ctypes binding of the fastmax_b200 C ABI (``include/fastmax_b200.h``).
+
+torch supplies device memory and the current stream; every compute call goes
+through the shared library.  There is no fallback: if the library is missing
+or a call fails, a ``RuntimeError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfastmax_b200.so")
+
+F32, BF16 = 0, 1
+IMPL = {"auto": 0, "dense_ffma": 1, "dense_tc": 2, "moments_ffma": 3, "moments_tc": 4}
+
+EXPORTS = (
+    "fastmax_b200_version", "fastmax_b200_last_error", "fastmax_b200_stats_bytes",
+    "fastmax_b200_forward_workspace_bytes", "fastmax_b200_backward_workspace_bytes",
+    "fastmax_b200_forward", "fastmax_b200_forward_packed", "fastmax_b200_backward",
+    "fastmax_b200_launch_count", "fastmax_b200_profile_enable", "fastmax_b200_profile_count",
+    "fastmax_b200_profile_get",
+)
+
+
+class Problem(ctypes.Structure):
+    """``struct fastmax_problem``."""
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("dtype", "bh", "bhkv", "nq", "nk", "d", "mask", "normalize", "p", "impl")] + \
+               [(n, ctypes.c_float) for n in ("a0", "a1", "a2", "lim", "temperature")]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m fastmax_b200.build` "
+                "(fastmax_b200 has no fallback path)")
+        L = ctypes.CDLL(LIB_PATH)
+        vp, sz, pp = ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(Problem)
+        L.fastmax_b200_version.restype = ctypes.c_int
+        L.fastmax_b200_last_error.restype = ctypes.c_char_p
+        for f in ("stats_bytes", "forward_workspace_bytes", "backward_workspace_bytes"):
+            fn = getattr(L, "fastmax_b200_" + f)
+            fn.restype, fn.argtypes = sz, [pp]
+        L.fastmax_b200_forward.restype = ctypes.c_int
+        L.fastmax_b200_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+        L.fastmax_b200_forward_packed.restype = ctypes.c_int
+        L.fastmax_b200_forward_packed.argtypes = [pp, vp, vp, vp, vp, vp, vp, sz, vp]
+        L.fastmax_b200_backward.restype = ctypes.c_int
+        L.fastmax_b200_backward.argtypes = [pp] + [vp] * 12 + [sz, vp]
+        L.fastmax_b200_launch_count.restype = ctypes.c_ulonglong
+        L.fastmax_b200_profile_enable.argtypes = [ctypes.c_int]
+        L.fastmax_b200_profile_get.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int,
+                                               ctypes.POINTER(ctypes.c_float)]
+        _lib = L
+    return _lib
+
+
+def launch_count() -> int:
+    """Kernels launched through the library by this process so far."""
+    return int(lib().fastmax_b200_launch_count())
+
+
+def profile(on: bool):
+    """Start (discarding earlier records) or stop per-launch event timing."""
+    lib().fastmax_b200_profile_enable(int(bool(on)))
+
+
+def profile_records():
+    """[(kernel name, milliseconds)] for every launch since ``profile(True)``; waits for them."""
+    L = lib()
+    out = []
+    buf = ctypes.create_string_buffer(64)
+    ms = ctypes.c_float()
+    for i in range(L.fastmax_b200_profile_count()):
+        _check(L.fastmax_b200_profile_get(i, buf, 64, ctypes.byref(ms)), "fastmax_b200_profile_get")
+        out.append((buf.value.decode(), float(ms.value)))
+    return out
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        msg = lib().fastmax_b200_last_error().decode()
+        if rc == -1:
+            raise ValueError(f"{what}: {msg}")
+        raise RuntimeError(f"{what} failed (code {rc}): {msg}")
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"fastmax_b200 supports float32 and bfloat16 tensors, got {t.dtype}")
+
+
+def make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl="auto") -> Problem:
+    if p not in (1, 2):
+        raise ValueError(f"p must be 1 or 2, got: {p}")
+    return Problem(dtype=_dtype_code(q), bh=q.shape[0], bhkv=k.shape[0], nq=q.shape[1], nk=k.shape[1],
+                   d=q.shape[2], mask=int(bool(mask)), normalize=int(bool(normalize)), p=int(p),
+                   impl=IMPL[impl] if isinstance(impl, str) else int(impl),
+                   a0=float(a0), a1=float(a1), a2=float(a2), lim=float(lim),
+                   temperature=float(temperature))
+
+
+def _require(q, k, v, *more):
+    if not q.is_cuda:
+        raise RuntimeError("fastmax_b200 runs on CUDA tensors only (there is no CPU path)")
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        raise ValueError("q, k and v must be (b*h, n, d) here")
+    if k.shape != v.shape or q.shape[2] != k.shape[2]:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    for t in (q, k, v) + more:
+        if t.device != q.device or t.dtype != q.dtype:
+            raise ValueError("all tensors must share one device and dtype")
+        if not t.is_contiguous():
+            raise ValueError("tensors must be contiguous")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)
+
+
+def forward(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2,
+            impl="auto"):
+    """q (bh,nq,d), k/v (bhkv,nk,d) -> out (bh,nq,d), den (bh,nq) fp32, stats (opaque)."""
+    _require(q, k, v)
+    L = lib()
+    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl)
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q)
+        den = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
+        stats = torch.empty(max(L.fastmax_b200_stats_bytes(prob), 8), dtype=torch.uint8, device=q.device)
+        wsb = L.fastmax_b200_forward_workspace_bytes(prob)
+        ws = _workspace(wsb, q.device)
+        rc = L.fastmax_b200_forward(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                    den.data_ptr(), stats.data_ptr(), ws.data_ptr(), wsb, _stream(q))
+    _check(rc, "fastmax_b200_forward")
+    return out, den, stats
+
+
+def forward_packed(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0,
+                   p=2, impl="auto"):
+    """Reference layout: (bh, nq, d+1) fp32, denominator in the last channel."""
+    _require(q, k, v)
+    L = lib()
+    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl)
+    with torch.cuda.device(q.device):
+        o = torch.empty(q.shape[0], q.shape[1], q.shape[2] + 1, dtype=torch.float32, device=q.device)
+        stats = torch.empty(max(L.fastmax_b200_stats_bytes(prob), 8), dtype=torch.uint8, device=q.device)
+        wsb = L.fastmax_b200_forward_workspace_bytes(prob)
+        ws = _workspace(wsb, q.device)
+        rc = L.fastmax_b200_forward_packed(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                           stats.data_ptr(), ws.data_ptr(), wsb, _stream(q))
+    _check(rc, "fastmax_b200_forward_packed")
+    return o, stats
+
+
+def backward(q, k, v, out, den, stats, grad_out, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0,
+             a2=0.5, lim=1.0, p=2, impl="auto"):
+    """Gradients (grad_q, grad_k, grad_v) in the dtype of the inputs."""
+    _require(q, k, v, out, grad_out)
+    L = lib()
+    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl)
+    with torch.cuda.device(q.device):
+        gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        wsb = L.fastmax_b200_backward_workspace_bytes(prob)
+        ws = _workspace(wsb, q.device)
+        rc = L.fastmax_b200_backward(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                     den.data_ptr(), stats.data_ptr(), grad_out.data_ptr(),
+                                     gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), ws.data_ptr(), wsb,
+                                     _stream(q))
+    _check(rc, "fastmax_b200_backward")
+    return gq, gk, gv

@@ -1,0 +1,243 @@
+// C ABI of the fastmax_b200 library: argument validation, workspace layout and
+// dispatch to the kernel families.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <atomic>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "fm_common.cuh"
+
+namespace fm {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// ---- launch accounting ------------------------------------------------------
+struct ProfRec {
+  const char* name;
+  cudaEvent_t e0, e1;
+};
+static std::atomic<unsigned long long> g_launches{0};
+static std::atomic<int> g_prof_on{0};
+static std::mutex g_prof_mu;
+static std::vector<ProfRec> g_prof;
+static thread_local int g_prof_open = -1;
+static const size_t kProfMax = 1u << 16;
+
+void prof_before(const char* name, cudaStream_t s) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  g_prof_open = -1;
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (g_prof.size() >= kProfMax) return;
+  ProfRec r{name, nullptr, nullptr};
+  if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) return;
+  cudaEventRecord(r.e0, s);
+  g_prof.push_back(r);
+  g_prof_open = (int)g_prof.size() - 1;
+}
+
+void prof_after(cudaStream_t s) {
+  if (g_prof_open < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if ((size_t)g_prof_open < g_prof.size()) cudaEventRecord(g_prof[g_prof_open].e1, s);
+  g_prof_open = -1;
+}
+
+static void prof_clear() {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof) {
+    if (r.e0) cudaEventDestroy(r.e0);
+    if (r.e1) cudaEventDestroy(r.e1);
+  }
+  g_prof.clear();
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+static int validate(const fastmax_problem* p) {
+  if (!p) return fail(FASTMAX_E_ARG, "problem is NULL");
+  if (p->dtype != FASTMAX_F32 && p->dtype != FASTMAX_BF16)
+    return fail(FASTMAX_E_ARG, "dtype %d is neither FASTMAX_F32 nor FASTMAX_BF16", p->dtype);
+  if (p->p != 1 && p->p != 2) return fail(FASTMAX_E_ARG, "p must be 1 or 2, got: %d", p->p);
+  if (p->d != 8 && p->d != 16 && p->d != 32 && p->d != 64 && p->d != 128)
+    return fail(FASTMAX_E_ARG, "head dimension %d is not one of 8,16,32,64,128", p->d);
+  if (p->bh < 0 || p->bhkv < 0 || p->nq < 0 || p->nk < 0)
+    return fail(FASTMAX_E_ARG, "negative size");
+  if (p->bh > 0 && (p->bhkv <= 0 || p->bh % p->bhkv != 0))
+    return fail(FASTMAX_E_ARG, "bh=%d is not a multiple of bhkv=%d", p->bh, p->bhkv);
+  if (p->nq > (1 << 22) || p->nk > (1 << 22))
+    return fail(FASTMAX_E_ARG, "sequence longer than 4194304 tokens");
+  if (p->mask && p->nk < p->nq)
+    return fail(FASTMAX_E_ARG, "causal attention needs nk >= nq (nq=%d, nk=%d)", p->nq, p->nk);
+  if (p->nq > 0 && p->nk == 0) return fail(FASTMAX_E_ARG, "no keys (nk == 0)");
+  if (p->impl < FASTMAX_IMPL_AUTO || p->impl > FASTMAX_IMPL_MOMENTS_TC)
+    return fail(FASTMAX_E_ARG, "unknown impl %d", p->impl);
+  return FASTMAX_OK;
+}
+
+static int check_device() {
+  int dev = 0;
+  FM_CUDA_TRY(cudaGetDevice(&dev));
+  int major = 0;
+  FM_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10)
+    return fail(FASTMAX_E_DEVICE, "device %d has compute capability %d.x; this library is built for sm_100a only",
+                dev, major);
+  return FASTMAX_OK;
+}
+
+// Family actually used for a problem.
+static int pick_impl(const fastmax_problem& p, int* impl) {
+  int want = p.impl;
+  if (want == FASTMAX_IMPL_AUTO) want = FASTMAX_IMPL_DENSE_FFMA;
+  if (want != FASTMAX_IMPL_DENSE_FFMA)
+    return fail(FASTMAX_E_UNSUPPORTED, "kernel family %d is not available in this build", want);
+  *impl = want;
+  return FASTMAX_OK;
+}
+
+// Backward workspace: [dots: bh+bhkv floats][delta: bh*nq floats], 256-byte aligned parts.
+struct BwdWs {
+  size_t dots_off, delta_off, total;
+};
+static BwdWs bwd_layout(const fastmax_problem& p) {
+  BwdWs w;
+  w.dots_off = 0;
+  w.delta_off = align_up(sizeof(float) * (size_t)(p.bh + p.bhkv), 256);
+  w.total = w.delta_off + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
+  return w;
+}
+
+}  // namespace fm
+
+using namespace fm;
+
+extern "C" {
+
+int fastmax_b200_version(void) { return 100; }
+
+const char* fastmax_b200_last_error(void) { return g_err; }
+
+unsigned long long fastmax_b200_launch_count(void) { return g_launches.load(); }
+
+int fastmax_b200_profile_enable(int on) {
+  g_prof_on.store(0);
+  prof_clear();
+  g_prof_on.store(on ? 1 : 0);
+  return FASTMAX_OK;
+}
+
+int fastmax_b200_profile_count(void) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  return (int)g_prof.size();
+}
+
+int fastmax_b200_profile_get(int i, char* name, int name_len, float* ms) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (i < 0 || (size_t)i >= g_prof.size()) return fail(FASTMAX_E_ARG, "profile record %d out of range", i);
+  const ProfRec& r = g_prof[i];
+  if (name && name_len > 0) {
+    strncpy(name, r.name, (size_t)name_len - 1);
+    name[name_len - 1] = 0;
+  }
+  if (ms) {
+    FM_CUDA_TRY(cudaEventSynchronize(r.e1));
+    FM_CUDA_TRY(cudaEventElapsedTime(ms, r.e0, r.e1));
+  }
+  return FASTMAX_OK;
+}
+
+size_t fastmax_b200_stats_bytes(const fastmax_problem* p) {
+  if (!p || p->bh < 0 || p->bhkv < 0) return 0;
+  return sizeof(stat_t) * (size_t)(p->bh + p->bhkv);
+}
+
+size_t fastmax_b200_forward_workspace_bytes(const fastmax_problem* p) {
+  (void)p;
+  return 0;
+}
+
+size_t fastmax_b200_backward_workspace_bytes(const fastmax_problem* p) {
+  if (validate(p)) return 0;
+  return bwd_layout(*p).total;
+}
+
+static int forward_impl(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                        const FwdOut& o, void* stats, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+  int rc = validate(prob);
+  if (rc) return rc;
+  const fastmax_problem& p = *prob;
+  if (p.bh == 0 || p.nq == 0) return FASTMAX_OK;
+  if (!q || !k || !v || !o.out || !o.den) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs a stats buffer");
+  if (workspace_bytes < fastmax_b200_forward_workspace_bytes(prob))
+    return fail(FASTMAX_E_WORKSPACE, "forward workspace too small");
+  (void)workspace;
+  if ((rc = check_device())) return rc;
+  int impl;
+  if ((rc = pick_impl(p, &impl))) return rc;
+  Ctx c{p, (cudaStream_t)stream};
+  if (p.normalize && (rc = launch_rowmax(c, q, k, (stat_t*)stats))) return rc;
+  return dense_ffma_forward(c, q, k, v, (const stat_t*)stats, o);
+}
+
+int fastmax_b200_forward(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                         void* out, float* den, void* stats, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  FwdOut o{out, den, prob ? prob->d : 0, 1, 0};
+  return forward_impl(prob, q, k, v, o, stats, workspace, workspace_bytes, stream);
+}
+
+int fastmax_b200_forward_packed(const fastmax_problem* prob, const void* q, const void* k,
+                                const void* v, float* o_packed, void* stats, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  int d = prob ? prob->d : 0;
+  FwdOut o{o_packed, o_packed ? o_packed + d : nullptr, d + 1, d + 1, 1};
+  return forward_impl(prob, q, k, v, o, stats, workspace, workspace_bytes, stream);
+}
+
+int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                          const void* out, const float* den, const void* stats,
+                          const void* grad_out, void* grad_q, void* grad_k, void* grad_v,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = validate(prob);
+  if (rc) return rc;
+  const fastmax_problem& p = *prob;
+  if (p.bh == 0 || (p.nq == 0 && p.nk == 0)) return FASTMAX_OK;
+  if (!q || !k || !v || !out || !den || !grad_out || !grad_q || !grad_k || !grad_v)
+    return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the forward's stats buffer");
+  BwdWs w = bwd_layout(p);
+  if (w.total > 0 && (!workspace || workspace_bytes < w.total))
+    return fail(FASTMAX_E_WORKSPACE, "backward workspace too small: need %zu bytes, got %zu",
+                w.total, workspace_bytes);
+  if ((rc = check_device())) return rc;
+  int impl;
+  if ((rc = pick_impl(p, &impl))) return rc;
+  Ctx c{p, (cudaStream_t)stream};
+  float* dots = (float*)((char*)workspace + w.dots_off);
+  float* delta = (float*)((char*)workspace + w.delta_off);
+  if (p.normalize)
+    FM_CUDA_TRY(cudaMemsetAsync(dots, 0, sizeof(float) * (size_t)(p.bh + p.bhkv), c.stream));
+  if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
+  if ((rc = dense_ffma_backward(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dots,
+                                grad_q, grad_k, grad_v)))
+    return rc;
+  if (p.normalize)
+    return launch_norm_fixup(c, q, k, (const stat_t*)stats, dots, grad_q, grad_k);
+  return FASTMAX_OK;
+}
+
+}  // extern "C"

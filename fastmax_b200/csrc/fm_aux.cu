@@ -1,0 +1,170 @@
+// HBM-bound helper kernels of the Fastmax passes: per-head max row norm (the
+// normalisation statistic), the grad_out.out row dots of the backward pass and
+// the single-row gradient of the max-norm scaling.
+#include "fm_common.cuh"
+
+namespace fm {
+
+// ---------------------------------------------------------------------------
+// Row statistics: for every head, max_n ||x_n||^2 and the row that attains it.
+// Replaces calc_norms + find_max (reference fastmax_cuda_forward.cu:223-253);
+// the scale lim/max is applied inside the attention kernels instead of
+// rewriting q and k in place (reference apply_norm, :255-269).
+// Each warp owns rows; a row of D elements is read by D/VEC lanes, so a warp
+// covers 32*VEC/D rows per load and every load is a full 128-byte line.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) rowmax_kernel(const T* __restrict__ x, int n,
+                                                     int rows_per_block,
+                                                     stat_t* __restrict__ stats) {
+  constexpr int VEC = (D >= 32) ? 4 : 1;       // elements per lane
+  constexpr int LPR = D / VEC;                 // lanes per row
+  constexpr int RPW = 32 / LPR;                // rows per warp per step
+  static_assert(D % VEC == 0 && LPR <= 32 && 32 % LPR == 0, "bad head dimension");
+  const int head = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / LPR, off = (lane % LPR) * VEC;
+  const int row0 = blockIdx.y * rows_per_block;
+  const int row1 = min(n, row0 + rows_per_block);
+  const T* base = x + (size_t)head * n * D;
+  float best = -1.0f;
+  int best_row = 0;
+  // the loop bound is warp-uniform: every lane takes part in every shuffle
+  for (int rb = row0 + warp * RPW; rb < row1; rb += 8 * RPW) {
+    const int r = rb + sub;
+    float s = 0.f;
+    if (r < row1) {
+      const T* p = base + (size_t)r * D + off;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float t = ldf(p + e);
+        s = fmaf(t, t, s);
+      }
+    }
+#pragma unroll
+    for (int m = LPR / 2; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if (r < row1 && s > best) { best = s; best_row = r; }
+  }
+  // NaN norms never compare greater, so they are ignored as a maximum.
+  if (best >= 0.f && (lane % LPR) == 0) {
+    stat_t w = ((stat_t)__float_as_uint(best) << 32) | (stat_t)(0xFFFFFFFFu - (unsigned)best_row);
+    atomicMax(&stats[head], w);
+  }
+}
+
+template <typename T>
+static int rowmax_one(const Ctx& c, const T* x, int heads, int n, stat_t* stats) {
+  if (heads == 0 || n == 0) return FASTMAX_OK;
+  // enough blocks per head to fill the GPU, at least 256 rows each
+  int splits = max(1, min((n + 255) / 256, (148 * 8 + heads - 1) / heads));
+  int rpb = (n + splits - 1) / splits;
+  dim3 grid(heads, (n + rpb - 1) / rpb);
+  switch (c.p.d) {
+#define FM_CASE(DD) \
+  case DD:                                                                              \
+    FM_LAUNCH("fm_rowmax", c.stream,                                                      \
+              (rowmax_kernel<T, DD><<<grid, 256, 0, c.stream>>>(x, n, rpb, stats)));      \
+    break;
+    FM_CASE(8) FM_CASE(16) FM_CASE(32) FM_CASE(64) FM_CASE(128)
+#undef FM_CASE
+    default: return fail(FASTMAX_E_ARG, "head dimension %d is not one of 8,16,32,64,128", c.p.d);
+  }
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+int launch_rowmax(const Ctx& c, const void* q, const void* k, stat_t* stats) {
+  const fastmax_problem& p = c.p;
+  FM_CUDA_TRY(cudaMemsetAsync(stats, 0, sizeof(stat_t) * (size_t)(p.bh + p.bhkv), c.stream));
+  int rc;
+  if (p.dtype == FASTMAX_F32) {
+    if ((rc = rowmax_one<float>(c, (const float*)q, p.bh, p.nq, stats))) return rc;
+    return rowmax_one<float>(c, (const float*)k, p.bhkv, p.nk, stats + p.bh);
+  }
+  if ((rc = rowmax_one<__nv_bfloat16>(c, (const __nv_bfloat16*)q, p.bh, p.nq, stats))) return rc;
+  return rowmax_one<__nv_bfloat16>(c, (const __nv_bfloat16*)k, p.bhkv, p.nk, stats + p.bh);
+}
+
+// ---------------------------------------------------------------------------
+// delta[row] = grad_out[row,:] . out[row,:]; one warp per row.  Together with
+// 1/den this is the "-O . dDen" part of the reference's backward
+// (fastmax_cuda_backward.cu:63-161 and div_grad_output :874-882), computed once
+// instead of inside every gradient kernel, and without touching grad_out.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ go,
+                                                    const T* __restrict__ out, size_t rows,
+                                                    int d, float* __restrict__ delta) {
+  size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f;
+  for (int c = lane; c < d; c += 32) s = fmaf(ldf(go + row * d + c), ldf(out + row * d + c), s);
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+  if (lane == 0) delta[row] = s;
+}
+
+int launch_delta(const Ctx& c, const void* go, const void* out, float* delta) {
+  size_t rows = (size_t)c.p.bh * c.p.nq;
+  if (rows == 0) return FASTMAX_OK;
+  unsigned blocks = (unsigned)((rows + 7) / 8);
+  if (c.p.dtype == FASTMAX_F32)
+    FM_LAUNCH("fm_delta", c.stream,
+              (delta_kernel<float><<<blocks, 256, 0, c.stream>>>((const float*)go, (const float*)out,
+                                                                  rows, c.p.d, delta)));
+  else
+    FM_LAUNCH("fm_delta", c.stream,
+              (delta_kernel<__nv_bfloat16><<<blocks, 256, 0, c.stream>>>(
+                  (const __nv_bfloat16*)go, (const __nv_bfloat16*)out, rows, c.p.d, delta)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Gradient of x_hat = lim * x / m, m = ||x_r|| the largest row norm of the head:
+//   dx_n = (lim/m) dx_hat_n  -  [n == r] (sum_n dx_hat_n . x_hat_n) x_r / m^2 .
+// The attention kernels already wrote (lim/m) dx_hat and accumulated
+// dots[head] = sum_n (lim/m) dx_hat_n . x_n, which equals the bracketed sum, so
+// only row r of each head is corrected here.  The reference's CUDA backward
+// has no such term; autograd through its PyTorch path (example.py:105-108) does.
+template <typename T>
+__global__ void norm_fixup_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                  const stat_t* __restrict__ stats,
+                                  const float* __restrict__ dots, T* __restrict__ gq,
+                                  T* __restrict__ gk, int bh, int nq, int nk, int d) {
+  int head = blockIdx.x;
+  const T* x;
+  T* g;
+  int n;
+  if (head < bh) { x = q + (size_t)head * nq * d; g = gq + (size_t)head * nq * d; n = nq; }
+  else { x = k + (size_t)(head - bh) * nk * d; g = gk + (size_t)(head - bh) * nk * d; n = nk; }
+  stat_t s = stats[head];
+  int r = stat_row(s);
+  float m2 = stat_norm2(s);
+  if (r < 0 || r >= n) return;
+  float coef = dots[head] / m2;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    size_t i = (size_t)r * d + c;
+    stf(g + i, ldf(g + i) - coef * ldf(x + i));
+  }
+}
+
+int launch_norm_fixup(const Ctx& c, const void* q, const void* k, const stat_t* stats,
+                      const float* dots, void* gq, void* gk) {
+  const fastmax_problem& p = c.p;
+  int heads = p.bh + p.bhkv;
+  if (heads == 0) return FASTMAX_OK;
+  if (p.dtype == FASTMAX_F32)
+    FM_LAUNCH("fm_norm_fixup", c.stream,
+              (norm_fixup_kernel<float><<<heads, 128, 0, c.stream>>>(
+                  (const float*)q, (const float*)k, stats, dots, (float*)gq, (float*)gk, p.bh, p.nq,
+                  p.nk, p.d)));
+  else
+    FM_LAUNCH("fm_norm_fixup", c.stream,
+              (norm_fixup_kernel<__nv_bfloat16><<<heads, 128, 0, c.stream>>>(
+                  (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, stats, dots, (__nv_bfloat16*)gq,
+                  (__nv_bfloat16*)gk, p.bh, p.nq, p.nk, p.d)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+}  // namespace fm

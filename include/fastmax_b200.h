@@ -1,0 +1,147 @@
+/*
+ * fastmax_b200 -- C ABI of the B200 (sm_100a) Fastmax attention library.
+ *
+ * Fastmax attention scores a query/key pair with the polynomial
+ *     f(s) = a0 + a1*s + a2*s^2,   s = q.k      (a2 = 0 when p == 1)
+ * and row-normalises:  out_i = sum_j f(s_ij) v_j / sum_j f(s_ij),
+ * j over all keys (mask == 0) or over j <= i + (nk - nq) (mask == 1, causal).
+ * With normalize != 0, q and k are first scaled per head to
+ *     x <- lim * x / max_n ||x_n||_2,
+ * and the backward pass differentiates through that scaling.
+ *
+ * This header is what a foreign-function binding of the reference project
+ * would bind instead of its `forward_cuda` / `backward_cuda` launchers.  Every
+ * pointer is a device pointer unless said otherwise; all tensors are dense,
+ * row-major and contiguous:
+ *     q, out, grad_out, grad_q : (bh,   nq, d)
+ *     k, v, grad_k, grad_v     : (bhkv, nk, d)      bh % bhkv == 0
+ *     den                      : (bh, nq) float32   row sums of f(s)
+ * The library allocates no device memory: the caller passes every output and
+ * scratch buffer, sized by the *_bytes queries below.  Calls are asynchronous
+ * on the given CUDA stream (a `cudaStream_t` passed as `void*`) and never
+ * synchronise the device.  Inputs are never written.
+ *
+ * Every function returns FASTMAX_OK (0) or a negative FASTMAX_E_* code;
+ * `fastmax_b200_last_error()` gives the message of the calling thread's last
+ * failure.
+ */
+#ifndef FASTMAX_B200_H
+#define FASTMAX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FASTMAX_OK = 0,
+  FASTMAX_E_ARG = -1,       /* bad shape, dtype, p, head dimension, null pointer */
+  FASTMAX_E_WORKSPACE = -2, /* scratch buffer smaller than the *_bytes query */
+  FASTMAX_E_CUDA = -3,      /* a CUDA runtime call or a kernel launch failed */
+  FASTMAX_E_UNSUPPORTED = -4, /* valid request that this build has no kernel for */
+  FASTMAX_E_DEVICE = -5     /* the current device is not compute capability 10.x */
+};
+
+enum { FASTMAX_F32 = 0, FASTMAX_BF16 = 1 };
+
+/* Kernel family selection.  AUTO picks the fastest family that supports the
+ * problem; the others force one family (used by the parity tests to compare
+ * families against each other). */
+enum {
+  FASTMAX_IMPL_AUTO = 0,
+  FASTMAX_IMPL_DENSE_FFMA = 1,   /* tiled score form on CUDA cores, fp32 math */
+  FASTMAX_IMPL_DENSE_TC = 2,     /* tiled score form on tcgen05 tensor cores (bf16) */
+  FASTMAX_IMPL_MOMENTS_FFMA = 3, /* chunked moment-state form on CUDA cores */
+  FASTMAX_IMPL_MOMENTS_TC = 4    /* chunked moment-state form on tcgen05 */
+};
+
+/* One attention problem.  Mirrors the argument list of the reference's
+ * forwardpass(q,k,v,drop_noise,[rpe_matrix,]mask,dropout,normalize,temperature,
+ * a0,a1,a2,lim,p) (reference fastmax_cuda.cpp:17-24).  `temperature` is carried
+ * for signature compatibility and has no effect, as in the reference's
+ * pure-PyTorch path (reference example.py:102,110-111). */
+typedef struct fastmax_problem {
+  int32_t dtype;      /* FASTMAX_F32 or FASTMAX_BF16: element type of q,k,v,out,grads */
+  int32_t bh;         /* batch*heads of q */
+  int32_t bhkv;       /* batch*heads of k and v; bh % bhkv == 0 */
+  int32_t nq;         /* query tokens */
+  int32_t nk;         /* key tokens; causal needs nk >= nq */
+  int32_t d;          /* head dimension: 8,16,32,64 or 128 */
+  int32_t mask;       /* 0 = all keys, 1 = causal */
+  int32_t normalize;  /* 0/1 */
+  int32_t p;          /* polynomial order, 1 or 2 */
+  int32_t impl;       /* FASTMAX_IMPL_* */
+  float a0, a1, a2;
+  float lim;
+  float temperature;
+} fastmax_problem;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fastmax_b200_version(void);
+
+/* Message of the calling thread's most recent failure ("" if none). */
+const char* fastmax_b200_last_error(void);
+
+/* Launch accounting (no counterpart in the reference, which times itself with
+ * host clocks around device-wide synchronisations, test_fastmax.py:351-356).
+ * launch_count: kernels this process has launched through the library so far.
+ * profile_enable(1) discards earlier records and starts bracketing every
+ * launch with CUDA events on its stream; profile_enable(0) stops and discards.
+ * profile_get waits for record i to finish and returns its kernel name and
+ * device time in milliseconds. */
+unsigned long long fastmax_b200_launch_count(void);
+int fastmax_b200_profile_enable(int on);
+int fastmax_b200_profile_count(void);
+int fastmax_b200_profile_get(int i, char* name, int name_len, float* ms);
+
+/* Bytes of the per-head statistics buffer (max row norms and their row
+ * indices) that forward writes and backward reads.  Replaces the reference's
+ * qnorms/knorms/qmaxes/kmaxes temporaries (reference fastmax_cuda_forward.cu:
+ * 349-358), which it needs because it rescales q and k in place. */
+size_t fastmax_b200_stats_bytes(const fastmax_problem* prob);
+
+/* Bytes of scratch the forward / backward pass needs (may be 0). */
+size_t fastmax_b200_forward_workspace_bytes(const fastmax_problem* prob);
+size_t fastmax_b200_backward_workspace_bytes(const fastmax_problem* prob);
+
+/* Forward pass.  Replaces forward_cuda (reference fastmax_cuda_forward.cu:
+ * 297-411): normalisation (223-269), moment/score kernels (25-197, and the
+ * second-order terms of `old stuff/fastmax_cuda_forward_quad.cu`:57-268) and
+ * the division (199-210).  Writes out (element type of the inputs), den and
+ * stats. */
+int fastmax_b200_forward(const fastmax_problem* prob,
+                         const void* q, const void* k, const void* v,
+                         void* out, float* den, void* stats,
+                         void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/* Forward pass in the reference's packed layout: o is (bh, nq, d+1) float32
+ * whose channels 0..d-1 hold the divided output and channel d the denominator
+ * (reference fastmax_cuda_forward.cu:347, 199-210; the reference wrapper
+ * slices o[:, :, :d], example.py:47).  stats may be NULL when normalize == 0. */
+int fastmax_b200_forward_packed(const fastmax_problem* prob,
+                                const void* q, const void* k, const void* v,
+                                float* o_packed, void* stats,
+                                void* workspace, size_t workspace_bytes,
+                                void* stream);
+
+/* Backward pass.  Replaces backward_cuda (reference fastmax_cuda_backward.cu:
+ * 900-1006 and `old stuff/fastmax_cuda_backward_quad.cu`:26-479): given the
+ * forward's out, den and stats and the upstream gradient, writes grad_q,
+ * grad_k, grad_v (element type of the inputs).  Unlike the reference it does
+ * not modify grad_out, and with normalize != 0 it includes the gradient of the
+ * max-norm scaling, as autograd through the reference's PyTorch path does. */
+int fastmax_b200_backward(const fastmax_problem* prob,
+                          const void* q, const void* k, const void* v,
+                          const void* out, const float* den, const void* stats,
+                          const void* grad_out,
+                          void* grad_q, void* grad_k, void* grad_v,
+                          void* workspace, size_t workspace_bytes,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTMAX_B200_H */

@@ -1,0 +1,168 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the reference
+vectors and the CPU oracle.  Tolerances (relative max error, outputs and
+gradients): 1e-4 for float32, 2e-2 for bfloat16."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, case_kwargs, load_small_cases
+from gpu_util import TOL, assert_close, oracle, run_cabi
+from oracle.fastmax_oracle import fastmax_dense, rel_err
+
+import fastmax_b200
+from fastmax_b200 import _cabi
+
+pytestmark = pytest.mark.gpu
+CASES = load_small_cases()
+FAMILIES = ["dense_ffma"]
+
+
+def randn(*shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * scale
+
+
+@pytest.mark.parametrize("impl", FAMILIES)
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_reference_vectors_fp32(c, impl):
+    got, _ = run_cabi(c["q"], c["k"], c["v"], c["go"], torch.float32, impl=impl, **case_kwargs(c))
+    assert_close(got, [c[n + "64"] for n in ("out", "dq", "dk", "dv")], torch.float32, c["tag"])
+
+
+@pytest.mark.parametrize("impl", FAMILIES)
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_reference_vectors_bf16(c, impl):
+    kw = case_kwargs(c)
+    got, _ = run_cabi(c["q"], c["k"], c["v"], c["go"], torch.bfloat16, impl=impl, **kw)
+    ref = oracle(c["q"], c["k"], c["v"], c["go"], torch.bfloat16, **kw)
+    assert_close(got, ref, torch.bfloat16, c["tag"])
+
+
+def test_c1_configuration_against_reference_rows():
+    """B=2,H=8,N=1024,D=32 unmasked p=2 normalised fp32: the reference's own CPU-runnable case."""
+    z = np.load(GOLDEN + "/c1_sampled.npz")
+    b, h, n, d = [int(x) for x in z["cfg"][:4]]
+    g = torch.Generator().manual_seed(int(z["seed"]))
+    q, k, v, go = [torch.randn(b, h, n, d, generator=g) for _ in range(4)]
+    chk = np.array([float(t.double().sum()) for t in (q, k, v, go)])
+    if not np.allclose(chk, z["input_checksum"], rtol=0, atol=1e-6):
+        pytest.skip("torch RNG stream differs from the one the fixture was made with")
+    got, _ = run_cabi(q, k, v, go, torch.float32, mask=0, normalize=1, p=2)
+    st = int(z["row_stride"])
+    for t, name in zip(got, ("out", "dq", "dk", "dv")):
+        pick = torch.stack([t[bb, hh, ::st] for bb, hh in z["heads"]])
+        err = float((pick.double() - torch.from_numpy(z[name + "64"])).abs().max()) / float(z[name + "64_absmax"])
+        assert err < 1e-4, (name, err)
+
+
+SWEEP = [
+    # bh, n, d, mask, p, normalize
+    (3, 1, 32, 1, 2, 1), (3, 2, 32, 1, 2, 1), (1, 17, 32, 0, 2, 1), (3, 127, 32, 1, 2, 1),
+    (3, 128, 32, 1, 1, 1), (2, 129, 32, 0, 1, 0), (33, 129, 32, 1, 2, 1), (2, 1000, 32, 1, 2, 1),
+    (2, 1000, 32, 0, 2, 1),
+]
+
+
+@pytest.mark.parametrize("impl", FAMILIES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("cfg", SWEEP, ids=[f"bh{c[0]}n{c[1]}d{c[2]}m{c[3]}p{c[4]}z{c[5]}" for c in SWEEP])
+def test_sweep_against_moment_oracle(cfg, dtype, impl):
+    bh, n, d, mask, p, norm = cfg
+    q, k, v, go = [randn(1, bh, n, d, seed=100 + i + n) for i in range(4)]
+    if not norm:
+        q, k = q * d ** -0.5, k * d ** -0.5
+    kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    got, _ = run_cabi(q, k, v, go, dtype, impl=impl, **kw)
+    ref = oracle(q, k, v, go, dtype, block=128, **kw)
+    assert_close(got, ref, dtype, str(cfg))
+
+
+BIG_D = [(2, 300, 64, 1, 2, 1), (2, 300, 64, 0, 1, 1), (1, 200, 128, 1, 2, 0), (2, 260, 128, 0, 2, 0),
+         (2, 1500, 64, 1, 2, 1)]
+
+
+@pytest.mark.parametrize("impl", FAMILIES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("cfg", BIG_D, ids=[f"bh{c[0]}n{c[1]}d{c[2]}m{c[3]}p{c[4]}z{c[5]}" for c in BIG_D])
+def test_large_head_dims_against_dense_oracle(cfg, dtype, impl):
+    bh, n, d, mask, p, norm = cfg
+    q, k, v, go = [randn(1, bh, n, d, seed=200 + i + d) for i in range(4)]
+    if not norm:
+        q, k = q * d ** -0.5, k * d ** -0.5
+    kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    got, _ = run_cabi(q, k, v, go, dtype, impl=impl, **kw)
+    ref = oracle(q, k, v, go, dtype, dense=True, **kw)
+    assert_close(got, ref, dtype, str(cfg))
+
+
+@pytest.mark.parametrize("impl", FAMILIES)
+def test_grouped_kv_heads_and_longer_keys(impl):
+    """bh = 3 * bhkv and nk > nq (queries aligned to the last nq keys)."""
+    q, go = randn(1, 6, 70, 32, seed=1), randn(1, 6, 70, 32, seed=2)
+    k, v = randn(1, 2, 100, 32, seed=3), randn(1, 2, 100, 32, seed=4)
+    for mask in (0, 1):
+        kw = dict(mask=mask, normalize=1, p=2, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+        got, _ = run_cabi(q, k, v, go, torch.float32, impl=impl, **kw)
+        kx, vx = [t.repeat_interleave(3, dim=1).double().requires_grad_(True) for t in (k, v)]
+        qx = q.double().requires_grad_(True)
+        out = fastmax_dense(qx, kx, vx, **kw)
+        out.backward(go.double())
+        ref = [out.detach(), qx.grad, kx.grad.reshape(1, 2, 3, 100, 32).sum(2),
+               vx.grad.reshape(1, 2, 3, 100, 32).sum(2)]
+        # the oracle normalises each expanded k head by the same maximum, so summing
+        # the expanded gradients is the gradient of the shared head
+        assert_close(got, ref, torch.float32, f"gqa mask={mask}")
+
+
+def test_packed_forward_has_reference_layout():
+    q, k, v = [randn(4, 50, 32, seed=s).cuda() for s in (1, 2, 3)]
+    kw = dict(mask=True, normalize=True, p=2)
+    out, den, _ = _cabi.forward(q, k, v, **kw)
+    o, _ = _cabi.forward_packed(q, k, v, **kw)
+    assert o.shape == (4, 50, 33) and o.dtype == torch.float32
+    assert torch.equal(o[:, :, :32], out) and torch.equal(o[:, :, 32], den)
+    qb, kb, vb = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    ob, _ = _cabi.forward_packed(qb, kb, vb, **kw)
+    outb, denb, _ = _cabi.forward(qb, kb, vb, **kw)
+    assert ob.dtype == torch.float32 and torch.equal(ob[:, :, 32], denb)
+    assert rel_err(ob[:, :, :32].cpu(), outb.float().cpu()) < 1e-2
+
+
+def test_inputs_are_left_untouched_and_forward_is_deterministic():
+    q, k, v, go = [randn(4, 300, 32, seed=s).cuda() for s in (1, 2, 3, 4)]
+    copies = [t.clone() for t in (q, k, v, go)]
+    kw = dict(mask=True, normalize=True, p=2)
+    out, den, stats = _cabi.forward(q, k, v, **kw)
+    out2, den2, _ = _cabi.forward(q, k, v, **kw)
+    _cabi.backward(q, k, v, out, den, stats, go, **kw)
+    assert torch.equal(out, out2) and torch.equal(den, den2)
+    for a, b in zip((q, k, v, go), copies):
+        assert torch.equal(a, b)
+
+
+def test_module_interface_matches_oracle_4d_and_3d():
+    mod = fastmax_b200.FASTMultiHeadAttention()
+    q, k, v, go = [randn(2, 3, 90, 32, seed=s) for s in (5, 6, 7, 8)]
+    kw = dict(mask=1, normalize=1, p=2, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    ref = oracle(q, k, v, go, torch.float32, **kw)
+    for flat in (False, True):
+        shp = (6, 90, 32) if flat else (2, 3, 90, 32)
+        qc, kc, vc = [t.reshape(shp).cuda().requires_grad_(True) for t in (q, k, v)]
+        out = mod(qc, kc, vc, None, True, 0.0, True, 1.0, 1.0, 1.0, 0.5, 1.0, 2)
+        assert out.shape == shp
+        out.backward(go.reshape(shp).cuda())
+        got = [t.detach().cpu().reshape(q.shape) for t in (out, qc.grad, kc.grad, vc.grad)]
+        assert_close(got, ref, torch.float32, f"module flat={flat}")
+
+
+def test_errors_surface_as_python_exceptions():
+    q = torch.randn(2, 16, 32, device="cuda")
+    with pytest.raises(ValueError):
+        _cabi.forward(q, q, q, mask=True, normalize=False, p=3)
+    q24 = torch.randn(2, 16, 24, device="cuda")
+    with pytest.raises(ValueError):
+        _cabi.forward(q24, q24, q24, mask=True, normalize=False, p=2)
+    with pytest.raises(TypeError):
+        _cabi.forward(q.half(), q.half(), q.half(), mask=True, normalize=False, p=2)
+    with pytest.raises(ValueError):
+        _cabi.forward(q.transpose(0, 1), q, q, mask=True, normalize=False, p=2)

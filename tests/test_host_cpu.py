@@ -1,0 +1,100 @@
+"""CPU-side checks: the C ABI library loads and exports what the header declares,
+the host wrappers validate their arguments, and the pure-PyTorch path of the
+package agrees with the reference-generated vectors."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT, case_kwargs, load_small_cases
+from oracle.fastmax_oracle import rel_err
+
+import fastmax_b200
+from fastmax_b200 import _cabi
+
+CASES = load_small_cases()
+
+
+def _declared_functions():
+    names = set()
+    for fn in os.listdir(os.path.join(ROOT, "include")):
+        if fn.endswith(".h"):
+            txt = open(os.path.join(ROOT, "include", fn)).read()
+            txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
+            names |= set(re.findall(r"\b(fastmax_b200_\w+)\s*\(", txt))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(_cabi.LIB_PATH)
+    declared = _declared_functions()
+    assert len(declared) >= 8
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
+    assert set(_cabi.EXPORTS) <= set(declared)
+
+
+def test_version_and_size_queries_need_no_gpu():
+    L = _cabi.lib()
+    assert L.fastmax_b200_version() >= 100
+    prob = _cabi.Problem(dtype=0, bh=6, bhkv=3, nq=10, nk=12, d=32, mask=1, normalize=1, p=2, impl=0,
+                         a0=1, a1=1, a2=0.5, lim=1, temperature=1)
+    assert L.fastmax_b200_stats_bytes(prob) == 8 * 9
+    assert L.fastmax_b200_backward_workspace_bytes(prob) >= 4 * (9 + 60)
+    assert ctypes.sizeof(_cabi.Problem) == 60
+
+
+def test_bad_arguments_are_rejected_before_any_launch():
+    L = _cabi.lib()
+    prob = _cabi.Problem(dtype=0, bh=2, bhkv=2, nq=4, nk=4, d=32, mask=1, normalize=0, p=3, impl=0,
+                         a0=1, a1=1, a2=0.5, lim=1, temperature=1)
+    rc = L.fastmax_b200_forward(prob, 1, 1, 1, 1, 1, 1, None, 0, None)
+    assert rc == -1 and b"p must be 1 or 2" in L.fastmax_b200_last_error()
+    prob.p, prob.d = 2, 24
+    assert L.fastmax_b200_forward(prob, 1, 1, 1, 1, 1, 1, None, 0, None) == -1
+    prob.d, prob.nk = 32, 3
+    assert L.fastmax_b200_forward(prob, 1, 1, 1, 1, 1, 1, None, 0, None) == -1
+    prob.nk, prob.bhkv = 4, 3
+    assert L.fastmax_b200_forward(prob, 1, 1, 1, 1, 1, 1, None, 0, None) == -1
+
+
+def test_custom_path_refuses_cpu_tensors():
+    q = torch.randn(1, 2, 8, 8)
+    with pytest.raises(RuntimeError):
+        fastmax_b200.FASTMultiHeadAttention()(q, q, q, None, True)
+    with pytest.raises(ValueError):
+        fastmax_b200.fastmax_function(q, q, q, p=3)
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_pytorch_path_matches_reference_vectors(c):
+    q, k, v, go = [c[x].double().requires_grad_(x != "go") for x in ("q", "k", "v", "go")]
+    mod = fastmax_b200.FASTMultiHeadAttention(use_custom_gradient=False)
+    out = mod(q, k, v, None, c["mask"], 0.0, c["normalize"], 1.0, c["a0"], c["a1"], c["a2"], c["lim"], c["p"])
+    out.backward(go)
+    tol = 1e-9 if c["a0"] == 1.0 else 1e-6   # see tests/test_oracle.py::tol64
+    for got, name in ((out.detach(), "out"), (q.grad, "dq"), (k.grad, "dk"), (v.grad, "dv")):
+        assert rel_err(got, c[name + "64"]) < tol, name
+
+
+def test_pytorch_path_blocked_scan_and_attn_matrix():
+    c = [x for x in CASES if x["tag"] == "m1p2n0_a"][0]
+    q, k, v = [c[x].double() for x in ("q", "k", "v")]
+    kw = dict(mask=1, normalize=0, a0=c["a0"], a1=c["a1"], a2=c["a2"], lim=c["lim"], p=2)
+    a = fastmax_b200.fastmax_function(q, k, v, block=5, **kw)
+    assert rel_err(a, c["out64"]) < 1e-10
+    n = q.shape[2]
+    tri = torch.tril(torch.ones(n, n))
+    ans, attn = fastmax_b200.fastmax_function(q, k, v, mask=tri, a0=c["a0"], a1=c["a1"], a2=c["a2"],
+                                              create_attn_matrix=1)
+    assert rel_err(ans, c["out64"]) < 1e-10
+    assert torch.allclose(attn.sum(-1), torch.ones_like(attn.sum(-1)))
+
+
+def test_rpe_matrix_creator_shapes():
+    r = fastmax_b200.rpe_matrix_creator(5, 8, "cpu", torch.float32)
+    assert r.shape == (9, 8) and float(r.abs().sum()) == 0.0
+    r = fastmax_b200.rpe_matrix_creator(5, 8, "cpu", torch.float32, structured=True)
+    assert r.shape == (9, 8) and torch.allclose(r[4], torch.tensor([0., 1.] * 4))
