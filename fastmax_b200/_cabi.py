@@ -56,7 +56,7 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_forward_packed.restype = ctypes.c_int
         L.fastmax_b200_forward_packed.argtypes = [pp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.fastmax_b200_backward.restype = ctypes.c_int
-        L.fastmax_b200_backward.argtypes = [pp] + [vp] * 12 + [sz, vp]
+        L.fastmax_b200_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
         L.fastmax_b200_launch_count.restype = ctypes.c_ulonglong
         L.fastmax_b200_profile_enable.argtypes = [ctypes.c_int]
         L.fastmax_b200_profile_get.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int,

@@ -27,6 +27,9 @@ def oracle(q, k, v, go, dtype, dense=False, **kw):
 
 
 def assert_close(got, ref, dtype, what=""):
+    """Relative max error per tensor; the denominator is floored at 1e-2 (inputs
+    are O(1) Gaussians) so that gradients that are zero by construction, such as
+    grad_q and grad_k at n == 1, compare by absolute error."""
     for g, r, name in zip(got, ref, ("out", "dq", "dk", "dv")):
-        e = rel_err(g, r)
+        e = float((g.double() - r.double()).abs().max() / r.double().abs().max().clamp_min(1e-2))
         assert e < TOL[dtype], f"{what} {name}: rel err {e:.3e} >= {TOL[dtype]}"

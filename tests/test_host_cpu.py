@@ -52,6 +52,8 @@ def test_bad_arguments_are_rejected_before_any_launch():
                          a0=1, a1=1, a2=0.5, lim=1, temperature=1)
     rc = L.fastmax_b200_forward(prob, 1, 1, 1, 1, 1, 1, None, 0, None)
     assert rc == -1 and b"p must be 1 or 2" in L.fastmax_b200_last_error()
+    assert L.fastmax_b200_backward(prob, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, None, 0, None) == -1
+    assert L.fastmax_b200_forward_packed(prob, 1, 1, 1, 1, 1, None, 0, None) == -1
     prob.p, prob.d = 2, 24
     assert L.fastmax_b200_forward(prob, 1, 1, 1, 1, 1, 1, None, 0, None) == -1
     prob.d, prob.nk = 32, 3
