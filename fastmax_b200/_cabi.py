@@ -22,7 +22,7 @@ EXPORTS = (
     "fastmax_b200_forward_workspace_bytes", "fastmax_b200_backward_workspace_bytes",
     "fastmax_b200_forward", "fastmax_b200_forward_packed", "fastmax_b200_backward",
     "fastmax_b200_launch_count", "fastmax_b200_profile_enable", "fastmax_b200_profile_count",
-    "fastmax_b200_profile_get",
+    "fastmax_b200_profile_get", "fastmax_b200_device_status",
 )
 
 
@@ -57,12 +57,23 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_forward_packed.argtypes = [pp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.fastmax_b200_backward.restype = ctypes.c_int
         L.fastmax_b200_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
+        L.fastmax_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), vp]
         L.fastmax_b200_launch_count.restype = ctypes.c_ulonglong
         L.fastmax_b200_profile_enable.argtypes = [ctypes.c_int]
         L.fastmax_b200_profile_get.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int,
                                                ctypes.POINTER(ctypes.c_float)]
         _lib = L
     return _lib
+
+
+def device_status(device=None) -> int:
+    """Synchronise the current stream and return the tensor-core kernels' status word (0 = fine)."""
+    st = ctypes.c_int(0)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _check(lib().fastmax_b200_device_status(ctypes.byref(st), torch.cuda.current_stream(dev).cuda_stream),
+               "fastmax_b200_device_status")
+    return int(st.value)
 
 
 def launch_count() -> int:

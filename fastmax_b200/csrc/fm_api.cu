@@ -97,25 +97,33 @@ static int check_device() {
   return FASTMAX_OK;
 }
 
-// Family actually used for a problem.
-static int pick_impl(const fastmax_problem& p, int* impl) {
+// Family actually used for a problem.  `packed` = forward into the reference's
+// float32 (d+1)-channel layout, which only the CUDA-core family writes.
+static int pick_impl(const fastmax_problem& p, bool packed, int* impl) {
   int want = p.impl;
-  if (want == FASTMAX_IMPL_AUTO) want = FASTMAX_IMPL_DENSE_FFMA;
-  if (want != FASTMAX_IMPL_DENSE_FFMA)
+  const bool tc_ok = dense_tc_supports(p) && !packed;
+  if (want == FASTMAX_IMPL_AUTO) want = tc_ok ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
+  if (want == FASTMAX_IMPL_DENSE_TC && !tc_ok)
+    return fail(FASTMAX_E_UNSUPPORTED,
+                "the tensor-core score family needs bf16, d == 64, bh == bhkv and the plain output layout");
+  if (want != FASTMAX_IMPL_DENSE_FFMA && want != FASTMAX_IMPL_DENSE_TC)
     return fail(FASTMAX_E_UNSUPPORTED, "kernel family %d is not available in this build", want);
   *impl = want;
   return FASTMAX_OK;
 }
 
-// Backward workspace: [dots: bh+bhkv floats][delta: bh*nq floats], 256-byte aligned parts.
+// Backward workspace: [dots: bh+bhkv floats][delta or dvec: bh*nq floats]
+// [gs: bh*nq*d bf16, tensor-core family only], 256-byte aligned parts.
 struct BwdWs {
-  size_t dots_off, delta_off, total;
+  size_t dots_off, delta_off, gs_off, total;
 };
 static BwdWs bwd_layout(const fastmax_problem& p) {
   BwdWs w;
   w.dots_off = 0;
   w.delta_off = align_up(sizeof(float) * (size_t)(p.bh + p.bhkv), 256);
-  w.total = w.delta_off + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
+  w.gs_off = w.delta_off + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
+  w.total = w.gs_off;
+  if (dense_tc_supports(p)) w.total += align_up((size_t)2 * p.bh * p.nq * p.d, 256);
   return w;
 }
 
@@ -130,6 +138,11 @@ int fastmax_b200_version(void) { return 100; }
 const char* fastmax_b200_last_error(void) { return g_err; }
 
 unsigned long long fastmax_b200_launch_count(void) { return g_launches.load(); }
+
+int fastmax_b200_device_status(int* status, void* stream) {
+  if (!status) return fail(FASTMAX_E_ARG, "status is NULL");
+  return tc_status(status, (cudaStream_t)stream);
+}
 
 int fastmax_b200_profile_enable(int on) {
   g_prof_on.store(0);
@@ -187,9 +200,11 @@ static int forward_impl(const fastmax_problem* prob, const void* q, const void* 
   (void)workspace;
   if ((rc = check_device())) return rc;
   int impl;
-  if ((rc = pick_impl(p, &impl))) return rc;
+  if ((rc = pick_impl(p, o.out_f32 != 0, &impl))) return rc;
   Ctx c{p, (cudaStream_t)stream};
   if (p.normalize && (rc = launch_rowmax(c, q, k, (stat_t*)stats))) return rc;
+  if (impl == FASTMAX_IMPL_DENSE_TC)
+    return dense_tc_forward(c, q, k, v, (const stat_t*)stats, o.out, o.den);
   return dense_ffma_forward(c, q, k, v, (const stat_t*)stats, o);
 }
 
@@ -225,16 +240,24 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
                 w.total, workspace_bytes);
   if ((rc = check_device())) return rc;
   int impl;
-  if ((rc = pick_impl(p, &impl))) return rc;
+  if ((rc = pick_impl(p, false, &impl))) return rc;
   Ctx c{p, (cudaStream_t)stream};
   float* dots = (float*)((char*)workspace + w.dots_off);
   float* delta = (float*)((char*)workspace + w.delta_off);
   if (p.normalize)
     FM_CUDA_TRY(cudaMemsetAsync(dots, 0, sizeof(float) * (size_t)(p.bh + p.bhkv), c.stream));
-  if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
-  if ((rc = dense_ffma_backward(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dots,
-                                grad_q, grad_k, grad_v)))
-    return rc;
+  if (impl == FASTMAX_IMPL_DENSE_TC) {
+    void* gs = (char*)workspace + w.gs_off;
+    if ((rc = launch_gprep(c, grad_out, out, den, gs, delta))) return rc;
+    if ((rc = dense_tc_backward(c, q, k, v, gs, delta, (const stat_t*)stats, dots, grad_q, grad_k,
+                                grad_v)))
+      return rc;
+  } else {
+    if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
+    if ((rc = dense_ffma_backward(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dots,
+                                  grad_q, grad_k, grad_v)))
+      return rc;
+  }
   if (p.normalize)
     return launch_norm_fixup(c, q, k, (const stat_t*)stats, dots, grad_q, grad_k);
   return FASTMAX_OK;

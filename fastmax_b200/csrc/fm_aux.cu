@@ -120,6 +120,45 @@ int launch_delta(const Ctx& c, const void* go, const void* out, float* delta) {
 }
 
 // ---------------------------------------------------------------------------
+// Backward preparation for the tensor-core family: the upstream gradient scaled
+// by 1/den (rounded to bf16, it becomes a matrix operand) and the scaled row dot
+// dvec = (grad_out . out)/den, so that w_ij = gs_i . v_j - dvec_i.  One warp per
+// row of 64 elements, two elements per lane.
+__global__ void __launch_bounds__(256) gprep_kernel(const __nv_bfloat16* __restrict__ go,
+                                                    const __nv_bfloat16* __restrict__ out,
+                                                    const float* __restrict__ den, size_t rows,
+                                                    __nv_bfloat16* __restrict__ gs,
+                                                    float* __restrict__ dvec) {
+  size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat162 g2 = ((const __nv_bfloat162*)(go + row * 64))[lane];
+  const __nv_bfloat162 o2 = ((const __nv_bfloat162*)(out + row * 64))[lane];
+  const float2 g = __bfloat1622float2(g2), o = __bfloat1622float2(o2);
+  float s = fmaf(g.x, o.x, g.y * o.y);
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+  const float inv = 1.0f / den[row];
+  ((__nv_bfloat162*)(gs + row * 64))[lane] = __floats2bfloat162_rn(g.x * inv, g.y * inv);
+  if (lane == 0) dvec[row] = s * inv;
+}
+
+int launch_gprep(const Ctx& c, const void* go, const void* out, const float* den, void* gs,
+                 float* dvec) {
+  size_t rows = (size_t)c.p.bh * c.p.nq;
+  if (rows == 0) return FASTMAX_OK;
+  if (c.p.d != 64 || c.p.dtype != FASTMAX_BF16)
+    return fail(FASTMAX_E_UNSUPPORTED, "gprep handles bf16 rows of 64 elements");
+  unsigned blocks = (unsigned)((rows + 7) / 8);
+  FM_LAUNCH("fm_gprep", c.stream,
+            (gprep_kernel<<<blocks, 256, 0, c.stream>>>((const __nv_bfloat16*)go,
+                                                       (const __nv_bfloat16*)out, den, rows,
+                                                       (__nv_bfloat16*)gs, dvec)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+// ---------------------------------------------------------------------------
 // Gradient of x_hat = lim * x / m, m = ||x_r|| the largest row norm of the head:
 //   dx_n = (lim/m) dx_hat_n  -  [n == r] (sum_n dx_hat_n . x_hat_n) x_r / m^2 .
 // The attention kernels already wrote (lim/m) dx_hat and accumulated

@@ -90,6 +90,20 @@ struct FwdOut {
   int out_f32;
 };
 
+// gs[h,i,:] = grad_out[h,i,:] / den[h,i]  (bf16) and dvec[h,i] = (grad_out[h,i,:] . out[h,i,:]) / den[h,i]
+int launch_gprep(const Ctx& c, const void* grad_out, const void* out, const float* den, void* gs,
+                 float* dvec);
+
+// Tensor-core score-form family (bf16, head dimension 64, bh == bhkv).
+bool dense_tc_supports(const fastmax_problem& p);
+int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,
+                     const stat_t* stats, void* out, float* den);
+int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
+                      const float* dvec, const stat_t* stats, float* dots, void* grad_q,
+                      void* grad_k, void* grad_v);
+// Copies the device-side protocol status word to *out (synchronises the stream).
+int tc_status(int* out, cudaStream_t stream);
+
 int dense_ffma_forward(const Ctx& c, const void* q, const void* k, const void* v,
                        const stat_t* stats, const FwdOut& o);
 int dense_ffma_backward(const Ctx& c, const void* q, const void* k, const void* v,

@@ -96,6 +96,13 @@ int fastmax_b200_profile_enable(int on);
 int fastmax_b200_profile_count(void);
 int fastmax_b200_profile_get(int i, char* name, int name_len, float* ms);
 
+/* Device-side protocol status (no counterpart in the reference).  The
+ * tensor-core kernels bound every wait on a barrier; a wait that gives up stores
+ * a non-zero code in a device word and the kernel winds down instead of
+ * hanging.  This call synchronises `stream` and copies the word to *status
+ * (host pointer): 0 means no kernel of this process ever gave up a wait. */
+int fastmax_b200_device_status(int* status, void* stream);
+
 /* Bytes of the per-head statistics buffer (max row norms and their row
  * indices) that forward writes and backward reads.  Replaces the reference's
  * qnorms/knorms/qmaxes/kmaxes temporaries (reference fastmax_cuda_forward.cu:
