@@ -1,0 +1,77 @@
+"""GPU parity of the tcgen05 tensor-core family (bf16, head dimension 64) against the
+CPU oracle, through the C ABI.  Tolerance: 2e-2 relative on outputs and gradients."""
+import pytest
+import torch
+
+from gpu_util import assert_close, oracle, run_cabi
+
+from fastmax_b200 import _cabi
+
+pytestmark = pytest.mark.gpu
+
+
+def randn(*shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g)
+
+
+# bh, nq, nk, mask, p, normalize
+EDGE = [(1, 1, 1, 1, 2, 1), (2, 2, 2, 1, 2, 1), (1, 17, 17, 0, 2, 1), (3, 127, 127, 1, 2, 1),
+        (3, 128, 128, 1, 1, 1), (2, 129, 129, 0, 1, 0), (3, 255, 255, 1, 2, 1), (2, 256, 256, 1, 2, 0),
+        (2, 257, 257, 1, 2, 1), (2, 300, 300, 0, 2, 1), (5, 1000, 1000, 1, 2, 1), (2, 1500, 1500, 0, 2, 0),
+        (2, 70, 100, 1, 2, 1), (2, 70, 100, 0, 2, 1), (2, 200, 457, 1, 1, 1), (1, 2500, 2500, 1, 2, 1)]
+
+
+@pytest.mark.parametrize("cfg", EDGE, ids=[f"bh{c[0]}nq{c[1]}nk{c[2]}m{c[3]}p{c[4]}z{c[5]}" for c in EDGE])
+def test_tensor_core_family_against_dense_oracle(cfg):
+    bh, nq, nk, mask, p, norm = cfg
+    q, go = randn(1, bh, nq, 64, seed=nq), randn(1, bh, nq, 64, seed=nq + 1)
+    k, v = randn(1, bh, nk, 64, seed=nk + 2), randn(1, bh, nk, 64, seed=nk + 3)
+    if not norm:
+        q, k = q / 8, k / 8
+    kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    got, _ = run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", **kw)
+    assert _cabi.device_status() == 0
+    ref = oracle(q, k, v, go, torch.bfloat16, dense=True, **kw)
+    assert_close(got, ref, torch.bfloat16, str(cfg))
+
+
+def test_other_coefficients_and_lim():
+    q, k, v, go = [randn(1, 3, 333, 64, seed=s) for s in (1, 2, 3, 4)]
+    kw = dict(mask=1, normalize=1, p=2, a0=0.7, a1=1.3, a2=0.4, lim=1.5)
+    got, _ = run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", **kw)
+    ref = oracle(q, k, v, go, torch.bfloat16, dense=True, **kw)
+    assert_close(got, ref, torch.bfloat16, "coefficients")
+
+
+def test_auto_dispatch_picks_tensor_cores_and_matches_cuda_core_family():
+    """Both families on the same device inputs at a size the CPU oracle would take long on."""
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(5)
+    q, k, v, go = [torch.randn(4, 4096, 64, generator=g, device=dev).bfloat16() for _ in range(4)]
+    kw = dict(mask=True, normalize=True, p=2)
+    res = {}
+    for impl in ("auto", "dense_ffma"):
+        _cabi.profile(True)
+        out, den, stats = _cabi.forward(q, k, v, impl=impl, **kw)
+        grads = _cabi.backward(q, k, v, out, den, stats, go, impl=impl, **kw)
+        names = {n for n, _ in _cabi.profile_records()}
+        _cabi.profile(False)
+        res[impl] = (out, den) + tuple(grads)
+        if impl == "auto":
+            assert "fm_dense_tc_fwd" in names and "fm_dense_tc_dq" in names
+    assert _cabi.device_status() == 0
+    for a, b, name in zip(res["auto"], res["dense_ffma"], ("out", "den", "dq", "dk", "dv")):
+        e = float((a.float() - b.float()).abs().max() / b.float().abs().max())
+        assert e < 2e-2, (name, e)
+
+
+def test_unsupported_requests_fail_loudly():
+    q = torch.randn(2, 64, 32, device="cuda").bfloat16()
+    with pytest.raises(RuntimeError):
+        _cabi.forward(q, q, q, mask=True, normalize=False, p=2, impl="dense_tc")   # d = 32
+    q = torch.randn(2, 64, 64, device="cuda")
+    with pytest.raises(RuntimeError):
+        _cabi.forward(q, q, q, mask=True, normalize=False, p=2, impl="dense_tc")   # fp32
+    with pytest.raises(RuntimeError):
+        _cabi.forward(q.bfloat16(), q.bfloat16(), q.bfloat16(), mask=True, normalize=False, p=2, impl="moments_tc")
