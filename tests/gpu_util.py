@@ -26,10 +26,12 @@ def oracle(q, k, v, go, dtype, dense=False, **kw):
     return fastmax_fwd_bwd(r(q), r(k), r(v), r(go), dense=dense, **kw)
 
 
-def assert_close(got, ref, dtype, what=""):
+def assert_close(got, ref, dtype, what="", floor=1e-2):
     """Relative max error per tensor; the denominator is floored at 1e-2 (inputs
     are O(1) Gaussians) so that gradients that are zero by construction, such as
-    grad_q and grad_k at n == 1, compare by absolute error."""
+    grad_q and grad_k at n == 1, compare by absolute error (callers raise the
+    floor to the magnitude of the cancelling terms where bf16 rounding of an
+    intermediate makes that cancellation inexact)."""
     for g, r, name in zip(got, ref, ("out", "dq", "dk", "dv")):
-        e = float((g.double() - r.double()).abs().max() / r.double().abs().max().clamp_min(1e-2))
+        e = float((g.double() - r.double()).abs().max() / r.double().abs().max().clamp_min(floor))
         assert e < TOL[dtype], f"{what} {name}: rel err {e:.3e} >= {TOL[dtype]}"
