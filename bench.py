@@ -39,6 +39,7 @@ WORKLOADS = {
     "c4p2": (32, 32, 16384, 128, "bf16", 0, 2, 0),
     "c4p1": (32, 32, 16384, 128, "bf16", 0, 1, 0),
     "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
+    "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),   # small case for ncu captures (inputs 4 x 67 MB)
 }
 A = dict(a0=1.0, a1=1.0, a2=0.5, lim=1.0)
 

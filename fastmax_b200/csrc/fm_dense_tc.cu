@@ -20,9 +20,12 @@
 //   the group's warps read S (W) from TMEM, apply the polynomial and the mask and
 //   write the bf16 result P back to TMEM
 //   O += P Z   (or P Y)                  TMEM x smem  -> TMEM accumulator
-// The issue order S0 S1 | O0 S0' | O1 S1' ... lets one group's CUDA-core work
-// overlap the other group's tensor-core work.  All waits are bounded; a wait that
-// gives up records an error status and the kernel winds down without hanging.
+// A group copies its whole S (W) row block to registers and hands the TMEM region
+// back at once, so the issuing thread -- which polls the groups' barriers and
+// issues whatever is ready -- can start the next tile's S while the group is still
+// computing; the tensor pipe therefore runs ahead of the CUDA cores of both groups.
+// The polynomial is evaluated on packed fp32 pairs.  All waits are bounded; a wait
+// that gives up records an error status and the kernel winds down without hanging.
 #include <climits>
 
 #include "fm_common.cuh"
@@ -55,7 +58,7 @@ constexpr int kThreads = 320;  // warps 0-3: group 0, 4-7: group 1, 8: TMA produ
 template <int MODE>
 struct Cfg {
   static constexpr int BN = (MODE == OP_A) ? 128 : 64;
-  static constexpr int NS = (MODE == OP_A) ? 3 : 4;
+  static constexpr int NS = (MODE == OP_A) ? 4 : 6;
   static constexpr int ROW_TILE = BM * D * 2;
   static constexpr int COL_TILE = BN * D * 2;
   static constexpr int NROWOPS = (MODE == OP_A) ? 1 : 2;
@@ -65,7 +68,7 @@ struct Cfg {
   static constexpr int OFF_ST = NROWOPS * 2 * ROW_TILE;
   static constexpr int OFF_VEC = OFF_ST + NS * STAGE;
   static constexpr int OFF_BAR = OFF_VEC + NS * BN * 4;
-  static constexpr int NBAR = 1 + 2 * NS + 6;
+  static constexpr int NBAR = 1 + 2 * NS + 8;
   static constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
   static constexpr int SMEM = OFF_TMEM + 16 + 1024;  // + slack for the 1024-byte alignment
   // TMEM columns inside a group's 256-column half
@@ -85,12 +88,14 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + C::OFF_BAR;
+  // barrier map: x | kv_full[NS] | kv_empty[NS] | s_full[2] | s_free[2] | p_full[2] | pv_done[2]
   auto BAR_X = [&]() { return bar0; };
   auto BAR_FULL = [&](int s) { return bar0 + 8u * (1 + s); };
   auto BAR_EMPTY = [&](int s) { return bar0 + 8u * (1 + NS + s); };
   auto BAR_S = [&](int g) { return bar0 + 8u * (1 + 2 * NS + g); };
-  auto BAR_P = [&](int g) { return bar0 + 8u * (3 + 2 * NS + g); };
-  auto BAR_O = [&](int g) { return bar0 + 8u * (5 + 2 * NS + g); };
+  auto BAR_SFREE = [&](int g) { return bar0 + 8u * (3 + 2 * NS + g); };
+  auto BAR_P = [&](int g) { return bar0 + 8u * (5 + 2 * NS + g); };
+  auto BAR_PV = [&](int g) { return bar0 + 8u * (7 + 2 * NS + g); };
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + C::OFF_TMEM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -99,24 +104,22 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   const int r0 = pair * 2 * BM;
   const bool colvec = (MODE == OP_B) && a.rev;
 
-  // ---- tile ranges ----------------------------------------------------------------
+  // ---- tile ranges: group g walks column tiles [tb_g, te_g) -------------------------
   const int ntile = (a.ncols + BN - 1) / BN;
-  int tbg[2], teg[2];
-  bool act[2];
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    const int R = r0 + g * BM;
-    act[g] = R < a.nrows;
-    tbg[g] = 0;
-    teg[g] = ntile;
-    if (a.mask) {
-      if (a.rev) tbg[g] = max(0, R - a.off) / BN;
-      else teg[g] = min(ntile, (min(R + BM - 1, a.nrows - 1) + a.off) / BN + 1);
+  int tb0 = 0, te0 = ntile, tb1 = 0, te1 = ntile;
+  if (a.mask) {
+    if (a.rev) {
+      tb0 = max(0, r0 - a.off) / BN;
+      tb1 = max(0, r0 + BM - a.off) / BN;
+    } else {
+      te0 = min(ntile, (min(r0 + BM - 1, a.nrows - 1) + a.off) / BN + 1);
+      te1 = min(ntile, (min(r0 + 2 * BM - 1, a.nrows - 1) + a.off) / BN + 1);
     }
-    if (!act[g]) { tbg[g] = INT_MAX; teg[g] = 0; }
   }
-  const int tb = min(tbg[0], tbg[1]);
-  const int te = max(teg[0], teg[1]);
+  const bool act1 = r0 + BM < a.nrows;  // group 0 always has rows
+  if (!act1) { tb1 = INT_MAX; te1 = 0; }
+  const int tb = min(tb0, tb1);
+  const int te = max(te0, te1);
 
   // ---- set-up -----------------------------------------------------------------------
   if (tid == 0) {
@@ -127,8 +130,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     }
     for (int g = 0; g < 2; ++g) {
       mbar_init(BAR_S(g), 1);
+      mbar_init(BAR_SFREE(g), 128);
       mbar_init(BAR_P(g), 128);
-      mbar_init(BAR_O(g), 1);
+      mbar_init(BAR_PV(g), 1);
     }
     mbar_fence_init();
   }
@@ -145,10 +149,8 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       tma_prefetch_desc(&tmY);
       tma_prefetch_desc(&tmZ);
       if (MODE == OP_B) tma_prefetch_desc(&tmU);
-      const int nact = (act[0] ? 1 : 0) + (act[1] ? 1 : 0);
-      mbar_expect_tx(BAR_X(), nact * C::NROWOPS * C::ROW_TILE);
-      for (int g = 0; g < 2; ++g) {
-        if (!act[g]) continue;
+      mbar_expect_tx(BAR_X(), (act1 ? 2 : 1) * C::NROWOPS * C::ROW_TILE);
+      for (int g = 0; g < (act1 ? 2 : 1); ++g) {
         tma_load_3d(sbase + C::OFF_X + g * C::ROW_TILE, &tmX, BAR_X(), 0, r0 + g * BM, head);
         if (MODE == OP_B)
           tma_load_3d(sbase + C::OFF_U + g * C::ROW_TILE, &tmU, BAR_X(), 0, r0 + g * BM, head);
@@ -173,80 +175,88 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
     }
   } else if (warp == 9) {
-    // ================= MMA issuer =================
-    constexpr uint32_t idescS = idesc_bf16(BM, BN, 0, 0);
-    constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
-    bool ok = te > tb ? mbar_wait(BAR_X(), 0) : true;
-    if (!ok) report(2);
-    tc_fence_after();
-    auto stage_of = [&](int t) { return (t - tb) % NS; };
-    auto full_parity = [&](int t) { return (uint32_t)(((t - tb) / NS) & 1); };
-    auto issue_S = [&](int g, int t) {
-      const uint32_t st = sbase + C::OFF_ST + stage_of(t) * C::STAGE;
-      const uint32_t xa = sbase + C::OFF_X + g * C::ROW_TILE;
-      const uint32_t tg = tmem + g * 256;
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks)
-        umma_ss(tg + C::T_S, smem_desc_sw128(xa + ks * 32, 16, 1024),
-                smem_desc_sw128(st + ks * 32, 16, 1024), idescS, ks > 0);
-      if (MODE == OP_B) {
-        const uint32_t ua = sbase + C::OFF_U + g * C::ROW_TILE;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          umma_ss(tg + C::T_W, smem_desc_sw128(ua + ks * 32, 16, 1024),
-                  smem_desc_sw128(st + C::COL_TILE + ks * 32, 16, 1024), idescS, ks > 0);
-      }
-      umma_commit(BAR_S(g));
-    };
-    auto issue_O = [&](int g, int t, bool acc) {
-      const uint32_t st = sbase + C::OFF_ST + stage_of(t) * C::STAGE;
-      const uint32_t b = (MODE == OP_A) ? st + C::COL_TILE : st;  // OP_A: Z tile, OP_B: Y tile
-      const uint32_t tg = tmem + g * 256;
-#pragma unroll
-      for (int ks = 0; ks < BN / 16; ++ks)
-        umma_ts(tg + C::T_O, tg + C::T_P + ks * 8, smem_desc_sw128(b + ks * 2048, C::COL_TILE, 1024),
-                idescO, (acc || ks > 0) ? 1u : 0u);
-    };
-    if (ok && te > tb) {
-      if (!mbar_wait(BAR_FULL(stage_of(tb)), full_parity(tb))) { report(3); ok = false; }
+    // ================= MMA issuer (one thread polls and issues) =================
+    if (lane == 0) {
+      constexpr uint32_t idescS = idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
+      const int tbg[2] = {tb0, tb1}, J[2] = {te0 - tb0, act1 ? te1 - tb1 : 0};
+      int nS[2] = {0, 0}, nPV[2] = {0, 0};
+      int rel = tb;  // next column tile whose ring stage is to be released
+      bool ok = mbar_wait(BAR_X(), 0);
+      if (!ok) report(2);
       tc_fence_after();
-      if (ok && lane == 0)
-        for (int g = 0; g < 2; ++g)
-          if (act[g] && tbg[g] == tb) issue_S(g, tb);
-      __syncwarp();
-    }
-    for (int t = tb; ok && t < te; ++t) {
-      for (int g = 0; ok && g < 2; ++g) {
-        if (!act[g]) continue;
-        if (t >= tbg[g] && t < teg[g]) {
-          if (!mbar_wait(BAR_P(g), (uint32_t)((t - tbg[g]) & 1))) { report(4); ok = false; break; }
-          tc_fence_after();
-          if (lane == 0) issue_O(g, t, t > tbg[g]);
-          if (t + 1 < teg[g]) {
-            if (!mbar_wait(BAR_FULL(stage_of(t + 1)), full_parity(t + 1))) { report(5); ok = false; break; }
-            tc_fence_after();
-            if (lane == 0) issue_S(g, t + 1);
-          } else if (lane == 0) {
-            umma_commit(BAR_O(g));
+      long long t_idle = clock64();
+      while (ok && (nPV[0] < J[0] || nPV[1] < J[1])) {
+        bool progress = false;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t tg = tmem + g * 256;
+          // S (and W) of the group's next tile, as soon as the previous one was read out
+          if (nS[g] < J[g]) {
+            const int t = tbg[g] + nS[g];
+            const int k = t - tb, s = k % NS;
+            if ((nS[g] == 0 || mbar_test(BAR_SFREE(g), (uint32_t)((nS[g] - 1) & 1))) &&
+                mbar_test(BAR_FULL(s), (uint32_t)((k / NS) & 1))) {
+              tc_fence_after();
+              const uint32_t st = sbase + C::OFF_ST + s * C::STAGE;
+              const uint32_t xa = sbase + C::OFF_X + g * C::ROW_TILE;
+#pragma unroll
+              for (int ks = 0; ks < D / 16; ++ks)
+                umma_ss(tg + C::T_S, smem_desc_sw128(xa + ks * 32, 16, 1024),
+                        smem_desc_sw128(st + ks * 32, 16, 1024), idescS, ks > 0);
+              if (MODE == OP_B) {
+                const uint32_t ua = sbase + C::OFF_U + g * C::ROW_TILE;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                  umma_ss(tg + C::T_W, smem_desc_sw128(ua + ks * 32, 16, 1024),
+                          smem_desc_sw128(st + C::COL_TILE + ks * 32, 16, 1024), idescS, ks > 0);
+              }
+              umma_commit(BAR_S(g));
+              ++nS[g];
+              progress = true;
+            }
           }
-        } else if (t + 1 == tbg[g]) {
-          if (!mbar_wait(BAR_FULL(stage_of(t + 1)), full_parity(t + 1))) { report(6); ok = false; break; }
-          tc_fence_after();
-          if (lane == 0) issue_S(g, t + 1);
+          // O += P (Z or Y) once the group wrote P
+          if (nPV[g] < nS[g] && mbar_test(BAR_P(g), (uint32_t)(nPV[g] & 1))) {
+            tc_fence_after();
+            const int t = tbg[g] + nPV[g];
+            const int s = (t - tb) % NS;
+            const uint32_t st = sbase + C::OFF_ST + s * C::STAGE;
+            const uint32_t b = (MODE == OP_A) ? st + C::COL_TILE : st;  // OP_A: Z tile, OP_B: Y tile
+#pragma unroll
+            for (int ks = 0; ks < BN / 16; ++ks)
+              umma_ts(tg + C::T_O, tg + C::T_P + ks * 8,
+                      smem_desc_sw128(b + ks * 2048, C::COL_TILE, 1024), idescO,
+                      (nPV[g] > 0 || ks > 0) ? 1u : 0u);
+            umma_commit(BAR_PV(g));
+            ++nPV[g];
+            progress = true;
+            // release ring stages every group is done with
+            while (rel < te) {
+              const bool d0 = rel < tb0 || rel >= te0 || rel < tb0 + nPV[0];
+              const bool d1 = !act1 || rel < tb1 || rel >= te1 || rel < tb1 + nPV[1];
+              if (!(d0 && d1)) break;
+              umma_commit(BAR_EMPTY((rel - tb) % NS));
+              ++rel;
+            }
+          }
         }
-        __syncwarp();
+        if (progress) t_idle = clock64();
+        else if (clock64() - t_idle > kWaitLimitClocks) { report(3); ok = false; }
       }
-      if (ok && lane == 0) umma_commit(BAR_EMPTY(stage_of(t)));
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ================= compute groups =================
     const int g = warp >> 2, qd = warp & 3;
-    if (act[g]) {
+    const int tbg = g ? tb1 : tb0, teg = g ? te1 : te0;
+    if (g == 0 || act1) {
       const int row = r0 + g * BM + qd * 32 + lane;
       const bool row_ok = row < a.nrows;
       const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
       const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
+      const uint64_t A0v = pack2(A0, A0), A1v = pack2(A1, A1);
+      const uint64_t A2v = (MODE == OP_A) ? pack2(A2, A2) : pack2(2.f * A2, 2.f * A2);
       // columns kept for this row: lowcol <= col <= limcol
       int limcol = a.ncols - 1, lowcol = 0;
       if (a.mask) {
@@ -256,12 +266,23 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       const int wrow_lo = r0 + g * BM + qd * 32, wrow_hi = wrow_lo + 31;
       float dl_row = 0.f;
       if (MODE == OP_B && !a.rev && row_ok) dl_row = __ldg(a.dvec + (size_t)head * a.nrows + row);
+      const uint64_t ndl_row = pack2(-dl_row, -dl_row);
       const uint32_t tg = tmem + g * 256 + ((uint32_t)(qd * 32) << 16);
-      float rowsum = 0.f;
+      uint64_t rs2 = pack2(0.f, 0.f);
       bool ok = true;
-      for (int t = tbg[g]; t < teg[g]; ++t) {
-        if (!mbar_wait(BAR_S(g), (uint32_t)((t - tbg[g]) & 1))) { report(7); ok = false; break; }
+      for (int t = tbg; t < teg; ++t) {
+        const int j = t - tbg;
+        if (!mbar_wait(BAR_S(g), (uint32_t)(j & 1))) { report(7); ok = false; break; }
         tc_fence_after();
+        // the whole tile row goes to registers, then the TMEM region is handed back
+        uint32_t sv[BN];
+        uint32_t wv[(MODE == OP_B) ? BN : 1];
+        tmem_ld64(tg + C::T_S, sv);
+        if constexpr (MODE == OP_A) tmem_ld64(tg + C::T_S + 64, sv + 64);
+        else tmem_ld64(tg + C::T_W, wv);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(BAR_SFREE(g));
         const float* vec = nullptr;
         if (colvec) {
           const int k = t - tb, s = k % NS;
@@ -269,61 +290,66 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           vec = (const float*)(smem + C::OFF_VEC) + s * BN;
         }
         const int c0 = t * BN;
-        // does any element of this warp's 32 x BN block need masking?
         bool need_mask = (c0 + BN > a.ncols);
         if (a.mask) need_mask = need_mask || (a.rev ? (c0 < wrow_hi - a.off) : (c0 + BN - 1 > wrow_lo + a.off));
+        uint32_t pk[BN / 2];
+        if (!need_mask) {
 #pragma unroll
-        for (int cc = 0; cc < BN / 32; ++cc) {
-          uint32_t sv[32], pk[16];
-          float pv[32];
-          tmem_ld32(tg + C::T_S + cc * 32, sv);
-          if (MODE == OP_B) {
-            uint32_t wv[32];
-            tmem_ld32(tg + C::T_W + cc * 32, wv);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const float s = __uint_as_float(sv[e]);
-              const float dl = a.rev ? vec[cc * 32 + e] : dl_row;
-              pv[e] = fmaf(2.f * A2, s, A1) * (__uint_as_float(wv[e]) - dl);
+          for (int e = 0; e < BN / 2; ++e) {
+            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+            uint64_t p2;
+            if (MODE == OP_A) {
+              p2 = fma2(fma2(A2v, s2, A1v), s2, A0v);
+              rs2 = add2(rs2, p2);
+            } else {
+              const uint64_t ndl = a.rev ? pack2(-vec[2 * e], -vec[2 * e + 1]) : ndl_row;
+              p2 = mul2(fma2(A2v, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl));
             }
-          } else {
-            tmem_wait_ld();
+            pk[e] = pack_bf16_2(p2);
+          }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const float s = __uint_as_float(sv[e]);
-              pv[e] = fmaf(fmaf(A2, s, A1), s, A0);
+          for (int e = 0; e < BN / 2; ++e) {
+            float pv[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col = c0 + 2 * e + h;
+              const float s = __uint_as_float(sv[2 * e + h]);
+              float v;
+              if (MODE == OP_A) {
+                v = fmaf(fmaf(A2, s, A1), s, A0);
+              } else {
+                const float dl = a.rev ? vec[2 * e + h] : dl_row;
+                v = fmaf(2.f * A2, s, A1) * (__uint_as_float(wv[2 * e + h]) - dl);
+              }
+              pv[h] = (col > limcol || col < lowcol) ? 0.f : v;
             }
+            if (MODE == OP_A) rs2 = add2(rs2, pack2(pv[0], pv[1]));
+            pk[e] = pack_bf16(pv[0], pv[1]);
           }
-          if (need_mask) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int col = c0 + cc * 32 + e;
-              if (col > limcol || col < lowcol) pv[e] = 0.f;
-            }
-          }
-          if (MODE == OP_A) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) rowsum += pv[e];
-          }
-#pragma unroll
-          for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pv[2 * e], pv[2 * e + 1]);
-          tmem_st16(tg + C::T_P + cc * 16, pk);
         }
+        // P(t-1) must have been consumed by its MMA before it is overwritten
+        if (j > 0 && !mbar_wait(BAR_PV(g), (uint32_t)((j - 1) & 1))) { report(9); ok = false; break; }
+        tc_fence_after();
+        tmem_st32(tg + C::T_P, pk);
+        if constexpr (BN == 128) tmem_st32(tg + C::T_P + 32, pk + 32);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR_P(g));
       }
       // ---- epilogue: this thread's row of the accumulator -> global ----
-      if (ok && teg[g] > tbg[g]) {
-        if (!mbar_wait(BAR_O(g), 0)) { report(9); ok = false; }
+      const int Jg = teg - tbg;
+      if (ok && Jg > 0) {
+        if (!mbar_wait(BAR_PV(g), (uint32_t)((Jg - 1) & 1))) { report(10); ok = false; }
       }
       tc_fence_after();
-      if (ok && teg[g] > tbg[g]) {
-        uint32_t o0[32], o1[32];
-        tmem_ld32(tg + C::T_O, o0);
-        tmem_ld32(tg + C::T_O + 32, o1);
+      if (ok && Jg > 0) {
+        uint32_t ov[64];
+        tmem_ld64(tg + C::T_O, ov);
         tmem_wait_ld();
+        float rlo, rhi;
+        unpack2(rs2, rlo, rhi);
+        const float rowsum = rlo + rhi;
         float scale = 1.f;
         if (MODE == OP_A && a.fwd_div) scale = 1.0f / rowsum;
         float part = 0.f;
@@ -336,10 +362,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           for (int v8 = 0; v8 < 8; ++v8) {
             float f[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int idx = v8 * 8 + e;
-              f[e] = __uint_as_float(idx < 32 ? o0[idx] : o1[idx - 32]) * scale;
-            }
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[v8 * 8 + e]) * scale;
             uint4 w;
             w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
             w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
