@@ -53,7 +53,7 @@ struct TcArgs {
 };
 
 constexpr int D = 64, BM = 128;
-constexpr int kThreads = 320;  // warps 0-3: group 0, 4-7: group 1, 8: TMA producer, 9: MMA issuer
+constexpr int kThreads = 352;  // warps 0-3: group 0, 4-7: group 1, 8: TMA producer, 9/10: MMA issuers
 
 template <int MODE>
 struct Cfg {
@@ -126,12 +126,12 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     mbar_init(BAR_X(), 1);
     for (int s = 0; s < NS; ++s) {
       mbar_init(BAR_FULL(s), colvec ? 33 : 1);
-      mbar_init(BAR_EMPTY(s), 1);
+      mbar_init(BAR_EMPTY(s), 2);
     }
     for (int g = 0; g < 2; ++g) {
       mbar_init(BAR_S(g), 1);
-      mbar_init(BAR_SFREE(g), 128);
-      mbar_init(BAR_P(g), 128);
+      mbar_init(BAR_SFREE(g), 4);
+      mbar_init(BAR_P(g), 4);
       mbar_init(BAR_PV(g), 1);
     }
     mbar_fence_init();
@@ -169,80 +169,56 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         float* vec = (float*)(smem + C::OFF_VEC) + s * BN;
         for (int e = lane; e < BN; e += 32) {
           const int col = t * BN + e;
-          vec[e] = (col < a.ncols) ? __ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;
+          vec[e] = (col < a.ncols) ? -__ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;  // negated
         }
         mbar_arrive(BAR_FULL(s));
       }
     }
-  } else if (warp == 9) {
-    // ================= MMA issuer (one thread polls and issues) =================
-    if (lane == 0) {
+  } else if (warp >= 9) {
+    // ================= MMA issuers: warp 9 serves group 0, warp 10 group 1 =================
+    const int g = warp - 9;
+    const int tbg = g ? tb1 : tb0, teg = g ? te1 : te0;
+    const int J = (g == 0 || act1) ? teg - tbg : 0;
+    if (lane == 0 && J > 0) {
       constexpr uint32_t idescS = idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
-      const int tbg[2] = {tb0, tb1}, J[2] = {te0 - tb0, act1 ? te1 - tb1 : 0};
-      int nS[2] = {0, 0}, nPV[2] = {0, 0};
-      int rel = tb;  // next column tile whose ring stage is to be released
+      const uint32_t tg = tmem + g * 256;
+      const uint32_t x_lo = desc_lo(sbase + C::OFF_X + g * C::ROW_TILE, 16);
+      const uint32_t u_lo = desc_lo(sbase + C::OFF_U + g * C::ROW_TILE, 16);
+      const uint32_t st_k = desc_lo(sbase + C::OFF_ST, 16);               // stage 0, K-major view
+      const uint32_t st_mn = desc_lo(sbase + C::OFF_ST, C::COL_TILE);     // stage 0, MN-major view
+      // the other group also reads tile t unless t is outside its range
+      const int otb = g ? tb0 : tb1, ote = g ? te0 : te1;
       bool ok = mbar_wait(BAR_X(), 0);
       if (!ok) report(2);
       tc_fence_after();
-      long long t_idle = clock64();
-      while (ok && (nPV[0] < J[0] || nPV[1] < J[1])) {
-        bool progress = false;
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const uint32_t tg = tmem + g * 256;
-          // S (and W) of the group's next tile, as soon as the previous one was read out
-          if (nS[g] < J[g]) {
-            const int t = tbg[g] + nS[g];
-            const int k = t - tb, s = k % NS;
-            if ((nS[g] == 0 || mbar_test(BAR_SFREE(g), (uint32_t)((nS[g] - 1) & 1))) &&
-                mbar_test(BAR_FULL(s), (uint32_t)((k / NS) & 1))) {
-              tc_fence_after();
-              const uint32_t st = sbase + C::OFF_ST + s * C::STAGE;
-              const uint32_t xa = sbase + C::OFF_X + g * C::ROW_TILE;
-#pragma unroll
-              for (int ks = 0; ks < D / 16; ++ks)
-                umma_ss(tg + C::T_S, smem_desc_sw128(xa + ks * 32, 16, 1024),
-                        smem_desc_sw128(st + ks * 32, 16, 1024), idescS, ks > 0);
-              if (MODE == OP_B) {
-                const uint32_t ua = sbase + C::OFF_U + g * C::ROW_TILE;
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks)
-                  umma_ss(tg + C::T_W, smem_desc_sw128(ua + ks * 32, 16, 1024),
-                          smem_desc_sw128(st + C::COL_TILE + ks * 32, 16, 1024), idescS, ks > 0);
-              }
-              umma_commit(BAR_S(g));
-              ++nS[g];
-              progress = true;
-            }
-          }
-          // O += P (Z or Y) once the group wrote P
-          if (nPV[g] < nS[g] && mbar_test(BAR_P(g), (uint32_t)(nPV[g] & 1))) {
-            tc_fence_after();
-            const int t = tbg[g] + nPV[g];
-            const int s = (t - tb) % NS;
-            const uint32_t st = sbase + C::OFF_ST + s * C::STAGE;
-            const uint32_t b = (MODE == OP_A) ? st + C::COL_TILE : st;  // OP_A: Z tile, OP_B: Y tile
-#pragma unroll
-            for (int ks = 0; ks < BN / 16; ++ks)
-              umma_ts(tg + C::T_O, tg + C::T_P + ks * 8,
-                      smem_desc_sw128(b + ks * 2048, C::COL_TILE, 1024), idescO,
-                      (nPV[g] > 0 || ks > 0) ? 1u : 0u);
-            umma_commit(BAR_PV(g));
-            ++nPV[g];
-            progress = true;
-            // release ring stages every group is done with
-            while (rel < te) {
-              const bool d0 = rel < tb0 || rel >= te0 || rel < tb0 + nPV[0];
-              const bool d1 = !act1 || rel < tb1 || rel >= te1 || rel < tb1 + nPV[1];
-              if (!(d0 && d1)) break;
-              umma_commit(BAR_EMPTY((rel - tb) % NS));
-              ++rel;
-            }
-          }
+      auto issue_S = [&](int t) -> bool {
+        const int k = t - tb, s = k % NS;
+        if (!mbar_wait(BAR_FULL(s), (uint32_t)((k / NS) & 1))) { report(3); return false; }
+        tc_fence_after();
+        const uint32_t y_lo = st_k + (uint32_t)s * (C::STAGE >> 4);
+        umma_ss_k64(tg + C::T_S, x_lo, y_lo, idescS);
+        if (MODE == OP_B) umma_ss_k64(tg + C::T_W, u_lo, y_lo + (C::COL_TILE >> 4), idescS);
+        umma_commit(BAR_S(g));
+        return true;
+      };
+      if (ok) ok = issue_S(tbg);
+      for (int j = 0; ok && j < J; ++j) {
+        const int t = tbg + j;
+        if (j + 1 < J) {
+          if (!mbar_wait(BAR_SFREE(g), (uint32_t)(j & 1))) { report(4); ok = false; break; }
+          if (!issue_S(t + 1)) { ok = false; break; }
         }
-        if (progress) t_idle = clock64();
-        else if (clock64() - t_idle > kWaitLimitClocks) { report(3); ok = false; }
+        if (!mbar_wait(BAR_P(g), (uint32_t)(j & 1))) { report(5); ok = false; break; }
+        tc_fence_after();
+        const int s = (t - tb) % NS;
+        // OP_A multiplies by the Z tile (second half of the stage), OP_B by the Y tile
+        const uint32_t b_lo = st_mn + (uint32_t)s * (C::STAGE >> 4) + ((MODE == OP_A) ? (C::COL_TILE >> 4) : 0);
+        umma_ts_steps<BN / 16>(tg + C::T_O, tg + C::T_P, b_lo, idescO, j > 0 ? 1u : 0u);
+        umma_commit(BAR_PV(g));
+        // the ring stage is free once both groups' MMAs on it are done (2 arrivals)
+        umma_commit(BAR_EMPTY(s));
+        if (t < otb || t >= ote) umma_commit(BAR_EMPTY(s));
       }
     }
     __syncwarp();
@@ -268,7 +244,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       if (MODE == OP_B && !a.rev && row_ok) dl_row = __ldg(a.dvec + (size_t)head * a.nrows + row);
       const uint64_t ndl_row = pack2(-dl_row, -dl_row);
       const uint32_t tg = tmem + g * 256 + ((uint32_t)(qd * 32) << 16);
-      uint64_t rs2 = pack2(0.f, 0.f);
+      uint64_t rs2[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
       bool ok = true;
       for (int t = tbg; t < teg; ++t) {
         const int j = t - tbg;
@@ -282,7 +258,8 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         else tmem_ld64(tg + C::T_W, wv);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(BAR_SFREE(g));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_SFREE(g));
         const float* vec = nullptr;
         if (colvec) {
           const int k = t - tb, s = k % NS;
@@ -300,9 +277,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             uint64_t p2;
             if (MODE == OP_A) {
               p2 = fma2(fma2(A2v, s2, A1v), s2, A0v);
-              rs2 = add2(rs2, p2);
+              rs2[e & 3] = add2(rs2[e & 3], p2);
             } else {
-              const uint64_t ndl = a.rev ? pack2(-vec[2 * e], -vec[2 * e + 1]) : ndl_row;
+              const uint64_t ndl = a.rev ? ((const uint64_t*)vec)[e] : ndl_row;
               p2 = mul2(fma2(A2v, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl));
             }
             pk[e] = pack_bf16_2(p2);
@@ -319,12 +296,12 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
               if (MODE == OP_A) {
                 v = fmaf(fmaf(A2, s, A1), s, A0);
               } else {
-                const float dl = a.rev ? vec[2 * e + h] : dl_row;
+                const float dl = a.rev ? -vec[2 * e + h] : dl_row;
                 v = fmaf(2.f * A2, s, A1) * (__uint_as_float(wv[2 * e + h]) - dl);
               }
               pv[h] = (col > limcol || col < lowcol) ? 0.f : v;
             }
-            if (MODE == OP_A) rs2 = add2(rs2, pack2(pv[0], pv[1]));
+            if (MODE == OP_A) rs2[e & 3] = add2(rs2[e & 3], pack2(pv[0], pv[1]));
             pk[e] = pack_bf16(pv[0], pv[1]);
           }
         }
@@ -335,7 +312,8 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         if constexpr (BN == 128) tmem_st32(tg + C::T_P + 32, pk + 32);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(BAR_P(g));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_P(g));
       }
       // ---- epilogue: this thread's row of the accumulator -> global ----
       const int Jg = teg - tbg;
@@ -348,7 +326,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         tmem_ld64(tg + C::T_O, ov);
         tmem_wait_ld();
         float rlo, rhi;
-        unpack2(rs2, rlo, rhi);
+        unpack2(add2(add2(rs2[0], rs2[1]), add2(rs2[2], rs2[3])), rlo, rhi);
         const float rowsum = rlo + rhi;
         float scale = 1.f;
         if (MODE == OP_A && a.fwd_div) scale = 1.0f / rowsum;

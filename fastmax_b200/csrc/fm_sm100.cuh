@@ -195,6 +195,77 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Descriptor halves for the 128-byte-swizzle layouts above: the high word is the
+// same for every tile (sbo = 1024, version 1, swizzle code 2); the low word is the
+// address (and lbo) in 16-byte units, so stepping through a tile is a 32-bit add.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+// Four K-steps of D[tmem] = A[smem] B[smem]^T for K-major operands whose K extent
+// (64 bf16) is one swizzle row: each step advances both descriptors by 32 bytes.
+// The first step overwrites D.
+__device__ __forceinline__ void umma_ss_k64(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                            uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .b64 da, db;\n"
+      ".reg .b32 a, b;\n"
+      ".reg .pred pf, pt;\n"
+      "setp.ne.b32 pf, 0, 0;\n"
+      "setp.eq.b32 pt, 0, 0;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pf;\n"
+      "add.u32 a, %1, 2;\n"
+      "add.u32 b, %2, 2;\n"
+      "mov.b64 da, {a, %3};\n"
+      "mov.b64 db, {b, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n"
+      "add.u32 a, %1, 4;\n"
+      "add.u32 b, %2, 4;\n"
+      "mov.b64 da, {a, %3};\n"
+      "mov.b64 db, {b, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n"
+      "add.u32 a, %1, 6;\n"
+      "add.u32 b, %2, 6;\n"
+      "mov.b64 da, {a, %3};\n"
+      "mov.b64 db, {b, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc)
+      : "memory");
+}
+// NK K-steps of D[tmem] (+)= A[tmem] B[smem] with B MN-major (16 K rows = 2048
+// bytes per step) and A advancing 8 columns per step.  `accumulate` applies to the
+// first step; later steps always accumulate.
+template <int NK>
+__device__ __forceinline__ void umma_ts_steps(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .b64 db;\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+#pragma unroll
+  for (int ks = 1; ks < NK; ++ks) {
+    asm volatile(
+        "{\n"
+        ".reg .b64 db;\n"
+        ".reg .pred pt;\n"
+        "setp.eq.b32 pt, 0, 0;\n"
+        "mov.b64 db, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, pt;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem + ks * 8), "r"(b_lo + ks * 128), "r"(kDescHi), "r"(idesc)
+        : "memory");
+  }
+}
 // Arrive on `bar` once every tcgen05 operation this thread issued so far is done.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
