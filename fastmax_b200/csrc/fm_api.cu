@@ -86,6 +86,9 @@ static int validate(const fastmax_problem* p) {
   return FASTMAX_OK;
 }
 
+// Argument check shared with other translation units of the library.
+int check_problem(const fastmax_problem* p) { return validate(p); }
+
 static int check_device() {
   int dev = 0;
   FM_CUDA_TRY(cudaGetDevice(&dev));

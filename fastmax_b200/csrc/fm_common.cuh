@@ -64,6 +64,9 @@ __device__ __forceinline__ float stat_scale(const stat_t* st, int head, float li
   return st ? lim / sqrtf(stat_norm2(st[head])) : 1.0f;
 }
 
+// FASTMAX_OK if the problem description is valid, else the error code (message recorded).
+int check_problem(const fastmax_problem* p);
+
 // ---- kernel launchers (each returns FASTMAX_OK or an error code) ------------
 struct Ctx {
   fastmax_problem p;

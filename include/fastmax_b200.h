@@ -148,6 +148,36 @@ int fastmax_b200_backward(const fastmax_problem* prob,
                           void* workspace, size_t workspace_bytes,
                           void* stream);
 
+/* Backward pass for callers that cannot supply or allocate scratch memory.  It
+ * has no counterpart in the reference, whose backward_cuda allocates its outputs
+ * and temporaries itself with torch::zeros (fastmax_cuda_backward.cu:951-959).
+ *
+ * Meant for programs in which device memory is not the library's to take: a
+ * server or framework that has claimed the whole GPU for its own arena, or a
+ * latency-critical loop that must not hit the device-wide synchronisation inside
+ * cudaMalloc/cudaFree.  The scratch is a fixed array inside the library image,
+ * fastmax_b200_static_scratch_bytes() bytes (8 MiB) on every GPU that loads the
+ * library, held until the process exits.  The call allocates nothing, by any
+ * route, and takes the same tensors as fastmax_b200_backward minus the workspace.
+ *
+ *  - Runs the CUDA-core score family (prob->impl AUTO or DENSE_FFMA), any
+ *    supported dtype and head dimension.
+ *  - Problems whose scratch does not fit -- roughly bh*nq above 2 million --
+ *    return FASTMAX_E_WORKSPACE; use fastmax_b200_backward for those.
+ *  - The first call on each GPU looks up the array's device address (with that
+ *    GPU current).  Make that first call before starting any stream capture.
+ *  - All calls on a GPU share the one array: calls that overlap on the GPU race,
+ *    so keep them on one stream or order them yourself.  Nothing is assumed
+ *    about the array's contents between calls; what must start at zero is
+ *    cleared on the stream at the start of each call. */
+size_t fastmax_b200_static_scratch_bytes(void);
+int fastmax_b200_backward_static(const fastmax_problem* prob,
+                                 const void* q, const void* k, const void* v,
+                                 const void* out, const float* den, const void* stats,
+                                 const void* grad_out,
+                                 void* grad_q, void* grad_k, void* grad_v,
+                                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif
