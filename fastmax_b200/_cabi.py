@@ -23,6 +23,10 @@ EXPORTS = (
     "fastmax_b200_forward", "fastmax_b200_forward_packed", "fastmax_b200_backward",
     "fastmax_b200_launch_count", "fastmax_b200_profile_enable", "fastmax_b200_profile_count",
     "fastmax_b200_profile_get", "fastmax_b200_device_status",
+    "fastmax_b200_moment_state_bytes", "fastmax_b200_moment_total_bytes",
+    "fastmax_b200_shard_forward_workspace_bytes", "fastmax_b200_shard_backward_workspace_bytes",
+    "fastmax_b200_shard_rowmax", "fastmax_b200_shard_kv_state", "fastmax_b200_shard_forward",
+    "fastmax_b200_shard_qg_state", "fastmax_b200_shard_backward", "fastmax_b200_shard_norm_fixup",
 )
 
 
@@ -30,7 +34,8 @@ class Problem(ctypes.Structure):
     """``struct fastmax_problem``."""
     _fields_ = [(n, ctypes.c_int32) for n in
                 ("dtype", "bh", "bhkv", "nq", "nk", "d", "mask", "normalize", "p", "impl")] + \
-               [(n, ctypes.c_float) for n in ("a0", "a1", "a2", "lim", "temperature")]
+               [(n, ctypes.c_float) for n in ("a0", "a1", "a2", "lim", "temperature")] + \
+               [("chunk", ctypes.c_int32)]
 
 
 _lib = None
@@ -57,6 +62,17 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_forward_packed.argtypes = [pp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.fastmax_b200_backward.restype = ctypes.c_int
         L.fastmax_b200_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
+        for f in ("moment_state_bytes", "moment_total_bytes", "shard_forward_workspace_bytes",
+                  "shard_backward_workspace_bytes"):
+            fn = getattr(L, "fastmax_b200_" + f)
+            fn.restype, fn.argtypes = sz, [pp]
+        i32 = ctypes.c_int32
+        L.fastmax_b200_shard_rowmax.argtypes = [pp, vp, vp, i32, vp, vp]
+        L.fastmax_b200_shard_kv_state.argtypes = [pp, vp, vp, vp, vp, vp]
+        L.fastmax_b200_shard_forward.argtypes = [pp] + [vp] * 9 + [sz, vp]
+        L.fastmax_b200_shard_qg_state.argtypes = [pp] + [vp] * 8
+        L.fastmax_b200_shard_backward.argtypes = [pp] + [vp] * 16 + [sz, vp]
+        L.fastmax_b200_shard_norm_fixup.argtypes = [pp, vp, vp, vp, vp, i32, vp, vp, vp]
         L.fastmax_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), vp]
         L.fastmax_b200_launch_count.restype = ctypes.c_ulonglong
         L.fastmax_b200_profile_enable.argtypes = [ctypes.c_int]
@@ -114,14 +130,14 @@ def _dtype_code(t: torch.Tensor) -> int:
     raise TypeError(f"fastmax_b200 supports float32 and bfloat16 tensors, got {t.dtype}")
 
 
-def make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl="auto") -> Problem:
+def make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl="auto", chunk=0) -> Problem:
     if p not in (1, 2):
         raise ValueError(f"p must be 1 or 2, got: {p}")
     return Problem(dtype=_dtype_code(q), bh=q.shape[0], bhkv=k.shape[0], nq=q.shape[1], nk=k.shape[1],
                    d=q.shape[2], mask=int(bool(mask)), normalize=int(bool(normalize)), p=int(p),
                    impl=IMPL[impl] if isinstance(impl, str) else int(impl),
                    a0=float(a0), a1=float(a1), a2=float(a2), lim=float(lim),
-                   temperature=float(temperature))
+                   temperature=float(temperature), chunk=int(chunk))
 
 
 def _require(q, k, v, *more):
@@ -147,11 +163,11 @@ def _workspace(nbytes: int, device) -> torch.Tensor:
 
 
 def forward(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2,
-            impl="auto"):
+            impl="auto", chunk=0):
     """q (bh,nq,d), k/v (bhkv,nk,d) -> out (bh,nq,d), den (bh,nq) fp32, stats (opaque)."""
     _require(q, k, v)
     L = lib()
-    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl)
+    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl, chunk)
     with torch.cuda.device(q.device):
         out = torch.empty_like(q)
         den = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
@@ -182,11 +198,11 @@ def forward_packed(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0,
 
 
 def backward(q, k, v, out, den, stats, grad_out, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0,
-             a2=0.5, lim=1.0, p=2, impl="auto"):
+             a2=0.5, lim=1.0, p=2, impl="auto", chunk=0):
     """Gradients (grad_q, grad_k, grad_v) in the dtype of the inputs."""
     _require(q, k, v, out, grad_out)
     L = lib()
-    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl)
+    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl, chunk)
     with torch.cuda.device(q.device):
         gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         wsb = L.fastmax_b200_backward_workspace_bytes(prob)

@@ -83,6 +83,8 @@ static int validate(const fastmax_problem* p) {
   if (p->nq > 0 && p->nk == 0) return fail(FASTMAX_E_ARG, "no keys (nk == 0)");
   if (p->impl < FASTMAX_IMPL_AUTO || p->impl > FASTMAX_IMPL_MOMENTS_TC)
     return fail(FASTMAX_E_ARG, "unknown impl %d", p->impl);
+  if (p->chunk < 0 || p->chunk % 256 != 0)
+    return fail(FASTMAX_E_ARG, "chunk=%d is not a non-negative multiple of 256", p->chunk);
   return FASTMAX_OK;
 }
 
@@ -102,10 +104,34 @@ static int check_device() {
 
 // Family actually used for a problem.  `packed` = forward into the reference's
 // float32 (d+1)-channel layout, which only the CUDA-core family writes.
+// Rough time of one pass per (token, head) in arbitrary units: score form grows with the
+// number of keys a row sees, the moment form is constant plus its own chunk in score form.
+static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
+  if (!moments_supports(p)) return false;
+  const double d = p.d, F = d + (p.p == 2 ? d * d : 0.0);
+  const double rate_score = tc_ok ? 600e12 : 25e12, rate_state = 20e12;
+  const double keys = p.mask ? 0.5 * p.nk : (double)p.nk;
+  const double chunk_keys = p.mask ? 0.5 * moments_chunk(p) : 0.0;
+  const double per_key = 14.0 * (d + 0.5);
+  const double t_score = keys * per_key / rate_score;
+  const double t_mom = 14.0 * F * (d + 1) / rate_state + chunk_keys * per_key / rate_score;
+  return t_mom < t_score && p.nk > moments_chunk(p);
+}
+
 static int pick_impl(const fastmax_problem& p, bool packed, int* impl) {
   int want = p.impl;
   const bool tc_ok = dense_tc_supports(p) && !packed;
-  if (want == FASTMAX_IMPL_AUTO) want = tc_ok ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
+  if (want == FASTMAX_IMPL_AUTO) {
+    want = tc_ok ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
+    if (!packed && moments_faster(p, tc_ok)) want = FASTMAX_IMPL_MOMENTS_FFMA;
+  }
+  if (want == FASTMAX_IMPL_MOMENTS_FFMA) {
+    if (!moments_supports(p) || packed)
+      return fail(FASTMAX_E_UNSUPPORTED,
+                  "the moment family needs bh == bhkv, nq == nk when causal, and the plain output layout");
+    *impl = want;
+    return FASTMAX_OK;
+  }
   if (want == FASTMAX_IMPL_DENSE_TC && !tc_ok)
     return fail(FASTMAX_E_UNSUPPORTED,
                 "the tensor-core score family needs bf16, d == 64, bh == bhkv and the plain output layout");
@@ -128,6 +154,15 @@ static BwdWs bwd_layout(const fastmax_problem& p) {
   w.total = w.gs_off;
   if (dense_tc_supports(p)) w.total += align_up((size_t)2 * p.bh * p.nq * p.d, 256);
   return w;
+}
+// the workspace must serve whichever family AUTO picks
+static size_t fwd_ws_bytes(const fastmax_problem& p) {
+  return moments_supports(p) ? moments_fwd_layout(p).bytes : 0;
+}
+static size_t bwd_ws_bytes(const fastmax_problem& p) {
+  size_t a = bwd_layout(p).total;
+  if (moments_supports(p)) { size_t b = moments_bwd_layout(p).bytes; if (b > a) a = b; }
+  return a;
 }
 
 }  // namespace fm
@@ -179,14 +214,19 @@ size_t fastmax_b200_stats_bytes(const fastmax_problem* p) {
   return sizeof(stat_t) * (size_t)(p->bh + p->bhkv);
 }
 
+// Sized for the family the call will run: the moment family needs room for its states.
 size_t fastmax_b200_forward_workspace_bytes(const fastmax_problem* p) {
-  (void)p;
-  return 0;
+  if (validate(p)) return 0;
+  int impl;
+  if (pick_impl(*p, false, &impl)) return 0;
+  return impl == FASTMAX_IMPL_MOMENTS_FFMA ? fwd_ws_bytes(*p) : 0;
 }
 
 size_t fastmax_b200_backward_workspace_bytes(const fastmax_problem* p) {
   if (validate(p)) return 0;
-  return bwd_layout(*p).total;
+  int impl;
+  if (pick_impl(*p, false, &impl)) return 0;
+  return impl == FASTMAX_IMPL_MOMENTS_FFMA ? bwd_ws_bytes(*p) : bwd_layout(*p).total;
 }
 
 static int forward_impl(const fastmax_problem* prob, const void* q, const void* k, const void* v,
@@ -198,14 +238,18 @@ static int forward_impl(const fastmax_problem* prob, const void* q, const void* 
   if (p.bh == 0 || p.nq == 0) return FASTMAX_OK;
   if (!q || !k || !v || !o.out || !o.den) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
   if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs a stats buffer");
-  if (workspace_bytes < fastmax_b200_forward_workspace_bytes(prob))
-    return fail(FASTMAX_E_WORKSPACE, "forward workspace too small");
-  (void)workspace;
   if ((rc = check_device())) return rc;
   int impl;
   if ((rc = pick_impl(p, o.out_f32 != 0, &impl))) return rc;
   Ctx c{p, (cudaStream_t)stream};
   if (p.normalize && (rc = launch_rowmax(c, q, k, (stat_t*)stats))) return rc;
+  if (impl == FASTMAX_IMPL_MOMENTS_FFMA) {
+    const size_t need = moments_fwd_layout(p).bytes;
+    if (!workspace || workspace_bytes < need)
+      return fail(FASTMAX_E_WORKSPACE, "forward workspace too small: need %zu bytes, got %zu", need,
+                  workspace_bytes);
+    return moments_forward(c, q, k, v, (const stat_t*)stats, o, workspace);
+  }
   if (impl == FASTMAX_IMPL_DENSE_TC)
     return dense_tc_forward(c, q, k, v, (const stat_t*)stats, o.out, o.den);
   return dense_ffma_forward(c, q, k, v, (const stat_t*)stats, o);
@@ -237,14 +281,18 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
   if (!q || !k || !v || !out || !den || !grad_out || !grad_q || !grad_k || !grad_v)
     return fail(FASTMAX_E_ARG, "NULL tensor pointer");
   if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the forward's stats buffer");
-  BwdWs w = bwd_layout(p);
-  if (w.total > 0 && (!workspace || workspace_bytes < w.total))
-    return fail(FASTMAX_E_WORKSPACE, "backward workspace too small: need %zu bytes, got %zu",
-                w.total, workspace_bytes);
-  if ((rc = check_device())) return rc;
   int impl;
   if ((rc = pick_impl(p, false, &impl))) return rc;
+  BwdWs w = bwd_layout(p);
+  const size_t need = impl == FASTMAX_IMPL_MOMENTS_FFMA ? moments_bwd_layout(p).bytes : w.total;
+  if (need > 0 && (!workspace || workspace_bytes < need))
+    return fail(FASTMAX_E_WORKSPACE, "backward workspace too small: need %zu bytes, got %zu", need,
+                workspace_bytes);
+  if ((rc = check_device())) return rc;
   Ctx c{p, (cudaStream_t)stream};
+  if (impl == FASTMAX_IMPL_MOMENTS_FFMA)
+    return moments_backward(c, q, k, v, out, den, (const stat_t*)stats, grad_out, grad_q, grad_k, grad_v,
+                            workspace);
   float* dots = (float*)((char*)workspace + w.dots_off);
   float* delta = (float*)((char*)workspace + w.delta_off);
   if (p.normalize)
@@ -264,6 +312,143 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
   if (p.normalize)
     return launch_norm_fixup(c, q, k, (const stat_t*)stats, dots, grad_q, grad_k);
   return FASTMAX_OK;
+}
+
+
+// ---- sequence sharding ------------------------------------------------------------------
+static int validate_shard(const fastmax_problem* prob) {
+  int rc = validate(prob);
+  if (rc) return rc;
+  if (!prob->mask || prob->nq != prob->nk || prob->bh != prob->bhkv)
+    return fail(FASTMAX_E_ARG, "a sequence shard needs mask = 1, nq == nk and bh == bhkv");
+  return check_device();
+}
+struct ShardFwdWs { size_t o_add, den_add, bytes; };
+static ShardFwdWs shard_fwd_layout(const fastmax_problem& p) {
+  ShardFwdWs w;
+  w.o_add = 0;
+  w.den_add = align_up(sizeof(float) * (size_t)p.bh * p.nq * p.d, 256);
+  w.bytes = w.den_add + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
+  return w;
+}
+struct ShardBwdWs { size_t gq, gk, gv, dvec, gs, bytes; };
+static ShardBwdWs shard_bwd_layout(const fastmax_problem& p) {
+  ShardBwdWs w;
+  const size_t t = align_up(sizeof(float) * (size_t)p.bh * p.nq * p.d, 256);
+  w.gq = 0;
+  w.gk = t;
+  w.gv = 2 * t;
+  w.dvec = 3 * t;
+  w.gs = w.dvec + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
+  w.bytes = w.gs + (dense_tc_supports(p) ? align_up((size_t)2 * p.bh * p.nq * p.d, 256) : 0);
+  return w;
+}
+
+size_t fastmax_b200_moment_state_bytes(const fastmax_problem* p) {
+  return validate(p) ? 0 : moment_state_bytes(*p, p->nk);
+}
+size_t fastmax_b200_moment_total_bytes(const fastmax_problem* p) {
+  return validate(p) ? 0 : moment_total_bytes(*p);
+}
+size_t fastmax_b200_shard_forward_workspace_bytes(const fastmax_problem* p) {
+  return validate(p) ? 0 : shard_fwd_layout(*p).bytes;
+}
+size_t fastmax_b200_shard_backward_workspace_bytes(const fastmax_problem* p) {
+  return validate(p) ? 0 : shard_bwd_layout(*p).bytes;
+}
+
+int fastmax_b200_shard_rowmax(const fastmax_problem* prob, const void* q, const void* k,
+                              int32_t row_offset, void* stats, void* stream) {
+  int rc = validate_shard(prob);
+  if (rc) return rc;
+  if (!q || !k || !stats) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  Ctx c{*prob, (cudaStream_t)stream};
+  return launch_rowmax(c, q, k, (stat_t*)stats, row_offset);
+}
+
+int fastmax_b200_shard_kv_state(const fastmax_problem* prob, const void* k, const void* v,
+                                float* kv_states, float* kv_total, void* stream) {
+  int rc = validate_shard(prob);
+  if (rc) return rc;
+  if (!k || !v || !kv_states || !kv_total) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  const fastmax_problem& p = *prob;
+  Ctx c{p, (cudaStream_t)stream};
+  const int L = moments_chunk(p);
+  if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, kv_states))) return rc;
+  return moments_prefix(c, p.bh, (p.nk + L - 1) / L, kv_states, nullptr, kv_total, 0, 0);
+}
+
+int fastmax_b200_shard_forward(const fastmax_problem* prob, const void* q, const void* k,
+                               const void* v, const void* stats, float* kv_states,
+                               const float* s_base, void* out, float* den, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  int rc = validate_shard(prob);
+  if (rc) return rc;
+  const fastmax_problem& p = *prob;
+  if (!q || !k || !v || !kv_states || !out || !den) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the reduced stats buffer");
+  const ShardFwdWs w = shard_fwd_layout(p);
+  if (!workspace || workspace_bytes < w.bytes)
+    return fail(FASTMAX_E_WORKSPACE, "shard forward workspace too small: need %zu bytes, got %zu", w.bytes,
+                workspace_bytes);
+  Ctx c{p, (cudaStream_t)stream};
+  FwdOut o{out, den, p.d, 1, 0};
+  return moments_forward_finish(c, q, k, v, (const stat_t*)stats, kv_states, s_base,
+                                (float*)((char*)workspace + w.o_add),
+                                (float*)((char*)workspace + w.den_add), o);
+}
+
+int fastmax_b200_shard_qg_state(const fastmax_problem* prob, const void* q, const void* out,
+                                const float* den, const void* grad_out, float* delta,
+                                float* qg_states, float* qg_total, void* stream) {
+  int rc = validate_shard(prob);
+  if (rc) return rc;
+  const fastmax_problem& p = *prob;
+  if (!q || !out || !den || !grad_out || !delta || !qg_states || !qg_total)
+    return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  Ctx c{p, (cudaStream_t)stream};
+  const int L = moments_chunk(p);
+  if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
+  if ((rc = moments_chunk_state(c, p.bh, p.nq, L, q, grad_out, den, delta, 1, qg_states))) return rc;
+  return moments_prefix(c, p.bh, (p.nq + L - 1) / L, qg_states, nullptr, qg_total, 1, 0);
+}
+
+int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, const void* k,
+                                const void* v, const void* out, const float* den,
+                                const void* stats, const void* grad_out, const float* delta,
+                                const float* kv_states, float* qg_states, const float* r_base,
+                                float* dots, void* grad_q, void* grad_k, void* grad_v,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = validate_shard(prob);
+  if (rc) return rc;
+  const fastmax_problem& p = *prob;
+  if (!q || !k || !v || !out || !den || !grad_out || !delta || !kv_states || !qg_states || !dots ||
+      !grad_q || !grad_k || !grad_v)
+    return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the reduced stats buffer");
+  const ShardBwdWs w = shard_bwd_layout(p);
+  if (!workspace || workspace_bytes < w.bytes)
+    return fail(FASTMAX_E_WORKSPACE, "shard backward workspace too small: need %zu bytes, got %zu", w.bytes,
+                workspace_bytes);
+  Ctx c{p, (cudaStream_t)stream};
+  char* ws = (char*)workspace;
+  FM_CUDA_TRY(cudaMemsetAsync(dots, 0, sizeof(float) * (size_t)(p.bh + p.bhkv), c.stream));
+  float* dvec = (float*)(ws + w.dvec);
+  void* gs = ws + w.gs;
+  if (dense_tc_supports(p) && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
+  return moments_backward_finish(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dvec, gs,
+                                 kv_states, qg_states, r_base, (float*)(ws + w.gq), (float*)(ws + w.gk),
+                                 (float*)(ws + w.gv), p.normalize ? dots : nullptr, grad_q, grad_k, grad_v);
+}
+
+int fastmax_b200_shard_norm_fixup(const fastmax_problem* prob, const void* q, const void* k,
+                                  const void* stats, const float* dots, int32_t row_offset,
+                                  void* grad_q, void* grad_k, void* stream) {
+  int rc = validate_shard(prob);
+  if (rc) return rc;
+  if (!q || !k || !stats || !dots || !grad_q || !grad_k) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  Ctx c{*prob, (cudaStream_t)stream};
+  return launch_norm_fixup(c, q, k, (const stat_t*)stats, dots, grad_q, grad_k, row_offset);
 }
 
 }  // extern "C"

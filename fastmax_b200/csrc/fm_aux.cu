@@ -14,7 +14,7 @@ namespace fm {
 // covers 32*VEC/D rows per load and every load is a full 128-byte line.
 template <typename T, int D>
 __global__ void __launch_bounds__(256) rowmax_kernel(const T* __restrict__ x, int n,
-                                                     int rows_per_block,
+                                                     int rows_per_block, int row_offset,
                                                      stat_t* __restrict__ stats) {
   constexpr int VEC = (D >= 32) ? 4 : 1;       // elements per lane
   constexpr int LPR = D / VEC;                 // lanes per row
@@ -46,13 +46,13 @@ __global__ void __launch_bounds__(256) rowmax_kernel(const T* __restrict__ x, in
   }
   // NaN norms never compare greater, so they are ignored as a maximum.
   if (best >= 0.f && (lane % LPR) == 0) {
-    stat_t w = ((stat_t)__float_as_uint(best) << 32) | (stat_t)(0xFFFFFFFFu - (unsigned)best_row);
+    stat_t w = ((stat_t)__float_as_uint(best) << 32) | (stat_t)(0xFFFFFFFFu - (unsigned)(best_row + row_offset));
     atomicMax(&stats[head], w);
   }
 }
 
 template <typename T>
-static int rowmax_one(const Ctx& c, const T* x, int heads, int n, stat_t* stats) {
+static int rowmax_one(const Ctx& c, const T* x, int heads, int n, stat_t* stats, int row_offset) {
   if (heads == 0 || n == 0) return FASTMAX_OK;
   // enough blocks per head to fill the GPU, at least 256 rows each
   int splits = max(1, min((n + 255) / 256, (148 * 8 + heads - 1) / heads));
@@ -62,7 +62,7 @@ static int rowmax_one(const Ctx& c, const T* x, int heads, int n, stat_t* stats)
 #define FM_CASE(DD) \
   case DD:                                                                              \
     FM_LAUNCH("fm_rowmax", c.stream,                                                      \
-              (rowmax_kernel<T, DD><<<grid, 256, 0, c.stream>>>(x, n, rpb, stats)));      \
+              (rowmax_kernel<T, DD><<<grid, 256, 0, c.stream>>>(x, n, rpb, row_offset, stats)));      \
     break;
     FM_CASE(8) FM_CASE(16) FM_CASE(32) FM_CASE(64) FM_CASE(128)
 #undef FM_CASE
@@ -72,16 +72,16 @@ static int rowmax_one(const Ctx& c, const T* x, int heads, int n, stat_t* stats)
   return FASTMAX_OK;
 }
 
-int launch_rowmax(const Ctx& c, const void* q, const void* k, stat_t* stats) {
+int launch_rowmax(const Ctx& c, const void* q, const void* k, stat_t* stats, int row_offset) {
   const fastmax_problem& p = c.p;
   FM_CUDA_TRY(cudaMemsetAsync(stats, 0, sizeof(stat_t) * (size_t)(p.bh + p.bhkv), c.stream));
   int rc;
   if (p.dtype == FASTMAX_F32) {
-    if ((rc = rowmax_one<float>(c, (const float*)q, p.bh, p.nq, stats))) return rc;
-    return rowmax_one<float>(c, (const float*)k, p.bhkv, p.nk, stats + p.bh);
+    if ((rc = rowmax_one<float>(c, (const float*)q, p.bh, p.nq, stats, row_offset))) return rc;
+    return rowmax_one<float>(c, (const float*)k, p.bhkv, p.nk, stats + p.bh, row_offset);
   }
-  if ((rc = rowmax_one<__nv_bfloat16>(c, (const __nv_bfloat16*)q, p.bh, p.nq, stats))) return rc;
-  return rowmax_one<__nv_bfloat16>(c, (const __nv_bfloat16*)k, p.bhkv, p.nk, stats + p.bh);
+  if ((rc = rowmax_one<__nv_bfloat16>(c, (const __nv_bfloat16*)q, p.bh, p.nq, stats, row_offset))) return rc;
+  return rowmax_one<__nv_bfloat16>(c, (const __nv_bfloat16*)k, p.bhkv, p.nk, stats + p.bh, row_offset);
 }
 
 // ---------------------------------------------------------------------------
@@ -169,7 +169,8 @@ template <typename T>
 __global__ void norm_fixup_kernel(const T* __restrict__ q, const T* __restrict__ k,
                                   const stat_t* __restrict__ stats,
                                   const float* __restrict__ dots, T* __restrict__ gq,
-                                  T* __restrict__ gk, int bh, int nq, int nk, int d) {
+                                  T* __restrict__ gk, int bh, int nq, int nk, int d,
+                                  int row_offset) {
   int head = blockIdx.x;
   const T* x;
   T* g;
@@ -177,7 +178,7 @@ __global__ void norm_fixup_kernel(const T* __restrict__ q, const T* __restrict__
   if (head < bh) { x = q + (size_t)head * nq * d; g = gq + (size_t)head * nq * d; n = nq; }
   else { x = k + (size_t)(head - bh) * nk * d; g = gk + (size_t)(head - bh) * nk * d; n = nk; }
   stat_t s = stats[head];
-  int r = stat_row(s);
+  int r = stat_row(s) - row_offset;
   float m2 = stat_norm2(s);
   if (r < 0 || r >= n) return;
   float coef = dots[head] / m2;
@@ -188,7 +189,7 @@ __global__ void norm_fixup_kernel(const T* __restrict__ q, const T* __restrict__
 }
 
 int launch_norm_fixup(const Ctx& c, const void* q, const void* k, const stat_t* stats,
-                      const float* dots, void* gq, void* gk) {
+                      const float* dots, void* gq, void* gk, int row_offset) {
   const fastmax_problem& p = c.p;
   int heads = p.bh + p.bhkv;
   if (heads == 0) return FASTMAX_OK;
@@ -196,12 +197,12 @@ int launch_norm_fixup(const Ctx& c, const void* q, const void* k, const stat_t* 
     FM_LAUNCH("fm_norm_fixup", c.stream,
               (norm_fixup_kernel<float><<<heads, 128, 0, c.stream>>>(
                   (const float*)q, (const float*)k, stats, dots, (float*)gq, (float*)gk, p.bh, p.nq,
-                  p.nk, p.d)));
+                  p.nk, p.d, row_offset)));
   else
     FM_LAUNCH("fm_norm_fixup", c.stream,
               (norm_fixup_kernel<__nv_bfloat16><<<heads, 128, 0, c.stream>>>(
                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, stats, dots, (__nv_bfloat16*)gq,
-                  (__nv_bfloat16*)gk, p.bh, p.nq, p.nk, p.d)));
+                  (__nv_bfloat16*)gk, p.bh, p.nq, p.nk, p.d, row_offset)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }

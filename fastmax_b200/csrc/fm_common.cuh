@@ -74,14 +74,16 @@ struct Ctx {
 };
 
 // Row statistics of q and k into `stats` (zeroes it first).
-int launch_rowmax(const Ctx& c, const void* q, const void* k, stat_t* stats);
+// row_offset is added to the row indices that are recorded (a sequence shard's first token).
+int launch_rowmax(const Ctx& c, const void* q, const void* k, stat_t* stats, int row_offset = 0);
 
 // delta[h,i] = grad_out[h,i,:] . out[h,i,:]
 int launch_delta(const Ctx& c, const void* grad_out, const void* out, float* delta);
 
 // Adds the gradient of the max-norm scaling to one row per head of grad_q/grad_k.
+// Rows are looked up as (recorded row - row_offset); heads whose row lies outside this shard are skipped.
 int launch_norm_fixup(const Ctx& c, const void* q, const void* k, const stat_t* stats,
-                      const float* dots, void* grad_q, void* grad_k);
+                      const float* dots, void* grad_q, void* grad_k, int row_offset = 0);
 
 // Where the forward writes: out has row stride `o_stride` elements and is fp32
 // when `out_f32` (the reference's packed layout), else the input element type.
@@ -99,19 +101,75 @@ int launch_gprep(const Ctx& c, const void* grad_out, const void* out, const floa
 
 // Tensor-core score-form family (bf16, head dimension 64, bh == bhkv).
 bool dense_tc_supports(const fastmax_problem& p);
+struct ChunkAdd;
 int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,
-                     const stat_t* stats, void* out, float* den);
+                     const stat_t* stats, void* out, float* den, const ChunkAdd* ca = nullptr);
 int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
                       const float* dvec, const stat_t* stats, float* dots, void* grad_q,
-                      void* grad_k, void* grad_v);
+                      void* grad_k, void* grad_v, const ChunkAdd* ca = nullptr);
 // Copies the device-side protocol status word to *out (synchronises the stream).
 int tc_status(int* out, cudaStream_t stream);
 
+// Optional coupling of the score-form kernels to the moment-state form: columns are
+// restricted to the row's own chunk of `chunk` tokens (0 = no restriction; needs
+// nq == nk and chunk % 256 == 0), and fp32 contributions of everything outside the
+// chunk are added before the result is divided / rounded.
+struct ChunkAdd {
+  int chunk = 0;
+  const float* out_add = nullptr;   // forward: (bh, nq, d) numerator part
+  const float* den_add = nullptr;   // forward: (bh, nq) denominator part
+  const float* gq_add = nullptr;    // backward: (bh, nq, d)
+  const float* gk_add = nullptr;    // backward: (bhkv, nk, d)
+  const float* gv_add = nullptr;    // backward: (bhkv, nk, d)
+};
+
 int dense_ffma_forward(const Ctx& c, const void* q, const void* k, const void* v,
-                       const stat_t* stats, const FwdOut& o);
+                       const stat_t* stats, const FwdOut& o, const ChunkAdd& ca = ChunkAdd());
 int dense_ffma_backward(const Ctx& c, const void* q, const void* k, const void* v,
                         const float* den, const stat_t* stats, const void* grad_out,
                         const float* delta, float* dots, void* grad_q, void* grad_k,
-                        void* grad_v);
+                        void* grad_v, const ChunkAdd& ca = ChunkAdd());
+
+// ---- moment-state form (fm_moments_ffma.cu) ---------------------------------------
+struct MomentDims {
+  int f;    // state rows: d*d + d + 1
+  int dvp;  // state columns: d + 1 rounded up to a multiple of 4
+};
+MomentDims moment_dims(int d);
+// state[h][c][f][col] = sum over the tokens of chunk c of feature_f(y) * [z | e];  ext 0: e = 1,
+// ext 1: z and e scaled: [z/den | -delta/den].
+int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
+                        const float* den, const float* delta, int ext, float* state);
+// exclusive running sum over chunks (reverse = suffix), started from base; total = own sum
+int moments_prefix(const Ctx& c, int heads, int nchunk, float* state, const float* base, float* total,
+                   int reverse, int write);
+int moments_readout(const Ctx& c, int mode_b, int heads, int n, int chunk, int state_per_chunk,
+                    const void* x, const void* u, const float* den, const float* delta, int ext,
+                    const float* state, const stat_t* stats, float* o_add, float* den_add);
+// host orchestration of the moment family (fm_moments.cu)
+struct MomFwdWs { size_t states, total, o_add, den_add, bytes; };
+struct MomBwdWs { size_t dots, delta, dvec, gs, states, total, gq_add, gk_add, gv_add, bytes; };
+int moments_chunk(const fastmax_problem& p);
+bool moments_supports(const fastmax_problem& p);
+size_t moment_state_bytes(const fastmax_problem& p, int n);
+size_t moment_total_bytes(const fastmax_problem& p);
+MomFwdWs moments_fwd_layout(const fastmax_problem& p);
+MomBwdWs moments_bwd_layout(const fastmax_problem& p);
+int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
+                    const FwdOut& o, void* workspace);
+int moments_forward_finish(const Ctx& c, const void* q, const void* k, const void* v,
+                           const stat_t* stats, float* kv_states, const float* s_base,
+                           float* o_add, float* den_add, const FwdOut& o);
+int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* out,
+                     const float* den, const stat_t* stats, const void* grad_out, void* grad_q,
+                     void* grad_k, void* grad_v, void* workspace);
+int moments_backward_finish(const Ctx& c, const void* q, const void* k, const void* v,
+                            const float* den, const stat_t* stats, const void* grad_out,
+                            const float* delta, const float* dvec, const void* gs,
+                            const float* s_states, float* r_states, const float* r_base,
+                            float* gq_add, float* gk_add, float* gv_add, float* dots, void* grad_q,
+                            void* grad_k, void* grad_v);
+int moments_finalize(const Ctx& c, int heads, int n, const float* r, const float* den_in, const void* x,
+                     void* out, float* den_out, float* dots, int mode);
 
 }  // namespace fm

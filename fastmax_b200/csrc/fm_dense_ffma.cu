@@ -44,6 +44,10 @@ struct DenseArgs {
   int nrows, ncols, ratio, off, mask;
   int o_stride, den_stride, out_f32;
   float a0, a1, a2, lim;
+  int chunk;              // > 0: only the columns of the row tile's own chunk
+  const float* o1_add;    // fp32 (row heads, nrows, D) added to o1 before it is divided / stored
+  const float* o2_add;    // same for o2
+  const float* den_add;   // FWD: added to the row sum
 };
 
 template <int D, typename T>
@@ -117,6 +121,10 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
     if (a.mask) {
       if (MODE == MODE_DKDV) ct0 = max(0, r0 - a.off) / BN;
       else ct1 = min(ct1, (min(r0 + BM - 1, a.nrows - 1) + a.off) / BN + 1);
+    }
+    if (a.chunk > 0) {
+      if (MODE == MODE_DKDV) ct1 = min(ct1, (r0 / a.chunk + 1) * (a.chunk / BN));
+      else ct0 = (r0 / a.chunk) * (a.chunk / BN);
     }
     for (int ct = ct0; ct < ct1; ++ct) {
       const int c0 = ct * BN;
@@ -226,13 +234,16 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
       const int r = r0 + ty + 16 * i;
       if (r < a.nrows) {
         const size_t grow = (size_t)hr * a.nrows + r;
-        const float inv = 1.0f / rsum[i];
-        if (tx == 0) a.den_out[grow * a.den_stride] = rsum[i];
+        const float dsum = rsum[i] + (a.den_add ? a.den_add[grow] : 0.f);
+        const float inv = 1.0f / dsum;
+        if (tx == 0) a.den_out[grow * a.den_stride] = dsum;
 #pragma unroll
         for (int m = 0; m < NC; ++m) {
           const int cidx = tx + 16 * m;
-          if (D % 16 == 0 || cidx < D)
-            store_any<T>(a.o1, grow * a.o_stride + cidx, o1[i][m] * inv, a.out_f32);
+          if (D % 16 == 0 || cidx < D) {
+            const float num = o1[i][m] + (a.o1_add ? a.o1_add[grow * D + cidx] : 0.f);
+            store_any<T>(a.o1, grow * a.o_stride + cidx, num * inv, a.out_f32);
+          }
         }
       }
     }
@@ -247,9 +258,11 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
         for (int m = 0; m < NC; ++m) {
           const int cidx = tx + 16 * m;
           if (D % 16 == 0 || cidx < D) {
-            stf((T*)a.o1 + grow * D + cidx, o1[i][m]);
-            if (MODE == MODE_DKDV) stf((T*)a.o2 + grow * D + cidx, o2[i][m]);
-            part = fmaf(o1[i][m], Xs[(ty + 16 * i) * LD + cidx], part);
+            const float g1 = o1[i][m] + (a.o1_add ? a.o1_add[grow * D + cidx] : 0.f);
+            stf((T*)a.o1 + grow * D + cidx, g1);
+            if (MODE == MODE_DKDV)
+              stf((T*)a.o2 + grow * D + cidx, o2[i][m] + (a.o2_add ? a.o2_add[grow * D + cidx] : 0.f));
+            part = fmaf(g1, Xs[(ty + 16 * i) * LD + cidx], part);
           }
         }
       }
@@ -322,8 +335,9 @@ DenseArgs base_args(const Ctx& c, const stat_t* stats) {
 }  // namespace
 
 int dense_ffma_forward(const Ctx& c, const void* q, const void* k, const void* v,
-                       const stat_t* stats, const FwdOut& o) {
+                       const stat_t* stats, const FwdOut& o, const ChunkAdd& ca) {
   DenseArgs a = base_args(c, stats);
+  a.chunk = ca.chunk; a.o1_add = ca.out_add; a.den_add = ca.den_add;
   a.x = q; a.y = k; a.z = v;
   a.nrows = c.p.nq; a.ncols = c.p.nk;
   a.o1 = o.out; a.den_out = o.den;
@@ -334,10 +348,11 @@ int dense_ffma_forward(const Ctx& c, const void* q, const void* k, const void* v
 int dense_ffma_backward(const Ctx& c, const void* q, const void* k, const void* v,
                         const float* den, const stat_t* stats, const void* grad_out,
                         const float* delta, float* dots, void* grad_q, void* grad_k,
-                        void* grad_v) {
+                        void* grad_v, const ChunkAdd& ca) {
   const fastmax_problem& p = c.p;
   DenseArgs a = base_args(c, stats);
   a.delta = delta; a.den = den;
+  a.chunk = ca.chunk; a.o1_add = ca.gq_add;
   // grad_q: rows are queries
   a.x = q; a.u = grad_out; a.y = k; a.z = v;
   a.nrows = p.nq; a.ncols = p.nk;
@@ -349,6 +364,7 @@ int dense_ffma_backward(const Ctx& c, const void* q, const void* k, const void* 
   a.x = k; a.u = v; a.y = q; a.z = grad_out;
   a.nrows = p.nk; a.ncols = p.nq;
   a.o1 = grad_k; a.o2 = grad_v;
+  a.o1_add = ca.gk_add; a.o2_add = ca.gv_add;
   a.dots = p.normalize ? dots + p.bh : nullptr;
   return launch_mode<MODE_DKDV>(c, a, p.bhkv);
 }

@@ -50,6 +50,9 @@ struct TcArgs {
   const stat_t* stat_k;
   int nrows, ncols, off, mask, rev, fwd_div;
   float a0, a1, a2, lim;
+  int chunk;             // > 0: only the columns of the row pair's own chunk
+  const float* o_add;    // fp32 (heads, nrows, 64) added to the accumulator row
+  const float* den_add;  // OP_A with fwd_div: added to the row sum
 };
 
 constexpr int D = 64, BM = 128;
@@ -115,6 +118,11 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       te0 = min(ntile, (min(r0 + BM - 1, a.nrows - 1) + a.off) / BN + 1);
       te1 = min(ntile, (min(r0 + 2 * BM - 1, a.nrows - 1) + a.off) / BN + 1);
     }
+  }
+  if (a.chunk > 0) {  // both row tiles lie in one chunk (chunk % 256 == 0)
+    const int cb = (r0 / a.chunk) * (a.chunk / BN), ce = cb + a.chunk / BN;
+    if (a.rev) { te0 = min(te0, ce); te1 = min(te1, ce); }
+    else { tb0 = cb; tb1 = cb; }
   }
   const bool act1 = r0 + BM < a.nrows;  // group 0 always has rows
   if (!act1) { tb1 = INT_MAX; te1 = 0; }
@@ -327,7 +335,8 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         tmem_wait_ld();
         float rlo, rhi;
         unpack2(add2(add2(rs2[0], rs2[1]), add2(rs2[2], rs2[3])), rlo, rhi);
-        const float rowsum = rlo + rhi;
+        float rowsum = rlo + rhi;
+        if (MODE == OP_A && a.fwd_div && a.den_add && row_ok) rowsum += a.den_add[(size_t)head * a.nrows + row];
         float scale = 1.f;
         if (MODE == OP_A && a.fwd_div) scale = 1.0f / rowsum;
         float part = 0.f;
@@ -336,11 +345,15 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           uint4* dst = (uint4*)((__nv_bfloat16*)a.o + grow * D);
           const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * D);
           const bool want_dots = (MODE == OP_B) && a.dots != nullptr;
+          const float4* addr = a.o_add ? (const float4*)(a.o_add + grow * D) : nullptr;
 #pragma unroll
           for (int v8 = 0; v8 < 8; ++v8) {
             float f[8];
+            float4 ad0 = make_float4(0.f, 0.f, 0.f, 0.f), ad1 = ad0;
+            if (addr) { ad0 = __ldg(addr + 2 * v8); ad1 = __ldg(addr + 2 * v8 + 1); }
+            const float ad[8] = {ad0.x, ad0.y, ad0.z, ad0.w, ad1.x, ad1.y, ad1.z, ad1.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[v8 * 8 + e]) * scale;
+            for (int e = 0; e < 8; ++e) f[e] = (__uint_as_float(ov[v8 * 8 + e]) + ad[e]) * scale;
             uint4 w;
             w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
             w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
@@ -456,7 +469,7 @@ bool dense_tc_supports(const fastmax_problem& p) {
 }
 
 int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,
-                     const stat_t* stats, void* out, float* den) {
+                     const stat_t* stats, void* out, float* den, const ChunkAdd* ca) {
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
     return fail(FASTMAX_E_ARG, "the tensor-core family needs 16-byte aligned tensors");
   TcArgs a = base_args(c, stats);
@@ -464,12 +477,13 @@ int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,
   a.den_out = den;
   a.fwd_div = 1;
   a.rev = 0;
+  if (ca) { a.chunk = ca->chunk; a.o_add = ca->out_add; a.den_add = ca->den_add; }
   return launch_tc<OP_A>(c, "fm_dense_tc_fwd", q, nullptr, k, v, c.p.nq, c.p.nk, a);
 }
 
 int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
                       const float* dvec, const stat_t* stats, float* dots, void* grad_q,
-                      void* grad_k, void* grad_v) {
+                      void* grad_k, void* grad_v, const ChunkAdd* ca) {
   const fastmax_problem& p = c.p;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(gs) || !aligned16(grad_q) ||
       !aligned16(grad_k) || !aligned16(grad_v))
@@ -481,16 +495,19 @@ int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v,
   a.o = grad_q;
   a.rev = 0;
   a.dots = p.normalize ? dots : nullptr;
+  if (ca) { a.chunk = ca->chunk; a.o_add = ca->gq_add; }
   if ((rc = launch_tc<OP_B>(c, "fm_dense_tc_dq", q, gs, k, v, p.nq, p.nk, a))) return rc;
   // grad_k: rows = keys, columns = queries
   a.o = grad_k;
   a.rev = 1;
   a.dots = p.normalize ? dots + p.bh : nullptr;
+  if (ca) a.o_add = ca->gk_add;
   if ((rc = launch_tc<OP_B>(c, "fm_dense_tc_dk", k, v, q, gs, p.nk, p.nq, a))) return rc;
   // grad_v: rows = keys, columns = queries, plain sum
   a.o = grad_v;
   a.dots = nullptr;
   a.fwd_div = 0;
+  if (ca) a.o_add = ca->gv_add;
   return launch_tc<OP_A>(c, "fm_dense_tc_dv", k, nullptr, q, gs, p.nk, p.nq, a);
 }
 

@@ -1,0 +1,216 @@
+// Host-side orchestration of the moment-state form: which kernels run, in which
+// order, on which slices of the caller's workspace.  The same stages serve a
+// whole sequence on one GPU and one contiguous shard of a sequence split over
+// several GPUs; in the sharded case the caller exchanges the per-shard totals
+// between the stages (see include/fastmax_b200.h).
+#include "fm_common.cuh"
+
+namespace fm {
+
+static size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+
+int moments_chunk(const fastmax_problem& p) {
+  int L = p.chunk > 0 ? p.chunk : 2048;
+  L = (L + 255) / 256 * 256;
+  return L;
+}
+
+size_t moment_state_bytes(const fastmax_problem& p, int n) {
+  const MomentDims m = moment_dims(p.d);
+  const int L = moments_chunk(p);
+  return up256(sizeof(float) * (size_t)p.bh * ((n + L - 1) / L) * m.f * m.dvp);
+}
+size_t moment_total_bytes(const fastmax_problem& p) {
+  const MomentDims m = moment_dims(p.d);
+  return up256(sizeof(float) * (size_t)p.bh * m.f * m.dvp);
+}
+
+bool moments_supports(const fastmax_problem& p) {
+  return p.bh == p.bhkv && (!p.mask || p.nq == p.nk);
+}
+
+// Workspace of the one-call forward: [states][total][o_add][den_add]
+MomFwdWs moments_fwd_layout(const fastmax_problem& p) {
+  MomFwdWs w;
+  w.states = 0;
+  w.total = w.states + moment_state_bytes(p, p.nk);
+  w.o_add = w.total + moment_total_bytes(p);
+  w.den_add = w.o_add + up256(sizeof(float) * (size_t)p.bh * p.nq * p.d);
+  w.bytes = w.den_add + up256(sizeof(float) * (size_t)p.bh * p.nq);
+  return w;
+}
+// Workspace of the one-call backward:
+// [dots][delta][dvec][gs][states][total][gq_add][gk_add][gv_add]
+MomBwdWs moments_bwd_layout(const fastmax_problem& p) {
+  MomBwdWs w;
+  w.dots = 0;
+  w.delta = up256(sizeof(float) * (size_t)(p.bh + p.bhkv));
+  w.dvec = w.delta + up256(sizeof(float) * (size_t)p.bh * p.nq);
+  w.gs = w.dvec + up256(sizeof(float) * (size_t)p.bh * p.nq);
+  w.states = w.gs + (dense_tc_supports(p) ? up256((size_t)2 * p.bh * p.nq * p.d) : 0);
+  w.total = w.states + moment_state_bytes(p, p.nk > p.nq ? p.nk : p.nq);
+  w.gq_add = w.total + moment_total_bytes(p);
+  w.gk_add = w.gq_add + up256(sizeof(float) * (size_t)p.bh * p.nq * p.d);
+  w.gv_add = w.gk_add + up256(sizeof(float) * (size_t)p.bhkv * p.nk * p.d);
+  w.bytes = w.gv_add + up256(sizeof(float) * (size_t)p.bhkv * p.nk * p.d);
+  return w;
+}
+
+// ---- forward -----------------------------------------------------------------------
+// kv_states: raw chunk states of (k, v) for this shard (already built); s_base: sum of the
+// totals of all earlier shards or null.  Turns the states into prefixes in place.
+int moments_forward_finish(const Ctx& c, const void* q, const void* k, const void* v,
+                           const stat_t* stats, float* kv_states, const float* s_base,
+                           float* o_add, float* den_add, const FwdOut& o) {
+  const fastmax_problem& p = c.p;
+  const int L = moments_chunk(p);
+  const int nchunk = (p.nk + L - 1) / L;
+  int rc;
+  if ((rc = moments_prefix(c, p.bh, nchunk, kv_states, s_base, nullptr, 0, 1))) return rc;
+  if ((rc = moments_readout(c, 0, p.bh, p.nq, L, 1, q, nullptr, nullptr, nullptr, 0, kv_states, stats,
+                            o_add, den_add)))
+    return rc;
+  ChunkAdd ca;
+  ca.chunk = L;
+  ca.out_add = o_add;
+  ca.den_add = den_add;
+  if (dense_tc_supports(p) && !o.out_f32) return dense_tc_forward(c, q, k, v, stats, o.out, o.den, &ca);
+  return dense_ffma_forward(c, q, k, v, stats, o, ca);
+}
+
+int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
+                    const FwdOut& o, void* workspace) {
+  const fastmax_problem& p = c.p;
+  const int L = moments_chunk(p);
+  const MomFwdWs w = moments_fwd_layout(p);
+  char* ws = (char*)workspace;
+  float* states = (float*)(ws + w.states);
+  float* total = (float*)(ws + w.total);
+  float* o_add = (float*)(ws + w.o_add);
+  float* den_add = (float*)(ws + w.den_add);
+  int rc;
+  if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, states))) return rc;
+  if (p.mask) return moments_forward_finish(c, q, k, v, stats, states, nullptr, o_add, den_add, o);
+  // unmasked: every query reads the total of all keys
+  const int nchunk = (p.nk + L - 1) / L;
+  if ((rc = moments_prefix(c, p.bh, nchunk, states, nullptr, total, 0, 0))) return rc;
+  if ((rc = moments_readout(c, 0, p.bh, p.nq, L, 0, q, nullptr, nullptr, nullptr, 0, total, stats, o_add,
+                            den_add)))
+    return rc;
+  if (o.out_f32 || o.o_stride != p.d)
+    return fail(FASTMAX_E_UNSUPPORTED, "the moment family writes the plain output layout only");
+  return moments_finalize(c, p.bh, p.nq, o_add, den_add, nullptr, o.out, o.den, nullptr, 0);
+}
+
+// ---- backward ----------------------------------------------------------------------
+// s_states: exclusive prefixes of the (k, v) chunk states (as left by the forward finish);
+// r_states: raw chunk states of (q, grad_out/den | -delta/den); r_base: sum of the totals of
+// all later shards or null.  Writes the three gradients without the normalisation row fix.
+int moments_backward_finish(const Ctx& c, const void* q, const void* k, const void* v,
+                            const float* den, const stat_t* stats, const void* grad_out,
+                            const float* delta, const float* dvec, const void* gs,
+                            const float* s_states, float* r_states, const float* r_base,
+                            float* gq_add, float* gk_add, float* gv_add, float* dots, void* grad_q,
+                            void* grad_k, void* grad_v) {
+  const fastmax_problem& p = c.p;
+  const int L = moments_chunk(p);
+  const int nchunk = (p.nq + L - 1) / L;
+  int rc;
+  // grad_q reads the key/value prefixes with u = [grad_out/den | -delta/den]
+  if ((rc = moments_readout(c, 1, p.bh, p.nq, L, 1, q, grad_out, den, delta, 1, s_states, stats, gq_add,
+                            nullptr)))
+    return rc;
+  // grad_k and grad_v read the suffix sums of the query/gradient states
+  if ((rc = moments_prefix(c, p.bh, nchunk, r_states, r_base, nullptr, 1, 1))) return rc;
+  if ((rc = moments_readout(c, 1, p.bh, p.nk, L, 1, k, v, nullptr, nullptr, 0, r_states, stats, gk_add,
+                            nullptr)))
+    return rc;
+  if ((rc = moments_readout(c, 0, p.bh, p.nk, L, 1, k, nullptr, nullptr, nullptr, 0, r_states, stats,
+                            gv_add, nullptr)))
+    return rc;
+  ChunkAdd ca;
+  ca.chunk = L;
+  ca.gq_add = gq_add;
+  ca.gk_add = gk_add;
+  ca.gv_add = gv_add;
+  if (dense_tc_supports(p))
+    return dense_tc_backward(c, q, k, v, gs, dvec, stats, dots, grad_q, grad_k, grad_v, &ca);
+  return dense_ffma_backward(c, q, k, v, den, stats, grad_out, delta, dots, grad_q, grad_k, grad_v, ca);
+}
+
+int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* out,
+                     const float* den, const stat_t* stats, const void* grad_out, void* grad_q,
+                     void* grad_k, void* grad_v, void* workspace) {
+  const fastmax_problem& p = c.p;
+  const int L = moments_chunk(p);
+  const MomBwdWs w = moments_bwd_layout(p);
+  char* ws = (char*)workspace;
+  float* dots = (float*)(ws + w.dots);
+  float* delta = (float*)(ws + w.delta);
+  float* dvec = (float*)(ws + w.dvec);
+  void* gs = ws + w.gs;
+  float* states = (float*)(ws + w.states);
+  float* total = (float*)(ws + w.total);
+  float* gq_add = (float*)(ws + w.gq_add);
+  float* gk_add = (float*)(ws + w.gk_add);
+  float* gv_add = (float*)(ws + w.gv_add);
+  int rc;
+  if (p.normalize)
+    FM_CUDA_TRY(cudaMemsetAsync(dots, 0, sizeof(float) * (size_t)(p.bh + p.bhkv), c.stream));
+  if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
+  const bool tc = dense_tc_supports(p);
+  if (tc && p.mask && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
+  const int nck = (p.nk + L - 1) / L, ncq = (p.nq + L - 1) / L;
+  if (p.mask) {
+    // the key/value prefixes are rebuilt (the forward does not keep them), used for grad_q,
+    // then the buffer is reused for the query/gradient states
+    if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, states))) return rc;
+    if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, nullptr, 0, 1))) return rc;
+    if ((rc = moments_readout(c, 1, p.bh, p.nq, L, 1, q, grad_out, den, delta, 1, states, stats, gq_add,
+                              nullptr)))
+      return rc;
+    if ((rc = moments_chunk_state(c, p.bh, p.nq, L, q, grad_out, den, delta, 1, states))) return rc;
+    if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, nullptr, 1, 1))) return rc;
+    if ((rc = moments_readout(c, 1, p.bh, p.nk, L, 1, k, v, nullptr, nullptr, 0, states, stats, gk_add,
+                              nullptr)))
+      return rc;
+    if ((rc = moments_readout(c, 0, p.bh, p.nk, L, 1, k, nullptr, nullptr, nullptr, 0, states, stats,
+                              gv_add, nullptr)))
+      return rc;
+    ChunkAdd ca;
+    ca.chunk = L;
+    ca.gq_add = gq_add;
+    ca.gk_add = gk_add;
+    ca.gv_add = gv_add;
+    if (tc) rc = dense_tc_backward(c, q, k, v, gs, dvec, stats, dots, grad_q, grad_k, grad_v, &ca);
+    else rc = dense_ffma_backward(c, q, k, v, den, stats, grad_out, delta, dots, grad_q, grad_k, grad_v, ca);
+    if (rc) return rc;
+  } else {
+    // unmasked: totals only, no score-form part
+    if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, states))) return rc;
+    if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, total, 0, 0))) return rc;
+    if ((rc = moments_readout(c, 1, p.bh, p.nq, L, 0, q, grad_out, den, delta, 1, total, stats, gq_add,
+                              nullptr)))
+      return rc;
+    if ((rc = moments_finalize(c, p.bh, p.nq, gq_add, nullptr, q, grad_q, nullptr,
+                               p.normalize ? dots : nullptr, 1)))
+      return rc;
+    if ((rc = moments_chunk_state(c, p.bh, p.nq, L, q, grad_out, den, delta, 1, states))) return rc;
+    if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, total, 0, 0))) return rc;
+    if ((rc = moments_readout(c, 1, p.bh, p.nk, L, 0, k, v, nullptr, nullptr, 0, total, stats, gk_add,
+                              nullptr)))
+      return rc;
+    if ((rc = moments_readout(c, 0, p.bh, p.nk, L, 0, k, nullptr, nullptr, nullptr, 0, total, stats,
+                              gv_add, nullptr)))
+      return rc;
+    if ((rc = moments_finalize(c, p.bh, p.nk, gk_add, nullptr, k, grad_k, nullptr,
+                               p.normalize ? dots + p.bh : nullptr, 1)))
+      return rc;
+    if ((rc = moments_finalize(c, p.bh, p.nk, gv_add, nullptr, nullptr, grad_v, nullptr, nullptr, 1)))
+      return rc;
+  }
+  if (p.normalize) return launch_norm_fixup(c, q, k, stats, dots, grad_q, grad_k);
+  return FASTMAX_OK;
+}
+
+}  // namespace fm

@@ -1,0 +1,172 @@
+"""Causal Fastmax attention over a sequence that is split across GPUs.
+
+One process per GPU (``torch.distributed``); rank r holds the r-th contiguous
+slice of the sequence for every head: ``q, k, v : (b*h, n_local, d)``.  The
+reference has nothing like this (single device, hard-wired to ``cuda:0``,
+reference ``fastmax_cuda_forward.cu:347``); what makes it possible is that the
+reference's moment tensors (Sum v, Sum k(x)v, Sum k(x)k(x)v and their v=1
+counterparts) are sums over tokens, so a shard only needs the *sum of the
+totals* of the shards before it (forward, grad_q) or after it (grad_k, grad_v).
+
+Per pass the ranks exchange
+
+* with ``normalize``: one MAX all-reduce of the per-head statistics words
+  (max row norm and its global row, packed in an int64) and, in backward, one
+  SUM all-reduce of ``2*b*h`` floats for the gradient of the max-norm scaling;
+* one all-gather of each rank's total state, ``b*h * (d*d+d+1) * (d+1)`` floats
+  rounded up, followed by a local sum over the earlier (or later) ranks.
+
+Everything else is local and runs through the C ABI's ``fastmax_b200_shard_*``
+stage calls.  The stage calls are reached through a small backend object so that
+the exchange logic can be exercised on CPU ranks (gloo) with a stand-in backend.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _cabi
+
+__all__ = ["CudaShardBackend", "SequenceShardedFastmax", "fastmax_sequence_parallel", "exclusive_rank_sum"]
+
+
+def exclusive_rank_sum(total: torch.Tensor, group=None, reverse: bool = False):
+    """Sum of ``total`` over the ranks before this one (after it when ``reverse``); None if there are none."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    parts = [torch.empty_like(total) for _ in range(world)]
+    dist.all_gather(parts, total.contiguous(), group=group)
+    pick = parts[rank + 1:] if reverse else parts[:rank]
+    if not pick:
+        return None
+    acc = pick[0].clone()
+    for t in pick[1:]:
+        acc += t
+    return acc
+
+
+class CudaShardBackend:
+    """The stage calls of ``include/fastmax_b200.h`` on the current CUDA device."""
+
+    def __init__(self, **kw):
+        self.kw = kw  # mask, normalize, a0.., p, chunk as for _cabi.make_problem
+
+    def _prob(self, q, k):
+        kw = self.kw
+        return _cabi.make_problem(q, k, True, kw["normalize"], 1.0, kw["a0"], kw["a1"], kw["a2"], kw["lim"],
+                                  kw["p"], "auto", kw.get("chunk", 0))
+
+    @staticmethod
+    def _ptr(t):
+        return None if t is None else t.data_ptr()
+
+    def rowmax(self, q, k, row_offset):
+        L, prob = _cabi.lib(), self._prob(q, k)
+        stats = torch.empty(q.shape[0] + k.shape[0], dtype=torch.int64, device=q.device)
+        _cabi._check(L.fastmax_b200_shard_rowmax(prob, q.data_ptr(), k.data_ptr(), int(row_offset),
+                                                 stats.data_ptr(), _cabi._stream(q)), "shard_rowmax")
+        return stats
+
+    def kv_state(self, k, v):
+        L, prob = _cabi.lib(), self._prob(k, k)
+        states = torch.empty(L.fastmax_b200_moment_state_bytes(prob) // 4, dtype=torch.float32, device=k.device)
+        total = torch.empty(L.fastmax_b200_moment_total_bytes(prob) // 4, dtype=torch.float32, device=k.device)
+        _cabi._check(L.fastmax_b200_shard_kv_state(prob, k.data_ptr(), v.data_ptr(), states.data_ptr(),
+                                                   total.data_ptr(), _cabi._stream(k)), "shard_kv_state")
+        return states, total
+
+    def forward(self, q, k, v, stats, kv_states, s_base):
+        L, prob = _cabi.lib(), self._prob(q, k)
+        out = torch.empty_like(q)
+        den = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
+        wsb = L.fastmax_b200_shard_forward_workspace_bytes(prob)
+        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)
+        _cabi._check(L.fastmax_b200_shard_forward(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), self._ptr(stats),
+                                                  kv_states.data_ptr(), self._ptr(s_base), out.data_ptr(),
+                                                  den.data_ptr(), ws.data_ptr(), wsb, _cabi._stream(q)),
+                     "shard_forward")
+        return out, den
+
+    def qg_state(self, q, out, den, go):
+        L, prob = _cabi.lib(), self._prob(q, q)
+        delta = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
+        states = torch.empty(L.fastmax_b200_moment_state_bytes(prob) // 4, dtype=torch.float32, device=q.device)
+        total = torch.empty(L.fastmax_b200_moment_total_bytes(prob) // 4, dtype=torch.float32, device=q.device)
+        _cabi._check(L.fastmax_b200_shard_qg_state(prob, q.data_ptr(), out.data_ptr(), den.data_ptr(), go.data_ptr(),
+                                                   delta.data_ptr(), states.data_ptr(), total.data_ptr(),
+                                                   _cabi._stream(q)), "shard_qg_state")
+        return delta, states, total
+
+    def backward(self, q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base):
+        L, prob = _cabi.lib(), self._prob(q, k)
+        gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dots = torch.empty(q.shape[0] + k.shape[0], dtype=torch.float32, device=q.device)
+        wsb = L.fastmax_b200_shard_backward_workspace_bytes(prob)
+        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)
+        _cabi._check(L.fastmax_b200_shard_backward(
+            prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), den.data_ptr(), self._ptr(stats),
+            go.data_ptr(), delta.data_ptr(), kv_states.data_ptr(), qg_states.data_ptr(), self._ptr(r_base),
+            dots.data_ptr(), gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), ws.data_ptr(), wsb, _cabi._stream(q)),
+            "shard_backward")
+        return gq, gk, gv, dots
+
+    def norm_fixup(self, q, k, stats, dots, row_offset, gq, gk):
+        L, prob = _cabi.lib(), self._prob(q, k)
+        _cabi._check(L.fastmax_b200_shard_norm_fixup(prob, q.data_ptr(), k.data_ptr(), stats.data_ptr(),
+                                                     dots.data_ptr(), int(row_offset), gq.data_ptr(), gk.data_ptr(),
+                                                     _cabi._stream(q)), "shard_norm_fixup")
+
+
+class SequenceShardedFastmax(torch.autograd.Function):
+    """``apply(q, k, v, backend, normalize, group)`` on this rank's slice; returns its slice of the output."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, backend, normalize, group):
+        rank = dist.get_rank(group)
+        n_local = q.shape[1]
+        lens = [torch.zeros(1, dtype=torch.int64, device=q.device) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(lens, torch.tensor([n_local], dtype=torch.int64, device=q.device), group=group)
+        if any(int(x) != n_local for x in lens):
+            raise ValueError("every rank must hold the same number of tokens")
+        row_offset = rank * n_local
+        stats = None
+        if normalize:
+            stats = backend.rowmax(q, k, row_offset)
+            dist.all_reduce(stats, op=dist.ReduceOp.MAX, group=group)
+        kv_states, kv_total = backend.kv_state(k, v)
+        s_base = exclusive_rank_sum(kv_total, group)
+        out, den = backend.forward(q, k, v, stats, kv_states, s_base)
+        ctx.backend, ctx.group, ctx.normalize, ctx.row_offset = backend, group, normalize, row_offset
+        ctx.save_for_backward(q, k, v, out, den, kv_states, *([stats] if normalize else []))
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, out, den, kv_states, *rest = ctx.saved_tensors
+        stats = rest[0] if rest else None
+        backend, group = ctx.backend, ctx.group
+        go = grad_out.contiguous().to(q.dtype)
+        delta, qg_states, qg_total = backend.qg_state(q, out, den, go)
+        r_base = exclusive_rank_sum(qg_total, group, reverse=True)
+        gq, gk, gv, dots = backend.backward(q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base)
+        if ctx.normalize:
+            dist.all_reduce(dots, op=dist.ReduceOp.SUM, group=group)
+            backend.norm_fixup(q, k, stats, dots, ctx.row_offset, gq, gk)
+        return gq, gk, gv, None, None, None
+
+
+def fastmax_sequence_parallel(q, k, v, *, normalize=False, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2, chunk=0,
+                              group=None, backend=None):
+    """Causal Fastmax on this rank's ``(b*h, n_local, d)`` slices of q, k, v (CUDA, float32 or bfloat16).
+
+    Rank r of ``group`` must hold tokens ``[r*n_local, (r+1)*n_local)``, the same ``n_local`` on every rank
+    (chunks of ``chunk`` tokens, default 2048, are laid out from the start of each shard).  Differentiable;
+    gradients come back sharded the same way.
+    """
+    if backend is None:
+        if not q.is_cuda:
+            raise RuntimeError("fastmax_sequence_parallel needs CUDA tensors")
+        backend = CudaShardBackend(normalize=bool(normalize), a0=a0, a1=a1, a2=a2, lim=lim, p=p, chunk=chunk)
+    return SequenceShardedFastmax.apply(q.contiguous(), k.contiguous(), v.contiguous(), backend, bool(normalize),
+                                        group)

@@ -53,8 +53,9 @@ enum {
   FASTMAX_IMPL_AUTO = 0,
   FASTMAX_IMPL_DENSE_FFMA = 1,   /* tiled score form on CUDA cores, fp32 math */
   FASTMAX_IMPL_DENSE_TC = 2,     /* tiled score form on tcgen05 tensor cores (bf16) */
-  FASTMAX_IMPL_MOMENTS_FFMA = 3, /* chunked moment-state form on CUDA cores */
-  FASTMAX_IMPL_MOMENTS_TC = 4    /* chunked moment-state form on tcgen05 */
+  FASTMAX_IMPL_MOMENTS_FFMA = 3, /* chunked moment-state form, states on CUDA cores; each chunk's own
+                                    block in score form on the best family for the problem */
+  FASTMAX_IMPL_MOMENTS_TC = 4    /* chunked moment-state form with states on tcgen05 (not built yet) */
 };
 
 /* One attention problem.  Mirrors the argument list of the reference's
@@ -76,6 +77,7 @@ typedef struct fastmax_problem {
   float a0, a1, a2;
   float lim;
   float temperature;
+  int32_t chunk;      /* moment family: tokens per chunk (multiple of 256); 0 = library default */
 } fastmax_problem;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -147,6 +149,58 @@ int fastmax_b200_backward(const fastmax_problem* prob,
                           void* grad_q, void* grad_k, void* grad_v,
                           void* workspace, size_t workspace_bytes,
                           void* stream);
+
+/* ---- sequence sharding ------------------------------------------------------
+ * No counterpart in the reference, which has no multi-GPU code (its outputs are
+ * hard-wired to cuda:0, fastmax_cuda_forward.cu:347).  A causal sequence is split
+ * into contiguous shards, one per GPU, every shard holding all heads; `prob`
+ * describes ONE shard (nq == nk == shard length, mask = 1, bh == bhkv).  The
+ * moment states are additive over tokens, so a shard needs from the others only
+ * the sum of their per-head totals: of all EARLIER shards' key/value states for
+ * the forward pass and grad_q, of all LATER shards' query/gradient states for
+ * grad_k and grad_v.  The caller moves those totals between GPUs (for instance an
+ * NCCL all-gather followed by a local sum) between the calls below; the library
+ * itself never communicates.  With normalize != 0 the caller also max-reduces the
+ * stats words (as 64-bit integers) and sum-reduces the `dots` array over shards.
+ *
+ *   shard_rowmax      stats of this shard; recorded rows are row_offset + local row
+ *   shard_kv_state    chunk states of (k, v) into kv_states, their sum into kv_total
+ *   shard_forward     s_base = sum of earlier shards' kv_total (NULL on the first);
+ *                     turns kv_states into running prefixes (keep them for backward)
+ *   shard_qg_state    delta = grad_out.out per row, chunk states of (q, grad_out/den)
+ *                     into qg_states, their sum into qg_total
+ *   shard_backward    r_base = sum of later shards' qg_total (NULL on the last);
+ *                     writes the gradients without the normalisation row and the
+ *                     per-head dots (bh + bhkv floats, zeroed here)
+ *   shard_norm_fixup  after dots were summed over shards: corrects the max-norm row
+ *                     on the shard that owns it
+ * Buffers: kv_states/qg_states fastmax_b200_moment_state_bytes, totals and bases
+ * fastmax_b200_moment_total_bytes (float32), workspaces by the *_workspace_bytes
+ * queries, delta bh*nq floats. */
+size_t fastmax_b200_moment_state_bytes(const fastmax_problem* prob);
+size_t fastmax_b200_moment_total_bytes(const fastmax_problem* prob);
+size_t fastmax_b200_shard_forward_workspace_bytes(const fastmax_problem* prob);
+size_t fastmax_b200_shard_backward_workspace_bytes(const fastmax_problem* prob);
+int fastmax_b200_shard_rowmax(const fastmax_problem* prob, const void* q, const void* k,
+                              int32_t row_offset, void* stats, void* stream);
+int fastmax_b200_shard_kv_state(const fastmax_problem* prob, const void* k, const void* v,
+                                float* kv_states, float* kv_total, void* stream);
+int fastmax_b200_shard_forward(const fastmax_problem* prob, const void* q, const void* k,
+                               const void* v, const void* stats, float* kv_states,
+                               const float* s_base, void* out, float* den, void* workspace,
+                               size_t workspace_bytes, void* stream);
+int fastmax_b200_shard_qg_state(const fastmax_problem* prob, const void* q, const void* out,
+                                const float* den, const void* grad_out, float* delta,
+                                float* qg_states, float* qg_total, void* stream);
+int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, const void* k,
+                                const void* v, const void* out, const float* den,
+                                const void* stats, const void* grad_out, const float* delta,
+                                const float* kv_states, float* qg_states, const float* r_base,
+                                float* dots, void* grad_q, void* grad_k, void* grad_v,
+                                void* workspace, size_t workspace_bytes, void* stream);
+int fastmax_b200_shard_norm_fixup(const fastmax_problem* prob, const void* q, const void* k,
+                                  const void* stats, const float* dots, int32_t row_offset,
+                                  void* grad_q, void* grad_k, void* stream);
 
 /* Backward pass for callers that cannot supply or allocate scratch memory.  It
  * has no counterpart in the reference, whose backward_cuda allocates its outputs

@@ -1,0 +1,99 @@
+"""GPU parity of the moment-state family (chunk states, prefix, read-outs, coupled to the
+score-form kernels for each chunk's own block) and of the sequence-shard stage calls,
+through the C ABI.  Tolerances: 1e-4 (float32), 2e-2 (bfloat16), relative max error."""
+import pytest
+import torch
+
+from conftest import case_kwargs, load_small_cases
+from gpu_util import assert_close, oracle, run_cabi
+
+from fastmax_b200 import _cabi
+from fastmax_b200.sharded import CudaShardBackend
+
+pytestmark = pytest.mark.gpu
+CASES = load_small_cases()
+
+
+def randn(*shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g)
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
+def test_reference_vectors_through_the_moment_family(c):
+    """Sequences shorter than one chunk: states are built and summed, the score-form part covers everything."""
+    got, _ = run_cabi(c["q"], c["k"], c["v"], c["go"], torch.float32, impl="moments_ffma", chunk=256,
+                      **case_kwargs(c))
+    assert_close(got, [c[n + "64"] for n in ("out", "dq", "dk", "dv")], torch.float32, c["tag"])
+
+
+# bh, n, d, mask, p, normalize, chunk
+MOM = [(2, 700, 32, 1, 2, 1, 256), (2, 700, 32, 0, 2, 1, 256), (3, 1024, 32, 1, 1, 1, 256),
+       (2, 600, 16, 1, 2, 0, 256), (1, 900, 64, 1, 2, 1, 256), (2, 520, 64, 0, 2, 0, 256),
+       (1, 600, 128, 1, 2, 0, 256), (2, 515, 128, 0, 1, 0, 256), (2, 1030, 64, 1, 2, 1, 512)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("cfg", MOM, ids=[f"bh{c[0]}n{c[1]}d{c[2]}m{c[3]}p{c[4]}z{c[5]}L{c[6]}" for c in MOM])
+def test_moment_family_over_several_chunks(cfg, dtype):
+    bh, n, d, mask, p, norm, chunk = cfg
+    q, k, v, go = [randn(1, bh, n, d, seed=300 + i + n) for i in range(4)]
+    if not norm:
+        q, k = q * d ** -0.5, k * d ** -0.5
+    kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    got, _ = run_cabi(q, k, v, go, dtype, impl="moments_ffma", chunk=chunk, **kw)
+    assert _cabi.device_status() == 0
+    ref = oracle(q, k, v, go, dtype, dense=True, **kw)
+    assert_close(got, ref, dtype, str(cfg))
+
+
+def test_unmasked_moments_with_more_keys_than_queries():
+    q, go = randn(1, 2, 300, 32, seed=1), randn(1, 2, 300, 32, seed=2)
+    k, v = randn(1, 2, 777, 32, seed=3), randn(1, 2, 777, 32, seed=4)
+    kw = dict(mask=0, normalize=1, p=2, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    got, _ = run_cabi(q, k, v, go, torch.float32, impl="moments_ffma", chunk=256, **kw)
+    ref = oracle(q, k, v, go, torch.float32, dense=True, **kw)
+    assert_close(got, ref, torch.float32, "unmasked nq != nk")
+
+
+@pytest.mark.parametrize("dtype,d,normalize", [(torch.float32, 32, True), (torch.bfloat16, 64, True),
+                                               (torch.float32, 16, False)])
+def test_shard_stage_calls_reproduce_the_unsharded_result(dtype, d, normalize):
+    """Three shards of one sequence evaluated one after another on this GPU, with the exchange
+    of totals done by hand, against the single-call result on the whole sequence."""
+    dev = torch.device("cuda", 0)
+    G, nl, bh = 3, 384, 3
+    g = torch.Generator(device=dev).manual_seed(9)
+    q, k, v, go = [torch.randn(bh, G * nl, d, generator=g, device=dev).to(dtype) for _ in range(4)]
+    kw = dict(mask=True, normalize=normalize, p=2)
+    out, den, stats = _cabi.forward(q, k, v, impl="dense_ffma", **kw)
+    want = (out,) + tuple(_cabi.backward(q, k, v, out, den, stats, go, impl="dense_ffma", **kw))
+
+    be = CudaShardBackend(normalize=normalize, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2, chunk=256)
+    sh = lambda t, r: t[:, r * nl:(r + 1) * nl].contiguous()
+    qs, ks, vs, gs = [[sh(t, r) for r in range(G)] for t in (q, k, v, go)]
+    st = None
+    if normalize:
+        st = torch.stack([be.rowmax(qs[r], ks[r], r * nl) for r in range(G)]).max(0).values
+    kv = [be.kv_state(ks[r], vs[r]) for r in range(G)]
+    outs, dens = [], []
+    for r in range(G):
+        base = sum(kv[j][1] for j in range(r)) if r else None
+        o, dn = be.forward(qs[r], ks[r], vs[r], st, kv[r][0], base)
+        outs.append(o); dens.append(dn)
+    qg = [be.qg_state(qs[r], outs[r], dens[r], gs[r]) for r in range(G)]
+    grads = []
+    for r in range(G):
+        base = sum(qg[j][2] for j in range(r + 1, G)) if r < G - 1 else None
+        grads.append(be.backward(qs[r], ks[r], vs[r], outs[r], dens[r], st, gs[r], qg[r][0], kv[r][0], qg[r][1], base))
+    if normalize:
+        dots = sum(gr[3] for gr in grads)
+        for r in range(G):
+            be.norm_fixup(qs[r], ks[r], st, dots, r * nl, grads[r][0], grads[r][1])
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    got = (torch.cat(outs, 1),) + tuple(torch.cat([gr[i] for gr in grads], 1) for i in range(3))
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    for a, b, name in zip(got, want, ("out", "dq", "dk", "dv")):
+        e = float((a.float() - b.float()).abs().max() / b.float().abs().max())
+        assert e < tol, (name, e)

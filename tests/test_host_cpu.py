@@ -43,7 +43,7 @@ def test_version_and_size_queries_need_no_gpu():
                          a0=1, a1=1, a2=0.5, lim=1, temperature=1)
     assert L.fastmax_b200_stats_bytes(prob) == 8 * 9
     assert L.fastmax_b200_backward_workspace_bytes(prob) >= 4 * (9 + 60)
-    assert ctypes.sizeof(_cabi.Problem) == 60
+    assert ctypes.sizeof(_cabi.Problem) == 64
 
 
 def test_bad_arguments_are_rejected_before_any_launch():
