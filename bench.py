@@ -38,6 +38,8 @@ WORKLOADS = {
     "c2": (64, 8, 1000, 32, "fp32", 1, 2, 1),
     "c4p2": (32, 32, 16384, 128, "bf16", 0, 2, 0),
     "c4p1": (32, 32, 16384, 128, "bf16", 0, 1, 0),
+    "c5": (1, 32, 262144, 64, "bf16", 1, 2, 1),   # long context; sharded along the sequence when N > 1
+    "c5s": (1, 8, 65536, 64, "bf16", 1, 2, 1),    # reduced long-context case
     "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
     "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),   # small case for ncu captures (inputs 4 x 67 MB)
 }
@@ -56,6 +58,9 @@ def alg_flops_per_token_head(D, p):
     F = D + (D * D if p == 2 else 0)
     u = F * (D + 1)
     return 4 * u, 4 * u, 6 * u
+
+
+KERNEL_FLOP_SHARE = {"fwd": "fwd", "dq": "dq", "dkdv": "dkdv", "dk": "dk", "dv": "dv"}
 
 
 class ClockSampler:
@@ -176,6 +181,9 @@ def run_ours(args):
     B, H, N, D, dt, mask, p, norm = WORKLOADS[args.workload]
     dtype = torch.bfloat16 if dt == "bf16" else torch.float32
     bh_total = B * H
+    seq_mode = args.workload.startswith("c5")
+    if seq_mode:
+        return run_seq(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
     if args.scaling == "strong":
         bh = bh_total // world + (1 if rank < bh_total % world else 0)
         tokens_job = B * N
@@ -260,7 +268,7 @@ def run_ours(args):
         dom = max(per, key=lambda n: per[n][1]) if per else None
         peaks = load_peaks()
         ff, fq, fkv = alg_flops_per_token_head(D, p)
-        flops_of = {"fwd": ff, "dq": fq, "dkdv": fkv}
+        flops_of = {"fwd": ff, "dq": fq, "dkdv": fkv, "dk": fkv * 2 // 3, "dv": fkv // 3}
         roof = None
         if dom is not None:
             cnt, tot = per[dom]
@@ -294,6 +302,87 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_sample(args.workload, 2, 1)[0]
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_seq(args, world, rank, dev, cfg):
+    """Long-context workload: the sequence is split into `world` contiguous shards (one per GPU, all heads
+    on every GPU); per pass the ranks exchange the per-shard moment totals (all-gather) and the
+    normalisation statistics (all-reduce).  Total work is fixed, so this is strong scaling."""
+    import torch
+    import torch.distributed as dist
+
+    import fastmax_b200
+    from fastmax_b200 import _cabi
+    from fastmax_b200.sharded import fastmax_sequence_parallel
+
+    B, H, N, D, dt, mask, p, norm = cfg
+    dtype = torch.bfloat16 if dt == "bf16" else torch.float32
+    nl = N // world
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v, go = [torch.randn(B * H, nl, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4)]
+    mod = fastmax_b200.FASTMultiHeadAttention()
+
+    def step():
+        qd, kd, vd = [t.detach().requires_grad_(True) for t in (q, k, v)]
+        if world > 1:
+            out = fastmax_sequence_parallel(qd, kd, vd, normalize=bool(norm), p=p, **A)
+        else:
+            out = mod(qd, kd, vd, None, True, 0.0, bool(norm), 1.0, A["a0"], A["a1"], A["a2"], A["lim"], p)
+        out.backward(go)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    _cabi.profile(True)
+    n0 = _cabi.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    launches = _cabi.launch_count() - n0
+    recs = _cabi.profile_records()
+    _cabi.profile(False)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    if rank == 0:
+        per = {}
+        for name, t in recs:
+            c, s = per.get(name, (0, 0.0))
+            per[name] = (c + 1, s + t)
+        ff, fq, fkv = alg_flops_per_token_head(D, p)
+        tot = sum(x[1] for x in per.values())
+        line = {
+            "metric": "fastmax_fwd_bwd_tokens_per_s", "value": B * N * args.steps / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": describe(args.workload), "tokens_per_gpu": nl,
+                       "parallelism": f"sequence sharded x{world}; all-gather of per-shard moment totals, "
+                                      "all-reduce of normalisation statistics",
+                       "l2": "inputs larger than the 126 MB L2"},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "alg_tflops_per_gpu": (ff + fq + fkv) * B * H * nl * args.steps / (ms * 1e-3) / 1e12,
+            "kernels": {n: {"launches": c, "ms_total": round(s, 3), "share": round(s / tot, 4)}
+                        for n, (c, s) in sorted(per.items(), key=lambda kv: -kv[1][1])},
+        }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
