@@ -48,7 +48,7 @@ struct TcArgs {
   float* dots;          // OP_B: per head sum of o . x  (null when not normalised)
   const stat_t* stat_q;
   const stat_t* stat_k;
-  int nrows, ncols, off, mask, rev, fwd_div;
+  int nrows, ncols, off, mask, rev, fwd_div, npairs;
   float a0, a1, a2, lim;
   int chunk;             // > 0: only the columns of the row pair's own chunk
   const float* o_add;    // fp32 (heads, nrows, 64) added to the accumulator row
@@ -102,8 +102,11 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + C::OFF_TMEM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int head = blockIdx.x;
-  const int pair = a.rev ? (int)blockIdx.y : (int)(gridDim.y - 1 - blockIdx.y);
+  // consecutive CTAs work on the same head, so its K/V (or Q/G) tiles stay in L2 while the
+  // row tiles that share them are in flight; causal row pairs are issued longest first
+  const int head = blockIdx.x / a.npairs;
+  const int pidx = blockIdx.x % a.npairs;
+  const int pair = a.rev ? pidx : a.npairs - 1 - pidx;
   const int r0 = pair * 2 * BM;
   const bool colvec = (MODE == OP_B) && a.rev;
 
@@ -439,7 +442,8 @@ int launch_tc(const Ctx& c, const char* name, const void* x, const void* u, cons
   a.x = x;
   FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    C::SMEM));
-  dim3 grid(heads, (nrows + 2 * BM - 1) / (2 * BM));
+  a.npairs = (nrows + 2 * BM - 1) / (2 * BM);
+  dim3 grid((unsigned)((size_t)heads * a.npairs));
   FM_LAUNCH(name, c.stream,
             (dense_tc_kernel<MODE><<<grid, kThreads, C::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
