@@ -13,8 +13,8 @@ device time ("weak" scaling); `--scaling strong` splits the single batch's
 batch*head units over the ranks instead.
 
 Rank 0 prints one JSON line.  `value` is measured with the inputs resident in
-HBM; `e2e` is the same metric through the public module with pinned host
-buffers, host<->device copies inside the timed region.  `--impl reference` times
+HBM; `e2e` is the same metric with pinned host buffers through
+fastmax_b200.host.HostPipeline, host<->device copies inside the timed region.  `--impl reference` times
 the CPU restatement of the reference's PyTorch path (oracle/) on the host
 cores, on a bounded sample of the same workload.
 """
@@ -230,21 +230,19 @@ def run_ours(args):
     ms = float(tms.item())
     value = tokens_job * args.steps / (ms * 1e-3)
 
-    # ---- end to end through the public module, host buffers ----------------------
-    mod = fastmax_b200.FASTMultiHeadAttention()
+    # ---- end to end with host buffers: fastmax_b200.host.HostPipeline streams groups of heads
+    # through the GPU (copy-in, forward+backward, copy-out overlapped) ----------------------
+    from fastmax_b200.host import HostPipeline
+
     del res
     host_in = [t.cpu().pin_memory() for t in (q, k, v, go)]
-    host_out = [torch.empty_like(h) for h in host_in]
+    host_out = [torch.empty_like(h).pin_memory() for h in host_in]
     del q, k, v, go
     torch.cuda.empty_cache()
+    pipe = HostPipeline(bh, N, D, dtype, dev, heads_per_group=64, **kw)
 
     def e2e_step():
-        qd, kd, vd, gd = [h.to(dev, non_blocking=True) for h in host_in]
-        qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
-        out = mod(qd, kd, vd, None, bool(mask), 0.0, bool(norm), 1.0, A["a0"], A["a1"], A["a2"], A["lim"], p)
-        out.backward(gd)
-        for h, t in zip(host_out, (out.detach(), qd.grad, kd.grad, vd.grad)):
-            h.copy_(t, non_blocking=True)
+        pipe.run(*host_in, *host_out)
 
     e2e_steps = max(1, min(args.steps, 3))
     e2e_step()

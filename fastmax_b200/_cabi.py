@@ -163,17 +163,25 @@ def _workspace(nbytes: int, device) -> torch.Tensor:
 
 
 def forward(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2,
-            impl="auto", chunk=0):
-    """q (bh,nq,d), k/v (bhkv,nk,d) -> out (bh,nq,d), den (bh,nq) fp32, stats (opaque)."""
+            impl="auto", chunk=0, buffers=None):
+    """q (bh,nq,d), k/v (bhkv,nk,d) -> out (bh,nq,d), den (bh,nq) fp32, stats (opaque).
+
+    ``buffers`` may hold preallocated ``out``, ``den``, ``stats`` and ``workspace`` tensors
+    (see ``forward_buffers``); otherwise they are allocated here."""
     _require(q, k, v)
     L = lib()
     prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl, chunk)
     with torch.cuda.device(q.device):
-        out = torch.empty_like(q)
-        den = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
-        stats = torch.empty(max(L.fastmax_b200_stats_bytes(prob), 8), dtype=torch.uint8, device=q.device)
         wsb = L.fastmax_b200_forward_workspace_bytes(prob)
-        ws = _workspace(wsb, q.device)
+        if buffers is None:
+            out = torch.empty_like(q)
+            den = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
+            stats = torch.empty(max(L.fastmax_b200_stats_bytes(prob), 8), dtype=torch.uint8, device=q.device)
+            ws = _workspace(wsb, q.device)
+        else:
+            out, den, stats, ws = buffers["out"], buffers["den"], buffers["stats"], buffers["workspace"]
+            if ws.numel() < wsb:
+                raise ValueError("preallocated forward workspace is too small")
         rc = L.fastmax_b200_forward(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                     den.data_ptr(), stats.data_ptr(), ws.data_ptr(), wsb, _stream(q))
     _check(rc, "fastmax_b200_forward")
@@ -197,16 +205,32 @@ def forward_packed(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0,
     return o, stats
 
 
+def workspace_bytes(q, k, **kw):
+    """(forward, backward, stats) scratch sizes in bytes for a problem of these shapes."""
+    L = lib()
+    prob = make_problem(q, k, kw["mask"], kw["normalize"], kw.get("temperature", 1.0), kw.get("a0", 1.0),
+                        kw.get("a1", 1.0), kw.get("a2", 0.5), kw.get("lim", 1.0), kw.get("p", 2),
+                        kw.get("impl", "auto"), kw.get("chunk", 0))
+    return (L.fastmax_b200_forward_workspace_bytes(prob), L.fastmax_b200_backward_workspace_bytes(prob),
+            max(L.fastmax_b200_stats_bytes(prob), 8))
+
+
 def backward(q, k, v, out, den, stats, grad_out, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0,
-             a2=0.5, lim=1.0, p=2, impl="auto", chunk=0):
-    """Gradients (grad_q, grad_k, grad_v) in the dtype of the inputs."""
+             a2=0.5, lim=1.0, p=2, impl="auto", chunk=0, buffers=None):
+    """Gradients (grad_q, grad_k, grad_v) in the dtype of the inputs; ``buffers`` as in ``forward``
+    with ``grad_q``, ``grad_k``, ``grad_v`` and ``workspace``."""
     _require(q, k, v, out, grad_out)
     L = lib()
     prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl, chunk)
     with torch.cuda.device(q.device):
-        gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         wsb = L.fastmax_b200_backward_workspace_bytes(prob)
-        ws = _workspace(wsb, q.device)
+        if buffers is None:
+            gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            ws = _workspace(wsb, q.device)
+        else:
+            gq, gk, gv, ws = buffers["grad_q"], buffers["grad_k"], buffers["grad_v"], buffers["workspace"]
+            if ws.numel() < wsb:
+                raise ValueError("preallocated backward workspace is too small")
         rc = L.fastmax_b200_backward(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                      den.data_ptr(), stats.data_ptr(), grad_out.data_ptr(),
                                      gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), ws.data_ptr(), wsb,

@@ -166,3 +166,21 @@ def test_errors_surface_as_python_exceptions():
         _cabi.forward(q.half(), q.half(), q.half(), mask=True, normalize=False, p=2)
     with pytest.raises(ValueError):
         _cabi.forward(q.transpose(0, 1), q, q, mask=True, normalize=False, p=2)
+
+
+def test_host_pipeline_matches_device_path():
+    """Pinned host tensors streamed through the GPU in head groups give the device-resident result."""
+    from fastmax_b200.host import HostPipeline
+    bh, n, d = 10, 500, 64
+    host = [randn(bh, n, d, seed=s).bfloat16().pin_memory() for s in (1, 2, 3, 4)]
+    outs = [torch.empty_like(h).pin_memory() for h in host]
+    kw = dict(mask=True, normalize=True, p=2)
+    pipe = HostPipeline(bh, n, d, torch.bfloat16, "cuda:0", heads_per_group=4, **kw)
+    pipe.run(*host, *outs)
+    pipe.run(*host, *outs)           # buffers are reused across calls
+    torch.cuda.synchronize()
+    q, k, v, go = [h.cuda() for h in host]
+    out, den, stats = _cabi.forward(q, k, v, **kw)
+    want = (out,) + tuple(_cabi.backward(q, k, v, out, den, stats, go, **kw))
+    for a, b in zip(outs, want):
+        assert torch.equal(a, b.cpu())
