@@ -190,7 +190,7 @@ def run_ours(args):
     else:
         bh = bh_total
         tokens_job = B * N * world
-    kw = dict(mask=bool(mask), normalize=bool(norm), p=p, **A)
+    kw = dict(mask=bool(mask), normalize=bool(norm), p=p, impl=args.family, chunk=args.chunk, **A)
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     q, k, v, go = [torch.randn(bh, N, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4)]
@@ -396,6 +396,9 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--family", default="auto", choices=["auto", "dense_ffma", "dense_tc", "moments_ffma"],
+                    help="kernel family to force (default: the library's own choice)")
+    ap.add_argument("--chunk", type=int, default=0, help="moment family: tokens per chunk (0 = default)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

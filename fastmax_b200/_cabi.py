@@ -70,7 +70,7 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_shard_rowmax.argtypes = [pp, vp, vp, i32, vp, vp]
         L.fastmax_b200_shard_kv_state.argtypes = [pp, vp, vp, vp, vp, vp]
         L.fastmax_b200_shard_forward.argtypes = [pp] + [vp] * 9 + [sz, vp]
-        L.fastmax_b200_shard_qg_state.argtypes = [pp] + [vp] * 8
+        L.fastmax_b200_shard_qg_state.argtypes = [pp] + [vp] * 8 + [sz, vp]
         L.fastmax_b200_shard_backward.argtypes = [pp] + [vp] * 16 + [sz, vp]
         L.fastmax_b200_shard_norm_fixup.argtypes = [pp, vp, vp, vp, vp, i32, vp, vp, vp]
         L.fastmax_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), vp]

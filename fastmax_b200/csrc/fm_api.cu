@@ -109,7 +109,8 @@ static int check_device() {
 static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   if (!moments_supports(p)) return false;
   const double d = p.d, F = d + (p.p == 2 ? d * d : 0.0);
-  const double rate_score = tc_ok ? 600e12 : 25e12, rate_state = 20e12;
+  const double rate_score = tc_ok ? 800e12 : 25e12;
+  const double rate_state = moments_tc_supports(p) ? 450e12 : 20e12;
   const double keys = p.mask ? 0.5 * p.nk : (double)p.nk;
   const double chunk_keys = p.mask ? 0.5 * moments_chunk(p) : 0.0;
   const double per_key = 14.0 * (d + 0.5);
@@ -179,7 +180,11 @@ unsigned long long fastmax_b200_launch_count(void) { return g_launches.load(); }
 
 int fastmax_b200_device_status(int* status, void* stream) {
   if (!status) return fail(FASTMAX_E_ARG, "status is NULL");
-  return tc_status(status, (cudaStream_t)stream);
+  int a = 0, b = 0, rc;
+  if ((rc = tc_status(&a, (cudaStream_t)stream))) return rc;
+  if ((rc = moments_tc_status(&b, (cudaStream_t)stream))) return rc;
+  *status = a ? a : b;
+  return FASTMAX_OK;
 }
 
 int fastmax_b200_profile_enable(int on) {
@@ -323,15 +328,21 @@ static int validate_shard(const fastmax_problem* prob) {
     return fail(FASTMAX_E_ARG, "a sequence shard needs mask = 1, nq == nk and bh == bhkv");
   return check_device();
 }
-struct ShardFwdWs { size_t o_add, den_add, bytes; };
+static size_t shard_s16_bytes(const fastmax_problem& p) {
+  if (!moments_tc_supports(p)) return 0;
+  const int L = moments_chunk(p);
+  return align_up(moments_tc_state_bytes(p.bh * ((p.nq + L - 1) / L)), 256);
+}
+struct ShardFwdWs { size_t o_add, den_add, s16, bytes; };
 static ShardFwdWs shard_fwd_layout(const fastmax_problem& p) {
   ShardFwdWs w;
   w.o_add = 0;
   w.den_add = align_up(sizeof(float) * (size_t)p.bh * p.nq * p.d, 256);
-  w.bytes = w.den_add + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
+  w.s16 = w.den_add + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
+  w.bytes = w.s16 + shard_s16_bytes(p);
   return w;
 }
-struct ShardBwdWs { size_t gq, gk, gv, dvec, gs, bytes; };
+struct ShardBwdWs { size_t gq, gk, gv, dvec, gs, s16, bytes; };
 static ShardBwdWs shard_bwd_layout(const fastmax_problem& p) {
   ShardBwdWs w;
   const size_t t = align_up(sizeof(float) * (size_t)p.bh * p.nq * p.d, 256);
@@ -340,7 +351,8 @@ static ShardBwdWs shard_bwd_layout(const fastmax_problem& p) {
   w.gv = 2 * t;
   w.dvec = 3 * t;
   w.gs = w.dvec + align_up(sizeof(float) * (size_t)p.bh * p.nq, 256);
-  w.bytes = w.gs + (dense_tc_supports(p) ? align_up((size_t)2 * p.bh * p.nq * p.d, 256) : 0);
+  w.s16 = w.gs + (dense_tc_supports(p) ? align_up((size_t)2 * p.bh * p.nq * p.d, 256) : 0);
+  w.bytes = w.s16 + shard_s16_bytes(p);
   return w;
 }
 
@@ -374,7 +386,7 @@ int fastmax_b200_shard_kv_state(const fastmax_problem* prob, const void* k, cons
   const fastmax_problem& p = *prob;
   Ctx c{p, (cudaStream_t)stream};
   const int L = moments_chunk(p);
-  if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, kv_states))) return rc;
+  if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, kv_states))) return rc;
   return moments_prefix(c, p.bh, (p.nk + L - 1) / L, kv_states, nullptr, kv_total, 0, 0);
 }
 
@@ -395,21 +407,30 @@ int fastmax_b200_shard_forward(const fastmax_problem* prob, const void* q, const
   FwdOut o{out, den, p.d, 1, 0};
   return moments_forward_finish(c, q, k, v, (const stat_t*)stats, kv_states, s_base,
                                 (float*)((char*)workspace + w.o_add),
-                                (float*)((char*)workspace + w.den_add), o);
+                                (float*)((char*)workspace + w.den_add), (char*)workspace + w.s16, o);
 }
 
 int fastmax_b200_shard_qg_state(const fastmax_problem* prob, const void* q, const void* out,
                                 const float* den, const void* grad_out, float* delta,
-                                float* qg_states, float* qg_total, void* stream) {
+                                float* qg_states, float* qg_total, void* workspace,
+                                size_t workspace_bytes, void* stream) {
   int rc = validate_shard(prob);
   if (rc) return rc;
   const fastmax_problem& p = *prob;
   if (!q || !out || !den || !grad_out || !delta || !qg_states || !qg_total)
     return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  const ShardBwdWs w = shard_bwd_layout(p);
+  if (!workspace || workspace_bytes < w.bytes)
+    return fail(FASTMAX_E_WORKSPACE, "shard backward workspace too small: need %zu bytes, got %zu", w.bytes,
+                workspace_bytes);
   Ctx c{p, (cudaStream_t)stream};
   const int L = moments_chunk(p);
+  char* ws = (char*)workspace;
+  float* dvec = (float*)(ws + w.dvec);
+  void* gs = ws + w.gs;
   if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
-  if ((rc = moments_chunk_state(c, p.bh, p.nq, L, q, grad_out, den, delta, 1, qg_states))) return rc;
+  if (dense_tc_supports(p) && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
+  if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, qg_states))) return rc;
   return moments_prefix(c, p.bh, (p.nq + L - 1) / L, qg_states, nullptr, qg_total, 1, 0);
 }
 
@@ -438,7 +459,8 @@ int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, cons
   if (dense_tc_supports(p) && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
   return moments_backward_finish(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dvec, gs,
                                  kv_states, qg_states, r_base, (float*)(ws + w.gq), (float*)(ws + w.gk),
-                                 (float*)(ws + w.gv), p.normalize ? dots : nullptr, grad_q, grad_k, grad_v);
+                                 (float*)(ws + w.gv), ws + w.s16, p.normalize ? dots : nullptr, grad_q, grad_k,
+                                 grad_v);
 }
 
 int fastmax_b200_shard_norm_fixup(const fastmax_problem* prob, const void* q, const void* k,

@@ -139,16 +139,29 @@ MomentDims moment_dims(int d);
 // state[h][c][f][col] = sum over the tokens of chunk c of feature_f(y) * [z | e];  ext 0: e = 1,
 // ext 1: z and e scaled: [z/den | -delta/den].
 int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
-                        const float* den, const float* delta, int ext, float* state);
+                        const float* den, const float* delta, int ext, float* state,
+                        int first_order_only = 0);
 // exclusive running sum over chunks (reverse = suffix), started from base; total = own sum
 int moments_prefix(const Ctx& c, int heads, int nchunk, float* state, const float* base, float* total,
                    int reverse, int write);
 int moments_readout(const Ctx& c, int mode_b, int heads, int n, int chunk, int state_per_chunk,
                     const void* x, const void* u, const float* den, const float* delta, int ext,
-                    const float* state, const stat_t* stats, float* o_add, float* den_add);
+                    const float* state, const stat_t* stats, float* o_add, float* den_add,
+                    int first_order_only = 0);
+
+// second-order part on tensor cores (fm_moments_tc.cu): bf16, d == 64, p == 2
+bool moments_tc_supports(const fastmax_problem& p);
+size_t moments_tc_state_bytes(int mats);
+int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
+                           const float* dvec, float* state);
+int moments_tc_convert(const Ctx& c, int mats, const float* state, void* state_bf16);
+int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int state_per_chunk,
+                       const void* x, const void* u, const float* uvec, const void* state_bf16,
+                       const stat_t* stats, float* out_a, float* den_a, float* out_b);
+int moments_tc_status(int* out, cudaStream_t stream);
 // host orchestration of the moment family (fm_moments.cu)
-struct MomFwdWs { size_t states, total, o_add, den_add, bytes; };
-struct MomBwdWs { size_t dots, delta, dvec, gs, states, total, gq_add, gk_add, gv_add, bytes; };
+struct MomFwdWs { size_t states, total, o_add, den_add, s16, bytes; };
+struct MomBwdWs { size_t dots, delta, dvec, gs, states, total, gq_add, gk_add, gv_add, s16, bytes; };
 int moments_chunk(const fastmax_problem& p);
 bool moments_supports(const fastmax_problem& p);
 size_t moment_state_bytes(const fastmax_problem& p, int n);
@@ -159,7 +172,11 @@ int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, c
                     const FwdOut& o, void* workspace);
 int moments_forward_finish(const Ctx& c, const void* q, const void* k, const void* v,
                            const stat_t* stats, float* kv_states, const float* s_base,
-                           float* o_add, float* den_add, const FwdOut& o);
+                           float* o_add, float* den_add, void* s16, const FwdOut& o);
+// chunk states of (y, z | e) with the best kernels for the problem; gs/dvec are the bf16
+// gradient rows and grad_out.out/den when ext == 1 and the tensor-core path is used
+int moments_build_states(const Ctx& c, int n, const void* y, const void* z, const float* den,
+                         const float* delta, int ext, const void* gs, const float* dvec, float* states);
 int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* out,
                      const float* den, const stat_t* stats, const void* grad_out, void* grad_q,
                      void* grad_k, void* grad_v, void* workspace);
@@ -167,8 +184,8 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
                             const float* den, const stat_t* stats, const void* grad_out,
                             const float* delta, const float* dvec, const void* gs,
                             const float* s_states, float* r_states, const float* r_base,
-                            float* gq_add, float* gk_add, float* gv_add, float* dots, void* grad_q,
-                            void* grad_k, void* grad_v);
+                            float* gq_add, float* gk_add, float* gv_add, void* s16, float* dots,
+                            void* grad_q, void* grad_k, void* grad_v);
 int moments_finalize(const Ctx& c, int heads, int n, const float* r, const float* den_in, const void* x,
                      void* out, float* den_out, float* dots, int mode);
 

@@ -10,7 +10,7 @@ namespace fm {
 static size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 
 int moments_chunk(const fastmax_problem& p) {
-  int L = p.chunk > 0 ? p.chunk : 2048;
+  int L = p.chunk > 0 ? p.chunk : (moments_tc_supports(p) ? 1024 : 2048);
   L = (L + 255) / 256 * 256;
   return L;
 }
@@ -25,6 +25,13 @@ size_t moment_total_bytes(const fastmax_problem& p) {
   return up256(sizeof(float) * (size_t)p.bh * m.f * m.dvp);
 }
 
+// bf16 transposed copy of the second-order block of every chunk state (tensor-core read-out)
+static size_t state16_bytes(const fastmax_problem& p, int n) {
+  if (!moments_tc_supports(p)) return 0;
+  const int L = moments_chunk(p);
+  return up256(moments_tc_state_bytes(p.bh * ((n + L - 1) / L)));
+}
+
 bool moments_supports(const fastmax_problem& p) {
   return p.bh == p.bhkv && (!p.mask || p.nq == p.nk);
 }
@@ -36,7 +43,8 @@ MomFwdWs moments_fwd_layout(const fastmax_problem& p) {
   w.total = w.states + moment_state_bytes(p, p.nk);
   w.o_add = w.total + moment_total_bytes(p);
   w.den_add = w.o_add + up256(sizeof(float) * (size_t)p.bh * p.nq * p.d);
-  w.bytes = w.den_add + up256(sizeof(float) * (size_t)p.bh * p.nq);
+  w.s16 = w.den_add + up256(sizeof(float) * (size_t)p.bh * p.nq);
+  w.bytes = w.s16 + state16_bytes(p, p.nk);
   return w;
 }
 // Workspace of the one-call backward:
@@ -52,8 +60,47 @@ MomBwdWs moments_bwd_layout(const fastmax_problem& p) {
   w.gq_add = w.total + moment_total_bytes(p);
   w.gk_add = w.gq_add + up256(sizeof(float) * (size_t)p.bh * p.nq * p.d);
   w.gv_add = w.gk_add + up256(sizeof(float) * (size_t)p.bhkv * p.nk * p.d);
-  w.bytes = w.gv_add + up256(sizeof(float) * (size_t)p.bhkv * p.nk * p.d);
+  w.s16 = w.gv_add + up256(sizeof(float) * (size_t)p.bhkv * p.nk * p.d);
+  w.bytes = w.s16 + state16_bytes(p, p.nk > p.nq ? p.nk : p.nq);
   return w;
+}
+
+int moments_build_states(const Ctx& c, int n, const void* y, const void* z, const float* den,
+                         const float* delta, int ext, const void* gs, const float* dvec, float* states) {
+  const fastmax_problem& p = c.p;
+  const int L = moments_chunk(p);
+  if (!moments_tc_supports(p)) return moments_chunk_state(c, p.bh, n, L, y, z, den, delta, ext, states);
+  int rc;
+  // second-order rows on the tensor cores, first-order and constant rows on the CUDA cores
+  if ((rc = moments_tc_chunk_state(c, p.bh, n, L, y, ext ? gs : z, ext ? dvec : nullptr, states))) return rc;
+  return moments_chunk_state(c, p.bh, n, L, y, z, den, delta, ext, states, 1);
+}
+
+// read-out of prefix (or total) states for n tokens; mode 0: type A, 1: type B, 2: both on x
+static int read_states(const Ctx& c, int mode, int n, int per_chunk, const void* x, const void* u,
+                       const float* den, const float* delta, int ext, const void* gs, const float* dvec,
+                       const float* states, void* s16, const stat_t* stats, float* out_a, float* den_a,
+                       float* out_b) {
+  const fastmax_problem& p = c.p;
+  const int L = moments_chunk(p);
+  int rc;
+  const bool tc = moments_tc_supports(p);
+  if (tc) {
+    const int mats = p.bh * (per_chunk ? (n + L - 1) / L : 1);
+    if ((rc = moments_tc_convert(c, mats, states, s16))) return rc;
+    if ((rc = moments_tc_readout(c, mode, p.bh, n, L, per_chunk, x, ext ? gs : u, ext ? dvec : nullptr, s16,
+                                 stats, out_a, den_a, out_b)))
+      return rc;
+  }
+  if (mode == 0 || mode == 2)
+    if ((rc = moments_readout(c, 0, p.bh, n, L, per_chunk, x, nullptr, nullptr, nullptr, 0, states, stats,
+                              out_a, den_a, tc)))
+      return rc;
+  if (mode == 1 || mode == 2)
+    if ((rc = moments_readout(c, 1, p.bh, n, L, per_chunk, x, u, den, delta, ext, states, stats, out_b,
+                              nullptr, tc)))
+      return rc;
+  return FASTMAX_OK;
 }
 
 // ---- forward -----------------------------------------------------------------------
@@ -61,14 +108,14 @@ MomBwdWs moments_bwd_layout(const fastmax_problem& p) {
 // totals of all earlier shards or null.  Turns the states into prefixes in place.
 int moments_forward_finish(const Ctx& c, const void* q, const void* k, const void* v,
                            const stat_t* stats, float* kv_states, const float* s_base,
-                           float* o_add, float* den_add, const FwdOut& o) {
+                           float* o_add, float* den_add, void* s16, const FwdOut& o) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   const int nchunk = (p.nk + L - 1) / L;
   int rc;
   if ((rc = moments_prefix(c, p.bh, nchunk, kv_states, s_base, nullptr, 0, 1))) return rc;
-  if ((rc = moments_readout(c, 0, p.bh, p.nq, L, 1, q, nullptr, nullptr, nullptr, 0, kv_states, stats,
-                            o_add, den_add)))
+  if ((rc = read_states(c, 0, p.nq, 1, q, nullptr, nullptr, nullptr, 0, nullptr, nullptr, kv_states, s16,
+                        stats, o_add, den_add, nullptr)))
     return rc;
   ChunkAdd ca;
   ca.chunk = L;
@@ -89,13 +136,14 @@ int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, c
   float* o_add = (float*)(ws + w.o_add);
   float* den_add = (float*)(ws + w.den_add);
   int rc;
-  if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, states))) return rc;
-  if (p.mask) return moments_forward_finish(c, q, k, v, stats, states, nullptr, o_add, den_add, o);
+  void* s16 = ws + w.s16;
+  if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
+  if (p.mask) return moments_forward_finish(c, q, k, v, stats, states, nullptr, o_add, den_add, s16, o);
   // unmasked: every query reads the total of all keys
   const int nchunk = (p.nk + L - 1) / L;
   if ((rc = moments_prefix(c, p.bh, nchunk, states, nullptr, total, 0, 0))) return rc;
-  if ((rc = moments_readout(c, 0, p.bh, p.nq, L, 0, q, nullptr, nullptr, nullptr, 0, total, stats, o_add,
-                            den_add)))
+  if ((rc = read_states(c, 0, p.nq, 0, q, nullptr, nullptr, nullptr, 0, nullptr, nullptr, total, s16, stats,
+                        o_add, den_add, nullptr)))
     return rc;
   if (o.out_f32 || o.o_stride != p.d)
     return fail(FASTMAX_E_UNSUPPORTED, "the moment family writes the plain output layout only");
@@ -110,23 +158,20 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
                             const float* den, const stat_t* stats, const void* grad_out,
                             const float* delta, const float* dvec, const void* gs,
                             const float* s_states, float* r_states, const float* r_base,
-                            float* gq_add, float* gk_add, float* gv_add, float* dots, void* grad_q,
-                            void* grad_k, void* grad_v) {
+                            float* gq_add, float* gk_add, float* gv_add, void* s16, float* dots,
+                            void* grad_q, void* grad_k, void* grad_v) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   const int nchunk = (p.nq + L - 1) / L;
   int rc;
   // grad_q reads the key/value prefixes with u = [grad_out/den | -delta/den]
-  if ((rc = moments_readout(c, 1, p.bh, p.nq, L, 1, q, grad_out, den, delta, 1, s_states, stats, gq_add,
-                            nullptr)))
+  if ((rc = read_states(c, 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec, s_states, s16, stats, nullptr,
+                        nullptr, gq_add)))
     return rc;
   // grad_k and grad_v read the suffix sums of the query/gradient states
   if ((rc = moments_prefix(c, p.bh, nchunk, r_states, r_base, nullptr, 1, 1))) return rc;
-  if ((rc = moments_readout(c, 1, p.bh, p.nk, L, 1, k, v, nullptr, nullptr, 0, r_states, stats, gk_add,
-                            nullptr)))
-    return rc;
-  if ((rc = moments_readout(c, 0, p.bh, p.nk, L, 1, k, nullptr, nullptr, nullptr, 0, r_states, stats,
-                            gv_add, nullptr)))
+  if ((rc = read_states(c, 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr, r_states, s16, stats,
+                        gv_add, nullptr, gk_add)))
     return rc;
   ChunkAdd ca;
   ca.chunk = L;
@@ -154,28 +199,26 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
   float* gq_add = (float*)(ws + w.gq_add);
   float* gk_add = (float*)(ws + w.gk_add);
   float* gv_add = (float*)(ws + w.gv_add);
+  void* s16 = ws + w.s16;
   int rc;
   if (p.normalize)
     FM_CUDA_TRY(cudaMemsetAsync(dots, 0, sizeof(float) * (size_t)(p.bh + p.bhkv), c.stream));
   if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
   const bool tc = dense_tc_supports(p);
-  if (tc && p.mask && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
+  if (tc && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
   const int nck = (p.nk + L - 1) / L, ncq = (p.nq + L - 1) / L;
   if (p.mask) {
     // the key/value prefixes are rebuilt (the forward does not keep them), used for grad_q,
     // then the buffer is reused for the query/gradient states
-    if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, states))) return rc;
+    if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, nullptr, 0, 1))) return rc;
-    if ((rc = moments_readout(c, 1, p.bh, p.nq, L, 1, q, grad_out, den, delta, 1, states, stats, gq_add,
-                              nullptr)))
+    if ((rc = read_states(c, 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec, states, s16, stats, nullptr,
+                          nullptr, gq_add)))
       return rc;
-    if ((rc = moments_chunk_state(c, p.bh, p.nq, L, q, grad_out, den, delta, 1, states))) return rc;
+    if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, nullptr, 1, 1))) return rc;
-    if ((rc = moments_readout(c, 1, p.bh, p.nk, L, 1, k, v, nullptr, nullptr, 0, states, stats, gk_add,
-                              nullptr)))
-      return rc;
-    if ((rc = moments_readout(c, 0, p.bh, p.nk, L, 1, k, nullptr, nullptr, nullptr, 0, states, stats,
-                              gv_add, nullptr)))
+    if ((rc = read_states(c, 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr, states, s16, stats,
+                          gv_add, nullptr, gk_add)))
       return rc;
     ChunkAdd ca;
     ca.chunk = L;
@@ -187,21 +230,18 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
     if (rc) return rc;
   } else {
     // unmasked: totals only, no score-form part
-    if ((rc = moments_chunk_state(c, p.bh, p.nk, L, k, v, nullptr, nullptr, 0, states))) return rc;
+    if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, total, 0, 0))) return rc;
-    if ((rc = moments_readout(c, 1, p.bh, p.nq, L, 0, q, grad_out, den, delta, 1, total, stats, gq_add,
-                              nullptr)))
+    if ((rc = read_states(c, 1, p.nq, 0, q, grad_out, den, delta, 1, gs, dvec, total, s16, stats, nullptr,
+                          nullptr, gq_add)))
       return rc;
     if ((rc = moments_finalize(c, p.bh, p.nq, gq_add, nullptr, q, grad_q, nullptr,
                                p.normalize ? dots : nullptr, 1)))
       return rc;
-    if ((rc = moments_chunk_state(c, p.bh, p.nq, L, q, grad_out, den, delta, 1, states))) return rc;
+    if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, total, 0, 0))) return rc;
-    if ((rc = moments_readout(c, 1, p.bh, p.nk, L, 0, k, v, nullptr, nullptr, 0, total, stats, gk_add,
-                              nullptr)))
-      return rc;
-    if ((rc = moments_readout(c, 0, p.bh, p.nk, L, 0, k, nullptr, nullptr, nullptr, 0, total, stats,
-                              gv_add, nullptr)))
+    if ((rc = read_states(c, 2, p.nk, 0, k, v, nullptr, nullptr, 0, nullptr, nullptr, total, s16, stats,
+                          gv_add, nullptr, gk_add)))
       return rc;
     if ((rc = moments_finalize(c, p.bh, p.nk, gk_add, nullptr, k, grad_k, nullptr,
                                p.normalize ? dots + p.bh : nullptr, 1)))

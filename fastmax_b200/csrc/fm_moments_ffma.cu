@@ -168,6 +168,7 @@ struct ReadArgs {
   const stat_t* stat_q;
   const stat_t* stat_k;
   int n, chunk, nchunk, ext, f_begin;
+  int accumulate;       // add to o_add / den_add instead of overwriting them
   float a0, a1, a2, lim;
 };
 
@@ -226,8 +227,8 @@ __global__ void __launch_bounds__(256) readout_a_kernel(const ReadArgs a) {
 #pragma unroll
     for (int cc = 0; cc < M::CW; ++cc) {
       const int col = cg * M::CW + cc;
-      if (col < D) a.o_add[row * D + col] = acc[k][cc];
-      else if (col == D && a.den_add) a.den_add[row] = acc[k][cc];
+      if (col < D) a.o_add[row * D + col] = acc[k][cc] + (a.accumulate ? a.o_add[row * D + col] : 0.f);
+      else if (col == D && a.den_add) a.den_add[row] = acc[k][cc] + (a.accumulate ? a.den_add[row] : 0.f);
     }
   }
 }
@@ -288,7 +289,8 @@ __global__ void __launch_bounds__(256) readout_b_kernel(const ReadArgs a) {
     if (tok >= a.n) continue;
     const size_t row = (size_t)head * a.n + tok;
 #pragma unroll
-    for (int m = 0; m < AW; ++m) a.o_add[row * D + m * 4 + ag] = acc[k][m];
+    for (int m = 0; m < AW; ++m)
+      a.o_add[row * D + m * 4 + ag] = acc[k][m] + (a.accumulate ? a.o_add[row * D + m * 4 + ag] : 0.f);
   }
 }
 
@@ -356,12 +358,12 @@ MomentDims moment_dims(int d) {
   }
 
 int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
-                        const float* den, const float* delta, int ext, float* state) {
+                        const float* den, const float* delta, int ext, float* state, int first_order_only) {
   if (heads == 0 || n == 0) return FASTMAX_OK;
   StateArgs a;
   a.y = y; a.z = z; a.den = den; a.delta = delta; a.state = state;
   a.n = n; a.chunk = chunk; a.nchunk = (n + chunk - 1) / chunk; a.ext = ext;
-  a.f_begin = (c.p.p == 1) ? c.p.d * c.p.d : 0;
+  a.f_begin = (c.p.p == 1 || first_order_only) ? c.p.d * c.p.d : 0;
   const bool f32 = c.p.dtype == FASTMAX_F32;
   FM_DISPATCH_D(c.p.d, {
     using M = MC<DD>;
@@ -388,7 +390,8 @@ int moments_prefix(const Ctx& c, int heads, int nchunk, float* state, const floa
 
 int moments_readout(const Ctx& c, int mode_b, int heads, int n, int chunk, int state_per_chunk,
                     const void* x, const void* u, const float* den, const float* delta, int ext,
-                    const float* state, const stat_t* stats, float* o_add, float* den_add) {
+                    const float* state, const stat_t* stats, float* o_add, float* den_add,
+                    int first_order_only) {
   if (heads == 0 || n == 0) return FASTMAX_OK;
   const fastmax_problem& p = c.p;
   ReadArgs a;
@@ -397,7 +400,8 @@ int moments_readout(const Ctx& c, int mode_b, int heads, int n, int chunk, int s
   a.stat_q = p.normalize ? stats : nullptr;
   a.stat_k = p.normalize ? stats + p.bh : nullptr;
   a.n = n; a.chunk = chunk; a.nchunk = (n + chunk - 1) / chunk; a.ext = ext;
-  a.f_begin = (p.p == 1) ? p.d * p.d : 0;
+  a.f_begin = (p.p == 1 || first_order_only) ? p.d * p.d : 0;
+  a.accumulate = first_order_only;   // the second-order part was written by the tensor-core read-out
   a.a0 = p.a0; a.a1 = p.a1; a.a2 = (p.p == 2) ? p.a2 : 0.f; a.lim = p.lim;
   const bool f32 = p.dtype == FASTMAX_F32;
   FM_DISPATCH_D(p.d, {

@@ -1,0 +1,610 @@
+// Second-order part of the moment-state form on the tcgen05 tensor cores (bf16
+// operands, fp32 accumulation), head dimension 64.  Two kernels:
+//
+// readout  -- for a tile of 128 tokens x and a prefix state S2[a][b][c] (symmetric in
+//   a, b; c = 0..63 value columns, c = 64 the normaliser column):
+//       T[i][c][b] = sum_a x_i[a] S2[a][b][c]                   tensor cores
+//       type A:  r_i[c] = A2   sum_b x_i[b] T[i][c][b]          (numerator | denominator, grad_v)
+//       type B:  r_i[b] = 2 A2 sum_c ut_i[c] T[i][c][b]         (grad_q, grad_k)
+//   The state is read as bf16 rows (c*64 + b) of 64 a-values -- a K-major B operand
+//   streamed by TMA -- and T never leaves the SM: each 128-column slice of it is
+//   produced in tensor memory and contracted by the CUDA cores straight from there.
+//   This replaces the d*d-wide feature contraction of the reference
+//   (`old stuff/fastmax_cuda_forward_quad.cu`:111-135, 240-268 and the matching
+//   backward loops) by a GEMM of the raw token tile against the state.
+//
+// state    -- T2[(a,b)][c] = sum_j y_j[a] y_j[b] z_j[c] over the tokens of a chunk: the
+//   features y_a y_b are generated on the CUDA cores into shared memory as the
+//   MN-major A operand, the value tile is the MN-major B operand delivered by TMA,
+//   and the accumulators stay in tensor memory for the whole chunk.
+//
+// The first-order and constant rows of the state and the normaliser column of the
+// state build stay on the CUDA-core kernels of fm_moments_ffma.cu.
+#include <cstdlib>
+
+#include "fm_common.cuh"
+#include "fm_sm100.cuh"
+
+namespace fm {
+
+__device__ int g_mtc_status = 0;  // first protocol error seen by a kernel of this file
+
+namespace {
+using namespace sm100;
+
+constexpr int D = 64;
+constexpr int NROWS_T = 65 * 64;          // rows (c, b) of the transposed bf16 state
+constexpr int NROWS_TP = 33 * 128;        // padded to whole 128-row tiles
+
+__device__ __forceinline__ void report(int code) { atomicCAS(&g_mtc_status, 0, code); }
+
+// =====================================================================================
+// readout
+// =====================================================================================
+struct RtArgs {
+  const void* x;       // (heads, n, 64) bf16 tokens
+  const void* u;       // type B: (heads, n, 64) bf16 second operand (gs or v)
+  const float* uvec;   // type B: (heads, n) dvec, whose negative is the 65th entry of ut; null = 1
+  float* out_a;        // type A result (heads, n, 64) fp32
+  float* den_a;        // type A normaliser column (heads, n), may be null
+  float* out_b;        // type B result (heads, n, 64) fp32
+  const stat_t* stat_q;
+  const stat_t* stat_k;
+  float a2, lim;
+  int n, chunk, nchunk, state_per_chunk;
+  int mode;            // 0: type A on two token tiles, 1: type B on two token tiles,
+                       // 2: one token tile, group 0 type A and group 1 type B
+};
+
+constexpr int RT_THREADS = 320;   // warps 0-3 group 0, 4-7 group 1, 8 TMA producer, 9 MMA issuer
+constexpr int RT_NS = 4;          // state-tile ring stages
+constexpr int RT_TILE = 128 * D * 2;
+constexpr int RT_OFF_X = 0;                         // two token tiles
+constexpr int RT_OFF_ST = 2 * RT_TILE;              // ring
+constexpr int RT_OFF_UT = RT_OFF_ST + RT_NS * RT_TILE;   // [2][128][66] fp32 (type B operand rows)
+constexpr int RT_UT_LD = 66;
+constexpr int RT_OFF_BAR = RT_OFF_UT + 2 * 128 * RT_UT_LD * 4;
+constexpr int RT_NBAR = 1 + 2 * RT_NS + 8;
+constexpr int RT_OFF_TMEM = RT_OFF_BAR + RT_NBAR * 8;
+constexpr int RT_SMEM = RT_OFF_TMEM + 16 + 1024;
+constexpr int RT_NT = NROWS_TP / 128;               // 33 slices of 128 columns of T
+
+__global__ void __launch_bounds__(RT_THREADS, 1)
+readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmS,
+                  const RtArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + RT_OFF_BAR;
+  // barriers: x | st_full[NS] | st_empty[NS] | t_full[tile][buf] (4) | t_free[tile][buf] (4)
+  auto BAR_X = [&]() { return bar0; };
+  auto BAR_FULL = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto BAR_EMPTY = [&](int s) { return bar0 + 8u * (1 + RT_NS + s); };
+  auto BAR_TFULL = [&](int t, int b) { return bar0 + 8u * (1 + 2 * RT_NS + t * 2 + b); };
+  auto BAR_TFREE = [&](int t, int b) { return bar0 + 8u * (5 + 2 * RT_NS + t * 2 + b); };
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + RT_OFF_TMEM);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_per_cta = (a.mode == 2) ? 1 : 2;
+  const int ctas_per_head = (a.n + 128 * tiles_per_cta - 1) / (128 * tiles_per_cta);
+  const int head = blockIdx.x / ctas_per_head;
+  const int tok0 = (blockIdx.x % ctas_per_head) * 128 * tiles_per_cta;
+  const int ntile = (tiles_per_cta == 2 && tok0 + 128 < a.n) ? 2 : 1;   // token tiles that have rows
+  const int chunk = a.state_per_chunk ? tok0 / a.chunk : 0;
+  const int srow = head * (a.state_per_chunk ? a.nchunk : 1) + chunk;   // index of the state matrix
+  const int readers = (a.mode == 2) ? 8 : 4;                            // warps that read each T buffer
+
+  if (tid == 0) {
+    mbar_init(BAR_X(), 1);
+    for (int s = 0; s < RT_NS; ++s) { mbar_init(BAR_FULL(s), 1); mbar_init(BAR_EMPTY(s), 1); }
+    for (int t = 0; t < 2; ++t)
+      for (int b = 0; b < 2; ++b) { mbar_init(BAR_TFULL(t, b), 1); mbar_init(BAR_TFREE(t, b), readers); }
+    mbar_fence_init();
+  }
+  if (warp == 9) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    // ---------------- TMA producer: token tiles once, then the 33 state tiles ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmS);
+      mbar_expect_tx(BAR_X(), ntile * RT_TILE);
+      for (int t = 0; t < ntile; ++t) tma_load_3d(sbase + RT_OFF_X + t * RT_TILE, &tmX, BAR_X(), 0, tok0 + t * 128, head);
+    }
+    for (int n = 0; n < RT_NT; ++n) {
+      const int s = n % RT_NS;
+      if (!mbar_wait(BAR_EMPTY(s), (((n / RT_NS) & 1) ^ 1))) { report(21); break; }
+      if (lane == 0) {
+        mbar_expect_tx(BAR_FULL(s), RT_TILE);
+        tma_load_3d(sbase + RT_OFF_ST + s * RT_TILE, &tmS, BAR_FULL(s), 0, n * 128, srow);
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(128, 128, 0, 0);
+      bool ok = mbar_wait(BAR_X(), 0);
+      if (!ok) report(22);
+      tc_fence_after();
+      const uint32_t st0 = desc_lo(sbase + RT_OFF_ST, 16);
+      for (int n = 0; ok && n < RT_NT; ++n) {
+        const int s = n % RT_NS, buf = n & 1;
+        if (!mbar_wait(BAR_FULL(s), (uint32_t)((n / RT_NS) & 1))) { report(23); ok = false; break; }
+        for (int t = 0; t < ntile; ++t) {
+          // the buffer was last used by slice n-2
+          if (n >= 2 && !mbar_wait(BAR_TFREE(t, buf), (uint32_t)(((n >> 1) - 1) & 1))) { report(24); ok = false; break; }
+          tc_fence_after();
+          umma_ss_k64(tmem + t * 256 + buf * 128, desc_lo(sbase + RT_OFF_X + t * RT_TILE, 16),
+                      st0 + (uint32_t)s * (RT_TILE >> 4), idesc);
+          umma_commit(BAR_TFULL(t, buf));
+        }
+        if (ok) umma_commit(BAR_EMPTY(s));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- contraction groups ----------------
+    const int g = warp >> 2, qd = warp & 3;
+    const int t = (a.mode == 2) ? 0 : g;                 // token tile this group reads
+    const bool type_b = (a.mode == 1) || (a.mode == 2 && g == 1);
+    if (t < ntile) {
+      const int tok = tok0 + t * 128 + qd * 32 + lane;
+      const bool tok_ok = tok < a.n;
+      const size_t grow = (size_t)head * a.n + (tok_ok ? tok : 0);
+      const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
+      const float A2 = a.a2 * c * c;
+      const uint32_t tbase = tmem + t * 256 + ((uint32_t)(qd * 32) << 16);
+      // this thread's token row, as 32 packed fp32 pairs
+      uint64_t x2[32];
+      {
+        const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * D);
+#pragma unroll
+        for (int v8 = 0; v8 < 8; ++v8) {
+          uint4 w = tok_ok ? __ldg(xr + v8) : make_uint4(0, 0, 0, 0);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            x2[v8 * 4 + e] = pack2(__uint_as_float(ww[e] << 16), __uint_as_float(ww[e] & 0xFFFF0000u));
+        }
+      }
+      float* ut = (float*)(smem + RT_OFF_UT) + ((size_t)g * 128 + qd * 32 + lane) * RT_UT_LD;
+      uint64_t acc2[32];
+      if (type_b) {
+        // ut row = [u_0 .. u_63 | e]; only this thread reads it back
+        const uint4* ur = (const uint4*)((const __nv_bfloat16*)a.u + grow * D);
+#pragma unroll
+        for (int v8 = 0; v8 < 8; ++v8) {
+          uint4 w = tok_ok ? __ldg(ur + v8) : make_uint4(0, 0, 0, 0);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            ut[v8 * 8 + 2 * e] = __uint_as_float(ww[e] << 16);
+            ut[v8 * 8 + 2 * e + 1] = __uint_as_float(ww[e] & 0xFFFF0000u);
+          }
+        }
+        ut[64] = tok_ok ? (a.uvec ? -a.uvec[grow] : 1.0f) : 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc2[e] = pack2(0.f, 0.f);
+      }
+      bool ok = true;
+      for (int n = 0; n < RT_NT; ++n) {
+        const int buf = n & 1;
+        if (!mbar_wait(BAR_TFULL(t, buf), (uint32_t)((n >> 1) & 1))) { report(25); ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int cidx = 2 * n + hf;       // column c of the state this half belongs to
+          uint32_t tv[64];
+          tmem_ld64(tbase + buf * 128 + hf * 64, tv);
+          tmem_wait_ld();
+          if (hf == 1) {                      // both halves are in registers or consumed: release
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_TFREE(t, buf));
+          }
+          if (cidx > 64) continue;            // padding rows of the last slice
+          if (!type_b) {
+            uint64_t s2 = pack2(0.f, 0.f), s3 = s2;
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              s2 = fma2(x2[e], pack2u(tv[2 * e], tv[2 * e + 1]), s2);
+              s3 = fma2(x2[e + 1], pack2u(tv[2 * e + 2], tv[2 * e + 3]), s3);
+            }
+            float lo, hi;
+            unpack2(add2(s2, s3), lo, hi);
+            const float r = A2 * (lo + hi);
+            if (tok_ok) {
+              if (cidx < 64) a.out_a[grow * D + cidx] = r;
+              else if (a.den_a) a.den_a[grow] = r;
+            }
+          } else {
+            const float uc = ut[cidx];
+            const uint64_t u2 = pack2(uc, uc);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) acc2[e] = fma2(u2, pack2u(tv[2 * e], tv[2 * e + 1]), acc2[e]);
+          }
+        }
+      }
+      if (ok && type_b && tok_ok) {
+        const float k2 = 2.f * A2;
+        float4* dst = (float4*)(a.out_b + grow * D);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float f0, f1, f2, f3;
+          unpack2(acc2[2 * e], f0, f1);
+          unpack2(acc2[2 * e + 1], f2, f3);
+          dst[e] = make_float4(k2 * f0, k2 * f1, k2 * f2, k2 * f3);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =====================================================================================
+// bf16 transposed copy of the second-order block of fp32 prefix states:
+//   out[m][c*64 + b][a] = state[m][(b*64 + a)][c]      (S2 is symmetric in a, b)
+// one CTA per (state matrix m, b); rows past 65*64 are zero.
+// =====================================================================================
+__global__ void __launch_bounds__(256) state_to_bf16t_kernel(const float* __restrict__ state,
+                                                             __nv_bfloat16* __restrict__ out, int dvp,
+                                                             size_t per_state) {
+  __shared__ float blk[64][69];
+  const int m = blockIdx.y, b = blockIdx.x;
+  if (b == 64) {  // zero the padding rows
+    __nv_bfloat16* o = out + ((size_t)m * NROWS_TP + NROWS_T) * 64;
+    for (int i = threadIdx.x; i < (NROWS_TP - NROWS_T) * 64; i += 256) o[i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const float* src = state + (size_t)m * per_state + (size_t)b * 64 * dvp;   // rows (b, a = 0..63)
+  for (int i = threadIdx.x; i < 64 * dvp; i += 256) blk[i / dvp][i % dvp] = src[i];
+  __syncthreads();
+  __nv_bfloat16* o = out + (size_t)m * NROWS_TP * 64;
+  for (int i = threadIdx.x; i < 65 * 64; i += 256) {
+    const int c = i / 64, aa = i % 64;
+    o[((size_t)c * 64 + b) * 64 + aa] = __float2bfloat16_rn(blk[aa][c]);
+  }
+}
+
+// =====================================================================================
+// state build: T2[(a,b)][c] = sum_j y_j[a] y_j[b] z_j[c],  c < 64
+// One CTA owns 16 values of a (8 accumulator tiles of 2 a x 64 b rows, 64 columns each =
+// all 512 TMEM columns) for one chunk of one head and walks the chunk in blocks of 128
+// tokens.  Two groups of 128 threads (one token each) write the feature tiles
+// A[m][(a,b)][token] = y[a] y[b] as bf16 into a ring of shared-memory buffers in the
+// 128-byte-swizzled MN-major layout; one thread issues, per tile, 8 K=16 MMAs against the
+// value tile that TMA delivered (MN-major B).
+// =====================================================================================
+struct StArgs {
+  const void* y;     // (heads, n, 64) bf16 feature source
+  float* state;      // (heads, nchunk, F, DVP) fp32; rows a*64+b, columns 0..63 are written
+  int n, chunk, nchunk, dvp;
+  size_t per_state;
+};
+
+constexpr int ST_THREADS = 320;       // warps 0-3, 4-7: generator groups; 8: TMA; 9: MMA issuer
+constexpr int ST_NA = 4;              // feature-tile ring
+constexpr int ST_NZ = 2;              // value-tile ring
+constexpr int ST_ATILE = 2 * 128 * 128;   // two 64-feature blocks of 128 tokens x 128 bytes
+constexpr int ST_ZTILE = 128 * 128;
+constexpr int ST_OFF_A = 0;
+constexpr int ST_OFF_Z = ST_NA * ST_ATILE;
+constexpr int ST_OFF_BAR = ST_OFF_Z + ST_NZ * ST_ZTILE;
+constexpr int ST_NBAR = 2 * ST_NA + 2 * ST_NZ + 1;
+constexpr int ST_OFF_TMEM = ST_OFF_BAR + ST_NBAR * 8;
+constexpr int ST_SMEM = ST_OFF_TMEM + 16 + 1024;
+
+__global__ void __launch_bounds__(ST_THREADS, 1)
+state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + ST_OFF_BAR;
+  auto BAR_AFULL = [&](int b) { return bar0 + 8u * b; };
+  auto BAR_AEMPTY = [&](int b) { return bar0 + 8u * (ST_NA + b); };
+  auto BAR_ZFULL = [&](int s) { return bar0 + 8u * (2 * ST_NA + s); };
+  auto BAR_ZEMPTY = [&](int s) { return bar0 + 8u * (2 * ST_NA + ST_NZ + s); };
+  auto BAR_DONE = [&]() { return bar0 + 8u * (2 * ST_NA + 2 * ST_NZ); };
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + ST_OFF_TMEM);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = blockIdx.x & 3;
+  const int hc = blockIdx.x >> 2;                 // head * nchunk + chunk
+  const int head = hc / a.nchunk, chunk = hc % a.nchunk;
+  const int t_begin = chunk * a.chunk, t_end = min(a.n, t_begin + a.chunk);
+  const int nblk = (t_end - t_begin + 127) / 128;
+  const int a0 = quarter * 16;
+
+  if (tid == 0) {
+    for (int b = 0; b < ST_NA; ++b) { mbar_init(BAR_AFULL(b), 4); mbar_init(BAR_AEMPTY(b), 1); }
+    for (int s = 0; s < ST_NZ; ++s) { mbar_init(BAR_ZFULL(s), 1); mbar_init(BAR_ZEMPTY(s), 1); }
+    mbar_init(BAR_DONE(), 1);
+    mbar_fence_init();
+  }
+  if (warp == 9) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) tma_prefetch_desc(&tmZ);
+    for (int k = 0; k < nblk; ++k) {
+      const int s = k % ST_NZ;
+      if (!mbar_wait(BAR_ZEMPTY(s), (((k / ST_NZ) & 1) ^ 1))) { report(31); break; }
+      if (lane == 0) {
+        mbar_expect_tx(BAR_ZFULL(s), ST_ZTILE);
+        // rows past the end of the sequence are zero-filled by TMA; rows past the end of the
+        // chunk but inside the sequence are cancelled by zero features
+        tma_load_3d(sbase + ST_OFF_Z + s * ST_ZTILE, &tmZ, BAR_ZFULL(s), 0, t_begin + k * 128, head);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(128, 64, 1, 1);
+      bool ok = true;
+      for (int k = 0; ok && k < nblk; ++k) {
+        const int s = k % ST_NZ;
+        if (!mbar_wait(BAR_ZFULL(s), (uint32_t)((k / ST_NZ) & 1))) { report(32); ok = false; break; }
+        const uint32_t z_lo = desc_lo(sbase + ST_OFF_Z + s * ST_ZTILE, ST_ZTILE);
+        for (int m = 0; m < 8; ++m) {
+          const int q = k * 8 + m, b = q % ST_NA;
+          if (!mbar_wait(BAR_AFULL(b), (uint32_t)((q / ST_NA) & 1))) { report(33); ok = false; break; }
+          tc_fence_after();
+          umma_ss_mn_steps<8>(tmem + m * 64, desc_lo(sbase + ST_OFF_A + b * ST_ATILE, ST_ATILE / 2), z_lo,
+                              idesc, k > 0 ? 1u : 0u);
+          umma_commit(BAR_AEMPTY(b));
+        }
+        if (ok) umma_commit(BAR_ZEMPTY(s));
+      }
+      if (ok) umma_commit(BAR_DONE());
+    }
+    __syncwarp();
+  } else {
+    const int g = warp >> 2, j = (warp & 3) * 32 + lane;   // group, token within the block
+    const __nv_bfloat16* ybase = (const __nv_bfloat16*)a.y + (size_t)head * a.n * D;
+    bool ok = true;
+    for (int k = 0; ok && k < nblk; ++k) {
+      const int tok = t_begin + k * 128 + j;
+      __nv_bfloat162 yp[32];
+      {
+        const uint4* yr = (const uint4*)(ybase + (size_t)tok * D);
+#pragma unroll
+        for (int v8 = 0; v8 < 8; ++v8) {
+          uint4 w = (tok < t_end) ? __ldg(yr + v8) : make_uint4(0, 0, 0, 0);
+          yp[v8 * 4 + 0] = *reinterpret_cast<__nv_bfloat162*>(&w.x);
+          yp[v8 * 4 + 1] = *reinterpret_cast<__nv_bfloat162*>(&w.y);
+          yp[v8 * 4 + 2] = *reinterpret_cast<__nv_bfloat162*>(&w.z);
+          yp[v8 * 4 + 3] = *reinterpret_cast<__nv_bfloat162*>(&w.w);
+        }
+      }
+#pragma unroll
+      for (int mm = 0; mm < 4; ++mm) {
+        const int m = 2 * mm + g;              // this group's accumulator tiles: g, g+2, g+4, g+6
+        const int q = k * 8 + m, b = q % ST_NA;
+        if (!mbar_wait(BAR_AEMPTY(b), (((q / ST_NA) & 1) ^ 1))) { report(34); ok = false; break; }
+        uint8_t* abuf = smem + ST_OFF_A + b * ST_ATILE;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int aa = a0 + 2 * m + half;    // value of a for this 64-feature block
+          // y[aa] broadcast to both halves of a bf16 pair; re-read from memory (a cache hit)
+          // because aa is not a compile-time index into the register copy of the row
+          const __nv_bfloat16 ys = (tok < t_end) ? ybase[(size_t)tok * D + aa] : __float2bfloat16_rn(0.f);
+          const __nv_bfloat162 ya = __halves2bfloat162(ys, ys);
+          uint4* row = (uint4*)(abuf + half * (ST_ATILE / 2) + (j >> 3) * 1024 + (j & 7) * 128);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            __nv_bfloat162 p0 = __hmul2(yp[ch * 4 + 0], ya), p1 = __hmul2(yp[ch * 4 + 1], ya);
+            __nv_bfloat162 p2 = __hmul2(yp[ch * 4 + 2], ya), p3 = __hmul2(yp[ch * 4 + 3], ya);
+            uint4 w;
+            w.x = *reinterpret_cast<uint32_t*>(&p0); w.y = *reinterpret_cast<uint32_t*>(&p1);
+            w.z = *reinterpret_cast<uint32_t*>(&p2); w.w = *reinterpret_cast<uint32_t*>(&p3);
+            row[ch ^ (j & 7)] = w;
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_AFULL(b));
+      }
+    }
+    // ---- epilogue: accumulator rows -> fp32 state (columns 0..63) ----
+    if (ok && !mbar_wait(BAR_DONE(), 0)) { report(35); ok = false; }
+    tc_fence_after();
+    if (ok) {
+      float* st = a.state + (size_t)hc * a.per_state;
+      const int l = (warp & 3) * 32 + lane;    // TMEM lane = row of the accumulator tile
+#pragma unroll 1
+      for (int mm = 0; mm < 4; ++mm) {
+        const int m = 2 * mm + g;
+        uint32_t tv[64];
+        tmem_ld64(tmem + m * 64 + ((uint32_t)((warp & 3) * 32) << 16), tv);
+        tmem_wait_ld();
+        const int f = (a0 + 2 * m + (l >> 6)) * 64 + (l & 63);
+        float4* dst = (float4*)(st + (size_t)f * a.dvp);
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          dst[e] = make_float4(__uint_as_float(tv[4 * e]), __uint_as_float(tv[4 * e + 1]),
+                               __uint_as_float(tv[4 * e + 2]), __uint_as_float(tv[4 * e + 3]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// Normaliser column of the second-order rows on the CUDA cores:
+//   state[(a,b)][64] = sum_j e_j y_j[a] y_j[b]   (e = 1, or -dvec), columns 65.. zeroed.
+__global__ void __launch_bounds__(256) state_ecol_kernel(const __nv_bfloat16* __restrict__ y,
+                                                         const float* __restrict__ dvec,
+                                                         float* __restrict__ state, int n, int chunk,
+                                                         int nchunk, int dvp, size_t per_state) {
+  __shared__ float ys[32][65], ye[32][65];
+  const int hc = blockIdx.x, head = hc / nchunk, ck = hc % nchunk;
+  const int t_begin = ck * chunk, t_end = min(n, t_begin + chunk);
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;   // 4 x 4 outputs: a = ty+16i, b = tx+16j
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.f;
+  const __nv_bfloat16* yb = y + (size_t)head * n * 64;
+  for (int t0 = t_begin; t0 < t_end; t0 += 32) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
+      const int r = idx >> 6, cc = idx & 63, tok = t0 + r;
+      const float v = (tok < t_end) ? __bfloat162float(yb[(size_t)tok * 64 + cc]) : 0.f;
+      const float e = (tok < t_end) ? (dvec ? -dvec[(size_t)head * n + tok] : 1.f) : 0.f;
+      ys[r][cc] = v;
+      ye[r][cc] = v * e;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int r = 0; r < 32; ++r) {
+      float xa[4], xb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { xa[i] = ye[r][ty + 16 * i]; xb[i] = ys[r][tx + 16 * i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) acc[i][jj] = fmaf(xa[i], xb[jj], acc[i][jj]);
+    }
+  }
+  float* st = state + (size_t)hc * per_state;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      float* row = st + (size_t)((ty + 16 * i) * 64 + tx + 16 * jj) * dvp;
+      row[64] = acc[i][jj];
+      for (int cc = 65; cc < dvp; ++cc) row[cc] = 0.f;
+    }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                             CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                             CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeFn)p;
+  }();
+  return fn;
+}
+// (mats, rows, 64) bf16 as a rank-3 map with boxes of 128 x 64, 128-byte swizzle
+int make_map(CUtensorMap* m, const void* base, size_t mats, size_t rows) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return fail(FASTMAX_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[3] = {64, (cuuint64_t)rows, (cuuint64_t)mats};
+  cuuint64_t gstr[2] = {128, (cuuint64_t)rows * 128};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FASTMAX_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return FASTMAX_OK;
+}
+
+}  // namespace
+
+int moments_tc_status(int* out, cudaStream_t stream) {
+  FM_CUDA_TRY(cudaMemcpyFromSymbolAsync(out, g_mtc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
+
+// FASTMAX_B200_NO_TC_MOMENTS=1 in the environment keeps the moment family on the CUDA-core
+// kernels (used by the tests to compare the two implementations of the same stages).
+bool moments_tc_supports(const fastmax_problem& p) {
+  static const bool off = [] {
+    const char* e = getenv("FASTMAX_B200_NO_TC_MOMENTS");
+    return e && e[0] == '1';
+  }();
+  return !off && p.dtype == FASTMAX_BF16 && p.d == 64 && p.p == 2 && p.bh == p.bhkv;
+}
+
+size_t moments_tc_state_bytes(int mats) { return (size_t)mats * NROWS_TP * 64 * 2; }
+
+int moments_tc_convert(const Ctx& c, int mats, const float* state, void* state_bf16) {
+  if (mats == 0) return FASTMAX_OK;
+  const MomentDims m = moment_dims(64);
+  dim3 grid(65, mats);
+  FM_LAUNCH("fm_moments_state_bf16", c.stream,
+            (state_to_bf16t_kernel<<<grid, 256, 0, c.stream>>>(state, (__nv_bfloat16*)state_bf16, m.dvp,
+                                                               (size_t)m.f * m.dvp)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+// Second-order rows of the chunk states of (y, z | e): columns 0..63 on the tensor cores,
+// the e column (e = 1 when dvec is null, else -dvec) on the CUDA cores.  The first-order and
+// constant rows are left to moments_chunk_state with p = 1 row range.
+int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
+                           const float* dvec, float* state) {
+  if (heads == 0 || n == 0) return FASTMAX_OK;
+  const MomentDims m = moment_dims(64);
+  const int nchunk = (n + chunk - 1) / chunk;
+  CUtensorMap tz;
+  int rc;
+  if ((rc = make_map(&tz, z, heads, n))) return rc;
+  StArgs a;
+  a.y = y; a.state = state; a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.dvp = m.dvp;
+  a.per_state = (size_t)m.f * m.dvp;
+  FM_CUDA_TRY(cudaFuncSetAttribute(state_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM));
+  FM_LAUNCH("fm_moments_tc_state", c.stream,
+            (state_tc_kernel<<<(unsigned)((size_t)heads * nchunk * 4), ST_THREADS, ST_SMEM, c.stream>>>(tz, a)));
+  FM_CUDA_TRY(cudaGetLastError());
+  FM_LAUNCH("fm_moments_state_ecol", c.stream,
+            (state_ecol_kernel<<<(unsigned)((size_t)heads * nchunk), 256, 0, c.stream>>>(
+                (const __nv_bfloat16*)y, dvec, state, n, chunk, nchunk, m.dvp, a.per_state)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+// mode 0: type A on x -> out_a (+ den_a);  mode 1: type B on (x, u, uvec) -> out_b;
+// mode 2: both on the same tokens.  Results overwrite; they hold the second-order part only.
+int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int state_per_chunk,
+                       const void* x, const void* u, const float* uvec, const void* state_bf16,
+                       const stat_t* stats, float* out_a, float* den_a, float* out_b) {
+  if (heads == 0 || n == 0) return FASTMAX_OK;
+  const fastmax_problem& p = c.p;
+  const int nchunk = (n + chunk - 1) / chunk;
+  CUtensorMap tx, ts;
+  int rc;
+  if ((rc = make_map(&tx, x, heads, n))) return rc;
+  if ((rc = make_map(&ts, state_bf16, (size_t)heads * (state_per_chunk ? nchunk : 1), NROWS_TP))) return rc;
+  RtArgs a;
+  a.x = x; a.u = u; a.uvec = uvec; a.out_a = out_a; a.den_a = den_a; a.out_b = out_b;
+  a.stat_q = p.normalize ? stats : nullptr;
+  a.stat_k = p.normalize ? stats + p.bh : nullptr;
+  a.a2 = p.a2; a.lim = p.lim;
+  a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.state_per_chunk = state_per_chunk; a.mode = mode;
+  const int per_cta = (mode == 2) ? 128 : 256;
+  const unsigned grid = (unsigned)((size_t)heads * ((n + per_cta - 1) / per_cta));
+  FM_CUDA_TRY(cudaFuncSetAttribute(readout_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));
+  static const char* const names[3] = {"fm_moments_tc_readout_a", "fm_moments_tc_readout_b",
+                                       "fm_moments_tc_readout_ab"};
+  FM_LAUNCH(names[mode], c.stream, (readout_tc_kernel<<<grid, RT_THREADS, RT_SMEM, c.stream>>>(tx, ts, a)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+}  // namespace fm

@@ -93,9 +93,11 @@ class CudaShardBackend:
         delta = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
         states = torch.empty(L.fastmax_b200_moment_state_bytes(prob) // 4, dtype=torch.float32, device=q.device)
         total = torch.empty(L.fastmax_b200_moment_total_bytes(prob) // 4, dtype=torch.float32, device=q.device)
+        wsb = L.fastmax_b200_shard_backward_workspace_bytes(prob)
+        self._bwd_ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)   # reused by backward()
         _cabi._check(L.fastmax_b200_shard_qg_state(prob, q.data_ptr(), out.data_ptr(), den.data_ptr(), go.data_ptr(),
                                                    delta.data_ptr(), states.data_ptr(), total.data_ptr(),
-                                                   _cabi._stream(q)), "shard_qg_state")
+                                                   self._bwd_ws.data_ptr(), wsb, _cabi._stream(q)), "shard_qg_state")
         return delta, states, total
 
     def backward(self, q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base):
@@ -103,7 +105,9 @@ class CudaShardBackend:
         gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dots = torch.empty(q.shape[0] + k.shape[0], dtype=torch.float32, device=q.device)
         wsb = L.fastmax_b200_shard_backward_workspace_bytes(prob)
-        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)
+        ws = getattr(self, "_bwd_ws", None)
+        if ws is None or ws.numel() < wsb or ws.device != q.device:
+            ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)
         _cabi._check(L.fastmax_b200_shard_backward(
             prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), den.data_ptr(), self._ptr(stats),
             go.data_ptr(), delta.data_ptr(), kv_states.data_ptr(), qg_states.data_ptr(), self._ptr(r_base),

@@ -168,7 +168,8 @@ int fastmax_b200_backward(const fastmax_problem* prob,
  *   shard_forward     s_base = sum of earlier shards' kv_total (NULL on the first);
  *                     turns kv_states into running prefixes (keep them for backward)
  *   shard_qg_state    delta = grad_out.out per row, chunk states of (q, grad_out/den)
- *                     into qg_states, their sum into qg_total
+ *                     into qg_states, their sum into qg_total; takes the workspace that
+ *                     shard_backward will be given (shard_backward_workspace_bytes)
  *   shard_backward    r_base = sum of later shards' qg_total (NULL on the last);
  *                     writes the gradients without the normalisation row and the
  *                     per-head dots (bh + bhkv floats, zeroed here)
@@ -191,7 +192,8 @@ int fastmax_b200_shard_forward(const fastmax_problem* prob, const void* q, const
                                size_t workspace_bytes, void* stream);
 int fastmax_b200_shard_qg_state(const fastmax_problem* prob, const void* q, const void* out,
                                 const float* den, const void* grad_out, float* delta,
-                                float* qg_states, float* qg_total, void* stream);
+                                float* qg_states, float* qg_total, void* workspace,
+                                size_t workspace_bytes, void* stream);
 int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, const void* k,
                                 const void* v, const void* out, const float* den,
                                 const void* stats, const void* grad_out, const float* delta,
