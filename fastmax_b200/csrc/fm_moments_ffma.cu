@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(256) chunk_state_kernel(const StateArgs a) {
 // Exclusive running sum over the chunks of every head (forward or reverse), started
 // from `base` (per head, may be null); `total` (may be null) gets this shard's own sum.
 // With write == 0 the states are left as they are and only the total is produced.
-__global__ void __launch_bounds__(256) prefix_kernel(float* __restrict__ state,
+__global__ void __launch_bounds__(256) prefix_kernel(float* state,
                                                      const float* __restrict__ base,
                                                      float* __restrict__ total, int nchunk,
                                                      size_t per, size_t first, int reverse,
@@ -145,12 +145,24 @@ __global__ void __launch_bounds__(256) prefix_kernel(float* __restrict__ state,
   if (e >= per) return;
   float run = base ? base[(size_t)head * per + e] : 0.f;
   const float start = run;
-  for (int i = 0; i < nchunk; ++i) {
-    const int c = reverse ? nchunk - 1 - i : i;
-    float* p = state + ((size_t)head * nchunk + c) * per + e;
-    const float v = *p;
-    if (write) *p = run;
-    run += v;
+  // batches of 8 chunks: the loads of a batch are independent and in flight together
+  for (int i0 = 0; i0 < nchunk; i0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u;
+      const int c = reverse ? nchunk - 1 - i : i;
+      v[u] = (i < nchunk) ? __ldcs(state + ((size_t)head * nchunk + c) * per + e) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u;
+      if (i < nchunk) {
+        const int c = reverse ? nchunk - 1 - i : i;
+        if (write) state[((size_t)head * nchunk + c) * per + e] = run;
+        run += v[u];
+      }
+    }
   }
   if (total) total[(size_t)head * per + e] = run - start;
 }

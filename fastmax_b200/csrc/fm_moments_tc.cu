@@ -216,11 +216,7 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             }
             float lo, hi;
             unpack2(add2(s2, s3), lo, hi);
-            const float r = A2 * (lo + hi);
-            if (tok_ok) {
-              if (cidx < 64) a.out_a[grow * D + cidx] = r;
-              else if (a.den_a) a.den_a[grow] = r;
-            }
+            ut[cidx] = A2 * (lo + hi);      // staged in this thread's row, written out at the end
           } else {
             const float uc = ut[cidx];
             const uint64_t u2 = pack2(uc, uc);
@@ -228,6 +224,12 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             for (int e = 0; e < 32; ++e) acc2[e] = fma2(u2, pack2u(tv[2 * e], tv[2 * e + 1]), acc2[e]);
           }
         }
+      }
+      if (ok && !type_b && tok_ok) {
+        float4* dst = (float4*)(a.out_a + grow * D);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) dst[e] = make_float4(ut[4 * e], ut[4 * e + 1], ut[4 * e + 2], ut[4 * e + 3]);
+        if (a.den_a) a.den_a[grow] = ut[64];
       }
       if (ok && type_b && tok_ok) {
         const float k2 = 2.f * A2;
