@@ -41,6 +41,7 @@ WORKLOADS = {
     "c5": (1, 32, 262144, 64, "bf16", 1, 2, 1),   # long context; sharded along the sequence when N > 1
     "c5s": (1, 8, 65536, 64, "bf16", 1, 2, 1),    # reduced long-context case
     "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
+    "c4s": (4, 8, 16384, 128, "bf16", 0, 2, 0),   # reduced unmasked d=128 case
     "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),   # small case for ncu captures (inputs 4 x 67 MB)
 }
 A = dict(a0=1.0, a1=1.0, a2=0.5, lim=1.0)

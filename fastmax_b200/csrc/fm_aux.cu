@@ -123,23 +123,31 @@ int launch_delta(const Ctx& c, const void* go, const void* out, float* delta) {
 // Backward preparation for the tensor-core family: the upstream gradient scaled
 // by 1/den (rounded to bf16, it becomes a matrix operand) and the scaled row dot
 // dvec = (grad_out . out)/den, so that w_ij = gs_i . v_j - dvec_i.  One warp per
-// row of 64 elements, two elements per lane.
+// row of 64 or 128 elements, one or two bf16 pairs per lane.
+template <int D>
 __global__ void __launch_bounds__(256) gprep_kernel(const __nv_bfloat16* __restrict__ go,
                                                     const __nv_bfloat16* __restrict__ out,
                                                     const float* __restrict__ den, size_t rows,
                                                     __nv_bfloat16* __restrict__ gs,
                                                     float* __restrict__ dvec) {
+  constexpr int PAIRS = D / 64;   // bf16 pairs per lane
   size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
-  const __nv_bfloat162 g2 = ((const __nv_bfloat162*)(go + row * 64))[lane];
-  const __nv_bfloat162 o2 = ((const __nv_bfloat162*)(out + row * 64))[lane];
-  const float2 g = __bfloat1622float2(g2), o = __bfloat1622float2(o2);
-  float s = fmaf(g.x, o.x, g.y * o.y);
+  float2 g[PAIRS];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < PAIRS; ++i) {
+    g[i] = __bfloat1622float2(((const __nv_bfloat162*)(go + row * D))[lane + 32 * i]);
+    const float2 o = __bfloat1622float2(((const __nv_bfloat162*)(out + row * D))[lane + 32 * i]);
+    s = fmaf(g[i].x, o.x, fmaf(g[i].y, o.y, s));
+  }
 #pragma unroll
   for (int m = 16; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
   const float inv = 1.0f / den[row];
-  ((__nv_bfloat162*)(gs + row * 64))[lane] = __floats2bfloat162_rn(g.x * inv, g.y * inv);
+#pragma unroll
+  for (int i = 0; i < PAIRS; ++i)
+    ((__nv_bfloat162*)(gs + row * D))[lane + 32 * i] = __floats2bfloat162_rn(g[i].x * inv, g[i].y * inv);
   if (lane == 0) dvec[row] = s * inv;
 }
 
@@ -147,13 +155,19 @@ int launch_gprep(const Ctx& c, const void* go, const void* out, const float* den
                  float* dvec) {
   size_t rows = (size_t)c.p.bh * c.p.nq;
   if (rows == 0) return FASTMAX_OK;
-  if (c.p.d != 64 || c.p.dtype != FASTMAX_BF16)
-    return fail(FASTMAX_E_UNSUPPORTED, "gprep handles bf16 rows of 64 elements");
+  if ((c.p.d != 64 && c.p.d != 128) || c.p.dtype != FASTMAX_BF16)
+    return fail(FASTMAX_E_UNSUPPORTED, "gprep handles bf16 rows of 64 or 128 elements");
   unsigned blocks = (unsigned)((rows + 7) / 8);
-  FM_LAUNCH("fm_gprep", c.stream,
-            (gprep_kernel<<<blocks, 256, 0, c.stream>>>((const __nv_bfloat16*)go,
-                                                       (const __nv_bfloat16*)out, den, rows,
-                                                       (__nv_bfloat16*)gs, dvec)));
+  if (c.p.d == 64)
+    FM_LAUNCH("fm_gprep", c.stream,
+              (gprep_kernel<64><<<blocks, 256, 0, c.stream>>>((const __nv_bfloat16*)go,
+                                                              (const __nv_bfloat16*)out, den, rows,
+                                                              (__nv_bfloat16*)gs, dvec)));
+  else
+    FM_LAUNCH("fm_gprep", c.stream,
+              (gprep_kernel<128><<<blocks, 256, 0, c.stream>>>((const __nv_bfloat16*)go,
+                                                               (const __nv_bfloat16*)out, den, rows,
+                                                               (__nv_bfloat16*)gs, dvec)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }

@@ -1,5 +1,5 @@
 // Fastmax attention in tiled score form on the tcgen05 tensor cores (bf16 inputs,
-// fp32 accumulation in tensor memory), head dimension 64.
+// fp32 accumulation in tensor memory), head dimension 64 or 128.
 //
 // Two kernel modes cover the forward pass and the three gradients:
 //
@@ -41,7 +41,7 @@ using namespace sm100;
 enum { OP_A = 0, OP_B = 1 };
 
 struct TcArgs {
-  void* o;              // (heads, nrows, 64) bf16 result rows
+  void* o;              // (heads, nrows, d) bf16 result rows
   float* den_out;       // OP_A with fwd_div: (heads, nrows) row sums
   const float* dvec;    // OP_B: (heads, nq) grad_out.out / den
   const void* x;        // row operand in global memory (for the normalisation dots)
@@ -51,42 +51,52 @@ struct TcArgs {
   int nrows, ncols, off, mask, rev, fwd_div, npairs;
   float a0, a1, a2, lim;
   int chunk;             // > 0: only the columns of the row pair's own chunk
-  const float* o_add;    // fp32 (heads, nrows, 64) added to the accumulator row
+  const float* o_add;    // fp32 (heads, nrows, d) added to the accumulator row
   const float* den_add;  // OP_A with fwd_div: added to the row sum
 };
 
-constexpr int D = 64, BM = 128;
+constexpr int BM = 128;
 constexpr int kThreads = 352;  // warps 0-3: group 0, 4-7: group 1, 8: TMA producer, 9/10: MMA issuers
 
-template <int MODE>
+// Tiling per mode and head dimension DD (64 or 128).  Tiles of 128-byte-swizzled rows hold
+// 64 bf16 per row, so a DD = 128 tile is two sub-tiles side by side.  TMEM columns per
+// group (stride 256): S | W | P | O.  DD = 128 needs 128 columns for O, so OP_A shrinks
+// the column tile to 64 and OP_B runs a single group per CTA.
+template <int MODE, int DD>
 struct Cfg {
-  static constexpr int BN = (MODE == OP_A) ? 128 : 64;
-  static constexpr int NS = (MODE == OP_A) ? 4 : 6;
-  static constexpr int ROW_TILE = BM * D * 2;
-  static constexpr int COL_TILE = BN * D * 2;
+  static constexpr int D = DD;
+  static constexpr int NSUB = DD / 64;
+  static constexpr int BN = (MODE == OP_A && DD == 64) ? 128 : 64;
+  static constexpr int NG = (MODE == OP_B && DD == 128) ? 1 : 2;
+  static constexpr int NS = (DD == 128) ? 3 : ((MODE == OP_A) ? 4 : 6);
+  static constexpr int ROW_SUB = BM * 128;          // one 64-wide sub-tile of a row tile
+  static constexpr int COL_SUB = BN * 128;
+  static constexpr int ROW_TILE = NSUB * ROW_SUB;
+  static constexpr int COL_TILE = NSUB * COL_SUB;
   static constexpr int NROWOPS = (MODE == OP_A) ? 1 : 2;
   static constexpr int STAGE = 2 * COL_TILE;
   static constexpr int OFF_X = 0;
-  static constexpr int OFF_U = 2 * ROW_TILE;
-  static constexpr int OFF_ST = NROWOPS * 2 * ROW_TILE;
+  static constexpr int OFF_U = NG * ROW_TILE;
+  static constexpr int OFF_ST = NROWOPS * NG * ROW_TILE;
   static constexpr int OFF_VEC = OFF_ST + NS * STAGE;
   static constexpr int OFF_BAR = OFF_VEC + NS * BN * 4;
   static constexpr int NBAR = 1 + 2 * NS + 8;
   static constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
   static constexpr int SMEM = OFF_TMEM + 16 + 1024;  // + slack for the 1024-byte alignment
-  // TMEM columns inside a group's 256-column half
-  static constexpr int T_S = 0, T_W = 64, T_P = 128, T_O = 192;
+  static constexpr int T_S = 0, T_W = 64;
+  static constexpr int T_P = (DD == 64) ? 128 : ((MODE == OP_A) ? 64 : 128);
+  static constexpr int T_O = (DD == 64) ? 192 : ((MODE == OP_A) ? 96 : 192);
 };
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_tc_status, 0, code); }
 
-template <int MODE>
+template <int MODE, int DD>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                 const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
                 const TcArgs a) {
-  using C = Cfg<MODE>;
-  constexpr int BN = C::BN, NS = C::NS;
+  using C = Cfg<MODE, DD>;
+  constexpr int BN = C::BN, NS = C::NS, D = DD;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -107,7 +117,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   const int head = blockIdx.x / a.npairs;
   const int pidx = blockIdx.x % a.npairs;
   const int pair = a.rev ? pidx : a.npairs - 1 - pidx;
-  const int r0 = pair * 2 * BM;
+  const int r0 = pair * C::NG * BM;
   const bool colvec = (MODE == OP_B) && a.rev;
 
   // ---- tile ranges: group g walks column tiles [tb_g, te_g) -------------------------
@@ -127,7 +137,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     if (a.rev) { te0 = min(te0, ce); te1 = min(te1, ce); }
     else { tb0 = cb; tb1 = cb; }
   }
-  const bool act1 = r0 + BM < a.nrows;  // group 0 always has rows
+  const bool act1 = C::NG == 2 && r0 + BM < a.nrows;  // group 0 always has rows
   if (!act1) { tb1 = INT_MAX; te1 = 0; }
   const int tb = min(tb0, tb1);
   const int te = max(te0, te1);
@@ -161,11 +171,14 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       tma_prefetch_desc(&tmZ);
       if (MODE == OP_B) tma_prefetch_desc(&tmU);
       mbar_expect_tx(BAR_X(), (act1 ? 2 : 1) * C::NROWOPS * C::ROW_TILE);
-      for (int g = 0; g < (act1 ? 2 : 1); ++g) {
-        tma_load_3d(sbase + C::OFF_X + g * C::ROW_TILE, &tmX, BAR_X(), 0, r0 + g * BM, head);
-        if (MODE == OP_B)
-          tma_load_3d(sbase + C::OFF_U + g * C::ROW_TILE, &tmU, BAR_X(), 0, r0 + g * BM, head);
-      }
+      for (int g = 0; g < (act1 ? 2 : 1); ++g)
+        for (int sub = 0; sub < C::NSUB; ++sub) {
+          tma_load_3d(sbase + C::OFF_X + g * C::ROW_TILE + sub * C::ROW_SUB, &tmX, BAR_X(), sub * 64,
+                      r0 + g * BM, head);
+          if (MODE == OP_B)
+            tma_load_3d(sbase + C::OFF_U + g * C::ROW_TILE + sub * C::ROW_SUB, &tmU, BAR_X(), sub * 64,
+                        r0 + g * BM, head);
+        }
     }
     for (int t = tb; t < te; ++t) {
       const int k = t - tb, s = k % NS;
@@ -173,8 +186,10 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       if (lane == 0) {
         mbar_expect_tx(BAR_FULL(s), C::STAGE);
         const uint32_t dst = sbase + C::OFF_ST + s * C::STAGE;
-        tma_load_3d(dst, &tmY, BAR_FULL(s), 0, t * BN, head);
-        tma_load_3d(dst + C::COL_TILE, &tmZ, BAR_FULL(s), 0, t * BN, head);
+        for (int sub = 0; sub < C::NSUB; ++sub) {
+          tma_load_3d(dst + sub * C::COL_SUB, &tmY, BAR_FULL(s), sub * 64, t * BN, head);
+          tma_load_3d(dst + C::COL_TILE + sub * C::COL_SUB, &tmZ, BAR_FULL(s), sub * 64, t * BN, head);
+        }
       }
       if (colvec) {
         float* vec = (float*)(smem + C::OFF_VEC) + s * BN;
@@ -193,11 +208,12 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     if (lane == 0 && J > 0) {
       constexpr uint32_t idescS = idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
+      static_assert(C::T_O + D <= 256 || C::NG == 1, "accumulator does not fit the group's TMEM columns");
       const uint32_t tg = tmem + g * 256;
       const uint32_t x_lo = desc_lo(sbase + C::OFF_X + g * C::ROW_TILE, 16);
       const uint32_t u_lo = desc_lo(sbase + C::OFF_U + g * C::ROW_TILE, 16);
       const uint32_t st_k = desc_lo(sbase + C::OFF_ST, 16);               // stage 0, K-major view
-      const uint32_t st_mn = desc_lo(sbase + C::OFF_ST, C::COL_TILE);     // stage 0, MN-major view
+      const uint32_t st_mn = desc_lo(sbase + C::OFF_ST, C::COL_SUB);      // stage 0, MN-major view
       // the other group also reads tile t unless t is outside its range
       const int otb = g ? tb0 : tb1, ote = g ? te0 : te1;
       bool ok = mbar_wait(BAR_X(), 0);
@@ -208,8 +224,15 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         if (!mbar_wait(BAR_FULL(s), (uint32_t)((k / NS) & 1))) { report(3); return false; }
         tc_fence_after();
         const uint32_t y_lo = st_k + (uint32_t)s * (C::STAGE >> 4);
-        umma_ss_k64(tg + C::T_S, x_lo, y_lo, idescS);
-        if (MODE == OP_B) umma_ss_k64(tg + C::T_W, u_lo, y_lo + (C::COL_TILE >> 4), idescS);
+#pragma unroll
+        for (int sub = 0; sub < C::NSUB; ++sub)
+          umma_ss_k64(tg + C::T_S, x_lo + sub * (C::ROW_SUB >> 4), y_lo + sub * (C::COL_SUB >> 4), idescS, sub > 0);
+        if (MODE == OP_B) {
+#pragma unroll
+          for (int sub = 0; sub < C::NSUB; ++sub)
+            umma_ss_k64(tg + C::T_W, u_lo + sub * (C::ROW_SUB >> 4),
+                        y_lo + (C::COL_TILE >> 4) + sub * (C::COL_SUB >> 4), idescS, sub > 0);
+        }
         umma_commit(BAR_S(g));
         return true;
       };
@@ -333,9 +356,6 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
       tc_fence_after();
       if (ok && Jg > 0) {
-        uint32_t ov[64];
-        tmem_ld64(tg + C::T_O, ov);
-        tmem_wait_ld();
         float rlo, rhi;
         unpack2(add2(add2(rs2[0], rs2[1]), add2(rs2[2], rs2[3])), rlo, rhi);
         float rowsum = rlo + rhi;
@@ -343,36 +363,42 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         float scale = 1.f;
         if (MODE == OP_A && a.fwd_div) scale = 1.0f / rowsum;
         float part = 0.f;
-        if (row_ok) {
-          const size_t grow = (size_t)head * a.nrows + row;
-          uint4* dst = (uint4*)((__nv_bfloat16*)a.o + grow * D);
-          const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * D);
-          const bool want_dots = (MODE == OP_B) && a.dots != nullptr;
-          const float4* addr = a.o_add ? (const float4*)(a.o_add + grow * D) : nullptr;
+        const size_t grow = (size_t)head * a.nrows + (row_ok ? row : 0);
+        const bool want_dots = (MODE == OP_B) && a.dots != nullptr;
+#pragma unroll 1
+        for (int hc = 0; hc < D / 64; ++hc) {      // 64 accumulator columns at a time
+          uint32_t ov[64];
+          tmem_ld64(tg + C::T_O + hc * 64, ov);
+          tmem_wait_ld();
+          if (row_ok) {
+            uint4* dst = (uint4*)((__nv_bfloat16*)a.o + grow * D + hc * 64);
+            const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * D + hc * 64);
+            const float4* addr = a.o_add ? (const float4*)(a.o_add + grow * D + hc * 64) : nullptr;
 #pragma unroll
-          for (int v8 = 0; v8 < 8; ++v8) {
-            float f[8];
-            float4 ad0 = make_float4(0.f, 0.f, 0.f, 0.f), ad1 = ad0;
-            if (addr) { ad0 = __ldg(addr + 2 * v8); ad1 = __ldg(addr + 2 * v8 + 1); }
-            const float ad[8] = {ad0.x, ad0.y, ad0.z, ad0.w, ad1.x, ad1.y, ad1.z, ad1.w};
+            for (int v8 = 0; v8 < 8; ++v8) {
+              float f[8];
+              float4 ad0 = make_float4(0.f, 0.f, 0.f, 0.f), ad1 = ad0;
+              if (addr) { ad0 = __ldg(addr + 2 * v8); ad1 = __ldg(addr + 2 * v8 + 1); }
+              const float ad[8] = {ad0.x, ad0.y, ad0.z, ad0.w, ad1.x, ad1.y, ad1.z, ad1.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = (__uint_as_float(ov[v8 * 8 + e]) + ad[e]) * scale;
-            uint4 w;
-            w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
-            w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
-            dst[v8] = w;
-            if (want_dots) {
-              const uint4 xv = __ldg(xr + v8);
-              const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+              for (int e = 0; e < 8; ++e) f[e] = (__uint_as_float(ov[v8 * 8 + e]) + ad[e]) * scale;
+              uint4 w;
+              w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
+              w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
+              dst[v8] = w;
+              if (want_dots) {
+                const uint4 xv = __ldg(xr + v8);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                part = fmaf(f[2 * e], __uint_as_float(xw[e] << 16), part);
-                part = fmaf(f[2 * e + 1], __uint_as_float(xw[e] & 0xFFFF0000u), part);
+                for (int e = 0; e < 4; ++e) {
+                  part = fmaf(f[2 * e], __uint_as_float(xw[e] << 16), part);
+                  part = fmaf(f[2 * e + 1], __uint_as_float(xw[e] & 0xFFFF0000u), part);
+                }
               }
             }
           }
-          if (MODE == OP_A && a.fwd_div) a.den_out[grow] = rowsum;
         }
+        if (MODE == OP_A && a.fwd_div && row_ok) a.den_out[grow] = rowsum;
         if (MODE == OP_B && a.dots != nullptr) {
 #pragma unroll
           for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
@@ -409,14 +435,14 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// (heads, n, 64) bf16 tensor as a rank-3 map with boxes of box_rows x 64, 128-byte swizzle;
+// (heads, n, d) bf16 tensor as a rank-3 map with boxes of box_rows x 64, 128-byte swizzle;
 // rows past n read as zero.
-int make_map(CUtensorMap* m, const void* base, int heads, int n, int box_rows) {
+int make_map(CUtensorMap* m, const void* base, int heads, int n, int box_rows, int d) {
   EncodeFn enc = encode_fn();
   if (!enc) return fail(FASTMAX_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[3] = {(cuuint64_t)D, (cuuint64_t)n, (cuuint64_t)heads};
-  cuuint64_t gstr[2] = {(cuuint64_t)D * 2, (cuuint64_t)n * D * 2};
-  cuuint32_t box[3] = {(cuuint32_t)D, (cuuint32_t)box_rows, 1};
+  cuuint64_t gdim[3] = {(cuuint64_t)d, (cuuint64_t)n, (cuuint64_t)heads};
+  cuuint64_t gstr[2] = {(cuuint64_t)d * 2, (cuuint64_t)n * d * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};   // 64 elements = one 128-byte swizzle row
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -425,29 +451,36 @@ int make_map(CUtensorMap* m, const void* base, int heads, int n, int box_rows) {
   return FASTMAX_OK;
 }
 
-template <int MODE>
-int launch_tc(const Ctx& c, const char* name, const void* x, const void* u, const void* y,
-              const void* z, int nrows, int ncols, TcArgs a) {
-  using C = Cfg<MODE>;
+template <int MODE, int DD>
+int launch_tc_d(const Ctx& c, const char* name, const void* x, const void* u, const void* y,
+                const void* z, int nrows, int ncols, TcArgs a) {
+  using C = Cfg<MODE, DD>;
   const int heads = c.p.bh;
   if (heads == 0 || nrows == 0) return FASTMAX_OK;
   CUtensorMap tx, tu, ty, tz;
   int rc;
-  if ((rc = make_map(&tx, x, heads, nrows, BM))) return rc;
-  if ((rc = make_map(&tu, u ? u : x, heads, nrows, BM))) return rc;
-  if ((rc = make_map(&ty, y, heads, ncols, C::BN))) return rc;
-  if ((rc = make_map(&tz, z, heads, ncols, C::BN))) return rc;
+  if ((rc = make_map(&tx, x, heads, nrows, BM, DD))) return rc;
+  if ((rc = make_map(&tu, u ? u : x, heads, nrows, BM, DD))) return rc;
+  if ((rc = make_map(&ty, y, heads, ncols, C::BN, DD))) return rc;
+  if ((rc = make_map(&tz, z, heads, ncols, C::BN, DD))) return rc;
   a.nrows = nrows;
   a.ncols = ncols;
   a.x = x;
-  FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_kernel<MODE, DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    C::SMEM));
-  a.npairs = (nrows + 2 * BM - 1) / (2 * BM);
+  a.npairs = (nrows + C::NG * BM - 1) / (C::NG * BM);
   dim3 grid((unsigned)((size_t)heads * a.npairs));
   FM_LAUNCH(name, c.stream,
-            (dense_tc_kernel<MODE><<<grid, kThreads, C::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+            (dense_tc_kernel<MODE, DD><<<grid, kThreads, C::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
+}
+
+template <int MODE>
+int launch_tc(const Ctx& c, const char* name, const void* x, const void* u, const void* y,
+              const void* z, int nrows, int ncols, const TcArgs& a) {
+  if (c.p.d == 128) return launch_tc_d<MODE, 128>(c, name, x, u, y, z, nrows, ncols, a);
+  return launch_tc_d<MODE, 64>(c, name, x, u, y, z, nrows, ncols, a);
 }
 
 TcArgs base_args(const Ctx& c, const stat_t* stats) {
@@ -469,7 +502,7 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 }  // namespace
 
 bool dense_tc_supports(const fastmax_problem& p) {
-  return p.dtype == FASTMAX_BF16 && p.d == 64 && p.bh == p.bhkv;
+  return p.dtype == FASTMAX_BF16 && (p.d == 64 || p.d == 128) && p.bh == p.bhkv;
 }
 
 int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,

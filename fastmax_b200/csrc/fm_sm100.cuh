@@ -204,15 +204,15 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) 
 }
 // Four K-steps of D[tmem] = A[smem] B[smem]^T for K-major operands whose K extent
 // (64 bf16) is one swizzle row: each step advances both descriptors by 32 bytes.
-// The first step overwrites D.
+// The first step overwrites D unless `accumulate` is set.
 __device__ __forceinline__ void umma_ss_k64(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
-                                            uint32_t idesc) {
+                                            uint32_t idesc, uint32_t accumulate = 0) {
   asm volatile(
       "{\n"
       ".reg .b64 da, db;\n"
       ".reg .b32 a, b;\n"
       ".reg .pred pf, pt;\n"
-      "setp.ne.b32 pf, 0, 0;\n"
+      "setp.ne.b32 pf, %5, 0;\n"
       "setp.eq.b32 pt, 0, 0;\n"
       "mov.b64 da, {%1, %3};\n"
       "mov.b64 db, {%2, %3};\n"
@@ -233,7 +233,7 @@ __device__ __forceinline__ void umma_ss_k64(uint32_t d_tmem, uint32_t a_lo, uint
       "mov.b64 db, {b, %3};\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n"
       "}\n"
-      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc)
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // NK K-steps of D[tmem] (+)= A[tmem] B[smem] with B MN-major (16 K rows = 2048

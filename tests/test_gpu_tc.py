@@ -37,6 +37,26 @@ def test_tensor_core_family_against_dense_oracle(cfg):
     assert_close(got, ref, torch.bfloat16, str(cfg), floor=1.0 if nq == 1 else 1e-2)
 
 
+# bh, nq, nk, mask, p, normalize  -- head dimension 128
+EDGE128 = [(1, 1, 1, 1, 2, 0), (2, 127, 127, 1, 2, 1), (2, 128, 128, 0, 2, 0), (3, 129, 129, 1, 1, 1),
+           (2, 300, 300, 1, 2, 1), (2, 257, 257, 0, 1, 0), (1, 1000, 1000, 1, 2, 0), (2, 70, 100, 1, 2, 1),
+           (2, 200, 457, 0, 2, 0), (1, 1500, 1500, 0, 2, 0)]
+
+
+@pytest.mark.parametrize("cfg", EDGE128, ids=[f"bh{c[0]}nq{c[1]}nk{c[2]}m{c[3]}p{c[4]}z{c[5]}" for c in EDGE128])
+def test_tensor_core_family_head_dimension_128(cfg):
+    bh, nq, nk, mask, p, norm = cfg
+    q, go = randn(1, bh, nq, 128, seed=nq), randn(1, bh, nq, 128, seed=nq + 1)
+    k, v = randn(1, bh, nk, 128, seed=nk + 2), randn(1, bh, nk, 128, seed=nk + 3)
+    if not norm:
+        q, k = q * 128 ** -0.5, k * 128 ** -0.5
+    kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    got, _ = run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", **kw)
+    assert _cabi.device_status() == 0
+    ref = oracle(q, k, v, go, torch.bfloat16, dense=True, **kw)
+    assert_close(got, ref, torch.bfloat16, str(cfg), floor=1.0 if nq == 1 else 1e-2)
+
+
 def test_other_coefficients_and_lim():
     q, k, v, go = [randn(1, 3, 333, 64, seed=s) for s in (1, 2, 3, 4)]
     kw = dict(mask=1, normalize=1, p=2, a0=0.7, a1=1.3, a2=0.4, lim=1.5)
