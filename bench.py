@@ -35,6 +35,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # name: (B, H, N, D, dtype, mask, p, normalize)
     "c3": (64, 16, 10000, 64, "bf16", 1, 2, 1),
+    "c1": (2, 8, 1024, 32, "fp32", 0, 2, 1),
     "c2": (64, 8, 1000, 32, "fp32", 1, 2, 1),
     "c4p2": (32, 32, 16384, 128, "bf16", 0, 2, 0),
     "c4p1": (32, 32, 16384, 128, "bf16", 0, 1, 0),
