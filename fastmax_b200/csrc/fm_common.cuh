@@ -132,10 +132,11 @@ int dense_ffma_backward(const Ctx& c, const void* q, const void* k, const void* 
 
 // ---- moment-state form (fm_moments_ffma.cu) ---------------------------------------
 struct MomentDims {
-  int f;    // state rows: d*d + d + 1
+  int f;    // state rows that are stored: d*d + d + 1, or d + 1 when p == 1
+  int f0;   // number of the first stored row (d*d when p == 1, else 0)
   int dvp;  // state columns: d + 1 rounded up to a multiple of 4
 };
-MomentDims moment_dims(int d);
+MomentDims moment_dims(int d, int p = 2);
 // state[h][c][f][col] = sum over the tokens of chunk c of feature_f(y) * [z | e];  ext 0: e = 1,
 // ext 1: z and e scaled: [z/den | -delta/den].
 int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,

@@ -16,12 +16,12 @@ int moments_chunk(const fastmax_problem& p) {
 }
 
 size_t moment_state_bytes(const fastmax_problem& p, int n) {
-  const MomentDims m = moment_dims(p.d);
+  const MomentDims m = moment_dims(p.d, p.p);
   const int L = moments_chunk(p);
   return up256(sizeof(float) * (size_t)p.bh * ((n + L - 1) / L) * m.f * m.dvp);
 }
 size_t moment_total_bytes(const fastmax_problem& p) {
-  const MomentDims m = moment_dims(p.d);
+  const MomentDims m = moment_dims(p.d, p.p);
   return up256(sizeof(float) * (size_t)p.bh * m.f * m.dvp);
 }
 

@@ -79,6 +79,7 @@ struct StateArgs {
   const float* delta;  // ext = 1: (heads, n)
   float* state;        // (heads, nchunk, F, DVP)
   int n, chunk, nchunk, ext, f_begin;
+  int f_store;         // first row that is stored (d*d when p == 1: the second-order rows do not exist)
 };
 
 template <int D, typename T>
@@ -121,13 +122,13 @@ __global__ void __launch_bounds__(256) chunk_state_kernel(const StateArgs a) {
       }
     }
   }
-  float* st = a.state + ((size_t)head * a.nchunk + chunk) * M::F * M::DVP;
+  float* st = a.state + ((size_t)head * a.nchunk + chunk) * (M::F - a.f_store) * M::DVP;
 #pragma unroll
   for (int k = 0; k < M::FPT; ++k) {
     const int f = f0 + k;
     if (f < M::F)
 #pragma unroll
-      for (int c = 0; c < M::CW; ++c) st[(size_t)f * M::DVP + cg * M::CW + c] = acc[k][c];
+      for (int c = 0; c < M::CW; ++c) st[(size_t)(f - a.f_store) * M::DVP + cg * M::CW + c] = acc[k][c];
   }
 }
 
@@ -179,7 +180,7 @@ struct ReadArgs {
   const float* delta;
   const stat_t* stat_q;
   const stat_t* stat_k;
-  int n, chunk, nchunk, ext, f_begin;
+  int n, chunk, nchunk, ext, f_begin, f_store;
   int accumulate;       // add to o_add / den_add instead of overwriting them
   float a0, a1, a2, lim;
 };
@@ -197,7 +198,8 @@ __global__ void __launch_bounds__(256) readout_a_kernel(const ReadArgs a) {
   const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
   const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
   const int chunk = a.state_per_chunk ? tok0 / a.chunk : 0;
-  const float* st = a.state + ((size_t)head * (a.state_per_chunk ? a.nchunk : 1) + chunk) * M::F * M::DVP;
+  const float* st = a.state + ((size_t)head * (a.state_per_chunk ? a.nchunk : 1) + chunk) * (M::F - a.f_store) * M::DVP
+                    - (size_t)a.f_store * M::DVP;   // indexed by the absolute row number below
   load_xe<D, T>(xe, (const T*)a.x + (size_t)head * a.n * D, tok0, M::TILE, a.n);
   float acc[M::FPT][M::CW];
 #pragma unroll
@@ -260,7 +262,8 @@ __global__ void __launch_bounds__(256) readout_b_kernel(const ReadArgs a) {
   const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
   const float A1 = a.a1 * c, A22 = 2.f * a.a2 * c * c;
   const int chunk = a.state_per_chunk ? tok0 / a.chunk : 0;
-  const float* st = a.state + ((size_t)head * (a.state_per_chunk ? a.nchunk : 1) + chunk) * M::F * M::DVP;
+  const float* st = a.state + ((size_t)head * (a.state_per_chunk ? a.nchunk : 1) + chunk) * (M::F - a.f_store) * M::DVP
+                    - (size_t)a.f_store * M::DVP;   // indexed by the absolute row number below
   load_xe<D, T>(xe, (const T*)a.x + (size_t)head * a.n * D, tok0, M::TILE, a.n);
   load_zt<D, T>(ut, (const T*)a.u + (size_t)head * a.n * D, a.den ? a.den + (size_t)head * a.n : nullptr,
                 a.delta ? a.delta + (size_t)head * a.n : nullptr, a.ext, tok0, M::TILE, a.n);
@@ -352,10 +355,11 @@ size_t readout_smem(bool b) {
 }  // namespace
 
 // ---- host-visible helpers ---------------------------------------------------------------
-MomentDims moment_dims(int d) {
+MomentDims moment_dims(int d, int p) {
   MomentDims m;
   m.dvp = (d + 1 + 3) / 4 * 4;
-  m.f = d * d + d + 1;
+  m.f0 = (p == 1) ? d * d : 0;
+  m.f = d * d + d + 1 - m.f0;
   return m;
 }
 
@@ -376,6 +380,7 @@ int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y
   a.y = y; a.z = z; a.den = den; a.delta = delta; a.state = state;
   a.n = n; a.chunk = chunk; a.nchunk = (n + chunk - 1) / chunk; a.ext = ext;
   a.f_begin = (c.p.p == 1 || first_order_only) ? c.p.d * c.p.d : 0;
+  a.f_store = moment_dims(c.p.d, c.p.p).f0;
   const bool f32 = c.p.dtype == FASTMAX_F32;
   FM_DISPATCH_D(c.p.d, {
     using M = MC<DD>;
@@ -390,9 +395,9 @@ int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y
 int moments_prefix(const Ctx& c, int heads, int nchunk, float* state, const float* base, float* total,
                    int reverse, int write) {
   if (heads == 0 || nchunk == 0) return FASTMAX_OK;
-  const MomentDims m = moment_dims(c.p.d);
+  const MomentDims m = moment_dims(c.p.d, c.p.p);
   const size_t per = (size_t)m.f * m.dvp;
-  const size_t first = (c.p.p == 1) ? (size_t)c.p.d * c.p.d * m.dvp : 0;
+  const size_t first = 0;
   dim3 grid((unsigned)((per - first + 255) / 256), heads);
   FM_LAUNCH("fm_moments_prefix", c.stream,
             (prefix_kernel<<<grid, 256, 0, c.stream>>>(state, base, total, nchunk, per, first, reverse, write)));
@@ -413,6 +418,7 @@ int moments_readout(const Ctx& c, int mode_b, int heads, int n, int chunk, int s
   a.stat_k = p.normalize ? stats + p.bh : nullptr;
   a.n = n; a.chunk = chunk; a.nchunk = (n + chunk - 1) / chunk; a.ext = ext;
   a.f_begin = (p.p == 1 || first_order_only) ? p.d * p.d : 0;
+  a.f_store = moment_dims(p.d, p.p).f0;
   a.accumulate = first_order_only;   // the second-order part was written by the tensor-core read-out
   a.a0 = p.a0; a.a1 = p.a1; a.a2 = (p.p == 2) ? p.a2 : 0.f; a.lim = p.lim;
   const bool f32 = p.dtype == FASTMAX_F32;
