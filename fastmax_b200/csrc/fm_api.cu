@@ -110,7 +110,7 @@ static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   if (!moments_supports(p)) return false;
   const double d = p.d, F = d + (p.p == 2 ? d * d : 0.0);
   const double rate_score = tc_ok ? 800e12 : 25e12;
-  const double rate_state = moments_tc_supports(p) ? 450e12 : 20e12;
+  const double rate_state = (p.p == 2 ? moments_tc_supports(p) : first_tc_supports(p)) ? 450e12 : 20e12;
   const double keys = p.mask ? 0.5 * p.nk : (double)p.nk;
   const double chunk_keys = p.mask ? 0.5 * moments_chunk(p) : 0.0;
   const double per_key = 14.0 * (d + 0.5);
@@ -180,10 +180,11 @@ unsigned long long fastmax_b200_launch_count(void) { return g_launches.load(); }
 
 int fastmax_b200_device_status(int* status, void* stream) {
   if (!status) return fail(FASTMAX_E_ARG, "status is NULL");
-  int a = 0, b = 0, rc;
+  int a = 0, b = 0, f = 0, rc;
   if ((rc = tc_status(&a, (cudaStream_t)stream))) return rc;
   if ((rc = moments_tc_status(&b, (cudaStream_t)stream))) return rc;
-  *status = a ? a : b;
+  if ((rc = first_tc_status(&f, (cudaStream_t)stream))) return rc;
+  *status = a ? a : (b ? b : f);
   return FASTMAX_OK;
 }
 
@@ -328,11 +329,7 @@ static int validate_shard(const fastmax_problem* prob) {
     return fail(FASTMAX_E_ARG, "a sequence shard needs mask = 1, nq == nk and bh == bhkv");
   return check_device();
 }
-static size_t shard_s16_bytes(const fastmax_problem& p) {
-  if (!moments_tc_supports(p)) return 0;
-  const int L = moments_chunk(p);
-  return align_up(moments_tc_state_bytes(p.bh * ((p.nq + L - 1) / L)), 256);
-}
+static size_t shard_s16_bytes(const fastmax_problem& p) { return state16_bytes(p, p.nq); }
 struct ShardFwdWs { size_t o_add, den_add, s16, bytes; };
 static ShardFwdWs shard_fwd_layout(const fastmax_problem& p) {
   ShardFwdWs w;

@@ -160,6 +160,18 @@ int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int 
                        const void* x, const void* u, const float* uvec, const void* state_bf16,
                        const stat_t* stats, float* out_a, float* den_a, float* out_b);
 int moments_tc_status(int* out, cudaStream_t stream);
+
+// first-order part on tensor cores (fm_first_tc.cu): bf16, d in {64, 128}
+bool first_tc_supports(const fastmax_problem& p);
+size_t first_tc_copy_bytes(const fastmax_problem& p, int mats);
+int first_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
+                         const float* dvec, float* state);
+int first_tc_convert(const Ctx& c, int mats, const float* state, void* s1b);
+int first_tc_readout(const Ctx& c, int type_b, int heads, int n, int chunk, int per_chunk, const void* tile,
+                     const void* x, const float* uvec, const float* state, const void* s1b,
+                     const stat_t* stats, float* o_add, float* den_add, int accumulate, int final = 0,
+                     void* out_final = nullptr, float* den_final = nullptr, float* dots = nullptr);
+int first_tc_status(int* out, cudaStream_t stream);
 // host orchestration of the moment family (fm_moments.cu)
 struct MomFwdWs { size_t states, total, o_add, den_add, s16, bytes; };
 struct MomBwdWs { size_t dots, delta, dvec, gs, states, total, gq_add, gk_add, gv_add, s16, bytes; };
@@ -167,6 +179,7 @@ int moments_chunk(const fastmax_problem& p);
 bool moments_supports(const fastmax_problem& p);
 size_t moment_state_bytes(const fastmax_problem& p, int n);
 size_t moment_total_bytes(const fastmax_problem& p);
+size_t state16_bytes(const fastmax_problem& p, int n);   // bf16 operand copies of the states of n tokens
 MomFwdWs moments_fwd_layout(const fastmax_problem& p);
 MomBwdWs moments_bwd_layout(const fastmax_problem& p);
 int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,

@@ -451,6 +451,24 @@ int make_map(CUtensorMap* m, const void* base, int heads, int n, int box_rows, i
   return FASTMAX_OK;
 }
 
+}  // namespace
+
+int tma_map_bf16(CUtensorMap* m, const void* base, size_t mats, size_t rows, int d, int box_rows) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return fail(FASTMAX_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[3] = {(cuuint64_t)d, (cuuint64_t)rows, (cuuint64_t)mats};
+  cuuint64_t gstr[2] = {(cuuint64_t)d * 2, (cuuint64_t)rows * d * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FASTMAX_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return FASTMAX_OK;
+}
+
+namespace {
+
 template <int MODE, int DD>
 int launch_tc_d(const Ctx& c, const char* name, const void* x, const void* u, const void* y,
                 const void* z, int nrows, int ncols, TcArgs a) {

@@ -26,10 +26,14 @@ size_t moment_total_bytes(const fastmax_problem& p) {
 }
 
 // bf16 transposed copy of the second-order block of every chunk state (tensor-core read-out)
-static size_t state16_bytes(const fastmax_problem& p, int n) {
-  if (!moments_tc_supports(p)) return 0;
+// layout: [second-order copies (tensor-core read-out)][first-order copies]
+static size_t state16_second(const fastmax_problem& p, int mats) {
+  return moments_tc_supports(p) ? up256(moments_tc_state_bytes(mats)) : 0;
+}
+size_t state16_bytes(const fastmax_problem& p, int n) {
   const int L = moments_chunk(p);
-  return up256(moments_tc_state_bytes(p.bh * ((n + L - 1) / L)));
+  const int mats = p.bh * ((n + L - 1) / L);
+  return state16_second(p, mats) + (first_tc_supports(p) ? up256(first_tc_copy_bytes(p, mats)) : 0);
 }
 
 bool moments_supports(const fastmax_problem& p) {
@@ -69,10 +73,15 @@ int moments_build_states(const Ctx& c, int n, const void* y, const void* z, cons
                          const float* delta, int ext, const void* gs, const float* dvec, float* states) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
-  if (!moments_tc_supports(p)) return moments_chunk_state(c, p.bh, n, L, y, z, den, delta, ext, states);
+  const bool tc2 = moments_tc_supports(p), tc1 = first_tc_supports(p);
   int rc;
-  // second-order rows on the tensor cores, first-order and constant rows on the CUDA cores
-  if ((rc = moments_tc_chunk_state(c, p.bh, n, L, y, ext ? gs : z, ext ? dvec : nullptr, states))) return rc;
+  // second-order rows: tensor cores where built, else everything on the CUDA cores
+  if (p.p == 2) {
+    if (!tc2) return moments_chunk_state(c, p.bh, n, L, y, z, den, delta, ext, states);
+    if ((rc = moments_tc_chunk_state(c, p.bh, n, L, y, ext ? gs : z, ext ? dvec : nullptr, states))) return rc;
+  }
+  // first-order and constant rows
+  if (tc1) return first_tc_chunk_state(c, p.bh, n, L, y, ext ? gs : z, ext ? dvec : nullptr, states);
   return moments_chunk_state(c, p.bh, n, L, y, z, den, delta, ext, states, 1);
 }
 
@@ -84,23 +93,50 @@ static int read_states(const Ctx& c, int mode, int n, int per_chunk, const void*
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   int rc;
-  const bool tc = moments_tc_supports(p);
-  if (tc) {
-    const int mats = p.bh * (per_chunk ? (n + L - 1) / L : 1);
+  const bool tc2 = moments_tc_supports(p);
+  const bool tc1 = first_tc_supports(p) && (p.p == 1 || tc2);
+  const int mats = p.bh * (per_chunk ? (n + L - 1) / L : 1);
+  if (tc2) {
     if ((rc = moments_tc_convert(c, mats, states, s16))) return rc;
     if ((rc = moments_tc_readout(c, mode, p.bh, n, L, per_chunk, x, ext ? gs : u, ext ? dvec : nullptr, s16,
                                  stats, out_a, den_a, out_b)))
       return rc;
   }
+  if (tc1) {
+    // first-order part on tensor cores; it adds to the second-order part when there is one
+    void* s1b = (char*)s16 + state16_second(p, mats);
+    if ((rc = first_tc_convert(c, mats, states, s1b))) return rc;
+    if (mode == 0 || mode == 2)
+      if ((rc = first_tc_readout(c, 0, p.bh, n, L, per_chunk, x, x, nullptr, states, s1b, stats, out_a, den_a,
+                                 tc2)))
+        return rc;
+    if (mode == 1 || mode == 2)
+      if ((rc = first_tc_readout(c, 1, p.bh, n, L, per_chunk, ext ? gs : u, x, ext ? dvec : nullptr, states,
+                                 s1b, stats, out_b, nullptr, tc2)))
+        return rc;
+    return FASTMAX_OK;
+  }
   if (mode == 0 || mode == 2)
     if ((rc = moments_readout(c, 0, p.bh, n, L, per_chunk, x, nullptr, nullptr, nullptr, 0, states, stats,
-                              out_a, den_a, tc)))
+                              out_a, den_a, tc2)))
       return rc;
   if (mode == 1 || mode == 2)
     if ((rc = moments_readout(c, 1, p.bh, n, L, per_chunk, x, u, den, delta, ext, states, stats, out_b,
-                              nullptr, tc)))
+                              nullptr, tc2)))
       return rc;
   return FASTMAX_OK;
+}
+
+// p = 1 on tensor cores without a score-form part: the read-out of the total state is the
+// result, so it is divided / rounded in the read-out kernel itself
+static bool first_is_whole(const fastmax_problem& p) { return p.p == 1 && !p.mask && first_tc_supports(p); }
+static int read_first_final(const Ctx& c, int type_b, int n, const void* tile, const void* x, const float* uvec,
+                            const float* total, void* s16, const stat_t* stats, int final, void* out,
+                            float* den_out, float* dots) {
+  int rc;
+  if ((rc = first_tc_convert(c, c.p.bh, total, s16))) return rc;
+  return first_tc_readout(c, type_b, c.p.bh, n, moments_chunk(c.p), 0, tile, x, uvec, total, s16, stats, nullptr,
+                          nullptr, 0, final, out, den_out, dots);
 }
 
 // ---- forward -----------------------------------------------------------------------
@@ -142,11 +178,13 @@ int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, c
   // unmasked: every query reads the total of all keys
   const int nchunk = (p.nk + L - 1) / L;
   if ((rc = moments_prefix(c, p.bh, nchunk, states, nullptr, total, 0, 0))) return rc;
+  if (o.out_f32 || o.o_stride != p.d)
+    return fail(FASTMAX_E_UNSUPPORTED, "the moment family writes the plain output layout only");
+  if (first_is_whole(p))
+    return read_first_final(c, 0, p.nq, q, q, nullptr, total, s16, stats, 1, o.out, o.den, nullptr);
   if ((rc = read_states(c, 0, p.nq, 0, q, nullptr, nullptr, nullptr, 0, nullptr, nullptr, total, s16, stats,
                         o_add, den_add, nullptr)))
     return rc;
-  if (o.out_f32 || o.o_stride != p.d)
-    return fail(FASTMAX_E_UNSUPPORTED, "the moment family writes the plain output layout only");
   return moments_finalize(c, p.bh, p.nq, o_add, den_add, nullptr, o.out, o.den, nullptr, 0);
 }
 
@@ -232,6 +270,20 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
     // unmasked: totals only, no score-form part
     if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, total, 0, 0))) return rc;
+    if (first_is_whole(p)) {
+      if ((rc = read_first_final(c, 1, p.nq, gs, q, dvec, total, s16, stats, 2, grad_q, nullptr,
+                                 p.normalize ? dots : nullptr)))
+        return rc;
+      if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
+      if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, total, 0, 0))) return rc;
+      if ((rc = read_first_final(c, 1, p.nk, v, k, nullptr, total, s16, stats, 2, grad_k, nullptr,
+                                 p.normalize ? dots + p.bh : nullptr)))
+        return rc;
+      if ((rc = read_first_final(c, 0, p.nk, k, k, nullptr, total, s16, stats, 2, grad_v, nullptr, nullptr)))
+        return rc;
+      if (p.normalize) return launch_norm_fixup(c, q, k, stats, dots, grad_q, grad_k);
+      return FASTMAX_OK;
+    }
     if ((rc = read_states(c, 1, p.nq, 0, q, grad_out, den, delta, 1, gs, dvec, total, s16, stats, nullptr,
                           nullptr, gq_add)))
       return rc;

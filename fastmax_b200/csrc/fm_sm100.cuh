@@ -292,6 +292,27 @@ __device__ __forceinline__ void umma_ss_mn_steps(uint32_t d_tmem, uint32_t a_lo,
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// NK K-steps of D[tmem] (+)= A[smem] B[smem] with A K-major (32 bytes per step inside a
+// 128-byte swizzle row) and B MN-major (16 K rows = 2048 bytes per step).
+template <int NK>
+__device__ __forceinline__ void umma_ss_kmn_steps(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                  uint32_t idesc, uint32_t accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < NK; ++ks) {
+    asm volatile(
+        "{\n"
+        ".reg .b64 da, db;\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "mov.b64 da, {%1, %3};\n"
+        "mov.b64 db, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo + ks * 2), "r"(b_lo + ks * 128), "r"(kDescHi), "r"(idesc),
+          "r"(ks == 0 ? accumulate : 1u)
+        : "memory");
+  }
+}
 // Arrive on `bar` once every tcgen05 operation this thread issued so far is done.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -340,4 +361,9 @@ __device__ __forceinline__ uint32_t pack_bf16_2(uint64_t v) {
 }
 
 }  // namespace sm100
+
+// Rank-3 tensor map over a (mats, rows, d) bf16 array with boxes of box_rows x 64 elements and
+// 128-byte swizzle; rows past `rows` read as zero.  Returns FASTMAX_OK or an error code.
+int tma_map_bf16(CUtensorMap* m, const void* base, size_t mats, size_t rows, int d, int box_rows);
+
 }  // namespace fm

@@ -30,7 +30,8 @@ def test_reference_vectors_through_the_moment_family(c):
 # bh, n, d, mask, p, normalize, chunk
 MOM = [(2, 700, 32, 1, 2, 1, 256), (2, 700, 32, 0, 2, 1, 256), (3, 1024, 32, 1, 1, 1, 256),
        (2, 600, 16, 1, 2, 0, 256), (1, 900, 64, 1, 2, 1, 256), (2, 520, 64, 0, 2, 0, 256),
-       (1, 600, 128, 1, 2, 0, 256), (2, 515, 128, 0, 1, 0, 256), (2, 1030, 64, 1, 2, 1, 512)]
+       (1, 600, 128, 1, 2, 0, 256), (2, 515, 128, 0, 1, 0, 256), (2, 1030, 64, 1, 2, 1, 512),
+       (2, 900, 64, 1, 1, 1, 256), (2, 700, 128, 1, 1, 1, 256), (3, 640, 64, 0, 1, 0, 256)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
