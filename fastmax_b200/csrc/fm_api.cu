@@ -180,8 +180,10 @@ unsigned long long fastmax_b200_launch_count(void) { return g_launches.load(); }
 
 int fastmax_b200_device_status(int* status, void* stream) {
   if (!status) return fail(FASTMAX_E_ARG, "status is NULL");
-  int a = 0, b = 0, f = 0, rc;
+  int a = 0, b = 0, f = 0, w = 0, rc;
   if ((rc = tc_status(&a, (cudaStream_t)stream))) return rc;
+  if ((rc = tc_wide_status(&w, (cudaStream_t)stream))) return rc;
+  if (!a) a = w;
   if ((rc = moments_tc_status(&b, (cudaStream_t)stream))) return rc;
   if ((rc = first_tc_status(&f, (cudaStream_t)stream))) return rc;
   *status = a ? a : (b ? b : f);

@@ -543,6 +543,8 @@ int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v,
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(gs) || !aligned16(grad_q) ||
       !aligned16(grad_k) || !aligned16(grad_v))
     return fail(FASTMAX_E_ARG, "the tensor-core family needs 16-byte aligned tensors");
+  if (dense_tc_wide_supports(p))
+    return dense_tc_wide_backward(c, q, k, v, gs, dvec, stats, dots, grad_q, grad_k, grad_v, ca);
   int rc;
   TcArgs a = base_args(c, stats);
   a.dvec = dvec;

@@ -1,0 +1,519 @@
+// Backward pass of the score form on the tcgen05 tensor cores, bf16, head dimension 64:
+// one CTA owns ONE 128-row tile and walks 64-column tiles that alternate between two
+// groups of compute warps ("ping-pong"), each with its own S / W / E / P regions in TMEM.
+//
+//   FUSED = 0   grad_q:  rows = queries (x = q, u = gs), columns = keys (y = k, z = v)
+//               E = f'(x.y) (u.z - dvec_row);          grad_q += E Y
+//   FUSED = 1   grad_k and grad_v in one pass: rows = keys (x = k, u = v), columns =
+//               queries (y = q, z = gs), reverse direction (column >= row - off)
+//               E = f'(x.y) (u.z - dvec_col), P = f(x.y);  grad_k += E Y,  grad_v += P Z
+//
+// Why this shape.  Per column tile the chain is S-MMA -> TMEM load -> polynomial on the CUDA
+// cores -> TMEM store -> accumulating MMA, and the round trip between the tensor pipe and the
+// CUDA cores (commit, barrier, tcgen05.ld latency) is as long as the MMAs themselves.  Two
+// groups working on alternate tiles keep two such chains in flight on the same rows, sixteen
+// compute warps (four per scheduler) hide the TMEM and FP32 latencies inside a chain, and
+// grad_k / grad_v share S, so a tile costs four products instead of five.
+//
+// TMEM columns: S[2] 0..127 | W[2] 128..255 | E[2] 256..319 (bf16 pairs) | P[2] 320..383 |
+// accumulator 384..447 | second accumulator 448..511.
+// Warps 0-7 are group 0 (even tiles), 8-15 group 1 (odd tiles); inside a group warp % 4 is
+// the TMEM lane quarter (32 rows) and (warp / 4) % 2 picks 32 of the 64 columns.  Warp 16 is
+// the TMA producer, warp 17 allocates TMEM and issues the S / W products, warp 18 issues the
+// accumulating products.
+// All waits are bounded; a wait that gives up records a status and the CTA winds down.
+#include <climits>
+#include <cstdlib>
+
+#include "fm_common.cuh"
+#include "fm_sm100.cuh"
+
+namespace fm {
+
+__device__ int g_wtc_status = 0;
+
+namespace {
+using namespace sm100;
+
+struct WArgs {
+  void* o;               // (heads, nrows, 64) bf16: grad_q, or grad_k when FUSED
+  void* o2;              // FUSED: grad_v
+  const float* o_add;    // fp32 rows added before rounding (may be null)
+  const float* o2_add;
+  const void* x;         // row operand in global memory (normalisation dots)
+  const float* dvec;     // (heads, nq)
+  float* dots;           // per head sum of o . x, or null
+  const stat_t* stat_q;
+  const stat_t* stat_k;
+  int nrows, ncols, off, mask, ntr, chunk;
+  float a0, a1, a2, lim;
+};
+
+constexpr int BM = 128, BN = 64, D = 64, NS = 8;
+constexpr int kThreads = 608;
+constexpr int kProducerWarp = 16, kIssuerWarp = 17, kAccIssuerWarp = 18, kComputeWarps = 16;
+constexpr int ROW_TILE = BM * 128, COL_TILE = BN * 128, STAGE = 2 * COL_TILE;
+constexpr int OFF_X = 0, OFF_U = ROW_TILE, OFF_ST = 2 * ROW_TILE;
+constexpr int OFF_VEC = OFF_ST + NS * STAGE;               // per compute warp 2 x 32 floats
+constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
+constexpr int NBAR = 2 + 2 * NS + 8;
+constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
+constexpr int SMEM = OFF_TMEM + 16 + 1024;
+constexpr int T_S = 0, T_W = 128, T_E = 256, T_P = 320, T_O = 384, T_O2 = 448;
+
+#ifdef FM_WIDE_TIMING
+__device__ unsigned long long g_wtime[16];
+#define TCK(var) const long long var = clock64()
+#define TADD(idx, a, b) tacc[idx] += (unsigned long long)((b) - (a))
+#else
+#define TCK(var)
+#define TADD(idx, a, b)
+#endif
+__device__ __forceinline__ void report(int code) { atomicCAS(&g_wtc_status, 0, code); }
+
+// One thread's accumulator row segment (NC fp32 columns from TMEM column tcol) -> bf16 global
+// row, with the optional fp32 addend; returns the dot product with the x row when wanted.
+template <int NC>
+__device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfloat16* dst,
+                                           const float* add, const __nv_bfloat16* xr) {
+  float part = 0.f;
+#pragma unroll
+  for (int c0 = 0; c0 < NC; c0 += 32) {
+    uint32_t ov[32];
+    tmem_ld32(taddr + c0, ov);
+    tmem_wait_ld();
+    if (row_ok) {
+#pragma unroll
+      for (int v8 = 0; v8 < 4; ++v8) {
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[v8 * 8 + e]);
+        if (add) {
+          const float4 a0 = __ldg((const float4*)(add + c0) + 2 * v8);
+          const float4 a1 = __ldg((const float4*)(add + c0) + 2 * v8 + 1);
+          f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
+          f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+        }
+        uint4 w;
+        w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
+        w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
+        ((uint4*)(dst + c0))[v8] = w;
+        if (xr) {
+          const uint4 xv = __ldg((const uint4*)(xr + c0) + v8);
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            part = fmaf(f[2 * e], __uint_as_float(xw[e] << 16), part);
+            part = fmaf(f[2 * e + 1], __uint_as_float(xw[e] & 0xFFFF0000u), part);
+          }
+        }
+      }
+    }
+  }
+  return part;
+}
+
+template <int FUSED>
+__global__ void __launch_bounds__(kThreads, 1)
+dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
+                     const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
+                     const WArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + OFF_BAR;
+  // barrier map: x | done | full[NS] | empty[NS] | s_full[2] | s_free[2] | p_full[2] | pv_done[2]
+  const uint32_t BAR_X = bar0, BAR_DONE = bar0 + 8;
+  auto BAR_FULL = [&](int s) { return bar0 + 8u * (2 + s); };
+  auto BAR_EMPTY = [&](int s) { return bar0 + 8u * (2 + NS + s); };
+  auto BAR_S = [&](int g) { return bar0 + 8u * (2 + 2 * NS + g); };
+  auto BAR_SFREE = [&](int g) { return bar0 + 8u * (4 + 2 * NS + g); };
+  auto BAR_P = [&](int g) { return bar0 + 8u * (6 + 2 * NS + g); };
+  auto BAR_PV = [&](int g) { return bar0 + 8u * (8 + 2 * NS + g); };
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + OFF_TMEM);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr bool rev = FUSED != 0;
+  // consecutive CTAs work on one head (its column tiles stay in L2); longest rows first
+  const int head = blockIdx.x / a.ntr;
+  const int pidx = blockIdx.x % a.ntr;
+  const int rt = rev ? pidx : a.ntr - 1 - pidx;
+  const int r0 = rt * BM;
+
+  const int ntile = (a.ncols + BN - 1) / BN;
+  int tb = 0, te = ntile;
+  if (a.mask) {
+    if (rev) tb = max(0, r0 - a.off) / BN;
+    else te = min(ntile, (min(r0 + BM - 1, a.nrows - 1) + a.off) / BN + 1);
+  }
+  if (a.chunk > 0) {  // the row tile lies in one chunk (chunk % 256 == 0)
+    const int cb = (r0 / a.chunk) * (a.chunk / BN), ce = cb + a.chunk / BN;
+    if (rev) te = min(te, ce);
+    else tb = cb;
+  }
+  const int J = max(te - tb, 0);
+
+  if (tid == 0) {
+    mbar_init(BAR_X, 1);
+    mbar_init(BAR_DONE, 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(BAR_FULL(s), 1);
+      mbar_init(BAR_EMPTY(s), 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(BAR_S(g), 1);
+      mbar_init(BAR_SFREE(g), kComputeWarps / 2);
+      mbar_init(BAR_P(g), kComputeWarps / 2);
+      mbar_init(BAR_PV(g), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == kIssuerWarp) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == kProducerWarp) {
+    // ================= TMA producer =================
+    if (lane == 0 && J > 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmU);
+      tma_prefetch_desc(&tmY);
+      tma_prefetch_desc(&tmZ);
+      mbar_expect_tx(BAR_X, 2 * ROW_TILE);
+      tma_load_3d(sbase + OFF_X, &tmX, BAR_X, 0, r0, head);
+      tma_load_3d(sbase + OFF_U, &tmU, BAR_X, 0, r0, head);
+    }
+    for (int j = 0; j < J; ++j) {
+      const int s = j % NS;
+      if (!mbar_wait(BAR_EMPTY(s), (((j / NS) & 1) ^ 1))) { report(1); break; }
+      if (lane == 0) {
+        mbar_expect_tx(BAR_FULL(s), STAGE);
+        const uint32_t dst = sbase + OFF_ST + s * STAGE;
+        tma_load_3d(dst, &tmY, BAR_FULL(s), 0, (tb + j) * BN, head);
+        tma_load_3d(dst + COL_TILE, &tmZ, BAR_FULL(s), 0, (tb + j) * BN, head);
+      }
+    }
+  } else if (warp == kIssuerWarp) {
+    // ================= MMA issuer =================
+    // The whole warp runs the loop (uniform control flow and operands); one elected lane
+    // executes the tcgen05 instructions.  S and W of tile j go to the TMEM regions of group
+    // j & 1 as soon as that group has copied tile j - 2 to registers, independently of the
+    // accumulating products, which the other issuer warp handles.
+    if (J > 0) {
+      constexpr uint32_t idescS = idesc_bf16(BM, BN, 0, 0);
+      const uint32_t x_lo = desc_lo(sbase + OFF_X, 16);
+      const uint32_t u_lo = desc_lo(sbase + OFF_U, 16);
+      const uint32_t st_k = desc_lo(sbase + OFF_ST, 16);         // stage 0, K-major view
+      bool ok = mbar_wait_warp(BAR_X, 0);
+      if (!ok) report(2);
+      tc_fence_after();
+#ifdef FM_WIDE_TIMING
+      unsigned long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+      for (int j = 0; ok && j < J; ++j) {
+        const int s = j % NS, g = j & 1;
+        TCK(s0k);
+        if (j >= 2 && !mbar_wait_warp(BAR_SFREE(g), (uint32_t)(((j >> 1) - 1) & 1))) { report(4); break; }
+        TCK(s1k);
+        TADD(3, s0k, s1k);
+        if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((j / NS) & 1))) { report(3); break; }
+        tc_fence_after();
+        TCK(s2k);
+        TADD(4, s1k, s2k);
+        const uint32_t y_lo = st_k + (uint32_t)s * (STAGE >> 4);
+        if (elect_one()) {
+          umma_ss_k64(tmem + T_S + g * 64, x_lo, y_lo, idescS);
+          umma_ss_k64(tmem + T_W + g * 64, u_lo, y_lo + (COL_TILE >> 4), idescS);
+          umma_commit(BAR_S(g));
+        }
+        __syncwarp();
+        TCK(s3k);
+        TADD(2, s2k, s3k);
+      }
+#ifdef FM_WIDE_TIMING
+      if (lane == 0)
+        for (int q = 2; q < 5; ++q) atomicAdd(&g_wtime[8 + q], tacc[q]);
+#endif
+    }
+    __syncwarp();
+  } else if (warp == kAccIssuerWarp) {
+    // ================= MMA issuer of the accumulating products =================
+    // The stage of tile j is known to be loaded and S / W of tile j complete once the
+    // group's P barrier has fired, so this warp waits on nothing else.
+    if (J > 0) {
+      constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
+      const uint32_t st_mn = desc_lo(sbase + OFF_ST, COL_TILE);  // stage 0, MN-major view
+#ifdef FM_WIDE_TIMING
+      unsigned long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+      for (int j = 0; j < J; ++j) {
+        const int s = j % NS, g = j & 1;
+        TCK(i0k);
+        if (!mbar_wait_warp(BAR_P(g), (uint32_t)((j >> 1) & 1))) { report(5); break; }
+        tc_fence_after();
+        TCK(i1k);
+        TADD(0, i0k, i1k);
+        const uint32_t y_mn = st_mn + (uint32_t)s * (STAGE >> 4);
+        if (elect_one()) {
+          umma_ts_steps<BN / 16>(tmem + T_O, tmem + T_E + g * 32, y_mn, idescO, j > 0 ? 1u : 0u);
+          if (FUSED)
+            umma_ts_steps<BN / 16>(tmem + T_O2, tmem + T_P + g * 32, y_mn + (COL_TILE >> 4), idescO,
+                                   j > 0 ? 1u : 0u);
+          umma_commit(BAR_PV(g));
+          umma_commit(BAR_EMPTY(s));
+          if (j + 1 == J) umma_commit(BAR_DONE);
+        }
+        __syncwarp();
+        TCK(i2k);
+        TADD(1, i1k, i2k);
+      }
+#ifdef FM_WIDE_TIMING
+      if (lane == 0)
+        for (int q = 0; q < 2; ++q) atomicAdd(&g_wtime[8 + q], tacc[q]);
+#endif
+    }
+    __syncwarp();
+  } else {
+    // ================= compute warps =================
+    const int gp = warp >> 3, cpart = (warp >> 2) & 1, qd = warp & 3;
+    const int row = r0 + qd * 32 + lane;
+    const bool row_ok = row < a.nrows;
+    const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
+    const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
+    const uint64_t A0v = pack2(A0, A0), A1v = pack2(A1, A1), A2v = pack2(A2, A2);
+    const uint64_t A2d = pack2(2.f * A2, 2.f * A2);
+    int limcol = a.ncols - 1, lowcol = 0;   // columns kept for this row: lowcol <= col <= limcol
+    if (a.mask) {
+      if (rev) lowcol = row - a.off;
+      else limcol = min(limcol, row + a.off);
+    }
+    const int wrow_lo = r0 + qd * 32, wrow_hi = wrow_lo + 31;
+    float dl_row = 0.f;
+    if (!rev && row_ok) dl_row = __ldg(a.dvec + (size_t)head * a.nrows + row);
+    const uint64_t ndl_row = pack2(-dl_row, -dl_row);
+    const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
+    float* myvec = (float*)(smem + OFF_VEC) + warp * 64;
+    // negated dvec of this lane's column in the warp's next tile, fetched one tile ahead
+    auto fetch_vec = [&](int j) -> float {
+      const int col = (tb + j) * BN + cpart * 32 + lane;
+      return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;
+    };
+    float nxt = rev ? fetch_vec(gp) : 0.f;
+    bool ok = true;
+#ifdef FM_WIDE_TIMING
+    unsigned long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+    for (int j = gp; j < J; j += 2) {
+      const int i = j >> 1;
+      const float cur = nxt;
+      if (rev) nxt = fetch_vec(j + 2);
+      TCK(c0k);
+      if (!mbar_wait(BAR_S(gp), (uint32_t)(i & 1))) { report(7); ok = false; break; }
+      tc_fence_after();
+      TCK(c1k);
+      TADD(0, c0k, c1k);
+      uint32_t sv[32], wv[32];
+      tmem_ld32(tl + T_S + gp * 64 + cpart * 32, sv);
+      tmem_ld32(tl + T_W + gp * 64 + cpart * 32, wv);
+      const float* vec = myvec + (i & 1) * 32;
+      if (rev) {
+        myvec[(i & 1) * 32 + lane] = cur;
+        __syncwarp();
+      }
+      tmem_wait_ld();
+      TCK(c2k);
+      TADD(1, c1k, c2k);
+      // S and W of this tile are in registers: the group's next tile may be issued
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_SFREE(gp));
+      const int c0 = (tb + j) * BN + cpart * 32;    // this warp's 32 columns
+      bool need_mask = (c0 + 32 > a.ncols);
+      if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
+      // the mask test stays outside the element loops so that each loop is one basic block
+      // whose sixteen independent pairs the compiler can interleave
+      uint32_t pe[16];
+      if (!need_mask) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+          const uint64_t ndl = rev ? ((const uint64_t*)vec)[e] : ndl_row;
+          pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+          const uint64_t ndl = rev ? ((const uint64_t*)vec)[e] : ndl_row;
+          const uint64_t e2 = mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl));
+          const int col = c0 + 2 * e;
+          float v0, v1;
+          unpack2(e2, v0, v1);
+          pe[e] = pack_bf16((col > limcol || col < lowcol) ? 0.f : v0,
+                            (col + 1 > limcol || col + 1 < lowcol) ? 0.f : v1);
+        }
+      }
+      TCK(c3k);
+      TADD(2, c2k, c3k);
+      // the group's previous products must have consumed E and P before they are overwritten
+      if (i > 0) {
+        if (!mbar_wait(BAR_PV(gp), (uint32_t)((i - 1) & 1))) { report(9); ok = false; break; }
+        tc_fence_after();
+      }
+      TCK(c4k);
+      TADD(3, c3k, c4k);
+      tmem_st16(tl + T_E + gp * 32 + cpart * 16, pe);
+      if (FUSED) {
+        uint32_t pp[16];
+        if (!need_mask) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+            pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+            const int col = c0 + 2 * e;
+            float v0, v1;
+            unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+            pp[e] = pack_bf16((col > limcol || col < lowcol) ? 0.f : v0,
+                              (col + 1 > limcol || col + 1 < lowcol) ? 0.f : v1);
+          }
+        }
+        tmem_st16(tl + T_P + gp * 32 + cpart * 16, pp);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_P(gp));
+      TCK(c5k);
+      TADD(4, c4k, c5k);
+      TADD(5, c0k, c0k + 1);
+    }
+#ifdef FM_WIDE_TIMING
+    if (warp == 0 && lane == 0)
+      for (int q = 0; q < 6; ++q) atomicAdd(&g_wtime[q], tacc[q]);
+#endif
+    // ---- epilogue: 32 accumulator columns per warp ----
+    if (ok && J > 0) {
+      if (!mbar_wait(BAR_DONE, 0)) { report(10); ok = false; }
+    }
+    tc_fence_after();
+    const int part4 = warp >> 2;
+    if (ok && J > 0 && (FUSED || part4 < 2)) {
+      const size_t grow = (size_t)head * a.nrows + (row_ok ? row : 0);
+      const bool second = FUSED && part4 >= 2;          // grad_v columns
+      const int cc = (part4 & 1) * 32;
+      const bool dots_here = !second && a.dots != nullptr;
+      const float* add = second ? a.o2_add : a.o_add;
+      const float part = store_row<32>(tl + (second ? T_O2 : T_O) + cc, row_ok,
+                                       (__nv_bfloat16*)(second ? a.o2 : a.o) + grow * D + cc,
+                                       add ? add + grow * D + cc : nullptr,
+                                       dots_here ? (const __nv_bfloat16*)a.x + grow * D + cc : nullptr);
+      if (dots_here) {
+        float sum = part;
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+        if (lane == 0) atomicAdd(a.dots + head, sum);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kIssuerWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int FUSED>
+int launch_wide(const Ctx& c, const char* name, const void* x, const void* u, const void* y,
+                const void* z, int nrows, int ncols, WArgs a) {
+  const int heads = c.p.bh;
+  if (heads == 0 || nrows == 0) return FASTMAX_OK;
+  CUtensorMap tx, tu, ty, tz;
+  int rc;
+  if ((rc = tma_map_bf16(&tx, x, heads, nrows, D, BM))) return rc;
+  if ((rc = tma_map_bf16(&tu, u, heads, nrows, D, BM))) return rc;
+  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, BN))) return rc;
+  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, BN))) return rc;
+  a.nrows = nrows;
+  a.ncols = ncols;
+  a.x = x;
+  a.ntr = (nrows + BM - 1) / BM;
+  FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   SMEM));
+  dim3 grid((unsigned)((size_t)heads * a.ntr));
+  FM_LAUNCH(name, c.stream,
+            (dense_tc_wide_kernel<FUSED><<<grid, kThreads, SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+}  // namespace
+
+// bf16, head dimension 64, bh == bhkv (the caller has checked the first and the last);
+// FASTMAX_B200_NO_WIDE=1 in the environment keeps the three-kernel backward.
+bool dense_tc_wide_supports(const fastmax_problem& p) {
+  static const bool off = [] {
+    const char* e = getenv("FASTMAX_B200_NO_WIDE");
+    return e && e[0] == '1';
+  }();
+  return !off && p.dtype == FASTMAX_BF16 && p.d == 64 && p.bh == p.bhkv;
+}
+
+int dense_tc_wide_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
+                           const float* dvec, const stat_t* stats, float* dots, void* grad_q,
+                           void* grad_k, void* grad_v, const ChunkAdd* ca) {
+  const fastmax_problem& p = c.p;
+  WArgs a = {};
+  a.stat_q = p.normalize ? stats : nullptr;
+  a.stat_k = p.normalize ? stats + p.bh : nullptr;
+  a.off = p.nk - p.nq;
+  a.mask = p.mask;
+  a.a0 = p.a0;
+  a.a1 = p.a1;
+  a.a2 = (p.p == 2) ? p.a2 : 0.f;
+  a.lim = p.lim;
+  a.dvec = dvec;
+  if (ca) a.chunk = ca->chunk;
+  int rc;
+  // grad_q: rows = queries, columns = keys
+  a.o = grad_q;
+  a.dots = p.normalize ? dots : nullptr;
+  a.o_add = ca ? ca->gq_add : nullptr;
+  if ((rc = launch_wide<0>(c, "fm_dense_tc_dq", q, gs, k, v, p.nq, p.nk, a))) return rc;
+  // grad_k and grad_v: rows = keys, columns = queries
+  a.o = grad_k;
+  a.o2 = grad_v;
+  a.dots = p.normalize ? dots + p.bh : nullptr;
+  a.o_add = ca ? ca->gk_add : nullptr;
+  a.o2_add = ca ? ca->gv_add : nullptr;
+  return launch_wide<1>(c, "fm_dense_tc_dkdv", k, v, q, gs, p.nk, p.nq, a);
+}
+
+int tc_wide_status(int* out, cudaStream_t stream) {
+  FM_CUDA_TRY(cudaMemcpyFromSymbolAsync(out, g_wtc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
+
+#ifdef FM_WIDE_TIMING
+extern "C" int fastmax_b200_debug_wide_times(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(g_wtime, z, sizeof(z));
+  } else {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_wtime, 16 * sizeof(unsigned long long));
+  }
+  return 0;
+}
+#endif
+
+}  // namespace fm

@@ -55,16 +55,34 @@ __device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok;
 }
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the
+// phase is incomplete (a waiting warp then costs no issue slots).
+__device__ __forceinline__ uint32_t mbar_try_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok;
+}
 // Bounded wait: gives up after about a second of SM clocks and returns false, so
 // a protocol error ends the kernel with an error status instead of hanging it.
+// The clock is read once per 16 suspended tries, so a waiting warp issues few instructions.
 constexpr long long kWaitLimitClocks = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try(bar, parity)) {
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try_suspend(bar, parity, 100000u)) return true;
     if (clock64() - t0 > kWaitLimitClocks) return false;
   }
-  return true;
 }
 
 // ---- TMA ----------------------------------------------------------------------
@@ -312,6 +330,24 @@ __device__ __forceinline__ void umma_ss_kmn_steps(uint32_t d_tmem, uint32_t a_lo
           "r"(ks == 0 ? accumulate : 1u)
         : "memory");
   }
+}
+// One lane of a converged warp (the same one every time).  MMA issue loops run on the whole
+// warp so that descriptors and addresses stay warp-uniform values; only the tcgen05
+// instructions themselves execute under this election.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+// Bounded wait by a whole warp with a warp-uniform result.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity));
 }
 // Arrive on `bar` once every tcgen05 operation this thread issued so far is done.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

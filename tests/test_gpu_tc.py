@@ -96,3 +96,45 @@ def test_unsupported_requests_fail_loudly():
         _cabi.forward(q, q, q, mask=True, normalize=False, p=2, impl="dense_tc")   # fp32
     with pytest.raises(RuntimeError):
         _cabi.forward(q.bfloat16(), q.bfloat16(), q.bfloat16(), mask=True, normalize=False, p=2, impl="moments_tc")
+
+
+_NARROW_CHILD = r"""
+import sys, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from gpu_util import assert_close, oracle, run_cabi
+from fastmax_b200 import _cabi
+for bh, nq, nk, mask, p, norm in [(2, 257, 257, 1, 2, 1), (2, 70, 100, 1, 2, 1), (2, 300, 300, 0, 1, 0)]:
+    g = torch.Generator().manual_seed(nq)
+    q, go = torch.randn(1, bh, nq, 64, generator=g), torch.randn(1, bh, nq, 64, generator=g)
+    k, v = torch.randn(1, bh, nk, 64, generator=g), torch.randn(1, bh, nk, 64, generator=g)
+    if not norm:
+        q, k = q / 8, k / 8
+    kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    _cabi.profile(True)
+    got, _ = run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", **kw)
+    names = {n for n, _ in _cabi.profile_records()}
+    _cabi.profile(False)
+    assert "fm_dense_tc_dv" in names and "fm_dense_tc_dkdv" not in names, names
+    assert _cabi.device_status() == 0
+    assert_close(got, oracle(q, k, v, go, torch.bfloat16, dense=True, **kw), torch.bfloat16, "narrow")
+print("NARROW-OK")
+"""
+
+
+def test_three_kernel_backward_stays_correct_when_the_fused_one_is_switched_off():
+    """FASTMAX_B200_NO_WIDE=1 is read once per process, so the check runs in a child."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, FASTMAX_B200_NO_WIDE="1")
+    r = subprocess.run([sys.executable, "-c", _NARROW_CHILD, root], env=env, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0 and "NARROW-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_fused_backward_is_the_default_for_head_dimension_64():
+    q, k, v, go = [randn(1, 2, 384, 64, seed=s) for s in (11, 12, 13, 14)]
+    _cabi.profile(True)
+    run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", mask=1, normalize=1, p=2)
+    names = {n for n, _ in _cabi.profile_records()}
+    _cabi.profile(False)
+    assert {"fm_dense_tc_dq", "fm_dense_tc_dkdv"} <= names and "fm_dense_tc_dv" not in names, names
