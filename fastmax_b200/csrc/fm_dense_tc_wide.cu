@@ -61,14 +61,6 @@ constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
 constexpr int SMEM = OFF_TMEM + 16 + 1024;
 constexpr int T_S = 0, T_W = 128, T_E = 256, T_P = 320, T_O = 384, T_O2 = 448;
 
-#ifdef FM_WIDE_TIMING
-__device__ unsigned long long g_wtime[16];
-#define TCK(var) const long long var = clock64()
-#define TADD(idx, a, b) tacc[idx] += (unsigned long long)((b) - (a))
-#else
-#define TCK(var)
-#define TADD(idx, a, b)
-#endif
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_wtc_status, 0, code); }
 
 // One thread's accumulator row segment (NC fp32 columns from TMEM column tcol) -> bf16 global
@@ -209,19 +201,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       bool ok = mbar_wait_warp(BAR_X, 0);
       if (!ok) report(2);
       tc_fence_after();
-#ifdef FM_WIDE_TIMING
-      unsigned long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
       for (int j = 0; ok && j < J; ++j) {
         const int s = j % NS, g = j & 1;
-        TCK(s0k);
         if (j >= 2 && !mbar_wait_warp(BAR_SFREE(g), (uint32_t)(((j >> 1) - 1) & 1))) { report(4); break; }
-        TCK(s1k);
-        TADD(3, s0k, s1k);
         if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((j / NS) & 1))) { report(3); break; }
         tc_fence_after();
-        TCK(s2k);
-        TADD(4, s1k, s2k);
         const uint32_t y_lo = st_k + (uint32_t)s * (STAGE >> 4);
         if (elect_one()) {
           umma_ss_k64(tmem + T_S + g * 64, x_lo, y_lo, idescS);
@@ -229,13 +213,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
           umma_commit(BAR_S(g));
         }
         __syncwarp();
-        TCK(s3k);
-        TADD(2, s2k, s3k);
       }
-#ifdef FM_WIDE_TIMING
-      if (lane == 0)
-        for (int q = 2; q < 5; ++q) atomicAdd(&g_wtime[8 + q], tacc[q]);
-#endif
     }
     __syncwarp();
   } else if (warp == kAccIssuerWarp) {
@@ -245,16 +223,10 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     if (J > 0) {
       constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
       const uint32_t st_mn = desc_lo(sbase + OFF_ST, COL_TILE);  // stage 0, MN-major view
-#ifdef FM_WIDE_TIMING
-      unsigned long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
       for (int j = 0; j < J; ++j) {
         const int s = j % NS, g = j & 1;
-        TCK(i0k);
         if (!mbar_wait_warp(BAR_P(g), (uint32_t)((j >> 1) & 1))) { report(5); break; }
         tc_fence_after();
-        TCK(i1k);
-        TADD(0, i0k, i1k);
         const uint32_t y_mn = st_mn + (uint32_t)s * (STAGE >> 4);
         if (elect_one()) {
           umma_ts_steps<BN / 16>(tmem + T_O, tmem + T_E + g * 32, y_mn, idescO, j > 0 ? 1u : 0u);
@@ -266,13 +238,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
           if (j + 1 == J) umma_commit(BAR_DONE);
         }
         __syncwarp();
-        TCK(i2k);
-        TADD(1, i1k, i2k);
       }
-#ifdef FM_WIDE_TIMING
-      if (lane == 0)
-        for (int q = 0; q < 2; ++q) atomicAdd(&g_wtime[8 + q], tacc[q]);
-#endif
     }
     __syncwarp();
   } else {
@@ -302,18 +268,12 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     };
     float nxt = rev ? fetch_vec(gp) : 0.f;
     bool ok = true;
-#ifdef FM_WIDE_TIMING
-    unsigned long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
     for (int j = gp; j < J; j += 2) {
       const int i = j >> 1;
       const float cur = nxt;
       if (rev) nxt = fetch_vec(j + 2);
-      TCK(c0k);
       if (!mbar_wait(BAR_S(gp), (uint32_t)(i & 1))) { report(7); ok = false; break; }
       tc_fence_after();
-      TCK(c1k);
-      TADD(0, c0k, c1k);
       uint32_t sv[32], wv[32];
       tmem_ld32(tl + T_S + gp * 64 + cpart * 32, sv);
       tmem_ld32(tl + T_W + gp * 64 + cpart * 32, wv);
@@ -323,8 +283,6 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         __syncwarp();
       }
       tmem_wait_ld();
-      TCK(c2k);
-      TADD(1, c1k, c2k);
       // S and W of this tile are in registers: the group's next tile may be issued
       tc_fence_before();
       __syncwarp();
@@ -355,15 +313,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                             (col + 1 > limcol || col + 1 < lowcol) ? 0.f : v1);
         }
       }
-      TCK(c3k);
-      TADD(2, c2k, c3k);
       // the group's previous products must have consumed E and P before they are overwritten
       if (i > 0) {
         if (!mbar_wait(BAR_PV(gp), (uint32_t)((i - 1) & 1))) { report(9); ok = false; break; }
         tc_fence_after();
       }
-      TCK(c4k);
-      TADD(3, c3k, c4k);
       tmem_st16(tl + T_E + gp * 32 + cpart * 16, pe);
       if (FUSED) {
         uint32_t pp[16];
@@ -390,14 +344,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR_P(gp));
-      TCK(c5k);
-      TADD(4, c4k, c5k);
-      TADD(5, c0k, c0k + 1);
     }
-#ifdef FM_WIDE_TIMING
-    if (warp == 0 && lane == 0)
-      for (int q = 0; q < 6; ++q) atomicAdd(&g_wtime[q], tacc[q]);
-#endif
     // ---- epilogue: 32 accumulator columns per warp ----
     if (ok && J > 0) {
       if (!mbar_wait(BAR_DONE, 0)) { report(10); ok = false; }
@@ -503,17 +450,5 @@ int tc_wide_status(int* out, cudaStream_t stream) {
   return FASTMAX_OK;
 }
 
-#ifdef FM_WIDE_TIMING
-extern "C" int fastmax_b200_debug_wide_times(unsigned long long* out, int reset) {
-  if (reset) {
-    unsigned long long z[16] = {0};
-    cudaMemcpyToSymbol(g_wtime, z, sizeof(z));
-  } else {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_wtime, 16 * sizeof(unsigned long long));
-  }
-  return 0;
-}
-#endif
 
 }  // namespace fm
