@@ -205,7 +205,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     const int g = warp - 9;
     const int tbg = g ? tb1 : tb0, teg = g ? te1 : te0;
     const int J = (g == 0 || act1) ? teg - tbg : 0;
-    if (lane == 0 && J > 0) {
+    // the whole warp runs the loop (uniform control flow and operands); one elected lane
+    // executes the tcgen05 instructions
+    if (J > 0) {
       constexpr uint32_t idescS = idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
       static_assert(C::T_O + D <= 256 || C::NG == 1, "accumulator does not fit the group's TMEM columns");
@@ -216,43 +218,49 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       const uint32_t st_mn = desc_lo(sbase + C::OFF_ST, C::COL_SUB);      // stage 0, MN-major view
       // the other group also reads tile t unless t is outside its range
       const int otb = g ? tb0 : tb1, ote = g ? te0 : te1;
-      bool ok = mbar_wait(BAR_X(), 0);
+      bool ok = mbar_wait_warp(BAR_X(), 0);
       if (!ok) report(2);
       tc_fence_after();
       auto issue_S = [&](int t) -> bool {
         const int k = t - tb, s = k % NS;
-        if (!mbar_wait(BAR_FULL(s), (uint32_t)((k / NS) & 1))) { report(3); return false; }
+        if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((k / NS) & 1))) { report(3); return false; }
         tc_fence_after();
         const uint32_t y_lo = st_k + (uint32_t)s * (C::STAGE >> 4);
-#pragma unroll
-        for (int sub = 0; sub < C::NSUB; ++sub)
-          umma_ss_k64(tg + C::T_S, x_lo + sub * (C::ROW_SUB >> 4), y_lo + sub * (C::COL_SUB >> 4), idescS, sub > 0);
-        if (MODE == OP_B) {
+        if (elect_one()) {
 #pragma unroll
           for (int sub = 0; sub < C::NSUB; ++sub)
-            umma_ss_k64(tg + C::T_W, u_lo + sub * (C::ROW_SUB >> 4),
-                        y_lo + (C::COL_TILE >> 4) + sub * (C::COL_SUB >> 4), idescS, sub > 0);
+            umma_ss_k64(tg + C::T_S, x_lo + sub * (C::ROW_SUB >> 4), y_lo + sub * (C::COL_SUB >> 4), idescS, sub > 0);
+          if (MODE == OP_B) {
+#pragma unroll
+            for (int sub = 0; sub < C::NSUB; ++sub)
+              umma_ss_k64(tg + C::T_W, u_lo + sub * (C::ROW_SUB >> 4),
+                          y_lo + (C::COL_TILE >> 4) + sub * (C::COL_SUB >> 4), idescS, sub > 0);
+          }
+          umma_commit(BAR_S(g));
         }
-        umma_commit(BAR_S(g));
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_S(tbg);
       for (int j = 0; ok && j < J; ++j) {
         const int t = tbg + j;
         if (j + 1 < J) {
-          if (!mbar_wait(BAR_SFREE(g), (uint32_t)(j & 1))) { report(4); ok = false; break; }
+          if (!mbar_wait_warp(BAR_SFREE(g), (uint32_t)(j & 1))) { report(4); ok = false; break; }
           if (!issue_S(t + 1)) { ok = false; break; }
         }
-        if (!mbar_wait(BAR_P(g), (uint32_t)(j & 1))) { report(5); ok = false; break; }
+        if (!mbar_wait_warp(BAR_P(g), (uint32_t)(j & 1))) { report(5); ok = false; break; }
         tc_fence_after();
         const int s = (t - tb) % NS;
         // OP_A multiplies by the Z tile (second half of the stage), OP_B by the Y tile
         const uint32_t b_lo = st_mn + (uint32_t)s * (C::STAGE >> 4) + ((MODE == OP_A) ? (C::COL_TILE >> 4) : 0);
-        umma_ts_steps<BN / 16>(tg + C::T_O, tg + C::T_P, b_lo, idescO, j > 0 ? 1u : 0u);
-        umma_commit(BAR_PV(g));
-        // the ring stage is free once both groups' MMAs on it are done (2 arrivals)
-        umma_commit(BAR_EMPTY(s));
-        if (t < otb || t >= ote) umma_commit(BAR_EMPTY(s));
+        if (elect_one()) {
+          umma_ts_steps<BN / 16>(tg + C::T_O, tg + C::T_P, b_lo, idescO, j > 0 ? 1u : 0u);
+          umma_commit(BAR_PV(g));
+          // the ring stage is free once both groups' MMAs on it are done (2 arrivals)
+          umma_commit(BAR_EMPTY(s));
+          if (t < otb || t >= ote) umma_commit(BAR_EMPTY(s));
+        }
+        __syncwarp();
       }
     }
     __syncwarp();
