@@ -273,10 +273,16 @@ def run_ours(args):
         if dom is not None:
             cnt, tot = per[dom]
             kind = dom.rsplit("_", 1)[-1]
+            # DRAM bytes per token-head of the score kernels (bf16, d = 64), from the ncu capture of the
+            # small case summarised under profiles/: heads are processed one after another, so every
+            # re-read of a head's tiles hits L2 and the traffic grows in proportion to heads x tokens
+            ncu_bytes = {"fm_dense_tc_fwd": 484.5, "fm_dense_tc_dq": 619.9, "fm_dense_tc_dkdv": 728.4}
+            traffic = ncu_bytes[dom] * bh * N if (dom in ncu_bytes and D == 64 and dt == "bf16") else None
             if kind in flops_of:
                 achieved = flops_of[kind] * bh * N / (tot / cnt * 1e-3) / 1e12
                 roof = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
-                        "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
+                        "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": traffic,
+                        "traffic_source": "ncu dram bytes of a small case scaled by heads x tokens" if traffic else None,
                         "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "ms_per_launch": tot / cnt,
                         "alg_flops_per_launch": flops_of[kind] * bh * N}
             else:
