@@ -291,26 +291,31 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       bool need_mask = (c0 + 32 > a.ncols);
       if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
       // the mask test stays outside the element loops so that each loop is one basic block
-      // whose sixteen independent pairs the compiler can interleave
-      uint32_t pe[16];
+      // whose sixteen independent pairs the compiler can interleave; E and P of a pair are
+      // formed together so that S and W die pair by pair
+      uint32_t pe[16], pp[FUSED ? 16 : 1];
       if (!need_mask) {
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
           const uint64_t ndl = rev ? ((const uint64_t*)vec)[e] : ndl_row;
           pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
+          if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
           const uint64_t ndl = rev ? ((const uint64_t*)vec)[e] : ndl_row;
-          const uint64_t e2 = mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl));
           const int col = c0 + 2 * e;
+          const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
           float v0, v1;
-          unpack2(e2, v0, v1);
-          pe[e] = pack_bf16((col > limcol || col < lowcol) ? 0.f : v0,
-                            (col + 1 > limcol || col + 1 < lowcol) ? 0.f : v1);
+          unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
+          pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+          if (FUSED) {
+            unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+            pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+          }
         }
       }
       // the group's previous products must have consumed E and P before they are overwritten
@@ -319,27 +324,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         tc_fence_after();
       }
       tmem_st16(tl + T_E + gp * 32 + cpart * 16, pe);
-      if (FUSED) {
-        uint32_t pp[16];
-        if (!need_mask) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-            pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-            const int col = c0 + 2 * e;
-            float v0, v1;
-            unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
-            pp[e] = pack_bf16((col > limcol || col < lowcol) ? 0.f : v0,
-                              (col + 1 > limcol || col + 1 < lowcol) ? 0.f : v1);
-          }
-        }
-        tmem_st16(tl + T_P + gp * 32 + cpart * 16, pp);
-      }
+      if constexpr (FUSED) tmem_st16(tl + T_P + gp * 32 + cpart * 16, pp);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
