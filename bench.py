@@ -241,7 +241,7 @@ def run_ours(args):
     host_out = [torch.empty_like(h).pin_memory() for h in host_in]
     del q, k, v, go
     torch.cuda.empty_cache()
-    pipe = HostPipeline(bh, N, D, dtype, dev, heads_per_group=64, **kw)
+    pipe = HostPipeline(bh, N, D, dtype, dev, heads_per_group=args.e2e_group, **kw)
 
     def e2e_step():
         pipe.run(*host_in, *host_out)
@@ -407,6 +407,8 @@ def main():
     ap.add_argument("--family", default="auto", choices=["auto", "dense_ffma", "dense_tc", "moments_ffma"],
                     help="kernel family to force (default: the library's own choice)")
     ap.add_argument("--chunk", type=int, default=0, help="moment family: tokens per chunk (0 = default)")
+    ap.add_argument("--e2e-group", type=int, default=32,
+                    help="batch*head units per group of the host-buffer pipeline of the e2e leg")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

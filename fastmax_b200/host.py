@@ -3,8 +3,10 @@
 Batch*head units are independent, so a problem whose q, k, v and upstream gradient sit in
 (pinned) host memory is streamed through the GPU in groups of heads: while one group is
 being computed, the next group's inputs are on their way in and the previous group's
-results on their way out (three CUDA streams, two sets of device buffers).  The step then
-costs about max(host->device time, device time, device->host time) instead of their sum.
+results on their way out (three CUDA streams, three sets of device buffers).  A set's input
+buffers may be refilled as soon as its kernels are done, its output buffers are rewritten only
+after they have left the device, so the step costs about max(host->device time, device time,
+device->host time) instead of their sum.
 The reference has no host-memory path; its wrapper expects device tensors (example.py:8-50).
 """
 from __future__ import annotations
@@ -21,6 +23,8 @@ class HostPipeline:
     ``run(q, k, v, grad_out, out, grad_q, grad_k, grad_v)`` with (bh, n, d) pinned host tensors
     (the last four are written).  Causal or unmasked self-attention (same n for q and k)."""
 
+    SETS = 3
+
     def __init__(self, bh, n, d, dtype, device, heads_per_group=64, **kw):
         self.dev = torch.device(device)
         self.kw = dict(kw)
@@ -31,7 +35,7 @@ class HostPipeline:
             probe = torch.empty(g, n, d, dtype=dtype, device=self.dev)
             fwd_b, bwd_b, st_b = _cabi.workspace_bytes(probe, probe, **self.kw)
             self.sets = []
-            for _ in range(2):
+            for _ in range(self.SETS):
                 t = lambda: torch.empty(g, n, d, dtype=dtype, device=self.dev)
                 self.sets.append(dict(
                     q=t(), k=t(), v=t(), go=t(), out=t(), grad_q=t(), grad_k=t(), grad_v=t(),
@@ -39,9 +43,9 @@ class HostPipeline:
                     stats=torch.empty(st_b, dtype=torch.uint8, device=self.dev),
                     workspace=torch.empty(max(fwd_b, bwd_b, 1), dtype=torch.uint8, device=self.dev)))
             self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
-            self.ev_in = [torch.cuda.Event() for _ in range(2)]
-            self.ev_cmp = [torch.cuda.Event() for _ in range(2)]
-            self.ev_out = [torch.cuda.Event() for _ in range(2)]
+            self.ev_in = [torch.cuda.Event() for _ in range(self.SETS)]
+            self.ev_cmp = [torch.cuda.Event() for _ in range(self.SETS)]
+            self.ev_out = [torch.cuda.Event() for _ in range(self.SETS)]
         torch.cuda.synchronize(self.dev)
 
     def run(self, q, k, v, go, out, gq, gk, gv):
@@ -51,16 +55,18 @@ class HostPipeline:
         for i, lo in enumerate(range(0, self.bh, self.group)):
             hi = min(lo + self.group, self.bh)
             m = hi - lo
-            b = i % 2
+            b = i % self.SETS
             S = self.sets[b]
             with torch.cuda.stream(self.s_in):
-                # the buffers of this set are free once their previous results left the device
-                self.s_in.wait_event(self.ev_out[b])
+                # the input buffers of this set are free once its previous kernels are done
+                self.s_in.wait_event(self.ev_cmp[b])
                 for name, src in (("q", q), ("k", k), ("v", v), ("go", go)):
                     S[name][:m].copy_(src[lo:hi], non_blocking=True)
                 self.ev_in[b].record(self.s_in)
             with torch.cuda.stream(self.s_cmp):
                 self.s_cmp.wait_event(self.ev_in[b])
+                # ... and its output buffers once their previous contents have left the device
+                self.s_cmp.wait_event(self.ev_out[b])
                 view = {n_: S[n_][:m] for n_ in ("q", "k", "v", "go", "out", "grad_q", "grad_k", "grad_v", "den")}
                 bufs = dict(out=view["out"], den=view["den"], stats=S["stats"], workspace=S["workspace"],
                             grad_q=view["grad_q"], grad_k=view["grad_k"], grad_v=view["grad_v"])
