@@ -19,8 +19,8 @@
 // accumulator 384..447 | second accumulator 448..511.
 // Warps 0-7 are group 0 (even tiles), 8-15 group 1 (odd tiles); inside a group warp % 4 is
 // the TMEM lane quarter (32 rows) and (warp / 4) % 2 picks 32 of the 64 columns.  Warp 16 is
-// the TMA producer, warp 17 allocates TMEM and issues the S / W products, warp 18 issues the
-// accumulating products.
+// the TMA producer, warps 17 and 18 issue the S / W products of group 0 and group 1 (warp 17
+// also allocates TMEM), warp 19 issues the accumulating products.
 // All waits are bounded; a wait that gives up records a status and the CTA winds down.
 #include <climits>
 #include <cstdlib>
@@ -50,8 +50,8 @@ struct WArgs {
 };
 
 constexpr int BM = 128, BN = 64, D = 64, NS = 8;
-constexpr int kThreads = 608;
-constexpr int kProducerWarp = 16, kIssuerWarp = 17, kAccIssuerWarp = 18, kComputeWarps = 16;
+constexpr int kThreads = 640;
+constexpr int kProducerWarp = 16, kIssuerWarp = 17, kAccIssuerWarp = 19, kComputeWarps = 16;  // warps 17, 18: S / W issuers
 constexpr int ROW_TILE = BM * 128, COL_TILE = BN * 128, STAGE = 2 * COL_TILE;
 constexpr int OFF_X = 0, OFF_U = ROW_TILE, OFF_ST = 2 * ROW_TILE;
 constexpr int OFF_VEC = OFF_ST + NS * STAGE;               // per compute warp 2 x 32 floats
@@ -187,8 +187,8 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         tma_load_3d(dst + COL_TILE, &tmZ, BAR_FULL(s), 0, (tb + j) * BN, head);
       }
     }
-  } else if (warp == kIssuerWarp) {
-    // ================= MMA issuer =================
+  } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
+    // ================= MMA issuers of the S / W products, one per group =================
     // The whole warp runs the loop (uniform control flow and operands); one elected lane
     // executes the tcgen05 instructions.  S and W of tile j go to the TMEM regions of group
     // j & 1 as soon as that group has copied tile j - 2 to registers, independently of the
@@ -201,8 +201,9 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       bool ok = mbar_wait_warp(BAR_X, 0);
       if (!ok) report(2);
       tc_fence_after();
-      for (int j = 0; ok && j < J; ++j) {
-        const int s = j % NS, g = j & 1;
+      const int g = warp - kIssuerWarp;
+      for (int j = g; ok && j < J; j += 2) {
+        const int s = j % NS;
         if (j >= 2 && !mbar_wait_warp(BAR_SFREE(g), (uint32_t)(((j >> 1) - 1) & 1))) { report(4); break; }
         if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((j / NS) & 1))) { report(3); break; }
         tc_fence_after();
@@ -294,11 +295,13 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       // whose sixteen independent pairs the compiler can interleave; E and P of a pair are
       // formed together so that S and W die pair by pair
       uint32_t pe[16], pp[FUSED ? 16 : 1];
+      ulonglong2 nd2 = make_ulonglong2(0ull, 0ull);
       if (!need_mask) {
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          const uint64_t ndl = rev ? ((const uint64_t*)vec)[e] : ndl_row;
+          if (rev && (e & 1) == 0) nd2 = ((const ulonglong2*)vec)[e >> 1];   // four column values per load
+          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
           pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
           if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
         }
@@ -306,7 +309,8 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          const uint64_t ndl = rev ? ((const uint64_t*)vec)[e] : ndl_row;
+          if (rev && (e & 1) == 0) nd2 = ((const ulonglong2*)vec)[e >> 1];
+          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
           const int col = c0 + 2 * e;
           const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
           float v0, v1;
