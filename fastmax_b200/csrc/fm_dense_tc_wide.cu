@@ -61,6 +61,12 @@ constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
 constexpr int SMEM = OFF_TMEM + 16 + 1024;
 constexpr int T_S = 0, T_W = 128, T_E = 256, T_P = 320, T_O = 384, T_O2 = 448;
 
+// 16 bytes from shared memory by shared-window address (keeps the load off the generic path)
+__device__ __forceinline__ ulonglong2 lds_v2(uint32_t saddr) {
+  ulonglong2 r;
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(r.x), "=l"(r.y) : "r"(saddr) : "memory");
+  return r;
+}
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_wtc_status, 0, code); }
 
 // One thread's accumulator row segment (NC fp32 columns from TMEM column tcol) -> bf16 global
@@ -262,6 +268,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     const uint64_t ndl_row = pack2(-dl_row, -dl_row);
     const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
     float* myvec = (float*)(smem + OFF_VEC) + warp * 64;
+    const uint32_t myvec_s = sbase + OFF_VEC + warp * 256;
     // negated dvec of this lane's column in the warp's next tile, fetched one tile ahead
     auto fetch_vec = [&](int j) -> float {
       const int col = (tb + j) * BN + cpart * 32 + lane;
@@ -278,7 +285,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       uint32_t sv[32], wv[32];
       tmem_ld32(tl + T_S + gp * 64 + cpart * 32, sv);
       tmem_ld32(tl + T_W + gp * 64 + cpart * 32, wv);
-      const float* vec = myvec + (i & 1) * 32;
+      const uint32_t vec_s = myvec_s + (i & 1) * 128;   // shared-window address of this tile's slot
       if (rev) {
         myvec[(i & 1) * 32 + lane] = cur;
         __syncwarp();
@@ -300,7 +307,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if (rev && (e & 1) == 0) nd2 = ((const ulonglong2*)vec)[e >> 1];   // four column values per load
+          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
           const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
           pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
           if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
@@ -309,7 +316,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if (rev && (e & 1) == 0) nd2 = ((const ulonglong2*)vec)[e >> 1];
+          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
           const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
           const int col = c0 + 2 * e;
           const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
