@@ -109,11 +109,13 @@ int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v,
                       void* grad_k, void* grad_v, const ChunkAdd* ca = nullptr);
 // Copies the device-side protocol status word to *out (synchronises the stream).
 int tc_status(int* out, cudaStream_t stream);
-// Backward with 128-column tiles and grad_k / grad_v in one kernel (fm_dense_tc_wide.cu): d == 64.
+// Ping-pong kernels for d == 64 (fm_dense_tc_wide.cu): forward, grad_q, and grad_k / grad_v in one kernel.
 bool dense_tc_wide_supports(const fastmax_problem& p);
 int dense_tc_wide_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
                            const float* dvec, const stat_t* stats, float* dots, void* grad_q,
                            void* grad_k, void* grad_v, const ChunkAdd* ca = nullptr);
+int dense_tc_wide_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
+                          void* out, float* den, const ChunkAdd* ca = nullptr);
 int tc_wide_status(int* out, cudaStream_t stream);
 
 // Optional coupling of the score-form kernels to the moment-state form: columns are

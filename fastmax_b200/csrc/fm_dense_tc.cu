@@ -535,6 +535,7 @@ int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,
                      const stat_t* stats, void* out, float* den, const ChunkAdd* ca) {
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
     return fail(FASTMAX_E_ARG, "the tensor-core family needs 16-byte aligned tensors");
+  if (dense_tc_wide_supports(c.p)) return dense_tc_wide_forward(c, q, k, v, stats, out, den, ca);
   TcArgs a = base_args(c, stats);
   a.o = out;
   a.den_out = den;

@@ -1,12 +1,16 @@
-// Backward pass of the score form on the tcgen05 tensor cores, bf16, head dimension 64:
-// one CTA owns ONE 128-row tile and walks 64-column tiles that alternate between two
-// groups of compute warps ("ping-pong"), each with its own S / W / E / P regions in TMEM.
+// Score form on the tcgen05 tensor cores, bf16, head dimension 64: one CTA owns ONE
+// 128-row tile and walks column tiles that alternate between two groups of compute warps
+// ("ping-pong"), each with its own S / W / E / P regions in TMEM.
 //
-//   FUSED = 0   grad_q:  rows = queries (x = q, u = gs), columns = keys (y = k, z = v)
-//               E = f'(x.y) (u.z - dvec_row);          grad_q += E Y
-//   FUSED = 1   grad_k and grad_v in one pass: rows = keys (x = k, u = v), columns =
-//               queries (y = q, z = gs), reverse direction (column >= row - off)
-//               E = f'(x.y) (u.z - dvec_col), P = f(x.y);  grad_k += E Y,  grad_v += P Z
+//   MODE_DQ    grad_q:  rows = queries (x = q, u = gs), columns = keys (y = k, z = v)
+//              E = f'(x.y) (u.z - dvec_row);          grad_q += E Y
+//   MODE_DKDV  grad_k and grad_v in one pass: rows = keys (x = k, u = v), columns =
+//              queries (y = q, z = gs), reverse direction (column >= row - off)
+//              E = f'(x.y) (u.z - dvec_col), P = f(x.y);  grad_k += E Y,  grad_v += P Z
+//   MODE_FWD   forward: rows = queries (x = q), columns = keys (y = k, z = v)
+//              P = f(x.y);  O += P Z,  den = row sums of P,  out = O / den
+// The gradients use 64-column tiles (S and W double-buffered fill TMEM); the forward has no
+// W and uses 128-column tiles, which halves the barrier hand-offs per score.
 //
 // Why this shape.  Per column tile the chain is S-MMA -> TMEM load -> polynomial on the CUDA
 // cores -> TMEM store -> accumulating MMA, and the round trip between the tensor pipe and the
@@ -16,9 +20,9 @@
 // grad_k / grad_v share S, so a tile costs four products instead of five.
 //
 // TMEM columns: S[2] 0..127 | W[2] 128..255 | E[2] 256..319 (bf16 pairs) | P[2] 320..383 |
-// accumulator 384..447 | second accumulator 448..511.
+// accumulator 384..447 | second accumulator 448..511 (forward: S[2] 0..255 | P[2] 256..383).
 // Warps 0-7 are group 0 (even tiles), 8-15 group 1 (odd tiles); inside a group warp % 4 is
-// the TMEM lane quarter (32 rows) and (warp / 4) % 2 picks 32 of the 64 columns.  Warp 16 is
+// the TMEM lane quarter (32 rows) and (warp / 4) % 2 picks one half of the tile's columns.  Warp 16 is
 // the TMA producer, warps 17 and 18 issue the S / W products of group 0 and group 1 (warp 17
 // also allocates TMEM), warp 19 issues the accumulating products.
 // All waits are bounded; a wait that gives up records a status and the CTA winds down.
@@ -36,8 +40,10 @@ namespace {
 using namespace sm100;
 
 struct WArgs {
-  void* o;               // (heads, nrows, 64) bf16: grad_q, or grad_k when FUSED
-  void* o2;              // FUSED: grad_v
+  void* o;               // (heads, nrows, 64) bf16: out, grad_q, or grad_k
+  void* o2;              // MODE_DKDV: grad_v
+  float* den_out;        // MODE_FWD: (heads, nrows) row sums
+  const float* den_add;  // MODE_FWD: added to the row sum (may be null)
   const float* o_add;    // fp32 rows added before rounding (may be null)
   const float* o2_add;
   const void* x;         // row operand in global memory (normalisation dots)
@@ -49,17 +55,24 @@ struct WArgs {
   float a0, a1, a2, lim;
 };
 
-constexpr int BM = 128, BN = 64, D = 64, NS = 8;
+enum { MODE_DQ = 0, MODE_DKDV = 1, MODE_FWD = 2 };
+constexpr int BM = 128, D = 64;
 constexpr int kThreads = 640;
 constexpr int kProducerWarp = 16, kIssuerWarp = 17, kAccIssuerWarp = 19, kComputeWarps = 16;  // warps 17, 18: S / W issuers
-constexpr int ROW_TILE = BM * 128, COL_TILE = BN * 128, STAGE = 2 * COL_TILE;
+constexpr int ROW_TILE = BM * 128;
 constexpr int OFF_X = 0, OFF_U = ROW_TILE, OFF_ST = 2 * ROW_TILE;
-constexpr int OFF_VEC = OFF_ST + NS * STAGE;               // per compute warp 2 x 32 floats
-constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
-constexpr int NBAR = 2 + 2 * NS + 8;
-constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
-constexpr int SMEM = OFF_TMEM + 16 + 1024;
 constexpr int T_S = 0, T_W = 128, T_E = 256, T_P = 320, T_O = 384, T_O2 = 448;
+template <int MODE>
+struct WCfg {
+  static constexpr int BN = (MODE == MODE_FWD) ? 128 : 64;   // columns per tile
+  static constexpr int NS = (MODE == MODE_FWD) ? 5 : 8;      // ring stages of (Y tile, Z tile)
+  static constexpr int COL_TILE = BN * 128, STAGE = 2 * COL_TILE;
+  static constexpr int OFF_VEC = OFF_ST + NS * STAGE;      // per compute warp 2 x 32 floats
+  static constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
+  static constexpr int NBAR = 2 + 2 * NS + 8;
+  static constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
+  static constexpr int SMEM = OFF_TMEM + 16 + 1024;
+};
 
 // 16 bytes from shared memory by shared-window address (keeps the load off the generic path)
 __device__ __forceinline__ ulonglong2 lds_v2(uint32_t saddr) {
@@ -73,7 +86,7 @@ __device__ __forceinline__ void report(int code) { atomicCAS(&g_wtc_status, 0, c
 // row, with the optional fp32 addend; returns the dot product with the x row when wanted.
 template <int NC>
 __device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfloat16* dst,
-                                           const float* add, const __nv_bfloat16* xr) {
+                                           const float* add, const __nv_bfloat16* xr, float scale) {
   float part = 0.f;
 #pragma unroll
   for (int c0 = 0; c0 < NC; c0 += 32) {
@@ -92,6 +105,8 @@ __device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfl
           f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
           f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
         }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= scale;
         uint4 w;
         w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
         w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
@@ -111,11 +126,16 @@ __device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfl
   return part;
 }
 
-template <int FUSED>
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                      const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
                      const WArgs a) {
+  using C = WCfg<MODE>;
+  constexpr bool FUSED = MODE == MODE_DKDV, FWD = MODE == MODE_FWD;
+  constexpr int BN = C::BN, NS = C::NS, COL_TILE = C::COL_TILE, STAGE = C::STAGE;
+  constexpr int OFF_VEC = C::OFF_VEC, OFF_BAR = C::OFF_BAR, OFF_TMEM = C::OFF_TMEM;
+  constexpr int HB = BN / 2;          // columns of one compute warp = packed bf16 columns of one group
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -131,7 +151,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + OFF_TMEM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr bool rev = FUSED != 0;
+  constexpr bool rev = FUSED;
   // consecutive CTAs work on one head (its column tiles stay in L2); longest rows first
   const int head = blockIdx.x / a.ntr;
   const int pidx = blockIdx.x % a.ntr;
@@ -179,9 +199,9 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       tma_prefetch_desc(&tmU);
       tma_prefetch_desc(&tmY);
       tma_prefetch_desc(&tmZ);
-      mbar_expect_tx(BAR_X, 2 * ROW_TILE);
+      mbar_expect_tx(BAR_X, (FWD ? 1 : 2) * ROW_TILE);
       tma_load_3d(sbase + OFF_X, &tmX, BAR_X, 0, r0, head);
-      tma_load_3d(sbase + OFF_U, &tmU, BAR_X, 0, r0, head);
+      if (!FWD) tma_load_3d(sbase + OFF_U, &tmU, BAR_X, 0, r0, head);
     }
     for (int j = 0; j < J; ++j) {
       const int s = j % NS;
@@ -210,13 +230,15 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const int g = warp - kIssuerWarp;
       for (int j = g; ok && j < J; j += 2) {
         const int s = j % NS;
-        if (j >= 2 && !mbar_wait_warp(BAR_SFREE(g), (uint32_t)(((j >> 1) - 1) & 1))) { report(4); break; }
+        // the stage has normally been loaded long ago: checking it first keeps that check out of
+        // the s_free -> S ready path, which bounds the group's tile period
         if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((j / NS) & 1))) { report(3); break; }
+        if (j >= 2 && !mbar_wait_warp(BAR_SFREE(g), (uint32_t)(((j >> 1) - 1) & 1))) { report(4); break; }
         tc_fence_after();
         const uint32_t y_lo = st_k + (uint32_t)s * (STAGE >> 4);
         if (elect_one()) {
-          umma_ss_k64(tmem + T_S + g * 64, x_lo, y_lo, idescS);
-          umma_ss_k64(tmem + T_W + g * 64, u_lo, y_lo + (COL_TILE >> 4), idescS);
+          umma_ss_k64(tmem + T_S + g * BN, x_lo, y_lo, idescS);
+          if (!FWD) umma_ss_k64(tmem + T_W + g * BN, u_lo, y_lo + (COL_TILE >> 4), idescS);
           umma_commit(BAR_S(g));
         }
         __syncwarp();
@@ -236,9 +258,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         tc_fence_after();
         const uint32_t y_mn = st_mn + (uint32_t)s * (STAGE >> 4);
         if (elect_one()) {
-          umma_ts_steps<BN / 16>(tmem + T_O, tmem + T_E + g * 32, y_mn, idescO, j > 0 ? 1u : 0u);
+          // the gradients multiply E by the Y tile, the forward multiplies P by the Z tile
+          umma_ts_steps<BN / 16>(tmem + T_O, tmem + T_E + g * HB, y_mn + (FWD ? (COL_TILE >> 4) : 0), idescO,
+                                 j > 0 ? 1u : 0u);
           if (FUSED)
-            umma_ts_steps<BN / 16>(tmem + T_O2, tmem + T_P + g * 32, y_mn + (COL_TILE >> 4), idescO,
+            umma_ts_steps<BN / 16>(tmem + T_O2, tmem + T_P + g * HB, y_mn + (COL_TILE >> 4), idescO,
                                    j > 0 ? 1u : 0u);
           umma_commit(BAR_PV(g));
           umma_commit(BAR_EMPTY(s));
@@ -264,7 +288,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     }
     const int wrow_lo = r0 + qd * 32, wrow_hi = wrow_lo + 31;
     float dl_row = 0.f;
-    if (!rev && row_ok) dl_row = __ldg(a.dvec + (size_t)head * a.nrows + row);
+    if (MODE == MODE_DQ && row_ok) dl_row = __ldg(a.dvec + (size_t)head * a.nrows + row);
     const uint64_t ndl_row = pack2(-dl_row, -dl_row);
     const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
     float* myvec = (float*)(smem + OFF_VEC) + warp * 64;
@@ -275,6 +299,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;
     };
     float nxt = rev ? fetch_vec(gp) : 0.f;
+    uint64_t rs2[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};  // forward: row sum
     bool ok = true;
     for (int j = gp; j < J; j += 2) {
       const int i = j >> 1;
@@ -282,60 +307,88 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       if (rev) nxt = fetch_vec(j + 2);
       if (!mbar_wait(BAR_S(gp), (uint32_t)(i & 1))) { report(7); ok = false; break; }
       tc_fence_after();
-      uint32_t sv[32], wv[32];
-      tmem_ld32(tl + T_S + gp * 64 + cpart * 32, sv);
-      tmem_ld32(tl + T_W + gp * 64 + cpart * 32, wv);
       const uint32_t vec_s = myvec_s + (i & 1) * 128;   // shared-window address of this tile's slot
       if (rev) {
         myvec[(i & 1) * 32 + lane] = cur;
         __syncwarp();
       }
-      tmem_wait_ld();
-      // S and W of this tile are in registers: the group's next tile may be issued
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(BAR_SFREE(gp));
-      const int c0 = (tb + j) * BN + cpart * 32;    // this warp's 32 columns
-      bool need_mask = (c0 + 32 > a.ncols);
-      if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
-      // the mask test stays outside the element loops so that each loop is one basic block
-      // whose sixteen independent pairs the compiler can interleave; E and P of a pair are
-      // formed together so that S and W die pair by pair
-      uint32_t pe[16], pp[FUSED ? 16 : 1];
-      ulonglong2 nd2 = make_ulonglong2(0ull, 0ull);
-      if (!need_mask) {
+      // the warp's HB columns in passes of 32
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
-          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
-          pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
-          if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+      for (int ps = 0; ps < HB / 32; ++ps) {
+        uint32_t sv[32], wv[FWD ? 1 : 32];
+        tmem_ld32(tl + T_S + gp * BN + cpart * HB + ps * 32, sv);
+        if constexpr (!FWD) tmem_ld32(tl + T_W + gp * BN + cpart * HB + ps * 32, wv);
+        tmem_wait_ld();
+        if (ps + 1 == HB / 32) {
+          // S and W of this tile are in registers: the group's next tile may be issued
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_SFREE(gp));
         }
-      } else {
+        const int c0 = (tb + j) * BN + cpart * HB + ps * 32;    // first of these 32 columns
+        bool need_mask = (c0 + 32 > a.ncols);
+        if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
+        // the mask test stays outside the element loops so that each loop is one basic block
+        // whose sixteen independent pairs the compiler can interleave; E and P of a pair are
+        // formed together so that S and W die pair by pair
+        uint32_t pe[16], pp[FUSED ? 16 : 1];
+        ulonglong2 nd2 = make_ulonglong2(0ull, 0ull);
+        if constexpr (FWD) {
+          if (!need_mask) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
-          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
-          const int col = c0 + 2 * e;
-          const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
-          float v0, v1;
-          unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
-          pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
-          if (FUSED) {
-            unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
-            pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+            for (int e = 0; e < 16; ++e) {
+              const uint64_t p2 = fma2(fma2(A2v, pack2u(sv[2 * e], sv[2 * e + 1]), A1v), pack2u(sv[2 * e], sv[2 * e + 1]), A0v);
+              rs2[e & 3] = add2(rs2[e & 3], p2);
+              pe[e] = pack_bf16_2(p2);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+              const int col = c0 + 2 * e;
+              float v0, v1;
+              unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+              v0 = (col > limcol || col < lowcol) ? 0.f : v0;
+              v1 = (col + 1 > limcol || col + 1 < lowcol) ? 0.f : v1;
+              rs2[e & 3] = add2(rs2[e & 3], pack2(v0, v1));
+              pe[e] = pack_bf16(v0, v1);
+            }
+          }
+        } else if (!need_mask) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+            if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
+            const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
+            pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
+            if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+            if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
+            const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
+            const int col = c0 + 2 * e;
+            const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
+            float v0, v1;
+            unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
+            pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+            if (FUSED) {
+              unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+              pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+            }
           }
         }
+        // the group's previous products must have consumed E and P before they are overwritten
+        if (ps == 0 && i > 0) {
+          if (!mbar_wait(BAR_PV(gp), (uint32_t)((i - 1) & 1))) { report(9); ok = false; break; }
+          tc_fence_after();
+        }
+        tmem_st16(tl + T_E + gp * HB + cpart * (HB / 2) + ps * 16, pe);
+        if constexpr (FUSED) tmem_st16(tl + T_P + gp * HB + cpart * (HB / 2) + ps * 16, pp);
       }
-      // the group's previous products must have consumed E and P before they are overwritten
-      if (i > 0) {
-        if (!mbar_wait(BAR_PV(gp), (uint32_t)((i - 1) & 1))) { report(9); ok = false; break; }
-        tc_fence_after();
-      }
-      tmem_st16(tl + T_E + gp * 32 + cpart * 16, pe);
-      if constexpr (FUSED) tmem_st16(tl + T_P + gp * 32 + cpart * 16, pp);
+      if (!ok) break;
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -347,16 +400,30 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     }
     tc_fence_after();
     const int part4 = warp >> 2;
+    float scale = 1.f, rowsum = 0.f;
+    if (FWD && J > 0) {
+      // a row's sum is spread over the four warps that share its TMEM lane quarter; every
+      // compute warp reaches this barrier, whatever happened before
+      float lo, hi;
+      unpack2(add2(add2(rs2[0], rs2[1]), add2(rs2[2], rs2[3])), lo, hi);
+      myvec[lane] = lo + hi;
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      const float* parts = (const float*)(smem + OFF_VEC) + qd * 64 + lane;
+      rowsum = (parts[0] + parts[4 * 64]) + (parts[8 * 64] + parts[12 * 64]);
+      if (a.den_add && row_ok) rowsum += a.den_add[(size_t)head * a.nrows + row];
+      scale = 1.0f / rowsum;
+    }
     if (ok && J > 0 && (FUSED || part4 < 2)) {
       const size_t grow = (size_t)head * a.nrows + (row_ok ? row : 0);
       const bool second = FUSED && part4 >= 2;          // grad_v columns
       const int cc = (part4 & 1) * 32;
-      const bool dots_here = !second && a.dots != nullptr;
+      const bool dots_here = !FWD && !second && a.dots != nullptr;
       const float* add = second ? a.o2_add : a.o_add;
       const float part = store_row<32>(tl + (second ? T_O2 : T_O) + cc, row_ok,
                                        (__nv_bfloat16*)(second ? a.o2 : a.o) + grow * D + cc,
                                        add ? add + grow * D + cc : nullptr,
-                                       dots_here ? (const __nv_bfloat16*)a.x + grow * D + cc : nullptr);
+                                       dots_here ? (const __nv_bfloat16*)a.x + grow * D + cc : nullptr, scale);
+      if (FWD && part4 == 0 && row_ok) a.den_out[grow] = rowsum;
       if (dots_here) {
         float sum = part;
 #pragma unroll
@@ -374,7 +441,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   }
 }
 
-template <int FUSED>
+template <int MODE>
 int launch_wide(const Ctx& c, const char* name, const void* x, const void* u, const void* y,
                 const void* z, int nrows, int ncols, WArgs a) {
   const int heads = c.p.bh;
@@ -382,18 +449,18 @@ int launch_wide(const Ctx& c, const char* name, const void* x, const void* u, co
   CUtensorMap tx, tu, ty, tz;
   int rc;
   if ((rc = tma_map_bf16(&tx, x, heads, nrows, D, BM))) return rc;
-  if ((rc = tma_map_bf16(&tu, u, heads, nrows, D, BM))) return rc;
-  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, BN))) return rc;
-  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, BN))) return rc;
+  if ((rc = tma_map_bf16(&tu, u ? u : x, heads, nrows, D, BM))) return rc;
+  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, WCfg<MODE>::BN))) return rc;
+  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, WCfg<MODE>::BN))) return rc;
   a.nrows = nrows;
   a.ncols = ncols;
   a.x = x;
   a.ntr = (nrows + BM - 1) / BM;
-  FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   SMEM));
+  FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   WCfg<MODE>::SMEM));
   dim3 grid((unsigned)((size_t)heads * a.ntr));
   FM_LAUNCH(name, c.stream,
-            (dense_tc_wide_kernel<FUSED><<<grid, kThreads, SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+            (dense_tc_wide_kernel<MODE><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }
@@ -430,14 +497,32 @@ int dense_tc_wide_backward(const Ctx& c, const void* q, const void* k, const voi
   a.o = grad_q;
   a.dots = p.normalize ? dots : nullptr;
   a.o_add = ca ? ca->gq_add : nullptr;
-  if ((rc = launch_wide<0>(c, "fm_dense_tc_dq", q, gs, k, v, p.nq, p.nk, a))) return rc;
+  if ((rc = launch_wide<MODE_DQ>(c, "fm_dense_tc_dq", q, gs, k, v, p.nq, p.nk, a))) return rc;
   // grad_k and grad_v: rows = keys, columns = queries
   a.o = grad_k;
   a.o2 = grad_v;
   a.dots = p.normalize ? dots + p.bh : nullptr;
   a.o_add = ca ? ca->gk_add : nullptr;
   a.o2_add = ca ? ca->gv_add : nullptr;
-  return launch_wide<1>(c, "fm_dense_tc_dkdv", k, v, q, gs, p.nk, p.nq, a);
+  return launch_wide<MODE_DKDV>(c, "fm_dense_tc_dkdv", k, v, q, gs, p.nk, p.nq, a);
+}
+
+int dense_tc_wide_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
+                          void* out, float* den, const ChunkAdd* ca) {
+  const fastmax_problem& p = c.p;
+  WArgs a = {};
+  a.stat_q = p.normalize ? stats : nullptr;
+  a.stat_k = p.normalize ? stats + p.bh : nullptr;
+  a.off = p.nk - p.nq;
+  a.mask = p.mask;
+  a.a0 = p.a0;
+  a.a1 = p.a1;
+  a.a2 = (p.p == 2) ? p.a2 : 0.f;
+  a.lim = p.lim;
+  a.o = out;
+  a.den_out = den;
+  if (ca) { a.chunk = ca->chunk; a.o_add = ca->out_add; a.den_add = ca->den_add; }
+  return launch_wide<MODE_FWD>(c, "fm_dense_tc_fwd", q, nullptr, k, v, p.nq, p.nk, a);
 }
 
 int tc_wide_status(int* out, cudaStream_t stream) {
