@@ -135,6 +135,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   constexpr bool FUSED = MODE == MODE_DKDV, FWD = MODE == MODE_FWD;
   constexpr int BN = C::BN, NS = C::NS, COL_TILE = C::COL_TILE, STAGE = C::STAGE;
   constexpr int OFF_VEC = C::OFF_VEC, OFF_BAR = C::OFF_BAR, OFF_TMEM = C::OFF_TMEM;
+  constexpr bool PV_EARLY = MODE == MODE_DQ;
   constexpr int HB = BN / 2;          // columns of one compute warp = packed bf16 columns of one group
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -305,6 +306,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const int i = j >> 1;
       const float cur = nxt;
       if (rev) nxt = fetch_vec(j + 2);
+      // The group's previous products must have consumed E and P before they are overwritten.
+      // grad_q waits for its S / W anyway (that path bounds its tile period), so the check goes
+      // here, where it costs nothing on the way to the stores; the other two modes are bound by
+      // their compute path and must not delay the S loads, so they check just before the stores.
+      if (PV_EARLY && i > 0 && !mbar_wait(BAR_PV(gp), (uint32_t)((i - 1) & 1))) { report(9); ok = false; break; }
       if (!mbar_wait(BAR_S(gp), (uint32_t)(i & 1))) { report(7); ok = false; break; }
       tc_fence_after();
       const uint32_t vec_s = myvec_s + (i & 1) * 128;   // shared-window address of this tile's slot
@@ -380,8 +386,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             }
           }
         }
-        // the group's previous products must have consumed E and P before they are overwritten
-        if (ps == 0 && i > 0) {
+        if (!PV_EARLY && ps == 0 && i > 0) {
           if (!mbar_wait(BAR_PV(gp), (uint32_t)((i - 1) & 1))) { report(9); ok = false; break; }
           tc_fence_after();
         }
