@@ -5,6 +5,11 @@
 
 namespace fm {
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(const uint32_t*)&v;
+}
+
 // ---------------------------------------------------------------------------
 // Row statistics: for every head, max_n ||x_n||^2 and the row that attains it.
 // Replaces calc_norms + find_max (reference fastmax_cuda_forward.cu:223-253);
@@ -12,11 +17,13 @@ namespace fm {
 // rewriting q and k in place (reference apply_norm, :255-269).
 // Each warp owns rows; a row of D elements is read by D/VEC lanes, so a warp
 // covers 32*VEC/D rows per load and every load is a full 128-byte line.
-template <typename T, int D>
+template <typename T, int D, bool WIDE>
 __global__ void __launch_bounds__(256) rowmax_kernel(const T* __restrict__ x, int n,
                                                      int rows_per_block, int row_offset,
                                                      stat_t* __restrict__ stats) {
-  constexpr int VEC = (D >= 32) ? 4 : 1;       // elements per lane
+  // elements per lane: 16 bytes for the wide bf16 rows, else 4 (or 1) elements
+  // (WIDE needs 16-byte aligned rows; the launcher checks the base pointer)
+  constexpr int VEC = WIDE ? 8 : ((D >= 32) ? 4 : 1);
   constexpr int LPR = D / VEC;                 // lanes per row
   constexpr int RPW = 32 / LPR;                // rows per warp per step
   static_assert(D % VEC == 0 && LPR <= 32 && 32 % LPR == 0, "bad head dimension");
@@ -34,10 +41,20 @@ __global__ void __launch_bounds__(256) rowmax_kernel(const T* __restrict__ x, in
     float s = 0.f;
     if (r < row1) {
       const T* p = base + (size_t)r * D + off;
+      if constexpr (VEC == 8) {
+        const uint4 w = __ldg((const uint4*)p);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        float t = ldf(p + e);
-        s = fmaf(t, t, s);
+        for (int e = 0; e < 4; ++e) {
+          const float lo = __uint_as_float(ww[e] << 16), hi = __uint_as_float(ww[e] & 0xFFFF0000u);
+          s = fmaf(lo, lo, fmaf(hi, hi, s));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float t = ldf(p + e);
+          s = fmaf(t, t, s);
+        }
       }
     }
 #pragma unroll
@@ -61,8 +78,12 @@ static int rowmax_one(const Ctx& c, const T* x, int heads, int n, stat_t* stats,
   switch (c.p.d) {
 #define FM_CASE(DD) \
   case DD:                                                                              \
-    FM_LAUNCH("fm_rowmax", c.stream,                                                      \
-              (rowmax_kernel<T, DD><<<grid, 256, 0, c.stream>>>(x, n, rpb, row_offset, stats)));      \
+    if (sizeof(T) == 2 && DD >= 64 && ((uintptr_t)x & 15) == 0)                           \
+      FM_LAUNCH("fm_rowmax", c.stream,                                                    \
+                (rowmax_kernel<T, DD, (sizeof(T) == 2 && DD >= 64)><<<grid, 256, 0, c.stream>>>(x, n, rpb, row_offset, stats))); \
+    else                                                                                  \
+      FM_LAUNCH("fm_rowmax", c.stream,                                                    \
+                (rowmax_kernel<T, DD, false><<<grid, 256, 0, c.stream>>>(x, n, rpb, row_offset, stats)));      \
     break;
     FM_CASE(8) FM_CASE(16) FM_CASE(32) FM_CASE(64) FM_CASE(128)
 #undef FM_CASE
@@ -130,25 +151,46 @@ __global__ void __launch_bounds__(256) gprep_kernel(const __nv_bfloat16* __restr
                                                     const float* __restrict__ den, size_t rows,
                                                     __nv_bfloat16* __restrict__ gs,
                                                     float* __restrict__ dvec) {
-  constexpr int PAIRS = D / 64;   // bf16 pairs per lane
-  size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  float2 g[PAIRS];
-  float s = 0.f;
+  constexpr int LPR = D / 8;        // lanes per row, 16 bytes (8 elements) each
+  constexpr int RPW = 32 / LPR;     // rows per warp and step
+  constexpr int STEPS = 2;          // independent steps per warp: more bytes in flight
+  const int lane = threadIdx.x & 31, sub = lane / LPR, part = lane % LPR;
+  const size_t row0 = ((size_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * (RPW * STEPS) + sub;
+  uint4 g[STEPS], o[STEPS];
 #pragma unroll
-  for (int i = 0; i < PAIRS; ++i) {
-    g[i] = __bfloat1622float2(((const __nv_bfloat162*)(go + row * D))[lane + 32 * i]);
-    const float2 o = __bfloat1622float2(((const __nv_bfloat162*)(out + row * D))[lane + 32 * i]);
-    s = fmaf(g[i].x, o.x, fmaf(g[i].y, o.y, s));
+  for (int t = 0; t < STEPS; ++t) {
+    const size_t row = row0 + (size_t)t * RPW;
+    if (row < rows) {
+      g[t] = __ldg((const uint4*)(go + row * D) + part);
+      o[t] = __ldg((const uint4*)(out + row * D) + part);
+    } else {
+      g[t] = make_uint4(0u, 0u, 0u, 0u);
+      o[t] = g[t];
+    }
   }
 #pragma unroll
-  for (int m = 16; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-  const float inv = 1.0f / den[row];
+  for (int t = 0; t < STEPS; ++t) {
+    const size_t row = row0 + (size_t)t * RPW;
+    const uint32_t gw[4] = {g[t].x, g[t].y, g[t].z, g[t].w}, ow[4] = {o[t].x, o[t].y, o[t].z, o[t].w};
+    float gf[8], s = 0.f;
 #pragma unroll
-  for (int i = 0; i < PAIRS; ++i)
-    ((__nv_bfloat162*)(gs + row * D))[lane + 32 * i] = __floats2bfloat162_rn(g[i].x * inv, g[i].y * inv);
-  if (lane == 0) dvec[row] = s * inv;
+    for (int e = 0; e < 4; ++e) {
+      gf[2 * e] = __uint_as_float(gw[e] << 16);
+      gf[2 * e + 1] = __uint_as_float(gw[e] & 0xFFFF0000u);
+      s = fmaf(gf[2 * e], __uint_as_float(ow[e] << 16), s);
+      s = fmaf(gf[2 * e + 1], __uint_as_float(ow[e] & 0xFFFF0000u), s);
+    }
+#pragma unroll
+    for (int m = LPR / 2; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if (row < rows) {
+      const float inv = 1.0f / __ldg(den + row);
+      uint4 w;
+      w.x = pack_bf16x2(gf[0] * inv, gf[1] * inv); w.y = pack_bf16x2(gf[2] * inv, gf[3] * inv);
+      w.z = pack_bf16x2(gf[4] * inv, gf[5] * inv); w.w = pack_bf16x2(gf[6] * inv, gf[7] * inv);
+      ((uint4*)(gs + row * D))[part] = w;
+      if (part == 0) dvec[row] = s * inv;
+    }
+  }
 }
 
 int launch_gprep(const Ctx& c, const void* go, const void* out, const float* den, void* gs,
@@ -157,7 +199,11 @@ int launch_gprep(const Ctx& c, const void* go, const void* out, const float* den
   if (rows == 0) return FASTMAX_OK;
   if ((c.p.d != 64 && c.p.d != 128) || c.p.dtype != FASTMAX_BF16)
     return fail(FASTMAX_E_UNSUPPORTED, "gprep handles bf16 rows of 64 or 128 elements");
-  unsigned blocks = (unsigned)((rows + 7) / 8);
+  if ((((uintptr_t)go | (uintptr_t)out | (uintptr_t)gs) & 15) != 0)
+    return fail(FASTMAX_E_ARG, "the tensor-core family needs 16-byte aligned tensors");
+  // a block of 8 warps covers 8 x (rows per warp-step) x 2 steps rows
+  const size_t rows_per_block = 8 * (32 / (c.p.d / 8)) * 2;
+  unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
   if (c.p.d == 64)
     FM_LAUNCH("fm_gprep", c.stream,
               (gprep_kernel<64><<<blocks, 256, 0, c.stream>>>((const __nv_bfloat16*)go,

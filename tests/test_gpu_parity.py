@@ -182,5 +182,15 @@ def test_host_pipeline_matches_device_path():
     q, k, v, go = [h.cuda() for h in host]
     out, den, stats = _cabi.forward(q, k, v, **kw)
     want = (out,) + tuple(_cabi.backward(q, k, v, out, den, stats, go, **kw))
-    for a, b in zip(outs, want):
-        assert torch.equal(a, b.cpu())
+    names = ("out", "grad_q", "grad_k", "grad_v")
+    for name, a, b in zip(names, outs, want):
+        b = b.cpu()
+        if name in ("out", "grad_v"):
+            assert torch.equal(a, b), name
+            continue
+        # grad_q and grad_k: the gradient of the max-norm scaling lands on one row per head and
+        # uses a per-head dot accumulated with atomics, whose order is not fixed; every other row
+        # must agree bit for bit, that row to bf16 rounding
+        rows_differ = (a != b).any(dim=-1)
+        assert int(rows_differ.sum(dim=-1).max()) <= 1, name
+        assert torch.allclose(a.float(), b.float(), rtol=2 ** -6, atol=1e-6), name
