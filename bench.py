@@ -234,7 +234,9 @@ def run_ours(args):
 
     # ---- end to end with host buffers: fastmax_b200.host.HostPipeline streams groups of heads
     # through the GPU (copy-in, forward+backward, copy-out overlapped) ----------------------
-    from fastmax_b200.host import HostPipeline
+    from fastmax_b200.host import HostPipeline, prefer_gpu_numa_node
+
+    numa_node = prefer_gpu_numa_node(dev)     # pinned buffers below land next to this rank's GPU
 
     del res
     host_in = [t.cpu().pin_memory() for t in (q, k, v, go)]
@@ -304,7 +306,7 @@ def run_ours(args):
                         for n, (c, s) in sorted(per.items(), key=lambda kv: -kv[1][1])},
             "roofline": roof,
             "e2e": {"value": tokens_job / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
-                    "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms},
+                    "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "host_numa_node_rank0": numa_node},
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_sample(args.workload, 2, 1)[0]

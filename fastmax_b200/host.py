@@ -15,7 +15,33 @@ import torch
 
 from . import _cabi
 
-__all__ = ["HostPipeline"]
+__all__ = ["HostPipeline", "prefer_gpu_numa_node"]
+
+
+def prefer_gpu_numa_node(device) -> int:
+    """Make this process prefer host memory on the NUMA node the GPU hangs off (Linux
+    ``set_mempolicy(MPOL_PREFERRED)``), so that pinned buffers allocated afterwards are local to
+    the GPU's PCIe root and host<->device copies of several ranks do not all cross one socket's
+    memory controllers.  Returns the node, or -1 when the topology cannot be read or the call is
+    refused (nothing is changed then)."""
+    import ctypes
+    import os
+    try:
+        props = torch.cuda.get_device_properties(torch.device(device))
+        bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/numa_node" % bdf) as f:
+            node = int(f.read().strip())
+        if node < 0 or node >= 1024 or os.uname().machine != "x86_64":
+            return -1
+        mask = (ctypes.c_ulong * 16)()
+        mask[node // 64] = 1 << (node % 64)
+        libc = ctypes.CDLL(None, use_errno=True)
+        MPOL_PREFERRED, SYS_set_mempolicy = 1, 238
+        rc = libc.syscall(ctypes.c_long(SYS_set_mempolicy), ctypes.c_int(MPOL_PREFERRED), mask,
+                          ctypes.c_ulong(16 * 64 + 1))
+        return node if rc == 0 else -1
+    except Exception:
+        return -1
 
 
 class HostPipeline:
