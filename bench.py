@@ -44,6 +44,7 @@ WORKLOADS = {
     "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
     "c4s": (4, 8, 16384, 128, "bf16", 0, 2, 0),   # reduced unmasked d=128 case
     "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),   # small case for ncu captures (inputs 4 x 67 MB)
+    "prof1": (2, 8, 16384, 128, "bf16", 0, 1, 0),  # small p = 1 case for ncu captures (inputs 4 x 67 MB)
 }
 A = dict(a0=1.0, a1=1.0, a2=0.5, lim=1.0)
 

@@ -208,6 +208,7 @@ struct F1ReadArgs {
   const stat_t* stat_k;
   float a0, a1, lim;
   int n, chunk, nchunk, per_chunk, dvp, rows, f_lin, type_b, accumulate;
+  int run;              // tiles per CTA (all of one state)
   // final != 0: the read-out is the whole result (p = 1, unmasked): write bf16 rows to out_final
   // instead of fp32 to o_add.  1: type A divided by its normaliser (which goes to den_final);
   // 2: plain rounding; the per-head dot with x is added to *dots when dots is not null.
@@ -222,12 +223,18 @@ struct F1R {
   static constexpr int NSUB = DD / 64;
   static constexpr int TILE = NSUB * 16384;        // 128 tokens x DD bf16
   static constexpr int SMAT = DD * DD * 2;         // bf16 copy of S1, NSUB sub-tiles of DD rows x 64
-  static constexpr int OFF_S = TILE;
-  static constexpr int OFF_BAR = OFF_S + SMAT;
-  static constexpr int OFF_TMEM = OFF_BAR + 2 * 8;
+  static constexpr int OFF_S = 2 * TILE;           // two token-tile stages first
+  static constexpr int OFF_VEC = OFF_S + SMAT;     // normaliser column [DD] | constant row [DD + 1]
+  static constexpr int OFF_BAR = OFF_VEC + (2 * DD + 8) * 4;
+  static constexpr int NBAR = 9;                   // s_full | t_full[2] | t_empty[2] | a_full[2] | a_free[2]
+  static constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
   static constexpr int SMEM = OFF_TMEM + 16 + 1024;
+  static constexpr int TCOLS = 2 * DD;             // two accumulators
 };
 
+// One CTA reads out a run of consecutive 128-token tiles that share one state: the bf16 state
+// copy is loaded once, token tiles stream through two stages, and two TMEM accumulators let the
+// epilogue of a tile overlap the load and the product of the next one.
 template <int DD>
 __global__ void __launch_bounds__(F1_THREADS, 2)
 first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmS,
@@ -236,93 +243,136 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t bar_in = sbase + C::OFF_BAR, bar_done = bar_in + 8;
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  const uint32_t BAR_SF = bar0;
+  auto BAR_TF = [&](int b) { return bar0 + 8u * (1 + b); };
+  auto BAR_TE = [&](int b) { return bar0 + 8u * (3 + b); };
+  auto BAR_AF = [&](int b) { return bar0 + 8u * (5 + b); };
+  auto BAR_AE = [&](int b) { return bar0 + 8u * (7 + b); };
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + C::OFF_TMEM);
+  float* ncol = (float*)(smem + C::OFF_VEC);       // S1[a][DD], a < DD
+  float* crow = ncol + DD;                         // constant row, DD + 1 values
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tiles = (a.n + 127) / 128;
-  const int head = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * 128;
-  const int mat = head * (a.per_chunk ? a.nchunk : 1) + (a.per_chunk ? tok0 / a.chunk : 0);
+  const int runs = (tiles + a.run - 1) / a.run;
+  const int head = blockIdx.x / runs;
+  const int tile0 = (blockIdx.x % runs) * a.run;
+  const int nt = min(a.run, tiles - tile0);        // tiles of this run
+  const int mat = head * (a.per_chunk ? a.nchunk : 1) + (a.per_chunk ? (tile0 * 128) / a.chunk : 0);
 
   if (tid == 0) {
-    mbar_init(bar_in, 1);
-    mbar_init(bar_done, 1);
+    mbar_init(BAR_SF, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(BAR_TF(b), 1);
+      mbar_init(BAR_TE(b), 1);
+      mbar_init(BAR_AF(b), 1);
+      mbar_init(BAR_AE(b), 4);
+    }
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), 128);
+  if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), C::TCOLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
+    // ================= TMA producer =================
     if (lane == 0) {
-      mbar_expect_tx(bar_in, C::TILE + C::SMAT);
-      for (int sub = 0; sub < C::NSUB; ++sub) {
-        tma_load_3d(sbase + sub * 16384, &tmT, bar_in, sub * 64, tok0, head);
-        tma_load_3d(sbase + C::OFF_S + sub * (DD * 128), &tmS, bar_in, sub * 64, 0, mat);
+      mbar_expect_tx(BAR_SF, C::SMAT);
+      for (int sub = 0; sub < C::NSUB; ++sub)
+        tma_load_3d(sbase + C::OFF_S + sub * (DD * 128), &tmS, BAR_SF, sub * 64, 0, mat);
+    }
+    for (int i = 0; i < nt; ++i) {
+      const int b = i & 1;
+      if (!mbar_wait(BAR_TE(b), (uint32_t)(((i >> 1) & 1) ^ 1))) { report(47); break; }
+      if (lane == 0) {
+        mbar_expect_tx(BAR_TF(b), C::TILE);
+        for (int sub = 0; sub < C::NSUB; ++sub)
+          tma_load_3d(sbase + b * C::TILE + sub * 16384, &tmT, BAR_TF(b), sub * 64, (tile0 + i) * 128, head);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      if (mbar_wait(bar_in, 0)) {
-        tc_fence_after();
-        const uint32_t t_lo = desc_lo(sbase, 16);
+    // ================= MMA issuer (whole warp, one elected lane issues) =================
+    bool ok = mbar_wait_warp(BAR_SF, 0);
+    if (!ok) report(44);
+    for (int i = 0; ok && i < nt; ++i) {
+      const int b = i & 1;
+      if (!mbar_wait_warp(BAR_TF(b), (uint32_t)((i >> 1) & 1))) { report(44); break; }
+      if (!mbar_wait_warp(BAR_AE(b), (uint32_t)(((i >> 1) & 1) ^ 1))) { report(48); break; }
+      tc_fence_after();
+      const uint32_t t_lo = desc_lo(sbase + b * C::TILE, 16);
+      const uint32_t acc = tmem + b * DD;
+      if (elect_one()) {
         if (a.type_b) {
           // acc[i][a'] = sum_c u_i[c] S1[a'][c]: B = S1 rows a' with c contiguous (K-major)
           constexpr uint32_t idesc = idesc_bf16(128, DD, 0, 0);
           const uint32_t s_lo = desc_lo(sbase + C::OFF_S, 16);
 #pragma unroll
           for (int sub = 0; sub < C::NSUB; ++sub)
-            umma_ss_k64(tmem, t_lo + sub * (16384 >> 4), s_lo + sub * ((DD * 128) >> 4), idesc, sub > 0);
+            umma_ss_k64(acc, t_lo + sub * (16384 >> 4), s_lo + sub * ((DD * 128) >> 4), idesc, sub > 0);
         } else {
           // acc[i][c] = sum_a x_i[a] S1[a][c]: B = the same bytes, K = rows a, N = c contiguous (MN-major)
           constexpr uint32_t idesc = idesc_bf16(128, DD, 0, 1);
           const uint32_t s_lo = desc_lo(sbase + C::OFF_S, DD * 128);
 #pragma unroll
           for (int sub = 0; sub < C::NSUB; ++sub)
-            umma_ss_kmn_steps<4>(tmem, t_lo + sub * (16384 >> 4), s_lo + sub * 4 * 128, idesc, sub > 0);
+            umma_ss_kmn_steps<4>(acc, t_lo + sub * (16384 >> 4), s_lo + sub * 4 * 128, idesc, sub > 0);
         }
-        umma_commit(bar_done);
-      } else {
-        report(44);
+        umma_commit(BAR_AF(b));
+        umma_commit(BAR_TE(b));
       }
+      __syncwarp();
     }
     __syncwarp();
   } else {
-    const int qd = warp & 3;
-    const int tok = tok0 + qd * 32 + lane;
-    const bool tok_ok = tok < a.n;
-    const size_t grow = (size_t)head * a.n + (tok_ok ? tok : 0);
+    // ================= epilogue warps =================
+    const int qd = warp & 3, t = tid - 64;
     const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
     const float A1 = a.a1 * c;
     const float* st = a.state + (size_t)mat * a.rows * a.dvp + (size_t)a.f_lin * a.dvp;   // first-order rows
-    const float* s0 = st + (size_t)DD * a.dvp;                                            // constant row
-    float extra = 0.f;   // type A: normaliser part; type B: e_i
-    if (a.type_b) {
-      extra = tok_ok ? (a.uvec ? -a.uvec[grow] : 1.f) : 0.f;
-    } else if (a.den_add || a.final == 1) {
-      const __nv_bfloat162* xr = (const __nv_bfloat162*)((const __nv_bfloat16*)a.x + grow * DD);
-      float dot = 0.f;
-      if (tok_ok)
-#pragma unroll 8
-        for (int e = 0; e < DD / 2; ++e) {
-          const float2 xv = __bfloat1622float2(xr[e]);
-          dot = fmaf(xv.x, __ldg(st + (size_t)(2 * e) * a.dvp + DD), dot);
-          dot = fmaf(xv.y, __ldg(st + (size_t)(2 * e + 1) * a.dvp + DD), dot);
-        }
-      extra = A1 * dot + a.a0 * __ldg(s0 + DD);
-    }
-    const bool ok = mbar_wait(bar_done, 0);
-    if (!ok) report(45);
-    tc_fence_after();
-    if (ok) {
+    for (int i = t; i < 2 * DD + 1; i += 128)
+      ncol[i] = (i < DD) ? __ldg(st + (size_t)i * a.dvp + DD) : __ldg(st + (size_t)DD * a.dvp + (i - DD));
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    float part = 0.f;
+    bool ok = true;
+    for (int i = 0; i < nt; ++i) {
+      const int b = i & 1;
+      const int tok = (tile0 + i) * 128 + qd * 32 + lane;
+      const bool tok_ok = tok < a.n;
+      const size_t grow = (size_t)head * a.n + (tok_ok ? tok : 0);
+      float extra = 0.f;   // type A: normaliser part; type B: e_i
+      if (a.type_b) {
+        extra = tok_ok ? (a.uvec ? -a.uvec[grow] : 1.f) : 0.f;
+      } else if (a.den_add || a.final == 1) {
+        const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * DD);
+        float dot = 0.f;
+        if (tok_ok)
+#pragma unroll 4
+          for (int v8 = 0; v8 < DD / 8; ++v8) {
+            const uint4 xv = __ldg(xr + v8);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              dot = fmaf(__uint_as_float(xw[e] << 16), ncol[8 * v8 + 2 * e], dot);
+              dot = fmaf(__uint_as_float(xw[e] & 0xFFFF0000u), ncol[8 * v8 + 2 * e + 1], dot);
+            }
+          }
+        extra = A1 * dot + a.a0 * crow[DD];
+      }
+      if (!mbar_wait(BAR_AF(b), (uint32_t)((i >> 1) & 1))) { report(45); ok = false; break; }
+      tc_fence_after();
       const float scale = (a.final == 1) ? 1.0f / extra : 1.0f;
-      float part = 0.f;
 #pragma unroll 1
       for (int hcol = 0; hcol < DD / 64; ++hcol) {
         uint32_t tv[64];
-        tmem_ld64(tmem + ((uint32_t)(qd * 32) << 16) + hcol * 64, tv);
+        tmem_ld64(tmem + b * DD + ((uint32_t)(qd * 32) << 16) + hcol * 64, tv);
         tmem_wait_ld();
+        if (hcol + 1 == DD / 64) {   // the accumulator is in registers: the next product may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_AE(b));
+        }
         if (tok_ok) {
 #pragma unroll
           for (int v8 = 0; v8 < 8; ++v8) {
@@ -331,8 +381,7 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
             for (int e = 0; e < 8; ++e) {
               const int col = hcol * 64 + 8 * v8 + e;
               const float acc = __uint_as_float(tv[8 * v8 + e]);
-              r[e] = a.type_b ? A1 * fmaf(extra, __ldg(st + (size_t)col * a.dvp + DD), acc)
-                              : fmaf(A1, acc, a.a0 * __ldg(s0 + col));
+              r[e] = a.type_b ? A1 * fmaf(extra, ncol[col], acc) : fmaf(A1, acc, a.a0 * crow[col]);
             }
             if (a.final) {
               uint4 w;
@@ -364,21 +413,21 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
       }
       if (a.final) {
         if (a.final == 1 && tok_ok) a.den_final[grow] = extra;
-        if (a.dots) {
-#pragma unroll
-          for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
-          if (lane == 0) atomicAdd(a.dots + head, part);
-        }
       } else if (!a.type_b && a.den_add && tok_ok) {
         a.den_add[grow] = extra + (a.accumulate ? a.den_add[grow] : 0.f);
       }
+    }
+    if (ok && a.final && a.dots) {
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+      if (lane == 0) atomicAdd(a.dots + head, part);
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, 128);
+    tmem_dealloc(tmem, C::TCOLS);
   }
 }
 
@@ -471,7 +520,15 @@ int first_tc_readout(const Ctx& c, int type_b, int heads, int n, int chunk, int 
   a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.per_chunk = per_chunk; a.dvp = m.dvp; a.rows = m.f;
   a.f_lin = p.d * p.d - m.f0; a.type_b = type_b; a.accumulate = accumulate;
   a.final = final; a.out_final = out_final; a.den_final = den_final; a.dots = dots;
-  const unsigned grid = (unsigned)((size_t)heads * ((n + 127) / 128));
+  // runs of up to 8 tiles that never cross a chunk (chunks are multiples of 256 tokens)
+  int run = 8;
+  if (per_chunk) {
+    const int tpc = chunk / 128;
+    while (tpc % run) run >>= 1;
+  }
+  a.run = run;
+  const int tiles = (n + 127) / 128;
+  const unsigned grid = (unsigned)((size_t)heads * ((tiles + run - 1) / run));
   const char* name = type_b ? "fm_first_tc_readout_b" : "fm_first_tc_readout_a";
   if (p.d == 128) {
     FM_CUDA_TRY(cudaFuncSetAttribute(first_readout_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, F1R<128>::SMEM));
