@@ -124,9 +124,55 @@ __global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ go,
   if (lane == 0) delta[row] = s;
 }
 
+// The same for bf16 rows of 64 or 128 elements with 16-byte aligned tensors: 16 bytes per lane,
+// several rows per warp, two independent steps per warp.
+template <int D>
+__global__ void __launch_bounds__(256) delta_wide_kernel(const __nv_bfloat16* __restrict__ go,
+                                                         const __nv_bfloat16* __restrict__ out, size_t rows,
+                                                         float* __restrict__ delta) {
+  constexpr int LPR = D / 8, RPW = 32 / LPR, STEPS = 2;
+  const int lane = threadIdx.x & 31, sub = lane / LPR, part = lane % LPR;
+  const size_t row0 = ((size_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * (RPW * STEPS) + sub;
+  uint4 g[STEPS], o[STEPS];
+#pragma unroll
+  for (int t = 0; t < STEPS; ++t) {
+    const size_t row = row0 + (size_t)t * RPW;
+    g[t] = (row < rows) ? __ldg((const uint4*)(go + row * D) + part) : make_uint4(0u, 0u, 0u, 0u);
+    o[t] = (row < rows) ? __ldg((const uint4*)(out + row * D) + part) : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int t = 0; t < STEPS; ++t) {
+    const size_t row = row0 + (size_t)t * RPW;
+    const uint32_t gw[4] = {g[t].x, g[t].y, g[t].z, g[t].w}, ow[4] = {o[t].x, o[t].y, o[t].z, o[t].w};
+    float s = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      s = fmaf(__uint_as_float(gw[e] << 16), __uint_as_float(ow[e] << 16), s);
+      s = fmaf(__uint_as_float(gw[e] & 0xFFFF0000u), __uint_as_float(ow[e] & 0xFFFF0000u), s);
+    }
+#pragma unroll
+    for (int m = LPR / 2; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if (row < rows && part == 0) delta[row] = s;
+  }
+}
+
 int launch_delta(const Ctx& c, const void* go, const void* out, float* delta) {
   size_t rows = (size_t)c.p.bh * c.p.nq;
   if (rows == 0) return FASTMAX_OK;
+  if (c.p.dtype == FASTMAX_BF16 && (c.p.d == 64 || c.p.d == 128) && (((uintptr_t)go | (uintptr_t)out) & 15) == 0) {
+    const size_t rows_per_block = 8 * (32 / (c.p.d / 8)) * 2;
+    const unsigned nb = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+    if (c.p.d == 64)
+      FM_LAUNCH("fm_delta", c.stream,
+                (delta_wide_kernel<64><<<nb, 256, 0, c.stream>>>((const __nv_bfloat16*)go, (const __nv_bfloat16*)out,
+                                                                 rows, delta)));
+    else
+      FM_LAUNCH("fm_delta", c.stream,
+                (delta_wide_kernel<128><<<nb, 256, 0, c.stream>>>((const __nv_bfloat16*)go, (const __nv_bfloat16*)out,
+                                                                  rows, delta)));
+    FM_CUDA_TRY(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   unsigned blocks = (unsigned)((rows + 7) / 8);
   if (c.p.dtype == FASTMAX_F32)
     FM_LAUNCH("fm_delta", c.stream,
