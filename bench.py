@@ -279,7 +279,7 @@ def run_ours(args):
             # DRAM bytes per token-head of the score kernels (bf16, d = 64), from the ncu capture of the
             # small case summarised under profiles/: heads are processed one after another, so every
             # re-read of a head's tiles hits L2 and the traffic grows in proportion to heads x tokens
-            ncu_bytes = {"fm_dense_tc_fwd": 484.5, "fm_dense_tc_dq": 619.9, "fm_dense_tc_dkdv": 728.4}
+            ncu_bytes = {"fm_dense_tc_fwd": 483.2, "fm_dense_tc_dq": 621.3, "fm_dense_tc_dkdv": 723.8}
             traffic = ncu_bytes[dom] * bh * N if (dom in ncu_bytes and D == 64 and dt == "bf16") else None
             if kind in flops_of:
                 achieved = flops_of[kind] * bh * N / (tot / cnt * 1e-3) / 1e12
