@@ -124,25 +124,29 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       }
     }
   } else if (warp == 9) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+    {
       constexpr uint32_t idesc = idesc_bf16(128, 128, 0, 0);
-      bool ok = mbar_wait(BAR_X(), 0);
+      bool ok = mbar_wait_warp(BAR_X(), 0);
       if (!ok) report(22);
       tc_fence_after();
       const uint32_t st0 = desc_lo(sbase + RT_OFF_ST, 16);
       for (int n = 0; ok && n < RT_NT; ++n) {
         const int s = n % RT_NS, buf = n & 1;
-        if (!mbar_wait(BAR_FULL(s), (uint32_t)((n / RT_NS) & 1))) { report(23); ok = false; break; }
+        if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((n / RT_NS) & 1))) { report(23); ok = false; break; }
         for (int t = 0; t < ntile; ++t) {
           // the buffer was last used by slice n-2
-          if (n >= 2 && !mbar_wait(BAR_TFREE(t, buf), (uint32_t)(((n >> 1) - 1) & 1))) { report(24); ok = false; break; }
+          if (n >= 2 && !mbar_wait_warp(BAR_TFREE(t, buf), (uint32_t)(((n >> 1) - 1) & 1))) { report(24); ok = false; break; }
           tc_fence_after();
-          umma_ss_k64(tmem + t * 256 + buf * 128, desc_lo(sbase + RT_OFF_X + t * RT_TILE, 16),
-                      st0 + (uint32_t)s * (RT_TILE >> 4), idesc);
-          umma_commit(BAR_TFULL(t, buf));
+          if (elect_one()) {
+            umma_ss_k64(tmem + t * 256 + buf * 128, desc_lo(sbase + RT_OFF_X + t * RT_TILE, 16),
+                        st0 + (uint32_t)s * (RT_TILE >> 4), idesc);
+            umma_commit(BAR_TFULL(t, buf));
+          }
+          __syncwarp();
         }
-        if (ok) umma_commit(BAR_EMPTY(s));
+        if (ok && elect_one()) umma_commit(BAR_EMPTY(s));
+        __syncwarp();
       }
     }
     __syncwarp();
@@ -351,24 +355,28 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
+    {   // the whole warp runs the loop, one elected lane issues
       constexpr uint32_t idesc = idesc_bf16(128, 64, 1, 1);
       bool ok = true;
       for (int k = 0; ok && k < nblk; ++k) {
         const int s = k % ST_NZ;
-        if (!mbar_wait(BAR_ZFULL(s), (uint32_t)((k / ST_NZ) & 1))) { report(32); ok = false; break; }
+        if (!mbar_wait_warp(BAR_ZFULL(s), (uint32_t)((k / ST_NZ) & 1))) { report(32); ok = false; break; }
         const uint32_t z_lo = desc_lo(sbase + ST_OFF_Z + s * ST_ZTILE, ST_ZTILE);
         for (int m = 0; m < 8; ++m) {
           const int q = k * 8 + m, b = q % ST_NA;
-          if (!mbar_wait(BAR_AFULL(b), (uint32_t)((q / ST_NA) & 1))) { report(33); ok = false; break; }
+          if (!mbar_wait_warp(BAR_AFULL(b), (uint32_t)((q / ST_NA) & 1))) { report(33); ok = false; break; }
           tc_fence_after();
-          umma_ss_mn_steps<8>(tmem + m * 64, desc_lo(sbase + ST_OFF_A + b * ST_ATILE, ST_ATILE / 2), z_lo,
-                              idesc, k > 0 ? 1u : 0u);
-          umma_commit(BAR_AEMPTY(b));
+          if (elect_one()) {
+            umma_ss_mn_steps<8>(tmem + m * 64, desc_lo(sbase + ST_OFF_A + b * ST_ATILE, ST_ATILE / 2), z_lo,
+                                idesc, k > 0 ? 1u : 0u);
+            umma_commit(BAR_AEMPTY(b));
+          }
+          __syncwarp();
         }
-        if (ok) umma_commit(BAR_ZEMPTY(s));
+        if (ok && elect_one()) umma_commit(BAR_ZEMPTY(s));
+        __syncwarp();
       }
-      if (ok) umma_commit(BAR_DONE());
+      if (ok && elect_one()) umma_commit(BAR_DONE());
     }
     __syncwarp();
   } else {
