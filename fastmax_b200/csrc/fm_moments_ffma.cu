@@ -136,36 +136,40 @@ __global__ void __launch_bounds__(256) chunk_state_kernel(const StateArgs a) {
 // Exclusive running sum over the chunks of every head (forward or reverse), started
 // from `base` (per head, may be null); `total` (may be null) gets this shard's own sum.
 // With write == 0 the states are left as they are and only the total is produced.
+// One thread owns four consecutive state elements (`per` is a multiple of 4: the column count is).
 __global__ void __launch_bounds__(256) prefix_kernel(float* state,
                                                      const float* __restrict__ base,
                                                      float* __restrict__ total, int nchunk,
                                                      size_t per, size_t first, int reverse,
                                                      int write) {
-  const size_t e = first + (size_t)blockIdx.x * 256 + threadIdx.x;
+  const size_t e = first + ((size_t)blockIdx.x * 256 + threadIdx.x) * 4;
   const int head = blockIdx.y;
   if (e >= per) return;
-  float run = base ? base[(size_t)head * per + e] : 0.f;
-  const float start = run;
+  float4 run = base ? *(const float4*)(base + (size_t)head * per + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 start = run;
   // batches of 8 chunks: the loads of a batch are independent and in flight together
   for (int i0 = 0; i0 < nchunk; i0 += 8) {
-    float v[8];
+    float4 v[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int i = i0 + u;
       const int c = reverse ? nchunk - 1 - i : i;
-      v[u] = (i < nchunk) ? __ldcs(state + ((size_t)head * nchunk + c) * per + e) : 0.f;
+      v[u] = (i < nchunk) ? __ldcs((const float4*)(state + ((size_t)head * nchunk + c) * per + e))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int i = i0 + u;
       if (i < nchunk) {
         const int c = reverse ? nchunk - 1 - i : i;
-        if (write) state[((size_t)head * nchunk + c) * per + e] = run;
-        run += v[u];
+        if (write) *(float4*)(state + ((size_t)head * nchunk + c) * per + e) = run;
+        run.x += v[u].x; run.y += v[u].y; run.z += v[u].z; run.w += v[u].w;
       }
     }
   }
-  if (total) total[(size_t)head * per + e] = run - start;
+  if (total)
+    *(float4*)(total + (size_t)head * per + e) =
+        make_float4(run.x - start.x, run.y - start.y, run.z - start.z, run.w - start.w);
 }
 
 // ---------------------------------------------------------------------------------
@@ -398,7 +402,9 @@ int moments_prefix(const Ctx& c, int heads, int nchunk, float* state, const floa
   const MomentDims m = moment_dims(c.p.d, c.p.p);
   const size_t per = (size_t)m.f * m.dvp;
   const size_t first = 0;
-  dim3 grid((unsigned)((per - first + 255) / 256), heads);
+  if ((((uintptr_t)state | (uintptr_t)base | (uintptr_t)total) & 15) != 0)
+    return fail(FASTMAX_E_ARG, "moment states and totals must be 16-byte aligned");
+  dim3 grid((unsigned)((per - first + 1023) / 1024), heads);   // four elements per thread
   FM_LAUNCH("fm_moments_prefix", c.stream,
             (prefix_kernel<<<grid, 256, 0, c.stream>>>(state, base, total, nchunk, per, first, reverse, write)));
   FM_CUDA_TRY(cudaGetLastError());
