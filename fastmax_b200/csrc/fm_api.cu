@@ -184,6 +184,8 @@ int fastmax_b200_device_status(int* status, void* stream) {
   if ((rc = tc_status(&a, (cudaStream_t)stream))) return rc;
   if ((rc = tc_wide_status(&w, (cudaStream_t)stream))) return rc;
   if (!a) a = w;
+  if ((rc = tc_dkdv128_status(&w, (cudaStream_t)stream))) return rc;
+  if (!a) a = w;
   if ((rc = moments_tc_status(&b, (cudaStream_t)stream))) return rc;
   if ((rc = first_tc_status(&f, (cudaStream_t)stream))) return rc;
   *status = a ? a : (b ? b : f);

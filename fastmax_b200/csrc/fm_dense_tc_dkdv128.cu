@@ -1,0 +1,345 @@
+// grad_k and grad_v of the score form in one pass for head dimension 128 (bf16, tcgen05):
+// rows = keys (x = k, u = v), columns = queries (y = q, z = gs), reverse direction
+// (column >= row - off):
+//   S = X Y^T, W = U Z^T,  E = f'(S) (W - dvec_col),  P = f(S),  grad_k += E Y,  grad_v += P Z.
+// Sharing S between the two gradients makes a 128 x 64 tile cost 24 + 8 MMA instructions instead
+// of the 40 + 8 of separate grad_k and grad_v kernels.
+//
+// One CTA owns one 128-row tile.  Two 128-column fp32 accumulators take 256 of the 512 TMEM
+// columns, so S, W (64 columns each) and E, P (32 each, bf16 pairs) are single-buffered:
+//   S 0..63 | W 64..127 | E 128..159 | P 160..191 | grad_k 192..319 | grad_v 320..447.
+// Warps 0-7 compute (warp % 4 = TMEM lane quarter = 32 rows, warp / 4 = which 32 of the 64
+// columns), warp 8 is the TMA producer, warp 9 allocates TMEM and issues the S / W products
+// (as soon as the compute warps have copied the previous tile to registers), warp 10 issues
+// the accumulating products.  All waits are bounded; a wait that gives up records a status
+// and the CTA winds down.
+#include <climits>
+#include <cstdlib>
+
+#include "fm_common.cuh"
+#include "fm_sm100.cuh"
+
+namespace fm {
+
+__device__ int g_ktc_status = 0;
+
+namespace {
+using namespace sm100;
+
+struct KArgs {
+  void* gk;              // (heads, nrows, 128) bf16
+  void* gv;
+  const float* gk_add;   // fp32 rows added before rounding (may be null)
+  const float* gv_add;
+  const void* x;         // keys in global memory (normalisation dot)
+  const float* dvec;     // (heads, ncols)
+  float* dots;           // per head sum of grad_k . k, or null
+  const stat_t* stat_q;
+  const stat_t* stat_k;
+  int nrows, ncols, off, mask, ntr, chunk;
+  float a0, a1, a2, lim;
+};
+
+constexpr int BM = 128, BN = 64, D = 128, NS = 4;
+constexpr int kThreads = 352, kComputeWarps = 8, kProducerWarp = 8, kIssuerWarp = 9, kAccIssuerWarp = 10;
+constexpr int ROW_SUB = BM * 128, ROW_TILE = 2 * ROW_SUB;   // a row tile is two 64-wide sub-tiles
+constexpr int COL_SUB = BN * 128, COL_TILE = 2 * COL_SUB, STAGE = 2 * COL_TILE;
+constexpr int OFF_X = 0, OFF_U = ROW_TILE, OFF_ST = 2 * ROW_TILE;
+constexpr int OFF_VEC = OFF_ST + NS * STAGE;                // per compute warp 2 x 32 floats
+constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
+constexpr int NBAR = 2 + 2 * NS + 4;
+constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
+constexpr int SMEM = OFF_TMEM + 16 + 1024;
+constexpr int T_S = 0, T_W = 64, T_E = 128, T_P = 160, T_GK = 192, T_GV = 320;
+
+__device__ __forceinline__ void report(int code) { atomicCAS(&g_ktc_status, 0, code); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
+               const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
+               const KArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + OFF_BAR;
+  // barrier map: x | done | full[NS] | empty[NS] | s_full | s_free | p_full | pv_done
+  const uint32_t BAR_X = bar0, BAR_DONE = bar0 + 8;
+  auto BAR_FULL = [&](int s) { return bar0 + 8u * (2 + s); };
+  auto BAR_EMPTY = [&](int s) { return bar0 + 8u * (2 + NS + s); };
+  const uint32_t BAR_S = bar0 + 8u * (2 + 2 * NS), BAR_SFREE = BAR_S + 8, BAR_P = BAR_S + 16, BAR_PV = BAR_S + 24;
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + OFF_TMEM);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // consecutive CTAs work on one head (its column tiles stay in L2); longest rows first
+  const int head = blockIdx.x / a.ntr;
+  const int r0 = (blockIdx.x % a.ntr) * BM;
+
+  const int ntile = (a.ncols + BN - 1) / BN;
+  int tb = 0, te = ntile;
+  if (a.mask) tb = max(0, r0 - a.off) / BN;
+  if (a.chunk > 0) te = min(te, (r0 / a.chunk + 1) * (a.chunk / BN));   // the row tile lies in one chunk
+  const int J = max(te - tb, 0);
+
+  if (tid == 0) {
+    mbar_init(BAR_X, 1);
+    mbar_init(BAR_DONE, 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(BAR_FULL(s), 1);
+      mbar_init(BAR_EMPTY(s), 1);
+    }
+    mbar_init(BAR_S, 1);
+    mbar_init(BAR_SFREE, kComputeWarps);
+    mbar_init(BAR_P, kComputeWarps);
+    mbar_init(BAR_PV, 1);
+    mbar_fence_init();
+  }
+  if (warp == kIssuerWarp) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == kProducerWarp) {
+    // ================= TMA producer =================
+    if (lane == 0 && J > 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmU);
+      tma_prefetch_desc(&tmY);
+      tma_prefetch_desc(&tmZ);
+      mbar_expect_tx(BAR_X, 2 * ROW_TILE);
+      for (int sub = 0; sub < 2; ++sub) {
+        tma_load_3d(sbase + OFF_X + sub * ROW_SUB, &tmX, BAR_X, sub * 64, r0, head);
+        tma_load_3d(sbase + OFF_U + sub * ROW_SUB, &tmU, BAR_X, sub * 64, r0, head);
+      }
+    }
+    for (int j = 0; j < J; ++j) {
+      const int s = j % NS;
+      if (!mbar_wait(BAR_EMPTY(s), (((j / NS) & 1) ^ 1))) { report(1); break; }
+      if (lane == 0) {
+        mbar_expect_tx(BAR_FULL(s), STAGE);
+        const uint32_t dst = sbase + OFF_ST + s * STAGE;
+        for (int sub = 0; sub < 2; ++sub) {
+          tma_load_3d(dst + sub * COL_SUB, &tmY, BAR_FULL(s), sub * 64, (tb + j) * BN, head);
+          tma_load_3d(dst + COL_TILE + sub * COL_SUB, &tmZ, BAR_FULL(s), sub * 64, (tb + j) * BN, head);
+        }
+      }
+    }
+  } else if (warp == kIssuerWarp) {
+    // ================= MMA issuer of the S / W products (whole warp, one elected lane issues) ============
+    if (J > 0) {
+      constexpr uint32_t idescS = idesc_bf16(BM, BN, 0, 0);
+      const uint32_t x_lo = desc_lo(sbase + OFF_X, 16), u_lo = desc_lo(sbase + OFF_U, 16);
+      const uint32_t st_k = desc_lo(sbase + OFF_ST, 16);   // stage 0, K-major view
+      bool ok = mbar_wait_warp(BAR_X, 0);
+      if (!ok) report(2);
+      tc_fence_after();
+      for (int j = 0; ok && j < J; ++j) {
+        const int s = j % NS;
+        if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((j / NS) & 1))) { report(3); break; }
+        if (j >= 1 && !mbar_wait_warp(BAR_SFREE, (uint32_t)((j - 1) & 1))) { report(4); break; }
+        tc_fence_after();
+        const uint32_t y_lo = st_k + (uint32_t)s * (STAGE >> 4);
+        if (elect_one()) {
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub)
+            umma_ss_k64(tmem + T_S, x_lo + sub * (ROW_SUB >> 4), y_lo + sub * (COL_SUB >> 4), idescS, sub > 0);
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub)
+            umma_ss_k64(tmem + T_W, u_lo + sub * (ROW_SUB >> 4), y_lo + (COL_TILE >> 4) + sub * (COL_SUB >> 4),
+                        idescS, sub > 0);
+          umma_commit(BAR_S);
+        }
+        __syncwarp();
+      }
+    }
+    __syncwarp();
+  } else if (warp == kAccIssuerWarp) {
+    // ================= MMA issuer of the accumulating products =================
+    if (J > 0) {
+      constexpr uint32_t idescO = idesc_bf16(BM, D, 0, 1);
+      const uint32_t st_mn = desc_lo(sbase + OFF_ST, COL_SUB);   // stage 0, MN-major view (two 64-wide blocks)
+      for (int j = 0; j < J; ++j) {
+        const int s = j % NS;
+        if (!mbar_wait_warp(BAR_P, (uint32_t)(j & 1))) { report(5); break; }
+        tc_fence_after();
+        const uint32_t y_mn = st_mn + (uint32_t)s * (STAGE >> 4);
+        if (elect_one()) {
+          umma_ts_steps<BN / 16>(tmem + T_GK, tmem + T_E, y_mn, idescO, j > 0 ? 1u : 0u);
+          umma_ts_steps<BN / 16>(tmem + T_GV, tmem + T_P, y_mn + (COL_TILE >> 4), idescO, j > 0 ? 1u : 0u);
+          umma_commit(BAR_PV);
+          umma_commit(BAR_EMPTY(s));
+          if (j + 1 == J) umma_commit(BAR_DONE);
+        }
+        __syncwarp();
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================= compute warps =================
+    const int cpart = warp >> 2, qd = warp & 3;
+    const int row = r0 + qd * 32 + lane;
+    const bool row_ok = row < a.nrows;
+    const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
+    const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
+    const uint64_t A0v = pack2(A0, A0), A1v = pack2(A1, A1), A2v = pack2(A2, A2);
+    const uint64_t A2d = pack2(2.f * A2, 2.f * A2);
+    const int limcol = a.ncols - 1;                         // columns kept: lowcol <= col <= limcol
+    const int lowcol = a.mask ? row - a.off : 0;
+    const int wrow_hi = r0 + qd * 32 + 31;
+    const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
+    float* myvec = (float*)(smem + OFF_VEC) + warp * 64;
+    const uint32_t myvec_s = sbase + OFF_VEC + warp * 256;
+    // negated dvec of this lane's column in the next tile, fetched one tile ahead
+    auto fetch_vec = [&](int j) -> float {
+      const int col = (tb + j) * BN + cpart * 32 + lane;
+      return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;
+    };
+    float nxt = fetch_vec(0);
+    bool ok = true;
+    for (int j = 0; j < J; ++j) {
+      const float cur = nxt;
+      nxt = fetch_vec(j + 1);
+      if (!mbar_wait(BAR_S, (uint32_t)(j & 1))) { report(7); ok = false; break; }
+      tc_fence_after();
+      const uint32_t vec_s = myvec_s + (j & 1) * 128;
+      myvec[(j & 1) * 32 + lane] = cur;
+      __syncwarp();
+      uint32_t sv[32], wv[32];
+      tmem_ld32(tl + T_S + cpart * 32, sv);
+      tmem_ld32(tl + T_W + cpart * 32, wv);
+      tmem_wait_ld();
+      // S and W of this tile are in registers: the next tile's may be issued
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_SFREE);
+      const int c0 = (tb + j) * BN + cpart * 32;    // this warp's 32 columns
+      bool need_mask = (c0 + 32 > a.ncols);
+      if (a.mask) need_mask = need_mask || (c0 < wrow_hi - a.off);
+      // the mask test stays outside the element loops so that each loop is one basic block whose
+      // sixteen independent pairs the compiler can interleave
+      uint32_t pe[16], pp[16];
+      ulonglong2 nd2 = make_ulonglong2(0ull, 0ull);
+      if (!need_mask) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+          if ((e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
+          const uint64_t ndl = (e & 1) ? nd2.y : nd2.x;
+          pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
+          pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+          if ((e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
+          const uint64_t ndl = (e & 1) ? nd2.y : nd2.x;
+          const int col = c0 + 2 * e;
+          const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
+          float v0, v1;
+          unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
+          pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+          unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+          pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+        }
+      }
+      // the previous tile's products must have consumed E and P before they are overwritten
+      if (j > 0) {
+        if (!mbar_wait(BAR_PV, (uint32_t)((j - 1) & 1))) { report(9); ok = false; break; }
+        tc_fence_after();
+      }
+      tmem_st16(tl + T_E + cpart * 16, pe);
+      tmem_st16(tl + T_P + cpart * 16, pp);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_P);
+    }
+    // ---- epilogue: warps 0-3 write grad_k (and the normalisation dot), warps 4-7 grad_v ----
+    if (ok && J > 0) {
+      if (!mbar_wait(BAR_DONE, 0)) { report(10); ok = false; }
+    }
+    tc_fence_after();
+    if (ok && J > 0) {
+      const size_t grow = (size_t)head * a.nrows + (row_ok ? row : 0);
+      const bool second = cpart == 1;
+      const bool dots_here = !second && a.dots != nullptr;
+      const float* add = second ? a.gv_add : a.gk_add;
+      const float part = store_row<D>(tl + (second ? T_GV : T_GK), row_ok,
+                                      (__nv_bfloat16*)(second ? a.gv : a.gk) + grow * D,
+                                      add ? add + grow * D : nullptr,
+                                      dots_here ? (const __nv_bfloat16*)a.x + grow * D : nullptr, 1.f);
+      if (dots_here) {
+        float sum = part;
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+        if (lane == 0) atomicAdd(a.dots + head, sum);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kIssuerWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace
+
+// bf16, head dimension 128, bh == bhkv; FASTMAX_B200_NO_WIDE=1 keeps separate grad_k / grad_v kernels.
+bool dense_tc_dkdv128_supports(const fastmax_problem& p) {
+  static const bool off = [] {
+    const char* e = getenv("FASTMAX_B200_NO_WIDE");
+    return e && e[0] == '1';
+  }();
+  return !off && p.dtype == FASTMAX_BF16 && p.d == 128 && p.bh == p.bhkv;
+}
+
+int dense_tc_dkdv128(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
+                     const float* dvec, const stat_t* stats, float* dots_k, void* grad_k, void* grad_v,
+                     const ChunkAdd* ca) {
+  const fastmax_problem& p = c.p;
+  const int heads = p.bh, nrows = p.nk, ncols = p.nq;
+  if (heads == 0 || nrows == 0) return FASTMAX_OK;
+  CUtensorMap tx, tu, ty, tz;
+  int rc;
+  if ((rc = tma_map_bf16(&tx, k, heads, nrows, D, BM))) return rc;
+  if ((rc = tma_map_bf16(&tu, v, heads, nrows, D, BM))) return rc;
+  if ((rc = tma_map_bf16(&ty, q, heads, ncols, D, BN))) return rc;
+  if ((rc = tma_map_bf16(&tz, gs, heads, ncols, D, BN))) return rc;
+  KArgs a = {};
+  a.gk = grad_k;
+  a.gv = grad_v;
+  a.gk_add = ca ? ca->gk_add : nullptr;
+  a.gv_add = ca ? ca->gv_add : nullptr;
+  a.x = k;
+  a.dvec = dvec;
+  a.dots = p.normalize ? dots_k : nullptr;
+  a.stat_q = p.normalize ? stats : nullptr;
+  a.stat_k = p.normalize ? stats + p.bh : nullptr;
+  a.nrows = nrows;
+  a.ncols = ncols;
+  a.off = p.nk - p.nq;
+  a.mask = p.mask;
+  a.chunk = ca ? ca->chunk : 0;
+  a.ntr = (nrows + BM - 1) / BM;
+  a.a0 = p.a0;
+  a.a1 = p.a1;
+  a.a2 = (p.p == 2) ? p.a2 : 0.f;
+  a.lim = p.lim;
+  FM_CUDA_TRY(cudaFuncSetAttribute(dkdv128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  dim3 grid((unsigned)((size_t)heads * a.ntr));
+  FM_LAUNCH("fm_dense_tc_dkdv", c.stream, (dkdv128_kernel<<<grid, kThreads, SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+int tc_dkdv128_status(int* out, cudaStream_t stream) {
+  FM_CUDA_TRY(cudaMemcpyFromSymbolAsync(out, g_ktc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
+
+}  // namespace fm

@@ -396,6 +396,58 @@ __device__ __forceinline__ uint32_t pack_bf16_2(uint64_t v) {
   return pack_bf16(lo, hi);
 }
 
+// ---- helpers shared by the score kernels ------------------------------------------------------
+// 16 bytes from shared memory by shared-window address (keeps the load off the generic path)
+__device__ __forceinline__ ulonglong2 lds_v2(uint32_t saddr) {
+  ulonglong2 r;
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(r.x), "=l"(r.y) : "r"(saddr) : "memory");
+  return r;
+}
+
+// One thread's accumulator row segment (NC fp32 columns from TMEM column tcol) -> bf16 global
+// row, with the optional fp32 addend; returns the dot product with the x row when wanted.
+template <int NC>
+__device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfloat16* dst,
+                                           const float* add, const __nv_bfloat16* xr, float scale) {
+  float part = 0.f;
+#pragma unroll
+  for (int c0 = 0; c0 < NC; c0 += 32) {
+    uint32_t ov[32];
+    tmem_ld32(taddr + c0, ov);
+    tmem_wait_ld();
+    if (row_ok) {
+#pragma unroll
+      for (int v8 = 0; v8 < 4; ++v8) {
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[v8 * 8 + e]);
+        if (add) {
+          const float4 a0 = __ldg((const float4*)(add + c0) + 2 * v8);
+          const float4 a1 = __ldg((const float4*)(add + c0) + 2 * v8 + 1);
+          f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
+          f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= scale;
+        uint4 w;
+        w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
+        w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
+        ((uint4*)(dst + c0))[v8] = w;
+        if (xr) {
+          const uint4 xv = __ldg((const uint4*)(xr + c0) + v8);
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            part = fmaf(f[2 * e], __uint_as_float(xw[e] << 16), part);
+            part = fmaf(f[2 * e + 1], __uint_as_float(xw[e] & 0xFFFF0000u), part);
+          }
+        }
+      }
+    }
+  }
+  return part;
+}
+
 }  // namespace sm100
 
 // Rank-3 tensor map over a (mats, rows, d) bf16 array with boxes of box_rows x 64 elements and
