@@ -117,11 +117,11 @@ int dense_tc_wide_backward(const Ctx& c, const void* q, const void* k, const voi
 int dense_tc_wide_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
                           void* out, float* den, const ChunkAdd* ca = nullptr);
 int tc_wide_status(int* out, cudaStream_t stream);
-// grad_k and grad_v in one kernel for d == 128 (fm_dense_tc_dkdv128.cu)
+// backward for d == 128: grad_q, and grad_k / grad_v in one kernel (fm_dense_tc_dkdv128.cu)
 bool dense_tc_dkdv128_supports(const fastmax_problem& p);
-int dense_tc_dkdv128(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
-                     const float* dvec, const stat_t* stats, float* dots_k, void* grad_k, void* grad_v,
-                     const ChunkAdd* ca = nullptr);
+int dense_tc_backward128(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
+                         const float* dvec, const stat_t* stats, float* dots, void* grad_q, void* grad_k,
+                         void* grad_v, const ChunkAdd* ca = nullptr);
 int tc_dkdv128_status(int* out, cudaStream_t stream);
 
 // Optional coupling of the score-form kernels to the moment-state form: columns are

@@ -554,6 +554,8 @@ int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v,
     return fail(FASTMAX_E_ARG, "the tensor-core family needs 16-byte aligned tensors");
   if (dense_tc_wide_supports(p))
     return dense_tc_wide_backward(c, q, k, v, gs, dvec, stats, dots, grad_q, grad_k, grad_v, ca);
+  if (dense_tc_dkdv128_supports(p))
+    return dense_tc_backward128(c, q, k, v, gs, dvec, stats, dots, grad_q, grad_k, grad_v, ca);
   int rc;
   TcArgs a = base_args(c, stats);
   a.dvec = dvec;
@@ -563,8 +565,6 @@ int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v,
   a.dots = p.normalize ? dots : nullptr;
   if (ca) { a.chunk = ca->chunk; a.o_add = ca->gq_add; }
   if ((rc = launch_tc<OP_B>(c, "fm_dense_tc_dq", q, gs, k, v, p.nq, p.nk, a))) return rc;
-  if (dense_tc_dkdv128_supports(p))
-    return dense_tc_dkdv128(c, q, k, v, gs, dvec, stats, dots + p.bh, grad_k, grad_v, ca);
   // grad_k: rows = keys, columns = queries
   a.o = grad_k;
   a.rev = 1;

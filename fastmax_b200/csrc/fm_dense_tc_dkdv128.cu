@@ -1,9 +1,12 @@
-// grad_k and grad_v of the score form in one pass for head dimension 128 (bf16, tcgen05):
-// rows = keys (x = k, u = v), columns = queries (y = q, z = gs), reverse direction
-// (column >= row - off):
-//   S = X Y^T, W = U Z^T,  E = f'(S) (W - dvec_col),  P = f(S),  grad_k += E Y,  grad_v += P Z.
-// Sharing S between the two gradients makes a 128 x 64 tile cost 24 + 8 MMA instructions instead
-// of the 40 + 8 of separate grad_k and grad_v kernels.
+// Backward of the score form for head dimension 128 (bf16, tcgen05).
+//   FUSED = 1  grad_k and grad_v in one pass: rows = keys (x = k, u = v), columns = queries
+//              (y = q, z = gs), reverse direction (column >= row - off):
+//                S = X Y^T, W = U Z^T,  E = f'(S) (W - dvec_col),  P = f(S),
+//                grad_k += E Y,  grad_v += P Z.
+//              Sharing S between the two gradients makes a 128 x 64 tile cost 24 + 8 MMA
+//              instructions instead of the 40 + 8 of separate grad_k and grad_v kernels.
+//   FUSED = 0  grad_q: rows = queries (x = q, u = gs), columns = keys (y = k, z = v), forward
+//              direction:  E = f'(S) (W - dvec_row),  grad_q += E Y.
 //
 // One CTA owns one 128-row tile.  Two 128-column fp32 accumulators take 256 of the 512 TMEM
 // columns, so S, W (64 columns each) and E, P (32 each, bf16 pairs) are single-buffered:
@@ -27,13 +30,13 @@ namespace {
 using namespace sm100;
 
 struct KArgs {
-  void* gk;              // (heads, nrows, 128) bf16
+  void* gk;              // (heads, nrows, 128) bf16: grad_k, or grad_q when not FUSED
   void* gv;
   const float* gk_add;   // fp32 rows added before rounding (may be null)
   const float* gv_add;
-  const void* x;         // keys in global memory (normalisation dot)
+  const void* x;         // row operand in global memory (normalisation dot)
   const float* dvec;     // (heads, ncols)
-  float* dots;           // per head sum of grad_k . k, or null
+  float* dots;           // per head sum of gk . x, or null
   const stat_t* stat_q;
   const stat_t* stat_k;
   int nrows, ncols, off, mask, ntr, chunk;
@@ -54,6 +57,7 @@ constexpr int T_S = 0, T_W = 64, T_E = 128, T_P = 160, T_GK = 192, T_GV = 320;
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_ktc_status, 0, code); }
 
+template <bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
 dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
@@ -71,13 +75,22 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // consecutive CTAs work on one head (its column tiles stay in L2); longest rows first
+  constexpr bool rev = FUSED;
   const int head = blockIdx.x / a.ntr;
-  const int r0 = (blockIdx.x % a.ntr) * BM;
+  const int pidx = blockIdx.x % a.ntr;
+  const int r0 = (rev ? pidx : a.ntr - 1 - pidx) * BM;
 
   const int ntile = (a.ncols + BN - 1) / BN;
   int tb = 0, te = ntile;
-  if (a.mask) tb = max(0, r0 - a.off) / BN;
-  if (a.chunk > 0) te = min(te, (r0 / a.chunk + 1) * (a.chunk / BN));   // the row tile lies in one chunk
+  if (a.mask) {
+    if (rev) tb = max(0, r0 - a.off) / BN;
+    else te = min(ntile, (min(r0 + BM - 1, a.nrows - 1) + a.off) / BN + 1);
+  }
+  if (a.chunk > 0) {  // the row tile lies in one chunk (chunk % 256 == 0)
+    const int cb = (r0 / a.chunk) * (a.chunk / BN), ce = cb + a.chunk / BN;
+    if (rev) te = min(te, ce);
+    else tb = cb;
+  }
   const int J = max(te - tb, 0);
 
   if (tid == 0) {
@@ -165,7 +178,8 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const uint32_t y_mn = st_mn + (uint32_t)s * (STAGE >> 4);
         if (elect_one()) {
           umma_ts_steps<BN / 16>(tmem + T_GK, tmem + T_E, y_mn, idescO, j > 0 ? 1u : 0u);
-          umma_ts_steps<BN / 16>(tmem + T_GV, tmem + T_P, y_mn + (COL_TILE >> 4), idescO, j > 0 ? 1u : 0u);
+          if (FUSED)
+            umma_ts_steps<BN / 16>(tmem + T_GV, tmem + T_P, y_mn + (COL_TILE >> 4), idescO, j > 0 ? 1u : 0u);
           umma_commit(BAR_PV);
           umma_commit(BAR_EMPTY(s));
           if (j + 1 == J) umma_commit(BAR_DONE);
@@ -183,9 +197,15 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
     const uint64_t A0v = pack2(A0, A0), A1v = pack2(A1, A1), A2v = pack2(A2, A2);
     const uint64_t A2d = pack2(2.f * A2, 2.f * A2);
-    const int limcol = a.ncols - 1;                         // columns kept: lowcol <= col <= limcol
-    const int lowcol = a.mask ? row - a.off : 0;
-    const int wrow_hi = r0 + qd * 32 + 31;
+    int limcol = a.ncols - 1, lowcol = 0;                   // columns kept: lowcol <= col <= limcol
+    if (a.mask) {
+      if (rev) lowcol = row - a.off;
+      else limcol = min(limcol, row + a.off);
+    }
+    const int wrow_lo = r0 + qd * 32, wrow_hi = wrow_lo + 31;
+    float dl_row = 0.f;
+    if (!rev && row_ok) dl_row = __ldg(a.dvec + (size_t)head * a.nrows + row);
+    const uint64_t ndl_row = pack2(-dl_row, -dl_row);
     const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
     float* myvec = (float*)(smem + OFF_VEC) + warp * 64;
     const uint32_t myvec_s = sbase + OFF_VEC + warp * 256;
@@ -194,16 +214,18 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const int col = (tb + j) * BN + cpart * 32 + lane;
       return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;
     };
-    float nxt = fetch_vec(0);
+    float nxt = rev ? fetch_vec(0) : 0.f;
     bool ok = true;
     for (int j = 0; j < J; ++j) {
       const float cur = nxt;
-      nxt = fetch_vec(j + 1);
+      if (rev) nxt = fetch_vec(j + 1);
       if (!mbar_wait(BAR_S, (uint32_t)(j & 1))) { report(7); ok = false; break; }
       tc_fence_after();
       const uint32_t vec_s = myvec_s + (j & 1) * 128;
-      myvec[(j & 1) * 32 + lane] = cur;
-      __syncwarp();
+      if (rev) {
+        myvec[(j & 1) * 32 + lane] = cur;
+        __syncwarp();
+      }
       uint32_t sv[32], wv[32];
       tmem_ld32(tl + T_S + cpart * 32, sv);
       tmem_ld32(tl + T_W + cpart * 32, wv);
@@ -214,33 +236,35 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (lane == 0) mbar_arrive(BAR_SFREE);
       const int c0 = (tb + j) * BN + cpart * 32;    // this warp's 32 columns
       bool need_mask = (c0 + 32 > a.ncols);
-      if (a.mask) need_mask = need_mask || (c0 < wrow_hi - a.off);
+      if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
       // the mask test stays outside the element loops so that each loop is one basic block whose
       // sixteen independent pairs the compiler can interleave
-      uint32_t pe[16], pp[16];
+      uint32_t pe[16], pp[FUSED ? 16 : 1];
       ulonglong2 nd2 = make_ulonglong2(0ull, 0ull);
       if (!need_mask) {
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if ((e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
-          const uint64_t ndl = (e & 1) ? nd2.y : nd2.x;
+          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
+          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
           pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
-          pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+          if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if ((e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
-          const uint64_t ndl = (e & 1) ? nd2.y : nd2.x;
+          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
+          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
           const int col = c0 + 2 * e;
           const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
           float v0, v1;
           unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
           pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
-          unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
-          pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+          if (FUSED) {
+            unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+            pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+          }
         }
       }
       // the previous tile's products must have consumed E and P before they are overwritten
@@ -249,26 +273,34 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         tc_fence_after();
       }
       tmem_st16(tl + T_E + cpart * 16, pe);
-      tmem_st16(tl + T_P + cpart * 16, pp);
+      if constexpr (FUSED) tmem_st16(tl + T_P + cpart * 16, pp);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR_P);
     }
-    // ---- epilogue: warps 0-3 write grad_k (and the normalisation dot), warps 4-7 grad_v ----
+    // ---- epilogue: fused: warps 0-3 write grad_k (and the normalisation dot), warps 4-7 grad_v;
+    // otherwise each warp writes 64 of the 128 grad_q columns of its rows ----
     if (ok && J > 0) {
       if (!mbar_wait(BAR_DONE, 0)) { report(10); ok = false; }
     }
     tc_fence_after();
     if (ok && J > 0) {
       const size_t grow = (size_t)head * a.nrows + (row_ok ? row : 0);
-      const bool second = cpart == 1;
+      const bool second = FUSED && cpart == 1;
       const bool dots_here = !second && a.dots != nullptr;
-      const float* add = second ? a.gv_add : a.gk_add;
-      const float part = store_row<D>(tl + (second ? T_GV : T_GK), row_ok,
-                                      (__nv_bfloat16*)(second ? a.gv : a.gk) + grow * D,
-                                      add ? add + grow * D : nullptr,
-                                      dots_here ? (const __nv_bfloat16*)a.x + grow * D : nullptr, 1.f);
+      float part;
+      if constexpr (FUSED) {
+        const float* add = second ? a.gv_add : a.gk_add;
+        part = store_row<D>(tl + (second ? T_GV : T_GK), row_ok, (__nv_bfloat16*)(second ? a.gv : a.gk) + grow * D,
+                            add ? add + grow * D : nullptr,
+                            dots_here ? (const __nv_bfloat16*)a.x + grow * D : nullptr, 1.f);
+      } else {
+        const int cc = cpart * 64;
+        part = store_row<64>(tl + T_GK + cc, row_ok, (__nv_bfloat16*)a.gk + grow * D + cc,
+                             a.gk_add ? a.gk_add + grow * D + cc : nullptr,
+                             dots_here ? (const __nv_bfloat16*)a.x + grow * D + cc : nullptr, 1.f);
+      }
       if (dots_here) {
         float sum = part;
 #pragma unroll
@@ -297,43 +329,58 @@ bool dense_tc_dkdv128_supports(const fastmax_problem& p) {
   return !off && p.dtype == FASTMAX_BF16 && p.d == 128 && p.bh == p.bhkv;
 }
 
-int dense_tc_dkdv128(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
-                     const float* dvec, const stat_t* stats, float* dots_k, void* grad_k, void* grad_v,
-                     const ChunkAdd* ca) {
-  const fastmax_problem& p = c.p;
-  const int heads = p.bh, nrows = p.nk, ncols = p.nq;
+namespace {
+template <bool FUSED>
+int launch128(const Ctx& c, const char* name, const void* x, const void* u, const void* y, const void* z,
+              int nrows, int ncols, KArgs a) {
+  const int heads = c.p.bh;
   if (heads == 0 || nrows == 0) return FASTMAX_OK;
   CUtensorMap tx, tu, ty, tz;
   int rc;
-  if ((rc = tma_map_bf16(&tx, k, heads, nrows, D, BM))) return rc;
-  if ((rc = tma_map_bf16(&tu, v, heads, nrows, D, BM))) return rc;
-  if ((rc = tma_map_bf16(&ty, q, heads, ncols, D, BN))) return rc;
-  if ((rc = tma_map_bf16(&tz, gs, heads, ncols, D, BN))) return rc;
-  KArgs a = {};
-  a.gk = grad_k;
-  a.gv = grad_v;
-  a.gk_add = ca ? ca->gk_add : nullptr;
-  a.gv_add = ca ? ca->gv_add : nullptr;
-  a.x = k;
-  a.dvec = dvec;
-  a.dots = p.normalize ? dots_k : nullptr;
-  a.stat_q = p.normalize ? stats : nullptr;
-  a.stat_k = p.normalize ? stats + p.bh : nullptr;
+  if ((rc = tma_map_bf16(&tx, x, heads, nrows, D, BM))) return rc;
+  if ((rc = tma_map_bf16(&tu, u, heads, nrows, D, BM))) return rc;
+  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, BN))) return rc;
+  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, BN))) return rc;
+  const fastmax_problem& p = c.p;
+  a.x = x;
   a.nrows = nrows;
   a.ncols = ncols;
   a.off = p.nk - p.nq;
   a.mask = p.mask;
-  a.chunk = ca ? ca->chunk : 0;
   a.ntr = (nrows + BM - 1) / BM;
   a.a0 = p.a0;
   a.a1 = p.a1;
   a.a2 = (p.p == 2) ? p.a2 : 0.f;
   a.lim = p.lim;
-  FM_CUDA_TRY(cudaFuncSetAttribute(dkdv128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  FM_CUDA_TRY(cudaFuncSetAttribute(dkdv128_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
   dim3 grid((unsigned)((size_t)heads * a.ntr));
-  FM_LAUNCH("fm_dense_tc_dkdv", c.stream, (dkdv128_kernel<<<grid, kThreads, SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+  FM_LAUNCH(name, c.stream, (dkdv128_kernel<FUSED><<<grid, kThreads, SMEM, c.stream>>>(tx, tu, ty, tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
+}
+}  // namespace
+
+// The whole backward for d == 128: grad_q, then grad_k and grad_v in one kernel.
+int dense_tc_backward128(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
+                         const float* dvec, const stat_t* stats, float* dots, void* grad_q, void* grad_k,
+                         void* grad_v, const ChunkAdd* ca) {
+  const fastmax_problem& p = c.p;
+  KArgs a = {};
+  a.dvec = dvec;
+  a.stat_q = p.normalize ? stats : nullptr;
+  a.stat_k = p.normalize ? stats + p.bh : nullptr;
+  a.chunk = ca ? ca->chunk : 0;
+  int rc;
+  a.gk = grad_q;
+  a.gk_add = ca ? ca->gq_add : nullptr;
+  a.dots = p.normalize ? dots : nullptr;
+  if ((rc = launch128<false>(c, "fm_dense_tc_dq", q, gs, k, v, p.nq, p.nk, a))) return rc;
+  a.gk = grad_k;
+  a.gv = grad_v;
+  a.gk_add = ca ? ca->gk_add : nullptr;
+  a.gv_add = ca ? ca->gv_add : nullptr;
+  a.dots = p.normalize ? dots + p.bh : nullptr;
+  return launch128<true>(c, "fm_dense_tc_dkdv", k, v, q, gs, p.nk, p.nq, a);
 }
 
 int tc_dkdv128_status(int* out, cudaStream_t stream) {
