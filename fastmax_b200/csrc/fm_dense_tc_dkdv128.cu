@@ -10,7 +10,8 @@
 //
 // One CTA owns one 128-row tile.  Two 128-column fp32 accumulators take 256 of the 512 TMEM
 // columns, so S, W (64 columns each) and E, P (32 each, bf16 pairs) are single-buffered:
-//   S 0..63 | W 64..127 | E 128..159 | P 160..191 | grad_k 192..319 | grad_v 320..447.
+//   S 0..63 | W 64..127 | E 128..159 | P 160..191 | grad_k 192..319 | grad_v 320..447
+// (grad_q, 128-column tiles: S 0..127 | W 128..255 | E 256..319 | grad_q 320..447).
 // Warps 0-7 compute (warp % 4 = TMEM lane quarter = 32 rows, warp / 4 = which 32 of the 64
 // columns), warp 8 is the TMA producer, warp 9 allocates TMEM and issues the S / W products
 // (as soon as the compute warps have copied the previous tile to registers), warp 10 issues
@@ -43,17 +44,26 @@ struct KArgs {
   float a0, a1, a2, lim;
 };
 
-constexpr int BM = 128, BN = 64, D = 128, NS = 4;
+constexpr int BM = 128, D = 128;
 constexpr int kThreads = 352, kComputeWarps = 8, kProducerWarp = 8, kIssuerWarp = 9, kAccIssuerWarp = 10;
 constexpr int ROW_SUB = BM * 128, ROW_TILE = 2 * ROW_SUB;   // a row tile is two 64-wide sub-tiles
-constexpr int COL_SUB = BN * 128, COL_TILE = 2 * COL_SUB, STAGE = 2 * COL_TILE;
 constexpr int OFF_X = 0, OFF_U = ROW_TILE, OFF_ST = 2 * ROW_TILE;
-constexpr int OFF_VEC = OFF_ST + NS * STAGE;                // per compute warp 2 x 32 floats
-constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
-constexpr int NBAR = 2 + 2 * NS + 4;
-constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
-constexpr int SMEM = OFF_TMEM + 16 + 1024;
-constexpr int T_S = 0, T_W = 64, T_E = 128, T_P = 160, T_GK = 192, T_GV = 320;
+// The fused kernel needs two 128-column accumulators and stays at 64-column tiles; grad_q has
+// room for 128-column tiles, whose S / W products are not bound by the shared-memory port.
+template <bool FUSED>
+struct KCfg {
+  static constexpr int BN = FUSED ? 64 : 128;
+  static constexpr int NS = FUSED ? 4 : 2;
+  static constexpr int COL_SUB = BN * 128, COL_TILE = 2 * COL_SUB, STAGE = 2 * COL_TILE;
+  static constexpr int OFF_VEC = OFF_ST + NS * STAGE;       // per compute warp 2 x 32 floats
+  static constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
+  static constexpr int NBAR = 2 + 2 * NS + 4;
+  static constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
+  static constexpr int SMEM = OFF_TMEM + 16 + 1024;
+  // TMEM columns: S | W | E (| P) | accumulator(s)
+  static constexpr int T_S = 0, T_W = BN, T_E = 2 * BN, T_P = T_E + BN / 2;
+  static constexpr int T_GK = FUSED ? 192 : 320, T_GV = 320;
+};
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_ktc_status, 0, code); }
 
@@ -62,6 +72,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
                const KArgs a) {
+  using C = KCfg<FUSED>;
+  constexpr int BN = C::BN, NS = C::NS, COL_SUB = C::COL_SUB, COL_TILE = C::COL_TILE, STAGE = C::STAGE;
+  constexpr int OFF_VEC = C::OFF_VEC, OFF_BAR = C::OFF_BAR, OFF_TMEM = C::OFF_TMEM;
+  constexpr int T_S = C::T_S, T_W = C::T_W, T_E = C::T_E, T_P = C::T_P, T_GK = C::T_GK, T_GV = C::T_GV;
+  constexpr int HB = BN / 2;          // columns of one compute warp = packed bf16 columns of a tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -226,54 +241,61 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         myvec[(j & 1) * 32 + lane] = cur;
         __syncwarp();
       }
-      uint32_t sv[32], wv[32];
-      tmem_ld32(tl + T_S + cpart * 32, sv);
-      tmem_ld32(tl + T_W + cpart * 32, wv);
-      tmem_wait_ld();
-      // S and W of this tile are in registers: the next tile's may be issued
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(BAR_SFREE);
-      const int c0 = (tb + j) * BN + cpart * 32;    // this warp's 32 columns
-      bool need_mask = (c0 + 32 > a.ncols);
-      if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
-      // the mask test stays outside the element loops so that each loop is one basic block whose
-      // sixteen independent pairs the compiler can interleave
-      uint32_t pe[16], pp[FUSED ? 16 : 1];
-      ulonglong2 nd2 = make_ulonglong2(0ull, 0ull);
-      if (!need_mask) {
+      // the warp's HB columns in passes of 32
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
-          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
-          pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
-          if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+      for (int ps = 0; ps < HB / 32; ++ps) {
+        uint32_t sv[32], wv[32];
+        tmem_ld32(tl + T_S + cpart * HB + ps * 32, sv);
+        tmem_ld32(tl + T_W + cpart * HB + ps * 32, wv);
+        tmem_wait_ld();
+        if (ps + 1 == HB / 32) {
+          // S and W of this tile are in registers: the next tile's may be issued
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_SFREE);
         }
-      } else {
+        const int c0 = (tb + j) * BN + cpart * HB + ps * 32;    // first of these 32 columns
+        bool need_mask = (c0 + 32 > a.ncols);
+        if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
+        // the mask test stays outside the element loops so that each loop is one basic block whose
+        // sixteen independent pairs the compiler can interleave
+        uint32_t pe[16], pp[FUSED ? 16 : 1];
+        ulonglong2 nd2 = make_ulonglong2(0ull, 0ull);
+        if (!need_mask) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
-          if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
-          const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
-          const int col = c0 + 2 * e;
-          const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
-          float v0, v1;
-          unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
-          pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
-          if (FUSED) {
-            unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
-            pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+          for (int e = 0; e < 16; ++e) {
+            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+            if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
+            const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
+            pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
+            if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
+            if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);
+            const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
+            const int col = c0 + 2 * e;
+            const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
+            float v0, v1;
+            unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
+            pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+            if (FUSED) {
+              unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+              pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
+            }
           }
         }
+        // the previous tile's products must have consumed E and P before they are overwritten
+        if (ps == 0 && j > 0) {
+          if (!mbar_wait(BAR_PV, (uint32_t)((j - 1) & 1))) { report(9); ok = false; break; }
+          tc_fence_after();
+        }
+        tmem_st16(tl + T_E + cpart * (HB / 2) + ps * 16, pe);
+        if constexpr (FUSED) tmem_st16(tl + T_P + cpart * (HB / 2) + ps * 16, pp);
       }
-      // the previous tile's products must have consumed E and P before they are overwritten
-      if (j > 0) {
-        if (!mbar_wait(BAR_PV, (uint32_t)((j - 1) & 1))) { report(9); ok = false; break; }
-        tc_fence_after();
-      }
-      tmem_st16(tl + T_E + cpart * 16, pe);
-      if constexpr (FUSED) tmem_st16(tl + T_P + cpart * 16, pp);
+      if (!ok) break;
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -339,8 +361,8 @@ int launch128(const Ctx& c, const char* name, const void* x, const void* u, cons
   int rc;
   if ((rc = tma_map_bf16(&tx, x, heads, nrows, D, BM))) return rc;
   if ((rc = tma_map_bf16(&tu, u, heads, nrows, D, BM))) return rc;
-  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, BN))) return rc;
-  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, BN))) return rc;
+  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, KCfg<FUSED>::BN))) return rc;
+  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, KCfg<FUSED>::BN))) return rc;
   const fastmax_problem& p = c.p;
   a.x = x;
   a.nrows = nrows;
@@ -352,9 +374,10 @@ int launch128(const Ctx& c, const char* name, const void* x, const void* u, cons
   a.a1 = p.a1;
   a.a2 = (p.p == 2) ? p.a2 : 0.f;
   a.lim = p.lim;
-  FM_CUDA_TRY(cudaFuncSetAttribute(dkdv128_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  FM_CUDA_TRY(cudaFuncSetAttribute(dkdv128_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   KCfg<FUSED>::SMEM));
   dim3 grid((unsigned)((size_t)heads * a.ntr));
-  FM_LAUNCH(name, c.stream, (dkdv128_kernel<FUSED><<<grid, kThreads, SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+  FM_LAUNCH(name, c.stream, (dkdv128_kernel<FUSED><<<grid, kThreads, KCfg<FUSED>::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }
