@@ -103,10 +103,11 @@ import sys, torch
 sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
 from gpu_util import assert_close, oracle, run_cabi
 from fastmax_b200 import _cabi
-for bh, nq, nk, mask, p, norm in [(2, 257, 257, 1, 2, 1), (2, 70, 100, 1, 2, 1), (2, 300, 300, 0, 1, 0)]:
+for bh, nq, nk, mask, p, norm, d in [(2, 257, 257, 1, 2, 1, 64), (2, 70, 100, 1, 2, 1, 64), (2, 300, 300, 0, 1, 0, 64),
+                                     (2, 300, 300, 1, 2, 1, 128)]:
     g = torch.Generator().manual_seed(nq)
-    q, go = torch.randn(1, bh, nq, 64, generator=g), torch.randn(1, bh, nq, 64, generator=g)
-    k, v = torch.randn(1, bh, nk, 64, generator=g), torch.randn(1, bh, nk, 64, generator=g)
+    q, go = torch.randn(1, bh, nq, d, generator=g), torch.randn(1, bh, nq, d, generator=g)
+    k, v = torch.randn(1, bh, nk, d, generator=g), torch.randn(1, bh, nk, d, generator=g)
     if not norm:
         q, k = q / 8, k / 8
     kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
@@ -131,8 +132,9 @@ def test_three_kernel_backward_stays_correct_when_the_fused_one_is_switched_off(
     assert r.returncode == 0 and "NARROW-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
-def test_fused_backward_is_the_default_for_head_dimension_64():
-    q, k, v, go = [randn(1, 2, 384, 64, seed=s) for s in (11, 12, 13, 14)]
+@pytest.mark.parametrize("d", [64, 128])
+def test_fused_backward_is_the_default(d):
+    q, k, v, go = [randn(1, 2, 384, d, seed=s) for s in (11, 12, 13, 14)]
     _cabi.profile(True)
     run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", mask=1, normalize=1, p=2)
     names = {n for n, _ in _cabi.profile_records()}
