@@ -10,7 +10,9 @@ namespace fm {
 static size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 
 int moments_chunk(const fastmax_problem& p) {
-  int L = p.chunk > 0 ? p.chunk : (moments_tc_supports(p) ? 1024 : 2048);
+  // 2048 tokens per chunk: measured best for the tensor-core kernels (8.9 ms at 1024, 7.8 at 2048, 8.2 at
+  // 4096 per step for 8 heads of 65536 tokens); fewer, larger chunks mean fewer states to build, scan and convert
+  int L = p.chunk > 0 ? p.chunk : 2048;
   L = (L + 255) / 256 * 256;
   return L;
 }

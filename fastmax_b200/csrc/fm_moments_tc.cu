@@ -426,7 +426,8 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
         if (lane == 0) mbar_arrive(BAR_AFULL(b));
       }
     }
-    // ---- epilogue: accumulator rows -> fp32 state (columns 0..63) ----
+    // ---- epilogue: accumulator rows -> fp32 state (columns 0..63); the normaliser column and the
+    // padding are zeroed here, state_ecol_kernel then adds its partial sums into column 64 ----
     if (ok && !mbar_wait(BAR_DONE(), 0)) { report(35); ok = false; }
     tc_fence_after();
     if (ok) {
@@ -444,6 +445,7 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
         for (int e = 0; e < 16; ++e)
           dst[e] = make_float4(__uint_as_float(tv[4 * e]), __uint_as_float(tv[4 * e + 1]),
                                __uint_as_float(tv[4 * e + 2]), __uint_as_float(tv[4 * e + 3]));
+        dst[16] = make_float4(0.f, 0.f, 0.f, 0.f);   // columns 64..67 (dvp == 68 at d == 64)
       }
     }
   }
@@ -456,14 +458,18 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
 }
 
 // Normaliser column of the second-order rows on the CUDA cores:
-//   state[(a,b)][64] = sum_j e_j y_j[a] y_j[b]   (e = 1, or -dvec), columns 65.. zeroed.
+//   state[(a,b)][64] += sum_j e_j y_j[a] y_j[b]   (e = 1, or -dvec)
+// over this CTA's slice of the chunk's tokens (blockIdx.y of gridDim.y slices); the column was
+// zeroed by state_tc_kernel, which runs before on the same stream.
 __global__ void __launch_bounds__(256) state_ecol_kernel(const __nv_bfloat16* __restrict__ y,
                                                          const float* __restrict__ dvec,
                                                          float* __restrict__ state, int n, int chunk,
                                                          int nchunk, int dvp, size_t per_state) {
   __shared__ float ys[32][65], ye[32][65];
   const int hc = blockIdx.x, head = hc / nchunk, ck = hc % nchunk;
-  const int t_begin = ck * chunk, t_end = min(n, t_begin + chunk);
+  const int slice = ((chunk + (int)gridDim.y - 1) / (int)gridDim.y + 31) / 32 * 32;
+  const int t_begin = ck * chunk + (int)blockIdx.y * slice;
+  const int t_end = min(min(n, ck * chunk + chunk), t_begin + slice);
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;   // 4 x 4 outputs: a = ty+16i, b = tx+16j
   float acc[4][4];
 #pragma unroll
@@ -497,9 +503,7 @@ __global__ void __launch_bounds__(256) state_ecol_kernel(const __nv_bfloat16* __
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
-      float* row = st + (size_t)((ty + 16 * i) * 64 + tx + 16 * jj) * dvp;
-      row[64] = acc[i][jj];
-      for (int cc = 65; cc < dvp; ++cc) row[cc] = 0.f;
+      if (t_begin < t_end) atomicAdd(st + (size_t)((ty + 16 * i) * 64 + tx + 16 * jj) * dvp + 64, acc[i][jj]);
     }
 }
 
@@ -583,7 +587,7 @@ int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void
             (state_tc_kernel<<<(unsigned)((size_t)heads * nchunk * 4), ST_THREADS, ST_SMEM, c.stream>>>(tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
   FM_LAUNCH("fm_moments_state_ecol", c.stream,
-            (state_ecol_kernel<<<(unsigned)((size_t)heads * nchunk), 256, 0, c.stream>>>(
+            (state_ecol_kernel<<<dim3((unsigned)((size_t)heads * nchunk), 8), 256, 0, c.stream>>>(
                 (const __nv_bfloat16*)y, dvec, state, n, chunk, nchunk, m.dvp, a.per_state)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;

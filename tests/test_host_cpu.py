@@ -100,3 +100,12 @@ def test_rpe_matrix_creator_shapes():
     assert r.shape == (9, 8) and float(r.abs().sum()) == 0.0
     r = fastmax_b200.rpe_matrix_creator(5, 8, "cpu", torch.float32, structured=True)
     assert r.shape == (9, 8) and torch.allclose(r[4], torch.tensor([0., 1.] * 4))
+
+
+def test_numa_preference_is_a_no_op_without_a_gpu():
+    """The helper must never raise: without CUDA (or without a readable topology) it reports -1."""
+    from fastmax_b200.host import prefer_gpu_numa_node
+    if not torch.cuda.is_available():
+        assert prefer_gpu_numa_node("cuda:0") == -1
+    else:
+        assert prefer_gpu_numa_node("cuda:0") >= -1
