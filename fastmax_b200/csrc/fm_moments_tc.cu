@@ -460,51 +460,89 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
 // Normaliser column of the second-order rows on the CUDA cores:
 //   state[(a,b)][64] += sum_j e_j y_j[a] y_j[b]   (e = 1, or -dvec)
 // over this CTA's slice of the chunk's tokens (blockIdx.y of gridDim.y slices); the column was
-// zeroed by state_tc_kernel, which runs before on the same stream.
+// zeroed by state_tc_kernel, which runs before on the same stream.  Four groups of 64 threads
+// take every fourth token of a 32-token stage; a thread owns an 8 x 8 block of (a, b), so a
+// token costs it four 16-byte shared-memory loads per 64 FMAs.
 __global__ void __launch_bounds__(256) state_ecol_kernel(const __nv_bfloat16* __restrict__ y,
                                                          const float* __restrict__ dvec,
                                                          float* __restrict__ state, int n, int chunk,
                                                          int nchunk, int dvp, size_t per_state) {
-  __shared__ float ys[32][65], ye[32][65];
+  __shared__ __align__(16) float stage[2][32][64];
+  float (*ys)[64] = stage[0], (*ye)[64] = stage[1];
   const int hc = blockIdx.x, head = hc / nchunk, ck = hc % nchunk;
   const int slice = ((chunk + (int)gridDim.y - 1) / (int)gridDim.y + 31) / 32 * 32;
   const int t_begin = ck * chunk + (int)blockIdx.y * slice;
   const int t_end = min(min(n, ck * chunk + chunk), t_begin + slice);
-  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;   // 4 x 4 outputs: a = ty+16i, b = tx+16j
-  float acc[4][4];
+  if (t_begin >= t_end) return;
+  const int grp = threadIdx.x >> 6, w = threadIdx.x & 63;
+  const int a0 = (w >> 3) * 8, b0 = (w & 7) * 8;
+  float acc[8][8];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 8; ++i)
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.f;
+    for (int jj = 0; jj < 8; ++jj) acc[i][jj] = 0.f;
   const __nv_bfloat16* yb = y + (size_t)head * n * 64;
+  // 32 tokens x 64 values per stage, 8 bf16 per thread; the next stage's values are fetched into
+  // registers while the current stage is being multiplied
+  const int lr = threadIdx.x >> 3, c8 = (threadIdx.x & 7) * 8;
+  auto fetch = [&](int t0, uint4& v, float& e) {
+    const int tok = t0 + lr;
+    v = make_uint4(0u, 0u, 0u, 0u);
+    e = 0.f;
+    if (tok < t_end) {
+      v = __ldg((const uint4*)(yb + (size_t)tok * 64 + c8));
+      e = dvec ? -__ldg(dvec + (size_t)head * n + tok) : 1.f;
+    }
+  };
+  uint4 v;
+  float e;
+  fetch(t_begin, v, e);
   for (int t0 = t_begin; t0 < t_end; t0 += 32) {
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
-      const int r = idx >> 6, cc = idx & 63, tok = t0 + r;
-      const float v = (tok < t_end) ? __bfloat162float(yb[(size_t)tok * 64 + cc]) : 0.f;
-      const float e = (tok < t_end) ? (dvec ? -dvec[(size_t)head * n + tok] : 1.f) : 0.f;
-      ys[r][cc] = v;
-      ye[r][cc] = v * e;
+    {
+      const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float lo = __uint_as_float(vw[q] << 16), hi = __uint_as_float(vw[q] & 0xFFFF0000u);
+        ys[lr][c8 + 2 * q] = lo;
+        ys[lr][c8 + 2 * q + 1] = hi;
+        ye[lr][c8 + 2 * q] = lo * e;
+        ye[lr][c8 + 2 * q + 1] = hi * e;
+      }
     }
     __syncthreads();
-#pragma unroll 4
-    for (int r = 0; r < 32; ++r) {
-      float xa[4], xb[4];
+    if (t0 + 32 < t_end) fetch(t0 + 32, v, e);
+#pragma unroll 2
+    for (int r = grp; r < 32; r += 4) {
+      const float4 xa0 = *(const float4*)&ye[r][a0], xa1 = *(const float4*)&ye[r][a0 + 4];
+      const float4 xb0 = *(const float4*)&ys[r][b0], xb1 = *(const float4*)&ys[r][b0 + 4];
+      const float xa[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
+      const float xb[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { xa[i] = ye[r][ty + 16 * i]; xb[i] = ys[r][tx + 16 * i]; }
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) acc[i][jj] = fmaf(xa[i], xb[jj], acc[i][jj]);
+        for (int jj = 0; jj < 8; ++jj) acc[i][jj] = fmaf(xa[i], xb[jj], acc[i][jj]);
     }
   }
-  float* st = state + (size_t)hc * per_state;
+  // the four groups' partial sums are added up in shared memory (the staging arrays are free now),
+  // so the CTA issues one atomic per (a, b)
+  float* red = &stage[0][0][0];
+  static_assert(sizeof(stage) == 4096 * sizeof(float), "the staging arrays must hold one 64 x 64 block");
+  for (int gsel = 0; gsel < 4; ++gsel) {
+    __syncthreads();
+    if (grp == gsel) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
-      if (t_begin < t_end) atomicAdd(st + (size_t)((ty + 16 * i) * 64 + tx + 16 * jj) * dvp + 64, acc[i][jj]);
+        for (int jj = 0; jj < 8; ++jj) {
+          float* dst = red + (a0 + i) * 64 + b0 + jj;
+          *dst = (gsel == 0) ? acc[i][jj] : *dst + acc[i][jj];
+        }
     }
+  }
+  __syncthreads();
+  float* st = state + (size_t)hc * per_state;
+  for (int i = threadIdx.x; i < 4096; i += 256) atomicAdd(st + (size_t)i * dvp + 64, red[i]);
 }
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -587,7 +625,7 @@ int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void
             (state_tc_kernel<<<(unsigned)((size_t)heads * nchunk * 4), ST_THREADS, ST_SMEM, c.stream>>>(tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
   FM_LAUNCH("fm_moments_state_ecol", c.stream,
-            (state_ecol_kernel<<<dim3((unsigned)((size_t)heads * nchunk), 8), 256, 0, c.stream>>>(
+            (state_ecol_kernel<<<dim3((unsigned)((size_t)heads * nchunk), 2), 256, 0, c.stream>>>(
                 (const __nv_bfloat16*)y, dvec, state, n, chunk, nchunk, m.dvp, a.per_state)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
