@@ -135,7 +135,7 @@ static int pick_impl(const fastmax_problem& p, bool packed, int* impl) {
   }
   if (want == FASTMAX_IMPL_DENSE_TC && !tc_ok)
     return fail(FASTMAX_E_UNSUPPORTED,
-                "the tensor-core score family needs bf16, d == 64, bh == bhkv and the plain output layout");
+                "the tensor-core score family needs bf16, d in {64, 128} (grouped k/v heads: d == 64) and the plain output layout");
   if (want != FASTMAX_IMPL_DENSE_FFMA && want != FASTMAX_IMPL_DENSE_TC)
     return fail(FASTMAX_E_UNSUPPORTED, "kernel family %d is not available in this build", want);
   *impl = want;

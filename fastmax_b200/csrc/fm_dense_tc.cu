@@ -50,6 +50,7 @@ struct TcArgs {
   const stat_t* stat_k;
   int nrows, ncols, off, mask, rev, fwd_div, npairs;
   float a0, a1, a2, lim;
+  int ratio;             // query heads per key/value head (forward-direction modes only)
   int chunk;             // > 0: only the columns of the row pair's own chunk
   const float* o_add;    // fp32 (heads, nrows, d) added to the accumulator row
   const float* den_add;  // OP_A with fwd_div: added to the row sum
@@ -187,8 +188,8 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         mbar_expect_tx(BAR_FULL(s), C::STAGE);
         const uint32_t dst = sbase + C::OFF_ST + s * C::STAGE;
         for (int sub = 0; sub < C::NSUB; ++sub) {
-          tma_load_3d(dst + sub * C::COL_SUB, &tmY, BAR_FULL(s), sub * 64, t * BN, head);
-          tma_load_3d(dst + C::COL_TILE + sub * C::COL_SUB, &tmZ, BAR_FULL(s), sub * 64, t * BN, head);
+          tma_load_3d(dst + sub * C::COL_SUB, &tmY, BAR_FULL(s), sub * 64, t * BN, head / a.ratio);
+          tma_load_3d(dst + C::COL_TILE + sub * C::COL_SUB, &tmZ, BAR_FULL(s), sub * 64, t * BN, head / a.ratio);
         }
       }
       if (colvec) {
@@ -271,7 +272,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     if (g == 0 || act1) {
       const int row = r0 + g * BM + qd * 32 + lane;
       const bool row_ok = row < a.nrows;
-      const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
+      const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head / a.ratio, a.lim);
       const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
       const uint64_t A0v = pack2(A0, A0), A1v = pack2(A1, A1);
       const uint64_t A2v = (MODE == OP_A) ? pack2(A2, A2) : pack2(2.f * A2, 2.f * A2);
@@ -487,8 +488,11 @@ int launch_tc_d(const Ctx& c, const char* name, const void* x, const void* u, co
   int rc;
   if ((rc = make_map(&tx, x, heads, nrows, BM, DD))) return rc;
   if ((rc = make_map(&tu, u ? u : x, heads, nrows, BM, DD))) return rc;
-  if ((rc = make_map(&ty, y, heads, ncols, C::BN, DD))) return rc;
-  if ((rc = make_map(&tz, z, heads, ncols, C::BN, DD))) return rc;
+  // grouped k/v heads reach this launcher only in the forward direction (rows = query heads)
+  const int col_heads = a.rev ? heads : c.p.bhkv;
+  a.ratio = a.rev ? 1 : c.p.bh / c.p.bhkv;
+  if ((rc = make_map(&ty, y, col_heads, ncols, C::BN, DD))) return rc;
+  if ((rc = make_map(&tz, z, col_heads, ncols, C::BN, DD))) return rc;
   a.nrows = nrows;
   a.ncols = ncols;
   a.x = x;
@@ -528,7 +532,10 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 }  // namespace
 
 bool dense_tc_supports(const fastmax_problem& p) {
-  return p.dtype == FASTMAX_BF16 && (p.d == 64 || p.d == 128) && p.bh == p.bhkv;
+  if (p.dtype != FASTMAX_BF16) return false;
+  if ((p.d == 64 || p.d == 128) && p.bh == p.bhkv) return true;
+  // grouped k/v heads: the kernels that walk a key/value head's tiles once per query head
+  return dense_tc_wide_supports(p) || dense_tc_dkdv128_supports(p);
 }
 
 int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,

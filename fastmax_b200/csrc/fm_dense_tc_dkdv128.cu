@@ -41,6 +41,7 @@ struct KArgs {
   const stat_t* stat_q;
   const stat_t* stat_k;
   int nrows, ncols, off, mask, ntr, chunk;
+  int ratio;             // query heads per key/value head (grouped k/v heads)
   float a0, a1, a2, lim;
 };
 
@@ -106,7 +107,19 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     if (rev) te = min(te, ce);
     else tb = cb;
   }
-  const int J = max(te - tb, 0);
+  // Grouped k/v heads: a query head reads the tiles of key/value head `head / ratio`; a key/value
+  // head (FUSED rows) walks the same tile range once for each of its `ratio` query heads.
+  const int Jh = max(te - tb, 0);
+  const int J = rev ? Jh * a.ratio : Jh;
+  // Column head and tile of the running tile number, advanced without divisions: `t` is the tile
+  // inside the head's range [tb, tb + Jh), `h` the column head.
+  struct ColPos { int t, h; };
+  const ColPos pos0 = {tb, rev ? head * a.ratio : head / a.ratio};
+  auto advance = [&](ColPos& cp, int steps) {
+    cp.t += steps;
+    if (rev)
+      while (cp.t >= tb + Jh && Jh > 0) { cp.t -= Jh; ++cp.h; }
+  };
 
   if (tid == 0) {
     mbar_init(BAR_X, 1);
@@ -140,15 +153,16 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         tma_load_3d(sbase + OFF_U + sub * ROW_SUB, &tmU, BAR_X, sub * 64, r0, head);
       }
     }
-    for (int j = 0; j < J; ++j) {
+    ColPos pc = pos0;
+    for (int j = 0; j < J; ++j, advance(pc, 1)) {
       const int s = j % NS;
       if (!mbar_wait(BAR_EMPTY(s), (((j / NS) & 1) ^ 1))) { report(1); break; }
       if (lane == 0) {
         mbar_expect_tx(BAR_FULL(s), STAGE);
         const uint32_t dst = sbase + OFF_ST + s * STAGE;
         for (int sub = 0; sub < 2; ++sub) {
-          tma_load_3d(dst + sub * COL_SUB, &tmY, BAR_FULL(s), sub * 64, (tb + j) * BN, head);
-          tma_load_3d(dst + COL_TILE + sub * COL_SUB, &tmZ, BAR_FULL(s), sub * 64, (tb + j) * BN, head);
+          tma_load_3d(dst + sub * COL_SUB, &tmY, BAR_FULL(s), sub * 64, pc.t * BN, pc.h);
+          tma_load_3d(dst + COL_TILE + sub * COL_SUB, &tmZ, BAR_FULL(s), sub * 64, pc.t * BN, pc.h);
         }
       }
     }
@@ -208,10 +222,19 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const int cpart = warp >> 2, qd = warp & 3;
     const int row = r0 + qd * 32 + lane;
     const bool row_ok = row < a.nrows;
-    const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
-    const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
-    const uint64_t A0v = pack2(A0, A0), A1v = pack2(A1, A1), A2v = pack2(A2, A2);
-    const uint64_t A2d = pack2(2.f * A2, 2.f * A2);
+    // scale of the scores: query-head statistic times key-head statistic (the query head of a
+    // FUSED tile changes with the tile when k/v heads are grouped)
+    const float ck = stat_scale(a.stat_k, rev ? head : head / a.ratio, a.lim);
+    const uint64_t A0v = pack2(a.a0, a.a0);
+    uint64_t A1v, A2v, A2d;
+    auto set_coefficients = [&](int hq) {
+      const float c = stat_scale(a.stat_q, hq, a.lim) * ck;
+      const float A1 = a.a1 * c, A2 = a.a2 * c * c;
+      A1v = pack2(A1, A1);
+      A2v = pack2(A2, A2);
+      A2d = pack2(2.f * A2, 2.f * A2);
+    };
+    set_coefficients(rev ? head * a.ratio : head);
     int limcol = a.ncols - 1, lowcol = 0;                   // columns kept: lowcol <= col <= limcol
     if (a.mask) {
       if (rev) lowcol = row - a.off;
@@ -225,15 +248,26 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     float* myvec = (float*)(smem + OFF_VEC) + warp * 64;
     const uint32_t myvec_s = sbase + OFF_VEC + warp * 256;
     // negated dvec of this lane's column in the next tile, fetched one tile ahead
-    auto fetch_vec = [&](int j) -> float {
-      const int col = (tb + j) * BN + cpart * 32 + lane;
-      return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;
+    auto fetch_vec = [&](int j, const ColPos& cp) -> float {
+      if (j >= J) return 0.f;
+      const int col = cp.t * BN + cpart * 32 + lane;
+      return (col < a.ncols) ? -__ldg(a.dvec + (size_t)cp.h * a.ncols + col) : 0.f;
     };
-    float nxt = rev ? fetch_vec(0) : 0.f;
+    ColPos pc = pos0;                     // position of the current tile
+    float nxt = rev ? fetch_vec(0, pc) : 0.f;
+    int hq_now = -1;
     bool ok = true;
-    for (int j = 0; j < J; ++j) {
+    for (int j = 0; j < J; ++j, advance(pc, 1)) {
       const float cur = nxt;
-      if (rev) nxt = fetch_vec(j + 1);
+      if (rev) {
+        ColPos pn = pc;                   // the next tile
+        advance(pn, 1);
+        nxt = fetch_vec(j + 1, pn);
+      }
+      if (rev && a.ratio > 1 && pc.h != hq_now) {
+        hq_now = pc.h;
+        set_coefficients(pc.h);
+      }
       if (!mbar_wait(BAR_S, (uint32_t)(j & 1))) { report(7); ok = false; break; }
       tc_fence_after();
       const uint32_t vec_s = myvec_s + (j & 1) * 128;
@@ -254,7 +288,7 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) mbar_arrive(BAR_SFREE);
         }
-        const int c0 = (tb + j) * BN + cpart * HB + ps * 32;    // first of these 32 columns
+        const int c0 = pc.t * BN + cpart * HB + ps * 32;    // first of these 32 columns
         bool need_mask = (c0 + 32 > a.ncols);
         if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
         // the mask test stays outside the element loops so that each loop is one basic block whose
@@ -342,27 +376,29 @@ dkdv128_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
 }  // namespace
 
-// bf16, head dimension 128, bh == bhkv; FASTMAX_B200_NO_WIDE=1 keeps separate grad_k / grad_v kernels.
+// bf16, head dimension 128, bh a multiple of bhkv; FASTMAX_B200_NO_WIDE=1 keeps separate grad_k / grad_v kernels.
 bool dense_tc_dkdv128_supports(const fastmax_problem& p) {
   static const bool off = [] {
     const char* e = getenv("FASTMAX_B200_NO_WIDE");
     return e && e[0] == '1';
   }();
-  return !off && p.dtype == FASTMAX_BF16 && p.d == 128 && p.bh == p.bhkv;
+  return !off && p.dtype == FASTMAX_BF16 && p.d == 128 && p.bhkv > 0 && p.bh % p.bhkv == 0;
 }
 
 namespace {
 template <bool FUSED>
 int launch128(const Ctx& c, const char* name, const void* x, const void* u, const void* y, const void* z,
               int nrows, int ncols, KArgs a) {
-  const int heads = c.p.bh;
+  // rows are key/value heads in the fused kernel and query heads in grad_q; the columns are the other kind
+  const int heads = FUSED ? c.p.bhkv : c.p.bh, col_heads = FUSED ? c.p.bh : c.p.bhkv;
+  a.ratio = c.p.bh / c.p.bhkv;
   if (heads == 0 || nrows == 0) return FASTMAX_OK;
   CUtensorMap tx, tu, ty, tz;
   int rc;
   if ((rc = tma_map_bf16(&tx, x, heads, nrows, D, BM))) return rc;
   if ((rc = tma_map_bf16(&tu, u, heads, nrows, D, BM))) return rc;
-  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, KCfg<FUSED>::BN))) return rc;
-  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, KCfg<FUSED>::BN))) return rc;
+  if ((rc = tma_map_bf16(&ty, y, col_heads, ncols, D, KCfg<FUSED>::BN))) return rc;
+  if ((rc = tma_map_bf16(&tz, z, col_heads, ncols, D, KCfg<FUSED>::BN))) return rc;
   const fastmax_problem& p = c.p;
   a.x = x;
   a.nrows = nrows;

@@ -28,6 +28,7 @@
 // All waits are bounded; a wait that gives up records a status and the CTA winds down.
 #include <climits>
 #include <cstdlib>
+#include <type_traits>
 
 #include "fm_common.cuh"
 #include "fm_sm100.cuh"
@@ -52,6 +53,7 @@ struct WArgs {
   const stat_t* stat_q;
   const stat_t* stat_k;
   int nrows, ncols, off, mask, ntr, chunk;
+  int ratio;             // query heads per key/value head (grouped k/v heads)
   float a0, a1, a2, lim;
 };
 
@@ -76,7 +78,7 @@ struct WCfg {
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_wtc_status, 0, code); }
 
-template <int MODE>
+template <int MODE, bool GQ>   // GQ: grouped k/v heads (bh > bhkv); the plain case compiles without the head walk
 __global__ void __launch_bounds__(kThreads, 1)
 dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                      const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
@@ -120,7 +122,23 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     if (rev) te = min(te, ce);
     else tb = cb;
   }
-  const int J = max(te - tb, 0);
+  // Grouped k/v heads: a query head reads the tiles of key/value head `head / ratio`; a key/value
+  // head (MODE_DKDV rows) walks the same tile range once for each of its `ratio` query heads.
+  const int ratio = GQ ? a.ratio : 1;
+  const int Jh = max(te - tb, 0);
+  const int J = rev ? Jh * ratio : Jh;
+  // Column head and tile of the running tile number, advanced without divisions: `t` is the tile
+  // inside the head's range [tb, tb + Jh), `h` the column head.
+  struct ColPos { int t, h; };
+  const ColPos pos0 = {tb, rev ? head * ratio : head / ratio};
+  auto advance = [&](ColPos& cp, int steps) {
+    cp.t += steps;
+    if (GQ && rev)
+      while (cp.t >= tb + Jh && Jh > 0) { cp.t -= Jh; ++cp.h; }
+  };
+  // without grouped heads the position follows from the tile number alone and the tracker is dead code
+  auto tile_of = [&](int j, const ColPos& cp) { return GQ ? cp.t : tb + j; };
+  auto head_of = [&](const ColPos& cp) { return GQ ? cp.h : head; };
 
   if (tid == 0) {
     mbar_init(BAR_X, 1);
@@ -154,14 +172,15 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       tma_load_3d(sbase + OFF_X, &tmX, BAR_X, 0, r0, head);
       if (!FWD) tma_load_3d(sbase + OFF_U, &tmU, BAR_X, 0, r0, head);
     }
-    for (int j = 0; j < J; ++j) {
+    ColPos pc = pos0;
+    for (int j = 0; j < J; ++j, advance(pc, 1)) {
       const int s = j % NS;
       if (!mbar_wait(BAR_EMPTY(s), (((j / NS) & 1) ^ 1))) { report(1); break; }
       if (lane == 0) {
         mbar_expect_tx(BAR_FULL(s), STAGE);
         const uint32_t dst = sbase + OFF_ST + s * STAGE;
-        tma_load_3d(dst, &tmY, BAR_FULL(s), 0, (tb + j) * BN, head);
-        tma_load_3d(dst + COL_TILE, &tmZ, BAR_FULL(s), 0, (tb + j) * BN, head);
+        tma_load_3d(dst, &tmY, BAR_FULL(s), 0, tile_of(j, pc) * BN, head_of(pc));
+        tma_load_3d(dst + COL_TILE, &tmZ, BAR_FULL(s), 0, tile_of(j, pc) * BN, head_of(pc));
       }
     }
   } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
@@ -228,10 +247,14 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     const int gp = warp >> 3, cpart = (warp >> 2) & 1, qd = warp & 3;
     const int row = r0 + qd * 32 + lane;
     const bool row_ok = row < a.nrows;
-    const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
+    // scale of the scores: query-head statistic times key-head statistic (the query head of a
+    // MODE_DKDV tile changes with the tile when k/v heads are grouped)
+    const float ck = stat_scale(a.stat_k, rev ? head : head / ratio, a.lim);
+    const float c = stat_scale(a.stat_q, rev ? head * ratio : head, a.lim) * ck;
     const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
-    const uint64_t A0v = pack2(A0, A0), A1v = pack2(A1, A1), A2v = pack2(A2, A2);
-    const uint64_t A2d = pack2(2.f * A2, 2.f * A2);
+    const uint64_t A0v = pack2(A0, A0);
+    using coef_t = typename std::conditional<GQ, uint64_t, const uint64_t>::type;   // fixed unless heads are grouped
+    coef_t A1v = pack2(A1, A1), A2v = pack2(A2, A2), A2d = pack2(2.f * A2, 2.f * A2);
     int limcol = a.ncols - 1, lowcol = 0;   // columns kept for this row: lowcol <= col <= limcol
     if (a.mask) {
       if (rev) lowcol = row - a.off;
@@ -245,17 +268,34 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     float* myvec = (float*)(smem + OFF_VEC) + warp * 64;
     const uint32_t myvec_s = sbase + OFF_VEC + warp * 256;
     // negated dvec of this lane's column in the warp's next tile, fetched one tile ahead
-    auto fetch_vec = [&](int j) -> float {
-      const int col = (tb + j) * BN + cpart * 32 + lane;
-      return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head * a.ncols + col) : 0.f;
+    auto fetch_vec = [&](int j, const ColPos& cp) -> float {
+      const int col = tile_of(j, cp) * BN + cpart * 32 + lane;
+      return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head_of(cp) * a.ncols + col) : 0.f;
     };
-    float nxt = rev ? fetch_vec(gp) : 0.f;
+    ColPos pc = pos0;                     // position of this group's current tile
+    advance(pc, gp);
+    float nxt = rev ? fetch_vec(gp, pc) : 0.f;
+    [[maybe_unused]] int hq_now = -1;
     uint64_t rs2[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};  // forward: row sum
     bool ok = true;
-    for (int j = gp; j < J; j += 2) {
+    for (int j = gp; j < J; j += 2, advance(pc, 2)) {
       const int i = j >> 1;
       const float cur = nxt;
-      if (rev) nxt = fetch_vec(j + 2);
+      if (rev) {
+        ColPos pn = pc;                   // the group's next tile
+        advance(pn, 2);
+        nxt = fetch_vec(j + 2, pn);
+      }
+      if constexpr (GQ) {
+        if (rev && pc.h != hq_now) {   // the tile belongs to the next query head of the group
+          hq_now = pc.h;
+          const float cq = stat_scale(a.stat_q, pc.h, a.lim) * ck;
+          const float B1 = a.a1 * cq, B2 = a.a2 * cq * cq;
+          A1v = pack2(B1, B1);
+          A2v = pack2(B2, B2);
+          A2d = pack2(2.f * B2, 2.f * B2);
+        }
+      }
       // The group's previous products must have consumed E and P before they are overwritten.
       // grad_q waits for its S / W anyway (that path bounds its tile period), so the check goes
       // here, where it costs nothing on the way to the stores; the other two modes are bound by
@@ -281,7 +321,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
           __syncwarp();
           if (lane == 0) mbar_arrive(BAR_SFREE(gp));
         }
-        const int c0 = (tb + j) * BN + cpart * HB + ps * 32;    // first of these 32 columns
+        const int c0 = tile_of(j, pc) * BN + cpart * HB + ps * 32;    // first of these 32 columns
         bool need_mask = (c0 + 32 > a.ncols);
         if (a.mask) need_mask = need_mask || (rev ? (c0 < wrow_hi - a.off) : (c0 + 31 > wrow_lo + a.off));
         // the mask test stays outside the element loops so that each loop is one basic block
@@ -399,37 +439,47 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 template <int MODE>
 int launch_wide(const Ctx& c, const char* name, const void* x, const void* u, const void* y,
                 const void* z, int nrows, int ncols, WArgs a) {
-  const int heads = c.p.bh;
+  // rows are key/value heads in MODE_DKDV and query heads otherwise; the columns are the other kind
+  const int heads = (MODE == MODE_DKDV) ? c.p.bhkv : c.p.bh;
+  const int col_heads = (MODE == MODE_DKDV) ? c.p.bh : c.p.bhkv;
+  a.ratio = c.p.bh / c.p.bhkv;
   if (heads == 0 || nrows == 0) return FASTMAX_OK;
   CUtensorMap tx, tu, ty, tz;
   int rc;
   if ((rc = tma_map_bf16(&tx, x, heads, nrows, D, BM))) return rc;
   if ((rc = tma_map_bf16(&tu, u ? u : x, heads, nrows, D, BM))) return rc;
-  if ((rc = tma_map_bf16(&ty, y, heads, ncols, D, WCfg<MODE>::BN))) return rc;
-  if ((rc = tma_map_bf16(&tz, z, heads, ncols, D, WCfg<MODE>::BN))) return rc;
+  if ((rc = tma_map_bf16(&ty, y, col_heads, ncols, D, WCfg<MODE>::BN))) return rc;
+  if ((rc = tma_map_bf16(&tz, z, col_heads, ncols, D, WCfg<MODE>::BN))) return rc;
   a.nrows = nrows;
   a.ncols = ncols;
   a.x = x;
   a.ntr = (nrows + BM - 1) / BM;
-  FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   WCfg<MODE>::SMEM));
   dim3 grid((unsigned)((size_t)heads * a.ntr));
-  FM_LAUNCH(name, c.stream,
-            (dense_tc_wide_kernel<MODE><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+  if (a.ratio > 1) {
+    FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     WCfg<MODE>::SMEM));
+    FM_LAUNCH(name, c.stream,
+              (dense_tc_wide_kernel<MODE, true><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+  } else {
+    FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     WCfg<MODE>::SMEM));
+    FM_LAUNCH(name, c.stream,
+              (dense_tc_wide_kernel<MODE, false><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+  }
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }
 
 }  // namespace
 
-// bf16, head dimension 64, bh == bhkv (the caller has checked the first and the last);
+// bf16, head dimension 64, bh a multiple of bhkv (grouped k/v heads are handled in the kernels);
 // FASTMAX_B200_NO_WIDE=1 in the environment keeps the three-kernel backward.
 bool dense_tc_wide_supports(const fastmax_problem& p) {
   static const bool off = [] {
     const char* e = getenv("FASTMAX_B200_NO_WIDE");
     return e && e[0] == '1';
   }();
-  return !off && p.dtype == FASTMAX_BF16 && p.d == 64 && p.bh == p.bhkv;
+  return !off && p.dtype == FASTMAX_BF16 && p.d == 64 && p.bhkv > 0 && p.bh % p.bhkv == 0;
 }
 
 int dense_tc_wide_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,

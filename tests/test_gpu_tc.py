@@ -140,3 +140,25 @@ def test_fused_backward_is_the_default(d):
     names = {n for n, _ in _cabi.profile_records()}
     _cabi.profile(False)
     assert {"fm_dense_tc_dq", "fm_dense_tc_dkdv"} <= names and "fm_dense_tc_dv" not in names, names
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("mask", [0, 1])
+def test_grouped_kv_heads_on_the_tensor_core_family(mask, d):
+    """bh = 3 * bhkv, nk > nq: each key/value head serves three query heads inside the kernels."""
+    from oracle.fastmax_oracle import fastmax_dense
+    q, go = randn(1, 6, 200, d, seed=1), randn(1, 6, 200, d, seed=2)
+    k, v = randn(1, 2, 300, d, seed=3), randn(1, 2, 300, d, seed=4)
+    kw = dict(mask=mask, normalize=1, p=2, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+    _cabi.profile(True)
+    got, _ = run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", **kw)
+    names = {n for n, _ in _cabi.profile_records()}
+    _cabi.profile(False)
+    assert "fm_dense_tc_dkdv" in names and _cabi.device_status() == 0
+    r = lambda t: t.bfloat16().double()
+    kx, vx = [r(t).repeat_interleave(3, dim=1).requires_grad_(True) for t in (k, v)]
+    qx = r(q).requires_grad_(True)
+    out = fastmax_dense(qx, kx, vx, **kw)
+    out.backward(r(go))
+    ref = [out.detach(), qx.grad, kx.grad.reshape(1, 2, 3, 300, d).sum(2), vx.grad.reshape(1, 2, 3, 300, d).sum(2)]
+    assert_close(got, ref, torch.bfloat16, f"gqa mask={mask}")
