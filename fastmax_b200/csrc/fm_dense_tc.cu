@@ -13,16 +13,20 @@
 // where gs_i = grad_out_i / den_i and dvec_i = (grad_out_i . out_i) / den_i, these are
 // the sums the reference evaluates through running moments (see fm_dense_ffma.cu).
 //
+// These kernels serve the forward pass at head dimension 128 and, with
+// FASTMAX_B200_NO_WIDE=1, everything else; the default d = 64 kernels and the d = 128
+// backward are in fm_dense_tc_wide.cu and fm_dense_tc_dkdv128.cu.
+//
 // One CTA owns two 128-row tiles (two "groups" of four warps each, one row per
 // thread) and streams column tiles through a shared-memory ring filled by TMA.
-// A single thread issues every tcgen05.mma; per column tile and group:
+// One issuer warp per group issues the group's tcgen05.mma (the whole warp runs the
+// loop, an elected lane issues); per column tile and group:
 //   S = X Y^T (and W = U Z^T)            smem x smem  -> TMEM
 //   the group's warps read S (W) from TMEM, apply the polynomial and the mask and
 //   write the bf16 result P back to TMEM
 //   O += P Z   (or P Y)                  TMEM x smem  -> TMEM accumulator
 // A group copies its whole S (W) row block to registers and hands the TMEM region
-// back at once, so the issuing thread -- which polls the groups' barriers and
-// issues whatever is ready -- can start the next tile's S while the group is still
+// back at once, so its issuer can start the next tile's S while the group is still
 // computing; the tensor pipe therefore runs ahead of the CUDA cores of both groups.
 // The polynomial is evaluated on packed fp32 pairs.  All waits are bounded; a wait
 // that gives up records an error status and the kernel winds down without hanging.
