@@ -53,7 +53,6 @@ struct WArgs {
   const stat_t* stat_q;
   const stat_t* stat_k;
   int nrows, ncols, off, mask, ntr, chunk;
-  int ratio;             // query heads per key/value head (grouped k/v heads)
   float a0, a1, a2, lim;
 };
 
@@ -82,7 +81,7 @@ template <int MODE, bool GQ>   // GQ: grouped k/v heads (bh > bhkv); the plain c
 __global__ void __launch_bounds__(kThreads, 1)
 dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                      const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
-                     const WArgs a) {
+                     const WArgs a, const int kv_ratio) {
   using C = WCfg<MODE>;
   constexpr bool FUSED = MODE == MODE_DKDV, FWD = MODE == MODE_FWD;
   constexpr int BN = C::BN, NS = C::NS, COL_TILE = C::COL_TILE, STAGE = C::STAGE;
@@ -124,7 +123,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   }
   // Grouped k/v heads: a query head reads the tiles of key/value head `head / ratio`; a key/value
   // head (MODE_DKDV rows) walks the same tile range once for each of its `ratio` query heads.
-  const int ratio = GQ ? a.ratio : 1;
+  const int ratio = GQ ? kv_ratio : 1;
   const int Jh = max(te - tb, 0);
   const int J = rev ? Jh * ratio : Jh;
   // Column head and tile of the running tile number, advanced without divisions: `t` is the tile
@@ -132,9 +131,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   struct ColPos { int t, h; };
   const ColPos pos0 = {tb, rev ? head * ratio : head / ratio};
   auto advance = [&](ColPos& cp, int steps) {
-    cp.t += steps;
-    if (GQ && rev)
-      while (cp.t >= tb + Jh && Jh > 0) { cp.t -= Jh; ++cp.h; }
+    if constexpr (GQ) {
+      cp.t += steps;
+      if (rev)
+        while (cp.t >= tb + Jh && Jh > 0) { cp.t -= Jh; ++cp.h; }
+    }
   };
   // without grouped heads the position follows from the tile number alone and the tracker is dead code
   auto tile_of = [&](int j, const ColPos& cp) { return GQ ? cp.t : tb + j; };
@@ -250,7 +251,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     // scale of the scores: query-head statistic times key-head statistic (the query head of a
     // MODE_DKDV tile changes with the tile when k/v heads are grouped)
     const float ck = stat_scale(a.stat_k, rev ? head : head / ratio, a.lim);
-    const float c = stat_scale(a.stat_q, rev ? head * ratio : head, a.lim) * ck;
+    const float c = stat_scale(a.stat_q, rev ? head * ratio : head, a.lim) * stat_scale(a.stat_k, rev ? head : head / ratio, a.lim);
     const float A0 = a.a0, A1 = a.a1 * c, A2 = a.a2 * c * c;
     const uint64_t A0v = pack2(A0, A0);
     using coef_t = typename std::conditional<GQ, uint64_t, const uint64_t>::type;   // fixed unless heads are grouped
@@ -282,9 +283,13 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const int i = j >> 1;
       const float cur = nxt;
       if (rev) {
-        ColPos pn = pc;                   // the group's next tile
-        advance(pn, 2);
-        nxt = fetch_vec(j + 2, pn);
+        if constexpr (GQ) {
+          ColPos pn = pc;                 // the group's next tile
+          advance(pn, 2);
+          nxt = fetch_vec(j + 2, pn);
+        } else {
+          nxt = fetch_vec(j + 2, pc);
+        }
       }
       if constexpr (GQ) {
         if (rev && pc.h != hq_now) {   // the tile belongs to the next query head of the group
@@ -442,7 +447,7 @@ int launch_wide(const Ctx& c, const char* name, const void* x, const void* u, co
   // rows are key/value heads in MODE_DKDV and query heads otherwise; the columns are the other kind
   const int heads = (MODE == MODE_DKDV) ? c.p.bhkv : c.p.bh;
   const int col_heads = (MODE == MODE_DKDV) ? c.p.bh : c.p.bhkv;
-  a.ratio = c.p.bh / c.p.bhkv;
+  const int kv_ratio = c.p.bh / c.p.bhkv;
   if (heads == 0 || nrows == 0) return FASTMAX_OK;
   CUtensorMap tx, tu, ty, tz;
   int rc;
@@ -455,16 +460,16 @@ int launch_wide(const Ctx& c, const char* name, const void* x, const void* u, co
   a.x = x;
   a.ntr = (nrows + BM - 1) / BM;
   dim3 grid((unsigned)((size_t)heads * a.ntr));
-  if (a.ratio > 1) {
+  if (kv_ratio > 1) {
     FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      WCfg<MODE>::SMEM));
     FM_LAUNCH(name, c.stream,
-              (dense_tc_wide_kernel<MODE, true><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+              (dense_tc_wide_kernel<MODE, true><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a, kv_ratio)));
   } else {
     FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      WCfg<MODE>::SMEM));
     FM_LAUNCH(name, c.stream,
-              (dense_tc_wide_kernel<MODE, false><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a)));
+              (dense_tc_wide_kernel<MODE, false><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(tx, tu, ty, tz, a, kv_ratio)));
   }
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
