@@ -329,8 +329,8 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
 static int validate_shard(const fastmax_problem* prob) {
   int rc = validate(prob);
   if (rc) return rc;
-  if (!prob->mask || prob->nq != prob->nk || prob->bh != prob->bhkv)
-    return fail(FASTMAX_E_ARG, "a sequence shard needs mask = 1, nq == nk and bh == bhkv");
+  if (prob->nq != prob->nk || prob->bh != prob->bhkv)
+    return fail(FASTMAX_E_ARG, "a sequence shard needs nq == nk and bh == bhkv");
   return check_device();
 }
 static size_t shard_s16_bytes(const fastmax_problem& p) { return state16_bytes(p, p.nq); }
@@ -398,7 +398,9 @@ int fastmax_b200_shard_forward(const fastmax_problem* prob, const void* q, const
   int rc = validate_shard(prob);
   if (rc) return rc;
   const fastmax_problem& p = *prob;
-  if (!q || !k || !v || !kv_states || !out || !den) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (!q || !k || !v || !out || !den) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (p.mask && !kv_states) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (!p.mask && !s_base) return fail(FASTMAX_E_ARG, "an unmasked shard needs the total of all shards in s_base");
   if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the reduced stats buffer");
   const ShardFwdWs w = shard_fwd_layout(p);
   if (!workspace || workspace_bytes < w.bytes)
@@ -406,6 +408,9 @@ int fastmax_b200_shard_forward(const fastmax_problem* prob, const void* q, const
                 workspace_bytes);
   Ctx c{p, (cudaStream_t)stream};
   FwdOut o{out, den, p.d, 1, 0};
+  if (!p.mask)   // every query reads the total over all shards
+    return moments_forward_total(c, q, (const stat_t*)stats, s_base, (float*)((char*)workspace + w.o_add),
+                                 (float*)((char*)workspace + w.den_add), (char*)workspace + w.s16, o);
   return moments_forward_finish(c, q, k, v, (const stat_t*)stats, kv_states, s_base,
                                 (float*)((char*)workspace + w.o_add),
                                 (float*)((char*)workspace + w.den_add), (char*)workspace + w.s16, o);
@@ -444,9 +449,12 @@ int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, cons
   int rc = validate_shard(prob);
   if (rc) return rc;
   const fastmax_problem& p = *prob;
-  if (!q || !k || !v || !out || !den || !grad_out || !delta || !kv_states || !qg_states || !dots ||
-      !grad_q || !grad_k || !grad_v)
+  if (!q || !k || !v || !out || !den || !grad_out || !delta || !kv_states || !dots || !grad_q || !grad_k ||
+      !grad_v)
     return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (p.mask && !qg_states) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (!p.mask && !r_base)
+    return fail(FASTMAX_E_ARG, "an unmasked shard needs the query/gradient total of all shards in r_base");
   if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the reduced stats buffer");
   const ShardBwdWs w = shard_bwd_layout(p);
   if (!workspace || workspace_bytes < w.bytes)
@@ -458,6 +466,10 @@ int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, cons
   float* dvec = (float*)(ws + w.dvec);
   void* gs = ws + w.gs;
   if (dense_tc_supports(p) && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
+  if (!p.mask)   // kv_states holds the key/value total of all shards, r_base the query/gradient total
+    return moments_backward_total(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dvec, gs, kv_states,
+                                  r_base, (float*)(ws + w.gq), (float*)(ws + w.gk), (float*)(ws + w.gv),
+                                  ws + w.s16, p.normalize ? dots : nullptr, grad_q, grad_k, grad_v);
   return moments_backward_finish(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dvec, gs,
                                  kv_states, qg_states, r_base, (float*)(ws + w.gq), (float*)(ws + w.gk),
                                  (float*)(ws + w.gv), ws + w.s16, p.normalize ? dots : nullptr, grad_q, grad_k,

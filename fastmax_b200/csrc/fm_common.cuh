@@ -214,6 +214,14 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
                             const float* s_states, float* r_states, const float* r_base,
                             float* gq_add, float* gk_add, float* gv_add, void* s16, float* dots,
                             void* grad_q, void* grad_k, void* grad_v);
+// unmasked passes from given total states (this device's, or the sum over all sequence shards)
+int moments_forward_total(const Ctx& c, const void* q, const stat_t* stats, const float* total, float* o_add,
+                          float* den_add, void* s16, const FwdOut& o);
+int moments_backward_total(const Ctx& c, const void* q, const void* k, const void* v, const float* den,
+                           const stat_t* stats, const void* grad_out, const float* delta, const float* dvec,
+                           const void* gs, const float* kv_total, const float* qg_total, float* gq_add,
+                           float* gk_add, float* gv_add, void* s16, float* dots, void* grad_q, void* grad_k,
+                           void* grad_v);
 int moments_finalize(const Ctx& c, int heads, int n, const float* r, const float* den_in, const void* x,
                      void* out, float* den_out, float* dots, int mode);
 

@@ -180,6 +180,14 @@ int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, c
   // unmasked: every query reads the total of all keys
   const int nchunk = (p.nk + L - 1) / L;
   if ((rc = moments_prefix(c, p.bh, nchunk, states, nullptr, total, 0, 0))) return rc;
+  return moments_forward_total(c, q, stats, total, o_add, den_add, s16, o);
+}
+
+// Unmasked forward from a given total state (this device's keys, or the sum over all shards).
+int moments_forward_total(const Ctx& c, const void* q, const stat_t* stats, const float* total, float* o_add,
+                          float* den_add, void* s16, const FwdOut& o) {
+  const fastmax_problem& p = c.p;
+  int rc;
   if (o.out_f32 || o.o_stride != p.d)
     return fail(FASTMAX_E_UNSUPPORTED, "the moment family writes the plain output layout only");
   if (first_is_whole(p))
@@ -269,41 +277,65 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
     else rc = dense_ffma_backward(c, q, k, v, den, stats, grad_out, delta, dots, grad_q, grad_k, grad_v, ca);
     if (rc) return rc;
   } else {
-    // unmasked: totals only, no score-form part
+    // unmasked: totals only, no score-form part.  The two totals share one buffer, so grad_q is
+    // read out before the query/gradient total replaces the key/value total.
     if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, total, 0, 0))) return rc;
-    if (first_is_whole(p)) {
-      if ((rc = read_first_final(c, 1, p.nq, gs, q, dvec, total, s16, stats, 2, grad_q, nullptr,
-                                 p.normalize ? dots : nullptr)))
-        return rc;
-      if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
-      if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, total, 0, 0))) return rc;
-      if ((rc = read_first_final(c, 1, p.nk, v, k, nullptr, total, s16, stats, 2, grad_k, nullptr,
-                                 p.normalize ? dots + p.bh : nullptr)))
-        return rc;
-      if ((rc = read_first_final(c, 0, p.nk, k, k, nullptr, total, s16, stats, 2, grad_v, nullptr, nullptr)))
-        return rc;
-      if (p.normalize) return launch_norm_fixup(c, q, k, stats, dots, grad_q, grad_k);
-      return FASTMAX_OK;
-    }
-    if ((rc = read_states(c, 1, p.nq, 0, q, grad_out, den, delta, 1, gs, dvec, total, s16, stats, nullptr,
-                          nullptr, gq_add)))
-      return rc;
-    if ((rc = moments_finalize(c, p.bh, p.nq, gq_add, nullptr, q, grad_q, nullptr,
-                               p.normalize ? dots : nullptr, 1)))
+    if ((rc = moments_backward_total(c, q, k, v, den, stats, grad_out, delta, dvec, gs, total, nullptr, gq_add,
+                                     gk_add, gv_add, s16, dots, grad_q, nullptr, nullptr)))
       return rc;
     if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, total, 0, 0))) return rc;
-    if ((rc = read_states(c, 2, p.nk, 0, k, v, nullptr, nullptr, 0, nullptr, nullptr, total, s16, stats,
-                          gv_add, nullptr, gk_add)))
-      return rc;
-    if ((rc = moments_finalize(c, p.bh, p.nk, gk_add, nullptr, k, grad_k, nullptr,
-                               p.normalize ? dots + p.bh : nullptr, 1)))
-      return rc;
-    if ((rc = moments_finalize(c, p.bh, p.nk, gv_add, nullptr, nullptr, grad_v, nullptr, nullptr, 1)))
+    if ((rc = moments_backward_total(c, q, k, v, den, stats, grad_out, delta, dvec, gs, nullptr, total, gq_add,
+                                     gk_add, gv_add, s16, dots, nullptr, grad_k, grad_v)))
       return rc;
   }
   if (p.normalize) return launch_norm_fixup(c, q, k, stats, dots, grad_q, grad_k);
+  return FASTMAX_OK;
+}
+
+// Unmasked gradients from given total states (this device's, or the sums over all shards): grad_q
+// from the key/value total when kv_total and grad_q are given, grad_k and grad_v from the
+// query/gradient total when qg_total and grad_k are given.  Without the normalisation row fix.
+int moments_backward_total(const Ctx& c, const void* q, const void* k, const void* v, const float* den,
+                           const stat_t* stats, const void* grad_out, const float* delta, const float* dvec,
+                           const void* gs, const float* kv_total, const float* qg_total, float* gq_add,
+                           float* gk_add, float* gv_add, void* s16, float* dots, void* grad_q, void* grad_k,
+                           void* grad_v) {
+  const fastmax_problem& p = c.p;
+  int rc;
+  if (kv_total && grad_q) {
+    if (first_is_whole(p)) {
+      if ((rc = read_first_final(c, 1, p.nq, gs, q, dvec, kv_total, s16, stats, 2, grad_q, nullptr,
+                                 p.normalize ? dots : nullptr)))
+        return rc;
+    } else {
+      if ((rc = read_states(c, 1, p.nq, 0, q, grad_out, den, delta, 1, gs, dvec, kv_total, s16, stats, nullptr,
+                            nullptr, gq_add)))
+        return rc;
+      if ((rc = moments_finalize(c, p.bh, p.nq, gq_add, nullptr, q, grad_q, nullptr,
+                                 p.normalize ? dots : nullptr, 1)))
+        return rc;
+    }
+  }
+  if (qg_total && grad_k) {
+    if (first_is_whole(p)) {
+      if ((rc = read_first_final(c, 1, p.nk, v, k, nullptr, qg_total, s16, stats, 2, grad_k, nullptr,
+                                 p.normalize ? dots + p.bh : nullptr)))
+        return rc;
+      if ((rc = read_first_final(c, 0, p.nk, k, k, nullptr, qg_total, s16, stats, 2, grad_v, nullptr, nullptr)))
+        return rc;
+    } else {
+      if ((rc = read_states(c, 2, p.nk, 0, k, v, nullptr, nullptr, 0, nullptr, nullptr, qg_total, s16, stats,
+                            gv_add, nullptr, gk_add)))
+        return rc;
+      if ((rc = moments_finalize(c, p.bh, p.nk, gk_add, nullptr, k, grad_k, nullptr,
+                                 p.normalize ? dots + p.bh : nullptr, 1)))
+        return rc;
+      if ((rc = moments_finalize(c, p.bh, p.nk, gv_add, nullptr, nullptr, grad_v, nullptr, nullptr, 1)))
+        return rc;
+    }
+  }
   return FASTMAX_OK;
 }
 

@@ -1,4 +1,4 @@
-"""Causal Fastmax attention over a sequence that is split across GPUs.
+"""Fastmax attention (causal, or unmasked) over a sequence that is split across GPUs.
 
 One process per GPU (``torch.distributed``); rank r holds the r-th contiguous
 slice of the sequence for every head: ``q, k, v : (b*h, n_local, d)``.  The
@@ -14,7 +14,8 @@ Per pass the ranks exchange
   (max row norm and its global row, packed in an int64) and, in backward, one
   SUM all-reduce of ``2*b*h`` floats for the gradient of the max-norm scaling;
 * one all-gather of each rank's total state, ``b*h * (d*d+d+1) * (d+1)`` floats
-  rounded up, followed by a local sum over the earlier (or later) ranks.
+  rounded up, followed by a local sum over the earlier (or later) ranks; unmasked
+  attention needs the sum over all ranks instead, one SUM all-reduce of the totals.
 
 Everything else is local and runs through the C ABI's ``fastmax_b200_shard_*``
 stage calls.  The stage calls are reached through a small backend object so that
@@ -49,12 +50,13 @@ def exclusive_rank_sum(total: torch.Tensor, group=None, reverse: bool = False):
 class CudaShardBackend:
     """The stage calls of ``include/fastmax_b200.h`` on the current CUDA device."""
 
-    def __init__(self, **kw):
-        self.kw = kw  # mask, normalize, a0.., p, chunk as for _cabi.make_problem
+    def __init__(self, mask=True, **kw):
+        self.mask = bool(mask)
+        self.kw = kw  # normalize, a0.., p, chunk as for _cabi.make_problem
 
     def _prob(self, q, k):
         kw = self.kw
-        return _cabi.make_problem(q, k, True, kw["normalize"], 1.0, kw["a0"], kw["a1"], kw["a2"], kw["lim"],
+        return _cabi.make_problem(q, k, self.mask, kw["normalize"], 1.0, kw["a0"], kw["a1"], kw["a2"], kw["lim"],
                                   kw["p"], "auto", kw.get("chunk", 0))
 
     @staticmethod
@@ -83,7 +85,7 @@ class CudaShardBackend:
         wsb = L.fastmax_b200_shard_forward_workspace_bytes(prob)
         ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)
         _cabi._check(L.fastmax_b200_shard_forward(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), self._ptr(stats),
-                                                  kv_states.data_ptr(), self._ptr(s_base), out.data_ptr(),
+                                                  self._ptr(kv_states), self._ptr(s_base), out.data_ptr(),
                                                   den.data_ptr(), ws.data_ptr(), wsb, _cabi._stream(q)),
                      "shard_forward")
         return out, den
@@ -110,7 +112,7 @@ class CudaShardBackend:
             ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)
         _cabi._check(L.fastmax_b200_shard_backward(
             prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), den.data_ptr(), self._ptr(stats),
-            go.data_ptr(), delta.data_ptr(), kv_states.data_ptr(), qg_states.data_ptr(), self._ptr(r_base),
+            go.data_ptr(), delta.data_ptr(), kv_states.data_ptr(), self._ptr(qg_states), self._ptr(r_base),
             dots.data_ptr(), gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), ws.data_ptr(), wsb, _cabi._stream(q)),
             "shard_backward")
         return gq, gk, gv, dots
@@ -139,8 +141,14 @@ class SequenceShardedFastmax(torch.autograd.Function):
             stats = backend.rowmax(q, k, row_offset)
             dist.all_reduce(stats, op=dist.ReduceOp.MAX, group=group)
         kv_states, kv_total = backend.kv_state(k, v)
-        s_base = exclusive_rank_sum(kv_total, group)
-        out, den = backend.forward(q, k, v, stats, kv_states, s_base)
+        if getattr(backend, "mask", True):
+            s_base = exclusive_rank_sum(kv_total, group)
+            out, den = backend.forward(q, k, v, stats, kv_states, s_base)
+        else:
+            # unmasked: every token reads the total of all shards
+            kv_states = kv_total.clone()
+            dist.all_reduce(kv_states, op=dist.ReduceOp.SUM, group=group)
+            out, den = backend.forward(q, k, v, stats, None, kv_states)
         ctx.backend, ctx.group, ctx.normalize, ctx.row_offset = backend, group, normalize, row_offset
         ctx.save_for_backward(q, k, v, out, den, kv_states, *([stats] if normalize else []))
         return out
@@ -152,7 +160,12 @@ class SequenceShardedFastmax(torch.autograd.Function):
         backend, group = ctx.backend, ctx.group
         go = grad_out.contiguous().to(q.dtype)
         delta, qg_states, qg_total = backend.qg_state(q, out, den, go)
-        r_base = exclusive_rank_sum(qg_total, group, reverse=True)
+        if getattr(backend, "mask", True):
+            r_base = exclusive_rank_sum(qg_total, group, reverse=True)
+        else:
+            # unmasked: kv_states already holds the key/value total of all shards
+            r_base, qg_states = qg_total.clone(), None
+            dist.all_reduce(r_base, op=dist.ReduceOp.SUM, group=group)
         gq, gk, gv, dots = backend.backward(q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base)
         if ctx.normalize:
             dist.all_reduce(dots, op=dist.ReduceOp.SUM, group=group)
@@ -160,9 +173,10 @@ class SequenceShardedFastmax(torch.autograd.Function):
         return gq, gk, gv, None, None, None
 
 
-def fastmax_sequence_parallel(q, k, v, *, normalize=False, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2, chunk=0,
-                              group=None, backend=None):
-    """Causal Fastmax on this rank's ``(b*h, n_local, d)`` slices of q, k, v (CUDA, float32 or bfloat16).
+def fastmax_sequence_parallel(q, k, v, *, mask=True, normalize=False, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2,
+                              chunk=0, group=None, backend=None):
+    """Fastmax (causal, or unmasked with ``mask=False``) on this rank's ``(b*h, n_local, d)`` slices of q, k, v
+    (CUDA, float32 or bfloat16).
 
     Rank r of ``group`` must hold tokens ``[r*n_local, (r+1)*n_local)``, the same ``n_local`` on every rank
     (chunks of ``chunk`` tokens, default 2048, are laid out from the start of each shard).  Differentiable;
@@ -171,6 +185,6 @@ def fastmax_sequence_parallel(q, k, v, *, normalize=False, a0=1.0, a1=1.0, a2=0.
     if backend is None:
         if not q.is_cuda:
             raise RuntimeError("fastmax_sequence_parallel needs CUDA tensors")
-        backend = CudaShardBackend(normalize=bool(normalize), a0=a0, a1=a1, a2=a2, lim=lim, p=p, chunk=chunk)
+        backend = CudaShardBackend(mask=mask, normalize=bool(normalize), a0=a0, a1=a1, a2=a2, lim=lim, p=p, chunk=chunk)
     return SequenceShardedFastmax.apply(q.contiguous(), k.contiguous(), v.contiguous(), backend, bool(normalize),
                                         group)

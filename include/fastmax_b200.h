@@ -152,9 +152,9 @@ int fastmax_b200_backward(const fastmax_problem* prob,
 
 /* ---- sequence sharding ------------------------------------------------------
  * No counterpart in the reference, which has no multi-GPU code (its outputs are
- * hard-wired to cuda:0, fastmax_cuda_forward.cu:347).  A causal sequence is split
+ * hard-wired to cuda:0, fastmax_cuda_forward.cu:347).  A sequence is split
  * into contiguous shards, one per GPU, every shard holding all heads; `prob`
- * describes ONE shard (nq == nk == shard length, mask = 1, bh == bhkv).  The
+ * describes ONE shard (nq == nk == shard length, bh == bhkv); causal first.  The
  * moment states are additive over tokens, so a shard needs from the others only
  * the sum of their per-head totals: of all EARLIER shards' key/value states for
  * the forward pass and grad_q, of all LATER shards' query/gradient states for
@@ -175,6 +175,11 @@ int fastmax_b200_backward(const fastmax_problem* prob,
  *                     per-head dots (bh + bhkv floats, zeroed here)
  *   shard_norm_fixup  after dots were summed over shards: corrects the max-norm row
  *                     on the shard that owns it
+ * Unmasked shards (mask = 0): every token reads the totals of ALL shards, so the caller
+ * sum-reduces kv_total and qg_total over the shards (an all-reduce) and passes
+ *   shard_forward     s_base    = key/value total of all shards (kv_states may be NULL)
+ *   shard_backward    kv_states = key/value total of all shards,
+ *                     r_base    = query/gradient total of all shards (qg_states may be NULL)
  * Buffers: kv_states/qg_states fastmax_b200_moment_state_bytes, totals and bases
  * fastmax_b200_moment_total_bytes (float32), workspaces by the *_workspace_bytes
  * queries, delta bh*nq floats. */

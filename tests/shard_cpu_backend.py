@@ -18,7 +18,9 @@ def _phi(x):
 
 
 class TorchShardBackend:
-    def __init__(self, normalize, a0, a1, a2, lim, p):
+    def __init__(self, normalize, a0, a1, a2, lim, p, mask=True):
+        # mask False: s_base / (kv_states, r_base) hold the totals of ALL shards and nothing is local
+        self.mask = mask
         self.normalize, self.a0, self.a1, self.lim, self.p = normalize, a0, a1, lim, p
         self.a2 = a2 if p == 2 else 0.0
 
@@ -52,12 +54,16 @@ class TorchShardBackend:
     def forward(self, q, k, v, stats, kv_states, s_base):
         h, n, d = q.shape
         if s_base is not None:
-            kv_states.copy_(s_base)
+            if kv_states is None:
+                kv_states = s_base.clone()
+            else:
+                kv_states.copy_(s_base)
         A0, A1, A2 = self._coef(stats, h)
         qd, kd = q.double(), k.double()
         vt = torch.cat([v, torch.ones_like(v[..., :1])], -1).double()
         s = qd @ kd.transpose(1, 2)
-        f = (A0 + A1 * s + A2 * s * s) * torch.tril(torch.ones(n, n, dtype=torch.float64))
+        tri = torch.tril(torch.ones(n, n, dtype=torch.float64)) if self.mask else torch.zeros(n, n, dtype=torch.float64)
+        f = (A0 + A1 * s + A2 * s * s) * tri
         w = torch.cat([A2.expand(h, 1, 1).repeat(1, 1, d * d), A1.expand(h, 1, 1).repeat(1, 1, d),
                        torch.full((h, 1, 1), A0, dtype=torch.float64)], -1)
         num = f @ vt + torch.einsum("hnf,hfc->hnc", _phi(qd) * w, kv_states)
@@ -77,12 +83,15 @@ class TorchShardBackend:
     def backward(self, q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base):
         h, n, d = q.shape
         if r_base is not None:
-            qg_states.copy_(r_base)
+            if qg_states is None:
+                qg_states = r_base.clone()
+            else:
+                qg_states.copy_(r_base)
         A0, A1, A2 = self._coef(stats, h)
         qd, kd = q.double(), k.double()
         vt = torch.cat([v, torch.ones_like(v[..., :1])], -1).double()
         ut = torch.cat([go.double() / den.double()[..., None], (-delta.double() / den.double())[..., None]], -1)
-        tri = torch.tril(torch.ones(n, n, dtype=torch.float64))
+        tri = torch.tril(torch.ones(n, n, dtype=torch.float64)) if self.mask else torch.zeros(n, n, dtype=torch.float64)
         s = qd @ kd.transpose(1, 2)
         e = (A1 + 2 * A2 * s) * (ut @ vt.transpose(1, 2)) * tri
         pf = (A0 + A1 * s + A2 * s * s) * tri

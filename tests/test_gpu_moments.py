@@ -98,3 +98,43 @@ def test_shard_stage_calls_reproduce_the_unsharded_result(dtype, d, normalize):
     for a, b, name in zip(got, want, ("out", "dq", "dk", "dv")):
         e = float((a.float() - b.float()).abs().max() / b.float().abs().max())
         assert e < tol, (name, e)
+
+
+@pytest.mark.parametrize("dtype,d,normalize,p", [(torch.float32, 32, True, 2), (torch.bfloat16, 64, True, 2),
+                                                 (torch.bfloat16, 128, False, 1), (torch.float32, 16, False, 2)])
+def test_unmasked_shard_stage_calls_reproduce_the_unsharded_result(dtype, d, normalize, p):
+    """Unmasked attention over three shards: the totals are summed over ALL shards (what an
+    all-reduce does) and every shard reads them."""
+    dev = torch.device("cuda", 0)
+    G, nl, bh = 3, 384, 3
+    g = torch.Generator(device=dev).manual_seed(19)
+    q, k, v, go = [torch.randn(bh, G * nl, d, generator=g, device=dev).to(dtype) for _ in range(4)]
+    if not normalize:
+        q, k = q * d ** -0.5, k * d ** -0.5
+    kw = dict(mask=False, normalize=normalize, p=p)
+    out, den, stats = _cabi.forward(q, k, v, impl="dense_ffma", **kw)
+    want = (out,) + tuple(_cabi.backward(q, k, v, out, den, stats, go, impl="dense_ffma", **kw))
+
+    be = CudaShardBackend(mask=False, normalize=normalize, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=p, chunk=256)
+    sh = lambda t, r: t[:, r * nl:(r + 1) * nl].contiguous()
+    qs, ks, vs, gs = [[sh(t, r) for r in range(G)] for t in (q, k, v, go)]
+    st = None
+    if normalize:
+        st = torch.stack([be.rowmax(qs[r], ks[r], r * nl) for r in range(G)]).max(0).values
+    kv_total = sum(be.kv_state(ks[r], vs[r])[1] for r in range(G))
+    outs, dens = zip(*[be.forward(qs[r], ks[r], vs[r], st, None, kv_total) for r in range(G)])
+    qg = [be.qg_state(qs[r], outs[r], dens[r], gs[r]) for r in range(G)]
+    qg_total = sum(x[2] for x in qg)
+    grads = [be.backward(qs[r], ks[r], vs[r], outs[r], dens[r], st, gs[r], qg[r][0], kv_total, None, qg_total)
+             for r in range(G)]
+    if normalize:
+        dots = sum(gr[3] for gr in grads)
+        for r in range(G):
+            be.norm_fixup(qs[r], ks[r], st, dots, r * nl, grads[r][0], grads[r][1])
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    got = (torch.cat(outs, 1),) + tuple(torch.cat([gr[i] for gr in grads], 1) for i in range(3))
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    for a, b, name in zip(got, want, ("out", "dq", "dk", "dv")):
+        e = float((a.float() - b.float()).abs().max() / b.float().abs().max())
+        assert e < tol, (name, e)

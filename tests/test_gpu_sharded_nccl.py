@@ -18,7 +18,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, mask, ret):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -33,13 +33,13 @@ def _worker(rank, world, port, ret):
         g = torch.Generator(device=dev).manual_seed(3)          # same full problem on every rank
         bh, n, d = 4, 4096, 64
         q, k, v, go = [torch.randn(bh, n, d, generator=g, device=dev).bfloat16() for _ in range(4)]
-        kw = dict(mask=True, normalize=True, p=2)
+        kw = dict(mask=mask, normalize=True, p=2)
         out, den, stats = _cabi.forward(q, k, v, impl="dense_tc", **kw)
         want = (out,) + tuple(_cabi.backward(q, k, v, out, den, stats, go, impl="dense_tc", **kw))
         nl = n // world
         sl = slice(rank * nl, (rank + 1) * nl)
         ql, kl, vl = [t[:, sl].contiguous().requires_grad_(True) for t in (q, k, v)]
-        o = fastmax_sequence_parallel(ql, kl, vl, normalize=True, p=2, chunk=512)
+        o = fastmax_sequence_parallel(ql, kl, vl, mask=mask, normalize=True, p=2, chunk=512)
         o.backward(go[:, sl].contiguous())
         torch.cuda.synchronize()
         errs = []
@@ -52,14 +52,15 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_two_gpu_sequence_sharding_matches_single_gpu():
+@pytest.mark.parametrize("mask", [True, False], ids=["causal", "unmasked"])
+def test_two_gpu_sequence_sharding_matches_single_gpu(mask):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), mask, ret), nprocs=2, join=True)
     assert len(ret) == 2
     for rank, (errs, status) in ret.items():
         assert status == 0

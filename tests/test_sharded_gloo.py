@@ -21,7 +21,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, normalize, p, ret):
+def _worker(rank, world, port, normalize, p, mask, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -34,13 +34,13 @@ def _worker(rank, world, port, normalize, p, ret):
         torch.manual_seed(11)                      # every rank builds the same full problem
         h, n, d = 3, 24 * world, 8
         q, k, v, go = [torch.randn(1, h, n, d, dtype=torch.float64) for _ in range(4)]
-        kw = dict(mask=1, normalize=int(normalize), p=p, a0=0.9, a1=1.1, a2=0.45, lim=1.3)
+        kw = dict(mask=int(mask), normalize=int(normalize), p=p, a0=0.9, a1=1.1, a2=0.45, lim=1.3)
         ref = fastmax_fwd_bwd(q, k, v, go, **kw)
         nl = n // world
         sl = slice(rank * nl, (rank + 1) * nl)
         ql, kl, vl = [t[0, :, sl].clone().requires_grad_(True) for t in (q, k, v)]
-        be = TorchShardBackend(normalize, 0.9, 1.1, 0.45, 1.3, p)
-        out = fastmax_sequence_parallel(ql, kl, vl, normalize=normalize, backend=be)
+        be = TorchShardBackend(normalize, 0.9, 1.1, 0.45, 1.3, p, mask=mask)
+        out = fastmax_sequence_parallel(ql, kl, vl, mask=mask, normalize=normalize, backend=be)
         out.backward(go[0, :, sl])
         errs = [rel_err(a, b[0, :, sl]) for a, b in zip((out.detach(), ql.grad, kl.grad, vl.grad), ref)]
         ret[rank] = errs
@@ -49,11 +49,12 @@ def _worker(rank, world, port, normalize, p, ret):
 
 
 @pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("mask", [True, False], ids=["causal", "unmasked"])
 @pytest.mark.parametrize("normalize,p", [(False, 2), (True, 2), (True, 1)])
-def test_sequence_sharding_matches_unsharded_oracle(world, normalize, p):
+def test_sequence_sharding_matches_unsharded_oracle(world, normalize, p, mask):
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), normalize, p, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), normalize, p, mask, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank, errs in ret.items():
         for e, name in zip(errs, ("out", "dq", "dk", "dv")):
