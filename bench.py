@@ -41,6 +41,7 @@ WORKLOADS = {
     "c4p1": (32, 32, 16384, 128, "bf16", 0, 1, 0),
     "c5": (1, 32, 262144, 64, "bf16", 1, 2, 1),   # long context; sharded along the sequence when N > 1
     "c5s": (1, 8, 65536, 64, "bf16", 1, 2, 1),    # reduced long-context case
+    "c5u": (1, 32, 262144, 128, "bf16", 0, 1, 0), # long unmasked p = 1 sequence, sharded along the sequence when N > 1
     "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
     "c4s": (4, 8, 16384, 128, "bf16", 0, 2, 0),   # reduced unmasked d=128 case
     "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),   # small case for ncu captures (inputs 4 x 67 MB)
@@ -184,7 +185,7 @@ def run_ours(args):
     B, H, N, D, dt, mask, p, norm = WORKLOADS[args.workload]
     dtype = torch.bfloat16 if dt == "bf16" else torch.float32
     bh_total = B * H
-    seq_mode = args.workload.startswith("c5")
+    seq_mode = args.workload.startswith("c5")   # one long sequence, split along n over the ranks
     if seq_mode:
         return run_seq(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
     if args.scaling == "strong":
@@ -333,14 +334,16 @@ def run_seq(args, world, rank, dev, cfg):
     nl = N // world
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     q, k, v, go = [torch.randn(B * H, nl, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4)]
+    if not norm:   # unnormalised configurations scale q and k by 1/sqrt(D)
+        q, k = q * D ** -0.5, k * D ** -0.5
     mod = fastmax_b200.FASTMultiHeadAttention()
 
     def step():
         qd, kd, vd = [t.detach().requires_grad_(True) for t in (q, k, v)]
         if world > 1:
-            out = fastmax_sequence_parallel(qd, kd, vd, normalize=bool(norm), p=p, **A)
+            out = fastmax_sequence_parallel(qd, kd, vd, mask=bool(mask), normalize=bool(norm), p=p, chunk=args.chunk, **A)
         else:
-            out = mod(qd, kd, vd, None, True, 0.0, bool(norm), 1.0, A["a0"], A["a1"], A["a2"], A["lim"], p)
+            out = mod(qd, kd, vd, None, bool(mask), 0.0, bool(norm), 1.0, A["a0"], A["a1"], A["a2"], A["lim"], p)
         out.backward(go)
         return out
 
@@ -384,7 +387,8 @@ def run_seq(args, world, rank, dev, cfg):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dt, "data": "synthetic",
             "config": {"workload": describe(args.workload), "tokens_per_gpu": nl,
-                       "parallelism": f"sequence sharded x{world}; all-gather of per-shard moment totals, "
+                       "parallelism": f"sequence sharded x{world}; "
+                                      + ("all-gather" if mask else "all-reduce") + " of per-shard moment totals, "
                                       "all-reduce of normalisation statistics",
                        "l2": "inputs larger than the 126 MB L2"},
             "clocks": clocks, "gpu_launches": int(launches),
