@@ -7,7 +7,8 @@ Drop-in for the Python interface of armingerami/fastmax: the module
 """
 from .attention import (FASTMultiHeadAttention, FASTMultiHeadAttention_Function, fastmax_function,
                         rpe_matrix_creator)
+from .call_site import fastmax_attention_from_qkv
 
 __all__ = ["FASTMultiHeadAttention", "FASTMultiHeadAttention_Function", "fastmax_function",
-           "rpe_matrix_creator"]
+           "rpe_matrix_creator", "fastmax_attention_from_qkv"]
 __version__ = "0.1.0"

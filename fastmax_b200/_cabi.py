@@ -27,6 +27,9 @@ EXPORTS = (
     "fastmax_b200_shard_forward_workspace_bytes", "fastmax_b200_shard_backward_workspace_bytes",
     "fastmax_b200_shard_rowmax", "fastmax_b200_shard_kv_state", "fastmax_b200_shard_forward",
     "fastmax_b200_shard_qg_state", "fastmax_b200_shard_backward", "fastmax_b200_shard_norm_fixup",
+    "fastmax_b200_static_scratch_bytes", "fastmax_b200_backward_static",
+    "fastmax_b200_qkv_split_rope", "fastmax_b200_qkv_merge_rope_grad", "fastmax_b200_swap_middle_axes",
+    "fastmax_b200_scale_by_noise",
 )
 
 
@@ -78,6 +81,11 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_profile_enable.argtypes = [ctypes.c_int]
         L.fastmax_b200_profile_get.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int,
                                                ctypes.POINTER(ctypes.c_float)]
+        i64, ci = ctypes.c_longlong, ctypes.c_int
+        L.fastmax_b200_qkv_split_rope.argtypes = [vp] * 6 + [i64, i64, ci, ci, ci, ci, ci, vp]
+        L.fastmax_b200_qkv_merge_rope_grad.argtypes = [vp] * 6 + [i64, i64, ci, ci, ci, ci, ci, vp]
+        L.fastmax_b200_swap_middle_axes.argtypes = [vp, vp, i64, i64, i64, ci, ci, vp]
+        L.fastmax_b200_scale_by_noise.argtypes = [vp, vp, vp, ctypes.c_float, sz, ci, vp]
         _lib = L
     return _lib
 
@@ -237,3 +245,85 @@ def backward(q, k, v, out, den, stats, grad_out, *, mask, normalize, temperature
                                      _stream(q))
     _check(rc, "fastmax_b200_backward")
     return gq, gk, gv
+
+
+# ---- the transformer call site around the attention ---------------------------------------------
+
+def _rope_tables(cos, sin, n, rope_n, device):
+    if rope_n == 0:
+        return None, None
+    out = []
+    for t in (cos, sin):
+        if t.shape != (n, rope_n):
+            raise ValueError(f"cos / sin must be ({n}, {rope_n}), got {tuple(t.shape)}")
+        out.append(t.to(device=device, dtype=torch.float32).contiguous())
+    return out
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def qkv_split_rope(qkv, cos, sin, rope_n):
+    """``qkv`` (B, T, G, Q+2, hs) -> q (B*G*Q, T, hs), k and v (B*G, T, hs), the first ``rope_n`` features
+    of q and k rotated by the (T, rope_n) tables.  One pass over HBM."""
+    if not qkv.is_cuda or qkv.dim() != 5 or not qkv.is_contiguous():
+        raise ValueError("qkv must be a contiguous CUDA tensor (B, T, G, Q+2, hs)")
+    b, n, g, total, d = qkv.shape
+    qper = total - 2
+    cs, sn = _rope_tables(cos, sin, n, rope_n, qkv.device)
+    q = torch.empty(b * g * qper, n, d, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(b * g, n, d, dtype=qkv.dtype, device=qkv.device)
+    v = torch.empty_like(k)
+    with torch.cuda.device(qkv.device):
+        rc = lib().fastmax_b200_qkv_split_rope(qkv.data_ptr(), _ptr(cs), _ptr(sn), q.data_ptr(), k.data_ptr(),
+                                               v.data_ptr(), b, n, g, qper, d, rope_n, _dtype_code(qkv),
+                                               _stream(qkv))
+    _check(rc, "fastmax_b200_qkv_split_rope")
+    return q, k, v
+
+
+def qkv_merge_rope_grad(gq, gk, gv, cos, sin, rope_n, batch):
+    """Gradient of the packed projection (B, T, G, Q+2, hs) from the per-head gradients."""
+    for t in (gq, gk, gv):
+        if not t.is_cuda or t.dim() != 3 or not t.is_contiguous() or t.dtype != gq.dtype:
+            raise ValueError("gradients must be contiguous CUDA tensors (heads, T, hs) of one dtype")
+    n, d = gq.shape[1], gq.shape[2]
+    g = gk.shape[0] // batch
+    qper = gq.shape[0] // gk.shape[0]
+    if gk.shape != gv.shape or g * batch != gk.shape[0] or qper * gk.shape[0] != gq.shape[0]:
+        raise ValueError("head counts do not match the batch size")
+    cs, sn = _rope_tables(cos, sin, n, rope_n, gq.device)
+    out = torch.empty(batch, n, g, qper + 2, d, dtype=gq.dtype, device=gq.device)
+    with torch.cuda.device(gq.device):
+        rc = lib().fastmax_b200_qkv_merge_rope_grad(gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), _ptr(cs), _ptr(sn),
+                                                    out.data_ptr(), batch, n, g, qper, d, rope_n,
+                                                    _dtype_code(gq), _stream(gq))
+    _check(rc, "fastmax_b200_qkv_merge_rope_grad")
+    return out
+
+
+def swap_middle_axes(x):
+    """(B, X, Y, hs) -> contiguous (B, Y, X, hs)."""
+    if not x.is_cuda or x.dim() != 4 or not x.is_contiguous():
+        raise ValueError("expected a contiguous CUDA tensor (B, X, Y, hs)")
+    b, nx, ny, d = x.shape
+    out = torch.empty(b, ny, nx, d, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib().fastmax_b200_swap_middle_axes(x.data_ptr(), out.data_ptr(), b, nx, ny, d, _dtype_code(x),
+                                                 _stream(x))
+    _check(rc, "fastmax_b200_swap_middle_axes")
+    return out
+
+
+def scale_by_noise(x, noise, dropout, out=None):
+    """``x * (1 + dropout * noise)``; ``out`` may be ``x``."""
+    if not x.is_cuda or not x.is_contiguous() or not noise.is_contiguous() or noise.shape != x.shape \
+            or noise.dtype != x.dtype or noise.device != x.device:
+        raise ValueError("x and noise must be contiguous CUDA tensors of one shape and dtype")
+    out = torch.empty_like(x) if out is None else out
+    with torch.cuda.device(x.device):
+        rc = lib().fastmax_b200_scale_by_noise(x.data_ptr(), noise.data_ptr(), out.data_ptr(), float(dropout),
+                                               x.numel(), _dtype_code(x), _stream(x))
+    _check(rc, "fastmax_b200_scale_by_noise")
+    return out

@@ -45,8 +45,11 @@ class FASTMultiHeadAttention_Function(torch.autograd.Function):
     ``apply(q, k, v, drop_noise, mask, dropout, normalize, temperature, a0, a1,
     a2, lim, p)`` -- the reference's argument list.  q, k, v are (b,h,n,d) or
     (b*h,n,d) CUDA tensors in float32 or bfloat16; the result has q's shape and
-    dtype.  ``drop_noise`` is accepted for signature compatibility; ``dropout``
-    must be 0.  ``temperature`` has no effect on the value (as in the reference's
+    dtype.  With ``dropout > 0`` the result is multiplied elementwise by
+    ``1 + dropout * drop_noise`` (``drop_noise`` shaped like q), the reference's
+    output dropout (``fastmax_cuda_forward.cu:271-280, 396-399``); the gradient
+    is the exact derivative of that product (the reference's backward instead
+    feeds the noised output into its gradient formulas).  ``temperature`` has no effect on the value (as in the reference's
     PyTorch path); grad_k is divided by it as the reference wrapper does
     (reference ``example.py:80``).  ``impl`` selects a kernel family and is
     meant for tests.
@@ -58,24 +61,34 @@ class FASTMultiHeadAttention_Function(torch.autograd.Function):
         if not q.is_cuda:
             raise RuntimeError("FASTMultiHeadAttention_Function needs CUDA tensors; "
                                "use fastmax_function for the pure-PyTorch path")
-        if dropout != 0.0:
-            raise NotImplementedError("dropout != 0 is not supported by the CUDA path")
+        if dropout < 0.0:
+            raise ValueError(f"dropout must be non-negative, got: {dropout}")
+        if dropout > 0.0 and (drop_noise is None or drop_noise.shape != q.shape):
+            raise ValueError("dropout > 0 needs drop_noise with the shape of q")
         shape_q, shape_k = q.shape, k.shape
         q3, k3, v3 = _to3d(q), _to3d(k), _to3d(v)
         kw = dict(mask=bool(mask), normalize=bool(normalize), temperature=temperature,
                   a0=a0, a1=a1, a2=a2, lim=lim, p=p, impl=impl)
         out, den, stats = _cabi.forward(q3, k3, v3, **kw)
-        ctx.save_for_backward(q3, k3, v3, out, den, stats)
+        noise = None
+        if dropout > 0.0:
+            noise = _to3d(drop_noise.to(q3.dtype))
+        ctx.save_for_backward(q3, k3, v3, out, den, stats, noise)
         ctx.kw = kw
+        ctx.dropout = float(dropout)
         ctx.shape_q, ctx.shape_k = shape_q, shape_k
+        if noise is not None:
+            out = _cabi.scale_by_noise(out, noise, ctx.dropout)
         return out.reshape(shape_q)
 
     @staticmethod
     def backward(ctx, grad_output):
-        q3, k3, v3, out, den, stats = ctx.saved_tensors
+        q3, k3, v3, out, den, stats, noise = ctx.saved_tensors
         go = grad_output.reshape(q3.shape).contiguous()
         if go.dtype != q3.dtype:
             go = go.to(q3.dtype)
+        if noise is not None:
+            go = _cabi.scale_by_noise(go, noise, ctx.dropout)
         gq, gk, gv = _cabi.backward(q3, k3, v3, out, den, stats, go, **ctx.kw)
         t = ctx.kw["temperature"]
         if t != 1.0:

@@ -239,6 +239,39 @@ int fastmax_b200_backward_static(const fastmax_problem* prob,
                                  void* grad_q, void* grad_k, void* grad_v,
                                  void* stream);
 
+/* ---- the transformer call site around the attention --------------------------
+ * Replaces the elementwise passes of the reference's caller, model.py:472-499
+ * and 557-603: the permute / split / expand of the packed projection, apply_rope
+ * (model.py:812-825), the three `.contiguous()` copies (model.py:572-574) and the
+ * transpose of the result (model.py:603).  Arrays are contiguous, 16-byte aligned,
+ * of type `dtype`; the head size d is a multiple of 8; cos_table and sin_table are
+ * float32 (n, rope_n) (NULL when rope_n == 0); rope_n is a multiple of 8, at most d.
+ *
+ * qkv_split_rope: qkv (batch, n, groups, q_per_group + 2, d) ->
+ *   q (batch * groups * q_per_group, n, d), k and v (batch * groups, n, d), with the
+ *   first rope_n features of q and k rotated:  y = x * cos + (-x2, x1) * sin, x1 / x2
+ *   the two halves of those features.  k and v are NOT expanded to the query head
+ *   count: pass bh = batch * groups * q_per_group and bhkv = batch * groups to the
+ *   attention calls.
+ * qkv_merge_rope_grad: the gradient of qkv from grad_q, grad_k, grad_v (same shapes),
+ *   i.e. the transposed rotation and the inverse placement.
+ * swap_middle_axes: src (batch, x, y, d) -> dst (batch, y, x, d); src != dst.
+ * scale_by_noise: y[i] = x[i] * (1 + dropout * noise[i]) over `count` elements, the
+ *   reference's output dropout (fastmax_cuda_forward.cu:271-280, applied at :396-399);
+ *   y may be x. */
+int fastmax_b200_qkv_split_rope(const void* qkv, const float* cos_table, const float* sin_table,
+                                void* q, void* k, void* v,
+                                long long batch, long long n, int groups, int q_per_group, int d,
+                                int rope_n, int dtype, void* stream);
+int fastmax_b200_qkv_merge_rope_grad(const void* grad_q, const void* grad_k, const void* grad_v,
+                                     const float* cos_table, const float* sin_table, void* grad_qkv,
+                                     long long batch, long long n, int groups, int q_per_group, int d,
+                                     int rope_n, int dtype, void* stream);
+int fastmax_b200_swap_middle_axes(const void* src, void* dst, long long batch, long long x, long long y,
+                                  int d, int dtype, void* stream);
+int fastmax_b200_scale_by_noise(const void* x, const void* noise, void* y, float dropout, size_t count,
+                                int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -90,3 +90,32 @@ def test_dense_rows_subset():
     rows = [0, 3, 69]
     part = fastmax_dense(q, k, v, rows=rows, **case_kwargs(c))
     assert rel_err(part, c["out64"][:, :, rows]) < 1e-10
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("tables", ["rot", "gen"])
+def test_rope_oracle_matches_reference_vectors(tag, tables):
+    """The call-site oracle's rotary embedding against outputs of the reference's apply_rope."""
+    from oracle.call_site_oracle import rope
+    z = np.load(os.path.join(GOLDEN, "rope.npz"))
+    x = torch.from_numpy(z[f"{tag}_x"]).requires_grad_(True)
+    cos, sin = [torch.from_numpy(z[f"{tag}_{tables}_{n}"]) for n in ("cos", "sin")]
+    y = rope(x, cos, sin)
+    (gx,) = torch.autograd.grad(y, x, torch.from_numpy(z[f"{tag}_go"]))
+    assert torch.equal(y.detach(), torch.from_numpy(z[f"{tag}_{tables}_y"]))
+    assert torch.equal(gx, torch.from_numpy(z[f"{tag}_{tables}_gx"]))
+
+
+def test_call_site_oracle_shapes_and_grouping():
+    """Expanded and grouped key/value heads describe the same attention."""
+    from oracle.call_site_oracle import call_site, split_heads
+    g = torch.Generator().manual_seed(3)
+    b, t, heads, groups, hs, r = 2, 11, 4, 2, 8, 8
+    qkv = torch.randn(b, t, (heads + 2 * groups) * hs, generator=g, dtype=torch.float64)
+    cos, sin = torch.randn(t, r, generator=g, dtype=torch.float64), torch.randn(t, r, generator=g, dtype=torch.float64)
+    q, k, v = split_heads(qkv, cos, sin, heads, groups, hs, r)
+    qg, kg, vg = split_heads(qkv, cos, sin, heads, groups, hs, r, expand=False)
+    assert q.shape == (b, heads, t, hs) and kg.shape == (b, groups, t, hs)
+    assert torch.equal(k, kg.repeat_interleave(heads // groups, dim=1)) and torch.equal(q, qg)
+    y = call_site(qkv, cos, sin, heads, groups, hs, r, mask=1, normalize=1, p=1)
+    assert y.shape == (b, t, heads * hs)
