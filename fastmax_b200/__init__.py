@@ -8,7 +8,8 @@ Drop-in for the Python interface of armingerami/fastmax: the module
 from .attention import (FASTMultiHeadAttention, FASTMultiHeadAttention_Function, fastmax_function,
                         rpe_matrix_creator)
 from .call_site import fastmax_attention_from_qkv
+from .decode import FastmaxDecodeState
 
 __all__ = ["FASTMultiHeadAttention", "FASTMultiHeadAttention_Function", "fastmax_function",
-           "rpe_matrix_creator", "fastmax_attention_from_qkv"]
+           "rpe_matrix_creator", "fastmax_attention_from_qkv", "FastmaxDecodeState"]
 __version__ = "0.1.0"

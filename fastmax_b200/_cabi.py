@@ -30,6 +30,8 @@ EXPORTS = (
     "fastmax_b200_static_scratch_bytes", "fastmax_b200_backward_static",
     "fastmax_b200_qkv_split_rope", "fastmax_b200_qkv_merge_rope_grad", "fastmax_b200_swap_middle_axes",
     "fastmax_b200_scale_by_noise",
+    "fastmax_b200_decode_state_bytes", "fastmax_b200_decode_scratch_bytes", "fastmax_b200_decode_append",
+    "fastmax_b200_decode_step",
 )
 
 
@@ -86,6 +88,11 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_qkv_merge_rope_grad.argtypes = [vp] * 6 + [i64, i64, ci, ci, ci, ci, ci, vp]
         L.fastmax_b200_swap_middle_axes.argtypes = [vp, vp, i64, i64, i64, ci, ci, vp]
         L.fastmax_b200_scale_by_noise.argtypes = [vp, vp, vp, ctypes.c_float, sz, ci, vp]
+        for f in ("decode_state_bytes", "decode_scratch_bytes"):
+            fn = getattr(L, "fastmax_b200_" + f)
+            fn.restype, fn.argtypes = sz, [pp]
+        L.fastmax_b200_decode_append.argtypes = [pp, vp, vp, i64, vp, vp]
+        L.fastmax_b200_decode_step.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
         _lib = L
     return _lib
 

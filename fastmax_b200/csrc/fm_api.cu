@@ -123,7 +123,9 @@ static int pick_impl(const fastmax_problem& p, bool packed, int* impl) {
   int want = p.impl;
   const bool tc_ok = dense_tc_supports(p) && !packed;
   if (want == FASTMAX_IMPL_AUTO) {
-    want = tc_ok ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
+    // Fewer query rows than one 128-row tile (decode-like calls: a handful of queries against a long
+    // key/value cache): the tile would be mostly padding, so the CUDA-core family takes those.
+    want = (tc_ok && p.nq >= 128) ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
     if (!packed && moments_faster(p, tc_ok)) want = FASTMAX_IMPL_MOMENTS_FFMA;
   }
   if (want == FASTMAX_IMPL_MOMENTS_FFMA) {

@@ -272,6 +272,28 @@ int fastmax_b200_swap_middle_axes(const void* src, void* dst, long long batch, l
 int fastmax_b200_scale_by_noise(const void* x, const void* noise, void* y, float dropout, size_t count,
                                 int dtype, void* stream);
 
+/* ---- decoding against a persistent moment state --------------------------------
+ * Replaces the key/value cache of the reference's model (model.py:501-504, 828-852)
+ * for causal Fastmax attention: instead of all earlier keys and values, a fixed-size
+ * fp32 state per key/value head (decode_state_bytes: 1 + d (+ d*d when p = 2) rows
+ * of d + 1 floats and a small header) is updated by each new token and read by its
+ * query, so a step costs the same at every length.  Only dtype, bh, bhkv, d, p,
+ * normalize, a0, a1, a2 and lim of the problem are used; d is 32, 64 or 128.
+ *
+ * decode_append: adds n_new tokens, k and v (bhkv, n_new, d), to the state (prompt
+ *   processing).  The state must be zero-filled (cudaMemsetAsync) before its first use.
+ * decode_step: adds one token, k and v (bhkv, 1, d), then evaluates the attention row
+ *   of q (bh, 1, d) over every token added so far into out (bh, 1, d).  The result
+ *   equals fastmax_b200_forward with nq = 1, nk = the number of tokens, mask = 1:
+ *   keys scaled by lim / max |k| over all of them, the query by lim / |q|.
+ *   scratch: decode_scratch_bytes, any contents. */
+size_t fastmax_b200_decode_state_bytes(const fastmax_problem* prob);
+size_t fastmax_b200_decode_scratch_bytes(const fastmax_problem* prob);
+int fastmax_b200_decode_append(const fastmax_problem* prob, const void* k, const void* v, long long n_new,
+                               void* state, void* stream);
+int fastmax_b200_decode_step(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                             void* state, void* scratch, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

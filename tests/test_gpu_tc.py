@@ -162,3 +162,22 @@ def test_grouped_kv_heads_on_the_tensor_core_family(mask, d):
     out.backward(r(go))
     ref = [out.detach(), qx.grad, kx.grad.reshape(1, 2, 3, 300, d).sum(2), vx.grad.reshape(1, 2, 3, 300, d).sum(2)]
     assert_close(got, ref, torch.bfloat16, f"gqa mask={mask}")
+
+
+def test_auto_dispatch_keeps_sub_tile_query_counts_on_the_cuda_cores():
+    """A handful of query rows against a long key/value cache (decode-like calls) would fill one
+    128-row tensor-core tile with padding: AUTO takes the CUDA-core family there."""
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(9)
+    q = torch.randn(8, 1, 64, generator=g, device=dev).bfloat16()
+    k, v = [torch.randn(8, 3000, 64, generator=g, device=dev).bfloat16() for _ in range(2)]
+    _cabi.profile(True)
+    out, den, _ = _cabi.forward(q, k, v, mask=True, normalize=True, p=2)
+    names = {n for n, _ in _cabi.profile_records()}
+    _cabi.profile(False)
+    assert "fm_dense_ffma_fwd" in names and "fm_dense_tc_fwd" not in names
+    s = torch.einsum("hqd,hkd->hqk", q.double() / q.double().norm(dim=-1, keepdim=True),
+                     k.double() / k.double().norm(dim=-1).amax(dim=-1)[:, None, None])
+    f = 1.0 + s + 0.5 * s * s
+    want = torch.einsum("hqk,hkd->hqd", f, v.double()) / f.sum(-1, keepdim=True)
+    assert float((out.double() - want).abs().max() / want.abs().max()) < 2e-2
