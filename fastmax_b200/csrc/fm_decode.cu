@@ -18,20 +18,22 @@
 // out = num[:d] / num[d]  -- the last row of causal attention over the tokens so far
 // (fastmax_cuda_forward.cu:109, 132-150 with nq = 1).
 //
-// The state is fp32, F = (d^2 +) d + 1 rows of d+1 floats (second-order rows first, the constant
-// row last) after a 4-float header {max |k|^2, tokens, 0, 0} per key/value head.  A step reads and writes it once:
-// HBM-bound, 2 * 4 * F * (d+1) bytes per key/value head per token, independent of
-// the length.  CTAs take slices of rows; a thread owns one column c of a few rows
-// (a CTA's threads cover whole rows, so state accesses are contiguous), keeps
-// them in registers across the tokens of a call, and adds its share of the
-// read-out to a small fp32 array with one atomicAdd per (query head, column, CTA).
+// The state is fp32, F = (d^2 +) d + 1 rows of d+1 floats (second-order rows first, the
+// constant row last) after a 4-float header {max |k|^2, tokens, 0, 0} per key/value head.
+// A step reads and writes it once: HBM-bound, 2 * 4 * F * (d+1) bytes per key/value head
+// per token, independent of the length.  A thread owns one column c of one block of rows
+// (a CTA's threads cover whole rows, so state accesses are contiguous), keeps the block
+// in registers across the tokens of a call, and adds its share of the read-out to a small
+// fp32 array with one atomicAdd per (query head, column, CTA).  Measured on B200 (1024
+// heads, d = 64, p = 2, bf16 inputs): 0.50 ms per token for the 1.11 GB state, 4.4 TB/s.
 #include "fm_common.cuh"
 
 namespace fm {
 namespace {
 
-constexpr int kIter = 16;      // state rows per thread: one aligned block of 16 consecutive rows
-constexpr int kTokBatch = 32;  // tokens staged in shared memory per pass (prompt processing)
+constexpr int kBlockA = 4;      // a thread's block of state rows: 4 values of a ...
+constexpr int kBlockB = 16;     // ... times 16 consecutive values of b
+constexpr int kTokBatch = 32;   // tokens staged in shared memory per pass (prompt processing)
 constexpr int kHeader = 4;
 
 struct DecArgs {
@@ -44,10 +46,11 @@ struct DecArgs {
 
 template <int D> struct DecCfg {
   static constexpr int DV = D + 1;
-  static constexpr int RPB = 256 / DV;          // 16-row blocks per CTA
+  static constexpr int RPB = 256 / DV;          // row blocks per CTA
   static constexpr int THREADS = RPB * DV;
-  static constexpr int ROWS = RPB * kIter;      // rows per CTA
   static constexpr int KS = D + 16;             // (k, 1, 0 x 15): a 16-float window may start at D
+  static constexpr int NB2 = (D / kBlockA) * (D / kBlockB);   // second-order blocks per head
+  static constexpr int NB1 = D / kBlockB;                     // first-order blocks per head
 };
 
 // Sum of squares of x[0..D) by one warp; the result is valid in every lane.
@@ -62,10 +65,12 @@ __device__ __forceinline__ float warp_norm2(const float* x, int lane) {
 }
 
 // Row order of a head's state: the d*d second-order rows (a, b) first (p = 2), then the d
-// first-order rows, then the constant row.  d is a multiple of 16, so every aligned block of 16
-// rows has one `a` and 16 consecutive `b`: feature(row i of the block) = kx[ia] * kx[ib0 + i] with
-// kx = (k, 1, 0, ...).  A thread owns one column c of one block: per token one product
-// kx[ia] * vt[c] and four 16-byte shared-memory loads feed its 16 multiply-adds.
+// first-order rows, then the constant row.  A thread owns one column c of one block of rows:
+// (a0..a0+3) x (b0..b0+15) of the second order, or 16 first-order rows, or the constant row.
+// feature(a, b) = kx[a] * kx[b] with kx = (k, 1, 0, ...): per token the thread forms four
+// products kx[a] * vt[c] and reads 16 values kx[b] (five 16-byte shared-memory loads and one
+// scalar one) for its 64 multiply-adds, so prompt processing is bound by the FMA pipe rather
+// than by shared memory; a decode step just streams the 64 accumulators through once.
 template <typename T, int D, bool READ>
 __global__ void __launch_bounds__(DecCfg<D>::THREADS) decode_kernel(const DecArgs a, const T* __restrict__ q,
                                                                     const T* __restrict__ k, const T* __restrict__ v,
@@ -78,17 +83,31 @@ __global__ void __launch_bounds__(DecCfg<D>::THREADS) decode_kernel(const DecArg
   __shared__ int s_kmax2_bits;   // max |k|^2 as its bit pattern: non-negative floats order like integers
   const int tid = threadIdx.x, r = tid / C::DV, c = tid - r * C::DV, lane = tid & 31;
   const int head = blockIdx.y;
-  const int blk = blockIdx.x * C::ROWS + r * kIter;   // first row of this thread's block
   float* hs = state + head * a.head_floats;
 
-  const int n2rows = (a.p == 2) ? D * D : 0;
-  int ia = D, ib0 = D, kind = 0;                      // the constant row (and padding behind it)
-  if (blk < n2rows) { ia = blk / D; ib0 = blk % D; kind = 2; }
-  else if (blk < n2rows + D) { ib0 = blk - n2rows; kind = 1; }
+  // this thread's block
+  const int nb2 = (a.p == 2) ? C::NB2 : 0, n2rows = (a.p == 2) ? D * D : 0;
+  const int sb = blockIdx.x * C::RPB + r;
+  int a0 = D, b0 = D, kind = 0, nu = 0, ni = 0;   // nu x ni valid rows
+  int row00 = 0, ustride = 0;                     // row of (u, i) = row00 + u * ustride + i
+  if (sb < nb2) {
+    a0 = (sb / C::NB1) * kBlockA; b0 = (sb % C::NB1) * kBlockB; kind = 2; nu = kBlockA; ni = kBlockB;
+    row00 = a0 * D + b0; ustride = D;
+  } else if (sb < nb2 + C::NB1) {
+    b0 = (sb - nb2) * kBlockB; kind = 1; nu = 1; ni = kBlockB; row00 = n2rows + b0;
+  } else if (sb == nb2 + C::NB1) {
+    nu = 1; ni = 1; row00 = n2rows + D;           // the constant row: kx[D] * kx[D] = 1
+  }
 
-  float s[kIter];
+  float* const base = hs + kHeader + (long long)row00 * C::DV + c;   // row (u, i) at base[(u * ustride + i) * DV]
+  const int ustep = ustride * C::DV;
+  float s[kBlockA][kBlockB];
 #pragma unroll
-  for (int i = 0; i < kIter; ++i) s[i] = (blk + i < a.rows) ? hs[kHeader + (long long)(blk + i) * C::DV + c] : 0.0f;
+  for (int u = 0; u < kBlockA; ++u) {
+    const float* pu = base + u * ustep;
+#pragma unroll
+    for (int i = 0; i < kBlockB; ++i) s[u][i] = (u < nu && i < ni) ? pu[i * C::DV] : 0.0f;
+  }
   if (tid == 0) s_kmax2_bits = __float_as_int(hs[0]);
   __syncthreads();
 
@@ -111,25 +130,33 @@ __global__ void __launch_bounds__(DecCfg<D>::THREADS) decode_kernel(const DecArg
         if (lane == 0) atomicMax(&s_kmax2_bits, __float_as_int(m));
       }
     }
-#pragma unroll 2
     for (int tok = 0; tok < nt; ++tok) {
-      const float t = ks[tok][ia] * vs[tok][c];
-      const float4* kb = reinterpret_cast<const float4*>(&ks[tok][ib0]);
+      const float vc = vs[tok][c];
+      const float4 ka = *reinterpret_cast<const float4*>(&ks[tok][a0]);   // (1, 0, 0, 0) when a0 == D
+      const float t[kBlockA] = {ka.x * vc, ka.y * vc, ka.z * vc, ka.w * vc};
+      const float4* kb = reinterpret_cast<const float4*>(&ks[tok][b0]);
 #pragma unroll
-      for (int i4 = 0; i4 < kIter / 4; ++i4) {
+      for (int i4 = 0; i4 < kBlockB / 4; ++i4) {
         const float4 b4 = kb[i4];
-        s[4 * i4 + 0] = fmaf(t, b4.x, s[4 * i4 + 0]);
-        s[4 * i4 + 1] = fmaf(t, b4.y, s[4 * i4 + 1]);
-        s[4 * i4 + 2] = fmaf(t, b4.z, s[4 * i4 + 2]);
-        s[4 * i4 + 3] = fmaf(t, b4.w, s[4 * i4 + 3]);
+#pragma unroll
+        for (int u = 0; u < kBlockA; ++u) {
+          s[u][4 * i4 + 0] = fmaf(t[u], b4.x, s[u][4 * i4 + 0]);
+          s[u][4 * i4 + 1] = fmaf(t[u], b4.y, s[u][4 * i4 + 1]);
+          s[u][4 * i4 + 2] = fmaf(t[u], b4.z, s[u][4 * i4 + 2]);
+          s[u][4 * i4 + 3] = fmaf(t[u], b4.w, s[u][4 * i4 + 3]);
+        }
       }
     }
     __syncthreads();
   }
 
 #pragma unroll
-  for (int i = 0; i < kIter; ++i)
-    if (blk + i < a.rows) hs[kHeader + (long long)(blk + i) * C::DV + c] = s[i];
+  for (int u = 0; u < kBlockA; ++u) {
+    float* pu = base + u * ustep;
+#pragma unroll
+    for (int i = 0; i < kBlockB; ++i)
+      if (u < nu && i < ni) pu[i * C::DV] = s[u][i];
+  }
   // every CTA of the head holds the same maximum; the first one records it
   if (blockIdx.x == 0 && tid == 0) {
     hs[0] = __int_as_float(s_kmax2_bits);
@@ -149,10 +176,14 @@ __global__ void __launch_bounds__(DecCfg<D>::THREADS) decode_kernel(const DecArg
     }
     __syncthreads();
     const float sc = a.normalize ? (a.lim * rsqrtf(s_q2)) * (a.lim * rsqrtf(__int_as_float(s_kmax2_bits))) : 1.0f;
-    const float coef = (kind == 0 ? a.a0 : (kind == 1 ? a.a1 * sc : a.a2 * sc * sc)) * qx[ia];
+    const float coef = kind == 0 ? a.a0 : (kind == 1 ? a.a1 * sc : a.a2 * sc * sc);
     float part = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kIter; ++i) part = fmaf((blk + i < a.rows) ? coef * qx[ib0 + i] : 0.0f, s[i], part);
+    for (int u = 0; u < kBlockA; ++u) {
+      const float cu = coef * qx[a0 + u];
+#pragma unroll
+      for (int i = 0; i < kBlockB; ++i) part = fmaf((u < nu && i < ni) ? cu * qx[b0 + i] : 0.0f, s[u][i], part);
+    }
     red[r][c] = part;
     __syncthreads();
     if (r == 0) {
@@ -190,7 +221,8 @@ int launch_decode(const fastmax_problem& p, const void* q, const void* k, const 
             kHeader + (long long)rows_of(p) * (D + 1)};
   if (p.bhkv == 0) return FASTMAX_OK;
   if (READ) FM_CUDA_TRY(cudaMemsetAsync(num, 0, sizeof(float) * (size_t)p.bh * (D + 1), st));
-  dim3 grid((a.rows + C::ROWS - 1) / C::ROWS, p.bhkv);
+  const int blocks_per_head = (p.p == 2 ? C::NB2 : 0) + C::NB1 + 1;
+  dim3 grid((blocks_per_head + C::RPB - 1) / C::RPB, p.bhkv);
   FM_LAUNCH(READ ? "fm_decode_step" : "fm_decode_append", st,
             (decode_kernel<T, D, READ><<<grid, C::THREADS, 0, st>>>(a, (const T*)q, (const T*)k, (const T*)v, state, num)));
   FM_CUDA_TRY(cudaGetLastError());
