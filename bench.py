@@ -46,6 +46,9 @@ WORKLOADS = {
     "c4s": (4, 8, 16384, 128, "bf16", 0, 2, 0),   # reduced unmasked d=128 case
     "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),   # small case for ncu captures (inputs 4 x 67 MB)
     "prof1": (2, 8, 16384, 128, "bf16", 0, 1, 0),  # small p = 1 case for ncu captures (inputs 4 x 67 MB)
+    # decoding against the persistent moment state: one new token per sequence and step (N is not used)
+    "decode": (64, 16, 1, 64, "bf16", 1, 2, 1),
+    "decodes": (16, 16, 1, 64, "bf16", 1, 2, 1),   # small case for ncu captures (277 MB of state)
 }
 A = dict(a0=1.0, a1=1.0, a2=0.5, lim=1.0)
 
@@ -108,6 +111,93 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_decode(args, world, rank, dev, cfg):
+    """One step = one new token for each of the B sequences on every rank (B*H heads, grouped 1:1), added to
+    the per-head moment state and read by its query.  The state (fp32, larger than L2) is read and written once
+    per step: HBM-bound, 2 x state bytes of algorithmic traffic.  Sequences are independent: no collective."""
+    import torch
+    import torch.distributed as dist
+
+    from fastmax_b200 import FastmaxDecodeState, _cabi
+
+    B, H, _, D, dt, _, p, norm = cfg
+    dtype = torch.bfloat16 if dt == "bf16" else torch.float32
+    st = FastmaxDecodeState(B * H, B * H, D, dtype=dtype, device=dev, normalize=bool(norm), p=p, **A)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v = [torch.randn(B * H, 1, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(3)]
+    st.append(torch.randn(B * H, 64, D, generator=g, device=dev, dtype=torch.float32).to(dtype),
+              torch.randn(B * H, 64, D, generator=g, device=dev, dtype=torch.float32).to(dtype))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        st.step(q, k, v)
+    barrier()
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    _cabi.profile(True)
+    n0 = _cabi.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        out = st.step(q, k, v)
+    e1.record()
+    barrier()
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    launches = _cabi.launch_count() - n0
+    recs = _cabi.profile_records()
+    _cabi.profile(False)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    # end to end: the new token's q, k, v from pinned host memory, the attention row back to the host
+    host = [t.cpu().pin_memory() for t in (q, k, v)]
+    host_out = torch.empty_like(out, device="cpu").pin_memory()
+    dq, dk, dv = [torch.empty_like(t) for t in (q, k, v)]
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for d_, h_ in zip((dq, dk, dv), host):
+            d_.copy_(h_, non_blocking=True)
+        host_out.copy_(st.step(dq, dk, dv), non_blocking=True)
+    barrier()
+    e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peaks = load_peaks()
+        step_ms = sum(t for n, t in recs if n == "fm_decode_step") / max(1, sum(1 for n, _ in recs if n == "fm_decode_step"))
+        state_bytes = st.state.numel() * 4
+        ach = 2 * state_bytes / (step_ms * 1e-3) / 1e9
+        nbytes = q.numel() * q.element_size()
+        line = {
+            "metric": "fastmax_decode_tokens_per_s", "value": B * world * args.steps / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": describe(args.workload) + " (one token per sequence and step; fp32 moment state of "
+                                   f"{state_bytes / 1e6:.0f} MB per GPU instead of a key/value cache)",
+                       "global_batch": B * world, "parallelism": f"sequences sharded x{world}, no collective",
+                       "l2": "the state read and written each step is larger than the 126 MB L2"
+                             if state_bytes > 126e6 else "state smaller than L2"},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "e2e": {"value": B * world * args.steps / (float(e2e_ms.item()) * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": nbytes},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "traffic": None, "kernel": "fm_decode_step",
+                         "peak_source": peaks["source"]},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def load_peaks():
@@ -188,6 +278,8 @@ def run_ours(args):
     seq_mode = args.workload.startswith("c5")   # one long sequence, split along n over the ranks
     if seq_mode:
         return run_seq(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
+    if args.workload.startswith("decode"):
+        return run_decode(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
     if args.scaling == "strong":
         bh = bh_total // world + (1 if rank < bh_total % world else 0)
         tokens_job = B * N
