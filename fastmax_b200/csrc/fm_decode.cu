@@ -64,6 +64,21 @@ __device__ __forceinline__ float warp_norm2(const float* x, int lane) {
   return n2;
 }
 
+// 16 bytes of T from global memory as fp32 values.
+__device__ __forceinline__ void load16_to_f32(const float* src, float* dst) {
+  const float4 w = __ldg(reinterpret_cast<const float4*>(src));
+  dst[0] = w.x; dst[1] = w.y; dst[2] = w.z; dst[3] = w.w;
+}
+__device__ __forceinline__ void load16_to_f32(const __nv_bfloat16* src, float* dst) {
+  const uint4 w = __ldg(reinterpret_cast<const uint4*>(src));
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    dst[2 * e] = __uint_as_float(ww[e] << 16);
+    dst[2 * e + 1] = __uint_as_float(ww[e] & 0xFFFF0000u);
+  }
+}
+
 // Row order of a head's state: the d*d second-order rows (a, b) first (p = 2), then the d
 // first-order rows, then the constant row.  A thread owns one column c of one block of rows:
 // (a0..a0+3) x (b0..b0+15) of the second order, or 16 first-order rows, or the constant row.
@@ -115,10 +130,17 @@ __global__ void __launch_bounds__(DecCfg<D>::THREADS) decode_kernel(const DecArg
   const T* vh = v + (long long)head * a.n_new * D;
   for (long long t0 = 0; t0 < a.n_new; t0 += kTokBatch) {
     const int nt = (int)((a.n_new - t0 < kTokBatch) ? a.n_new - t0 : kTokBatch);
-    for (int e = tid; e < nt * C::KS; e += C::THREADS) {
-      const int tok = e / C::KS, x = e - tok * C::KS;
-      ks[tok][x] = x < D ? ldf(kh + (t0 + tok) * D + x) : (x == D ? 1.0f : 0.0f);
-      if (x <= D) vs[tok][x] = x < D ? ldf(vh + (t0 + tok) * D + x) : 1.0f;
+    // stage the batch: 16-byte loads of k and v, converted to fp32; then the (1, 0, ...) tails
+    constexpr int EPV = 16 / (int)sizeof(T), VPT = D / EPV;   // elements per load, loads per token
+    for (int e = tid; e < nt * VPT; e += C::THREADS) {
+      const int tok = e / VPT, x = (e - tok * VPT) * EPV;
+      load16_to_f32(kh + (t0 + tok) * D + x, &ks[tok][x]);
+      load16_to_f32(vh + (t0 + tok) * D + x, &vs[tok][x]);
+    }
+    for (int e = tid; e < nt * 16; e += C::THREADS) {
+      const int tok = e >> 4, j = e & 15;
+      ks[tok][D + j] = j == 0 ? 1.0f : 0.0f;
+      if (j == 0) vs[tok][D] = 1.0f;
     }
     __syncthreads();
     {   // running maximum of |k|^2, the tokens spread over the CTA's full warps
@@ -272,6 +294,7 @@ int fastmax_b200_decode_append(const fastmax_problem* prob, const void* k, const
   if (n_new < 0) return fail(FASTMAX_E_ARG, "negative token count");
   if (n_new == 0 || prob->bhkv == 0) return FASTMAX_OK;
   if (!k || !v || !state) return fail(FASTMAX_E_ARG, "NULL array");
+  if (((uintptr_t)k | (uintptr_t)v) & 15) return fail(FASTMAX_E_ARG, "k and v must be 16-byte aligned");
   return dispatch_decode<false>(*prob, nullptr, k, v, n_new, (float*)state, nullptr, nullptr, (cudaStream_t)stream);
 }
 
@@ -281,5 +304,6 @@ int fastmax_b200_decode_step(const fastmax_problem* prob, const void* q, const v
   if (rc) return rc;
   if (prob->bh == 0) return FASTMAX_OK;
   if (!q || !k || !v || !state || !scratch || !out) return fail(FASTMAX_E_ARG, "NULL array");
+  if (((uintptr_t)k | (uintptr_t)v) & 15) return fail(FASTMAX_E_ARG, "k and v must be 16-byte aligned");
   return dispatch_decode<true>(*prob, q, k, v, 1, (float*)state, (float*)scratch, out, (cudaStream_t)stream);
 }
