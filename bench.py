@@ -49,6 +49,8 @@ WORKLOADS = {
     # decoding against the persistent moment state: one new token per sequence and step (N is not used)
     "decode": (64, 16, 1, 64, "bf16", 1, 2, 1),
     "decodes": (16, 16, 1, 64, "bf16", 1, 2, 1),   # small case for ncu captures (277 MB of state)
+    # the model's call site: packed projection -> rotary embedding -> attention -> (B, T, H*hs), and back
+    "site": (8, 32, 4096, 64, "bf16", 1, 1, 1),
 }
 A = dict(a0=1.0, a1=1.0, a2=0.5, lim=1.0)
 
@@ -200,6 +202,92 @@ def run_decode(args, world, rank, dev, cfg):
         dist.destroy_process_group()
 
 
+def run_site(args, world, rank, dev, cfg):
+    """One step = forward + backward of `fastmax_attention_from_qkv` on a packed projection (B, T, 3*H*hs) that
+    is resident on the GPU: split + rotary embedding, attention, axis swap, and the mirror-image gradient passes.
+    Batches are independent: every rank runs its own (weak scaling, no collective)."""
+    import torch
+    import torch.distributed as dist
+
+    from fastmax_b200 import _cabi, fastmax_attention_from_qkv
+
+    B, H, N, D, dt, mask, p, norm = cfg
+    dtype = torch.bfloat16 if dt == "bf16" else torch.float32
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    qkv = torch.randn(B, N, 3 * H * D, generator=g, device=dev, dtype=torch.float32).to(dtype)
+    gy = torch.randn(B, N, H * D, generator=g, device=dev, dtype=torch.float32).to(dtype)
+    ang = torch.outer(torch.arange(N, dtype=torch.float32, device=dev),
+                      1.0 / (10000 ** (torch.arange(0, D, 2, device=dev) / D)))
+    cos, sin = torch.cos(ang).repeat(1, 2), torch.sin(ang).repeat(1, 2)
+
+    def step():
+        x = qkv.detach().requires_grad_(True)
+        y = fastmax_attention_from_qkv(x, cos, sin, H, H, D, D, mask=bool(mask), normalize=bool(norm), p=p, **A)
+        y.backward(gy)
+        return x.grad
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    _cabi.profile(True)
+    n0 = _cabi.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    launches = _cabi.launch_count() - n0
+    recs = _cabi.profile_records()
+    _cabi.profile(False)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    if rank == 0:
+        peaks = load_peaks()
+        per = {}
+        for name, t in recs:
+            c, sm = per.get(name, (0, 0.0))
+            per[name] = (c + 1, sm + t)
+        tot = sum(x[1] for x in per.values())
+        c_split, t_split = per.get("fm_qkv_split_rope", (1, 0.0))
+        nbytes = qkv.numel() * qkv.element_size()
+        ach = 2 * nbytes / (t_split / max(c_split, 1) * 1e-3) / 1e9 if t_split else None
+        line = {
+            "metric": "fastmax_fwd_bwd_tokens_per_s", "value": B * N * world * args.steps / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": dt, "data": "synthetic",
+            "config": {"workload": describe(args.workload) + " through fastmax_attention_from_qkv (packed projection, "
+                                   "rotary embedding on all features)", "global_batch": B * world,
+                       "parallelism": f"batches sharded x{world}, no collective",
+                       "l2": f"projection of {nbytes / 1e6:.0f} MB larger than the 126 MB L2"},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"] if ach else None,
+                         # ncu, this workload: 412.0 MB read + 360.7 MB written per launch
+                         "traffic": 772.7e6 if (B, H, N, D) == (8, 32, 4096, 64) else None,
+                         "kernel": "fm_qkv_split_rope", "peak_source": peaks["source"]},
+            "kernels": {n: {"launches": c, "ms_total": round(sm, 3), "share": round(sm / tot, 4)}
+                        for n, (c, sm) in sorted(per.items(), key=lambda kv: -kv[1][1])},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -280,6 +368,8 @@ def run_ours(args):
         return run_seq(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
     if args.workload.startswith("decode"):
         return run_decode(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
+    if args.workload == "site":
+        return run_site(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
     if args.scaling == "strong":
         bh = bh_total // world + (1 if rank < bh_total % world else 0)
         tokens_job = B * N
