@@ -164,20 +164,27 @@ def test_grouped_kv_heads_on_the_tensor_core_family(mask, d):
     assert_close(got, ref, torch.bfloat16, f"gqa mask={mask}")
 
 
-def test_auto_dispatch_keeps_sub_tile_query_counts_on_the_cuda_cores():
-    """A handful of query rows against a long key/value cache (decode-like calls) would fill one
-    128-row tensor-core tile with padding: AUTO takes the CUDA-core family there."""
+def test_auto_dispatch_keeps_ragged_and_sub_tile_problems_on_the_cuda_cores():
+    """AUTO sends only square problems (nq == nk) of at least one 128-row tile to the tensor-core score
+    family: a handful of query rows against a long key/value cache would fill a tile with padding, and
+    nq != nk at large nk is closed on the tensor cores (forcing the family there is refused)."""
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(9)
-    q = torch.randn(8, 1, 64, generator=g, device=dev).bfloat16()
     k, v = [torch.randn(8, 3000, 64, generator=g, device=dev).bfloat16() for _ in range(2)]
-    _cabi.profile(True)
-    out, den, _ = _cabi.forward(q, k, v, mask=True, normalize=True, p=2)
-    names = {n for n, _ in _cabi.profile_records()}
-    _cabi.profile(False)
-    assert "fm_dense_ffma_fwd" in names and "fm_dense_tc_fwd" not in names
-    s = torch.einsum("hqd,hkd->hqk", q.double() / q.double().norm(dim=-1, keepdim=True),
-                     k.double() / k.double().norm(dim=-1).amax(dim=-1)[:, None, None])
-    f = 1.0 + s + 0.5 * s * s
-    want = torch.einsum("hqk,hkd->hqd", f, v.double()) / f.sum(-1, keepdim=True)
-    assert float((out.double() - want).abs().max() / want.abs().max()) < 2e-2
+    for nq in (1, 256):
+        q = torch.randn(8, nq, 64, generator=g, device=dev).bfloat16()
+        _cabi.profile(True)
+        out, den, _ = _cabi.forward(q, k, v, mask=True, normalize=True, p=2)
+        names = {n for n, _ in _cabi.profile_records()}
+        _cabi.profile(False)
+        assert "fm_dense_ffma_fwd" in names and "fm_dense_tc_fwd" not in names
+        qn = q.double() * (1.0 / q.double().norm(dim=-1).amax(dim=-1))[:, None, None]
+        kn = k.double() * (1.0 / k.double().norm(dim=-1).amax(dim=-1))[:, None, None]
+        s = torch.einsum("hqd,hkd->hqk", qn, kn)
+        f = 1.0 + s + 0.5 * s * s
+        allowed = torch.arange(3000, device=dev)[None, :] <= torch.arange(nq, device=dev)[:, None] + (3000 - nq)
+        f = f * allowed
+        want = torch.einsum("hqk,hkd->hqd", f, v.double()) / f.sum(-1, keepdim=True)
+        assert float((out.double() - want).abs().max() / want.abs().max()) < 2e-2
+        with pytest.raises(RuntimeError):
+            _cabi.forward(q, k, v, mask=True, normalize=True, p=2, impl="dense_tc")
