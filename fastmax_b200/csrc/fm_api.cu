@@ -123,11 +123,7 @@ static int pick_impl(const fastmax_problem& p, bool packed, int* impl) {
   int want = p.impl;
   const bool tc_ok = dense_tc_supports(p) && !packed;
   if (want == FASTMAX_IMPL_AUTO) {
-    // The tensor-core score family serves square problems (nq == nk) of at least one 128-row tile.
-    // Decode-like calls (a few queries against a long key/value cache) would fill a tile with
-    // padding, and calls with nq != nk at large nk have ended with a launch failure whose cause
-    // is not known, so the CUDA-core family takes both.
-    want = (tc_ok && p.nq >= 128 && p.nq == p.nk) ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
+    want = tc_ok ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
     if (!packed && moments_faster(p, tc_ok)) want = FASTMAX_IMPL_MOMENTS_FFMA;
   }
   if (want == FASTMAX_IMPL_MOMENTS_FFMA) {
@@ -137,10 +133,6 @@ static int pick_impl(const fastmax_problem& p, bool packed, int* impl) {
     *impl = want;
     return FASTMAX_OK;
   }
-  if (want == FASTMAX_IMPL_DENSE_TC && p.nq != p.nk && p.nk > 1024)
-    return fail(FASTMAX_E_UNSUPPORTED,
-                "the tensor-core score family is closed for nq != nk with more than 1024 keys "
-                "(a launch failure of unknown cause was seen there); use the CUDA-core family");
   if (want == FASTMAX_IMPL_DENSE_TC && !tc_ok)
     return fail(FASTMAX_E_UNSUPPORTED,
                 "the tensor-core score family needs bf16, d in {64, 128} (grouped k/v heads: d == 64) and the plain output layout");

@@ -61,13 +61,22 @@ constexpr int BM = 128, D = 64;
 constexpr int kThreads = 640;
 constexpr int kProducerWarp = 16, kIssuerWarp = 17, kAccIssuerWarp = 19, kComputeWarps = 16;  // warps 17, 18: S / W issuers
 constexpr int ROW_TILE = BM * 128;
-constexpr int OFF_X = 0, OFF_U = ROW_TILE, OFF_ST = 2 * ROW_TILE;
+constexpr int OFF_X = 0, OFF_U = ROW_TILE;
 constexpr int T_S = 0, T_W = 128, T_E = 256, T_P = 320, T_O = 384, T_O2 = 448;
 template <int MODE>
 struct WCfg {
   static constexpr int BN = (MODE == MODE_FWD) ? 128 : 64;   // columns per tile
-  static constexpr int NS = (MODE == MODE_FWD) ? 5 : 8;      // ring stages of (Y tile, Z tile)
+  // Ring stages of (Y tile, Z tile).  The count must be even: the two S / W issuer warps take
+  // alternate tiles, and with an even count each stage barrier is only ever waited on by one of
+  // them, on consecutive phases.  With an odd count a stage alternates between the two warps, each
+  // would wait on every second phase of its barrier -- always the same parity -- and a parity wait
+  // cannot tell "the phase before mine has not completed yet" from "mine has completed": when the
+  // loads arrive late and out of order (many heads streaming from DRAM at once) the warp then issues
+  // on a stage that is still being written and the CTA can finish with loads in flight.
+  static constexpr int NS = (MODE == MODE_FWD) ? 6 : 8;
+  static_assert(NS % 2 == 0, "each stage barrier must belong to one issuer warp");
   static constexpr int COL_TILE = BN * 128, STAGE = 2 * COL_TILE;
+  static constexpr int OFF_ST = (MODE == MODE_FWD ? 1 : 2) * ROW_TILE;   // the forward has no U tile
   static constexpr int OFF_VEC = OFF_ST + NS * STAGE;      // per compute warp 2 x 32 floats
   static constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
   static constexpr int NBAR = 2 + 2 * NS + 8;
@@ -85,7 +94,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   using C = WCfg<MODE>;
   constexpr bool FUSED = MODE == MODE_DKDV, FWD = MODE == MODE_FWD;
   constexpr int BN = C::BN, NS = C::NS, COL_TILE = C::COL_TILE, STAGE = C::STAGE;
-  constexpr int OFF_VEC = C::OFF_VEC, OFF_BAR = C::OFF_BAR, OFF_TMEM = C::OFF_TMEM;
+  constexpr int OFF_ST = C::OFF_ST, OFF_VEC = C::OFF_VEC, OFF_BAR = C::OFF_BAR, OFF_TMEM = C::OFF_TMEM;
   constexpr bool PV_EARLY = MODE == MODE_DQ;
   constexpr int HB = BN / 2;          // columns of one compute warp = packed bf16 columns of one group
   extern __shared__ uint8_t smem_raw[];
