@@ -11,7 +11,13 @@ is taken:
                             attention oracle;
 ``output_dropout``          ``o * (1 + dropout * drop_noise)`` (reference
                             ``fastmax_cuda_forward.cu:271-280``, applied at
-                            ``:396-399``).
+                            ``:396-399``);
+``MomentState``             the recurrence a decoder can keep instead of the
+                            reference's key/value cache (``model.py:501-504,
+                            828-852``): running sums of (v,1), k (x) (v,1) and
+                            k (x) k (x) (v,1) over raw keys plus the running
+                            max |k|; ``tests/test_oracle.py`` checks that a step
+                            equals the dense attention row over the tokens so far.
 
 Parity pin: ``tests/golden/make_golden_rope.py`` lifts ``apply_rope`` out of the
 reference source with ``ast`` and stores its outputs on seeded inputs in
@@ -30,7 +36,7 @@ import torch
 
 from .fastmax_oracle import fastmax_dense
 
-__all__ = ["rope", "split_heads", "call_site", "output_dropout"]
+__all__ = ["rope", "split_heads", "call_site", "output_dropout", "MomentState"]
 
 
 def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -74,3 +80,34 @@ def call_site(qkv, cos, sin, n_head, n_query_groups, head_size, rope_n, round_dt
 
 def output_dropout(o: torch.Tensor, drop_noise: torch.Tensor, dropout: float) -> torch.Tensor:
     return o * (1 + dropout * drop_noise)
+
+
+class MomentState:
+    """Per-head running moments of raw keys and values; float64, CPU, heads on the leading axis."""
+
+    def __init__(self, heads, d, p=2, normalize=True, a0=1.0, a1=1.0, a2=0.5, lim=1.0):
+        self.p, self.normalize, self.a0, self.a1, self.a2, self.lim = p, normalize, a0, a1, a2, lim
+        self.s0 = torch.zeros(heads, d + 1, dtype=torch.float64)
+        self.s1 = torch.zeros(heads, d, d + 1, dtype=torch.float64)
+        self.s2 = torch.zeros(heads, d, d, d + 1, dtype=torch.float64)
+        self.kmax = torch.zeros(heads, dtype=torch.float64)
+
+    def append(self, k, v):
+        """k, v: (heads, n, d)."""
+        vt = torch.cat([v.double(), torch.ones_like(v[..., :1], dtype=torch.float64)], dim=-1)
+        k = k.double()
+        self.s0 += vt.sum(1)
+        self.s1 += torch.einsum("hna,hnc->hac", k, vt)
+        if self.p == 2:
+            self.s2 += torch.einsum("hna,hnb,hnc->habc", k, k, vt)
+        self.kmax = torch.maximum(self.kmax, k.norm(dim=-1).amax(dim=-1))
+
+    def step(self, q, k, v):
+        """Add one token (heads, 1, d) and return the attention row of q (heads, 1, d)."""
+        self.append(k, v)
+        q = q.double()[:, 0]
+        s = (self.lim / q.norm(dim=-1)) * (self.lim / self.kmax) if self.normalize else torch.ones_like(self.kmax)
+        num = self.a0 * self.s0 + self.a1 * s[:, None] * torch.einsum("ha,hac->hc", q, self.s1)
+        if self.p == 2:
+            num = num + self.a2 * (s * s)[:, None] * torch.einsum("ha,hb,habc->hc", q, q, self.s2)
+        return (num[:, :-1] / num[:, -1:])[:, None]

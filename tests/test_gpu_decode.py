@@ -72,3 +72,23 @@ def test_bad_arguments_raise():
                 torch.zeros(2, 1, 32, device="cuda"))
     with pytest.raises(ValueError):
         st.append(torch.zeros(2, 3, 32, device="cuda").bfloat16(), torch.zeros(2, 3, 32, device="cuda").bfloat16())
+
+
+@pytest.mark.parametrize("p", [1, 2])
+def test_steps_match_the_oracle_recurrence_with_other_coefficients(p):
+    """Against the CPU restatement of the recurrence itself, with a0, a1, a2, lim away from their defaults."""
+    from oracle.call_site_oracle import MomentState
+    g = torch.Generator().manual_seed(3)
+    heads, n, d, n0 = 4, 30, 32, 21
+    q, k, v = [torch.randn(heads, n, d, generator=g) for _ in range(3)]
+    coef = dict(a0=0.7, a1=1.3, a2=0.4, lim=1.5)
+    ref = MomentState(heads, d, p=p, normalize=True, **coef)
+    st = FastmaxDecodeState(heads, heads, d, dtype=torch.float32, device="cuda:0", normalize=True, p=p, **coef)
+    ref.append(k[:, :n0], v[:, :n0])
+    st.append(k[:, :n0].contiguous().cuda(), v[:, :n0].contiguous().cuda())
+    for t in range(n0, n):
+        sl = slice(t, t + 1)
+        want = ref.step(q[:, sl], k[:, sl], v[:, sl])
+        got = st.step(q[:, sl].contiguous().cuda(), k[:, sl].contiguous().cuda(), v[:, sl].contiguous().cuda())
+        err = float((got.double().cpu() - want).abs().max() / want.abs().max())
+        assert err < TOL[torch.float32], (t, err)

@@ -119,3 +119,22 @@ def test_call_site_oracle_shapes_and_grouping():
     assert torch.equal(k, kg.repeat_interleave(heads // groups, dim=1)) and torch.equal(q, qg)
     y = call_site(qkv, cos, sin, heads, groups, hs, r, mask=1, normalize=1, p=1)
     assert y.shape == (b, t, heads * hs)
+
+
+@pytest.mark.parametrize("p", [1, 2])
+@pytest.mark.parametrize("normalize", [0, 1])
+def test_moment_state_recurrence_equals_dense_rows(p, normalize):
+    """The fixed-size decode state gives, token by token, the causal attention row over the tokens so far."""
+    from oracle.call_site_oracle import MomentState
+    g = torch.Generator().manual_seed(17)
+    heads, n, d, n0 = 3, 14, 8, 5
+    scale = 1.0 if normalize else d ** -0.5
+    q, k = [torch.randn(heads, n, d, generator=g, dtype=torch.float64) * scale for _ in range(2)]
+    v = torch.randn(heads, n, d, generator=g, dtype=torch.float64)
+    st = MomentState(heads, d, p=p, normalize=bool(normalize), a0=0.7, a1=1.3, a2=0.4, lim=1.5)
+    st.append(k[:, :n0], v[:, :n0])
+    for t in range(n0, n):
+        got = st.step(q[:, t:t + 1], k[:, t:t + 1], v[:, t:t + 1])
+        want = fastmax_dense(q[None, :, t:t + 1], k[None, :, :t + 1], v[None, :, :t + 1], mask=1,
+                             normalize=normalize, p=p, a0=0.7, a1=1.3, a2=0.4, lim=1.5)[0]
+        assert rel_err(got, want) < 1e-12
