@@ -593,7 +593,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--family", default="auto", choices=["auto", "dense_ffma", "dense_tc", "moments_ffma"],
+    ap.add_argument("--family", default="auto", choices=["auto", "dense_ffma", "dense_tc", "moments", "moments_ffma"],
                     help="kernel family to force (default: the library's own choice)")
     ap.add_argument("--chunk", type=int, default=0, help="moment family: tokens per chunk (0 = default)")
     ap.add_argument("--e2e-group", type=int, default=32,

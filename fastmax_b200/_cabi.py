@@ -15,21 +15,22 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfastmax_b200.so")
 
 F32, BF16 = 0, 1
-IMPL = {"auto": 0, "dense_ffma": 1, "dense_tc": 2, "moments_ffma": 3, "moments_tc": 4}
+IMPL = {"auto": 0, "dense_ffma": 1, "dense_tc": 2, "moments": 3, "moments_ffma": 4}
 
 EXPORTS = (
     "fastmax_b200_version", "fastmax_b200_last_error", "fastmax_b200_stats_bytes",
     "fastmax_b200_forward_workspace_bytes", "fastmax_b200_backward_workspace_bytes",
     "fastmax_b200_forward", "fastmax_b200_forward_packed", "fastmax_b200_backward",
     "fastmax_b200_launch_count", "fastmax_b200_profile_enable", "fastmax_b200_profile_count",
-    "fastmax_b200_profile_get", "fastmax_b200_device_status",
+    "fastmax_b200_profile_get", "fastmax_b200_device_status", "fastmax_b200_device_status_reset",
+    "fastmax_b200_wait_selftest",
     "fastmax_b200_moment_state_bytes", "fastmax_b200_moment_total_bytes",
     "fastmax_b200_shard_forward_workspace_bytes", "fastmax_b200_shard_backward_workspace_bytes",
     "fastmax_b200_shard_rowmax", "fastmax_b200_shard_kv_state", "fastmax_b200_shard_forward",
     "fastmax_b200_shard_qg_state", "fastmax_b200_shard_backward", "fastmax_b200_shard_norm_fixup",
     "fastmax_b200_static_scratch_bytes", "fastmax_b200_backward_static",
     "fastmax_b200_qkv_split_rope", "fastmax_b200_qkv_merge_rope_grad", "fastmax_b200_swap_middle_axes",
-    "fastmax_b200_scale_by_noise",
+    "fastmax_b200_scale_by_noise", "fastmax_b200_scale_packed_by_noise",
     "fastmax_b200_decode_state_bytes", "fastmax_b200_decode_scratch_bytes", "fastmax_b200_decode_append",
     "fastmax_b200_decode_step",
 )
@@ -79,6 +80,8 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_shard_backward.argtypes = [pp] + [vp] * 16 + [sz, vp]
         L.fastmax_b200_shard_norm_fixup.argtypes = [pp, vp, vp, vp, vp, i32, vp, vp, vp]
         L.fastmax_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), vp]
+        L.fastmax_b200_device_status_reset.argtypes = [vp]
+        L.fastmax_b200_wait_selftest.argtypes = [ctypes.c_longlong, vp]
         L.fastmax_b200_launch_count.restype = ctypes.c_ulonglong
         L.fastmax_b200_profile_enable.argtypes = [ctypes.c_int]
         L.fastmax_b200_profile_get.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int,
@@ -105,6 +108,22 @@ def device_status(device=None) -> int:
         _check(lib().fastmax_b200_device_status(ctypes.byref(st), torch.cuda.current_stream(dev).cuda_stream),
                "fastmax_b200_device_status")
     return int(st.value)
+
+
+def device_status_reset(device=None):
+    """Clear the status word (synchronises the current stream)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _check(lib().fastmax_b200_device_status_reset(torch.cuda.current_stream(dev).cuda_stream),
+               "fastmax_b200_device_status_reset")
+
+
+def wait_selftest(limit_clocks: int, device=None):
+    """Launch the one-warp kernel whose bounded wait is designed to run out (status 99 afterwards)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _check(lib().fastmax_b200_wait_selftest(int(limit_clocks), torch.cuda.current_stream(dev).cuda_stream),
+               "fastmax_b200_wait_selftest")
 
 
 def launch_count() -> int:

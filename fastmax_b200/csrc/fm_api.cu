@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <atomic>
+#include <initializer_list>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -81,7 +82,7 @@ static int validate(const fastmax_problem* p) {
   if (p->mask && p->nk < p->nq)
     return fail(FASTMAX_E_ARG, "causal attention needs nk >= nq (nq=%d, nk=%d)", p->nq, p->nk);
   if (p->nq > 0 && p->nk == 0) return fail(FASTMAX_E_ARG, "no keys (nk == 0)");
-  if (p->impl < FASTMAX_IMPL_AUTO || p->impl > FASTMAX_IMPL_MOMENTS_TC)
+  if (p->impl < FASTMAX_IMPL_AUTO || p->impl > FASTMAX_IMPL_MOMENTS_FFMA)
     return fail(FASTMAX_E_ARG, "unknown impl %d", p->impl);
   if (p->chunk < 0 || p->chunk % 256 != 0)
     return fail(FASTMAX_E_ARG, "chunk=%d is not a non-negative multiple of 256", p->chunk);
@@ -124,22 +125,31 @@ static int pick_impl(const fastmax_problem& p, bool packed, int* impl) {
   const bool tc_ok = dense_tc_supports(p) && !packed;
   if (want == FASTMAX_IMPL_AUTO) {
     want = tc_ok ? FASTMAX_IMPL_DENSE_TC : FASTMAX_IMPL_DENSE_FFMA;
-    if (!packed && moments_faster(p, tc_ok)) want = FASTMAX_IMPL_MOMENTS_FFMA;
+    if (!packed && moments_faster(p, tc_ok)) want = FASTMAX_IMPL_MOMENTS;
   }
-  if (want == FASTMAX_IMPL_MOMENTS_FFMA) {
+  if (want == FASTMAX_IMPL_MOMENTS || want == FASTMAX_IMPL_MOMENTS_FFMA) {
     if (!moments_supports(p) || packed)
       return fail(FASTMAX_E_UNSUPPORTED,
                   "the moment family needs bh == bhkv, nq == nk when causal, and the plain output layout");
-    *impl = want;
+    *impl = FASTMAX_IMPL_MOMENTS;   // callers branch on the family; the state kernels look at p.impl
     return FASTMAX_OK;
   }
   if (want == FASTMAX_IMPL_DENSE_TC && !tc_ok)
     return fail(FASTMAX_E_UNSUPPORTED,
-                "the tensor-core score family needs bf16, d in {64, 128} (grouped k/v heads: d == 64) and the plain output layout");
+                "the tensor-core score family needs bf16, d in {64, 128} and the plain output layout");
   if (want != FASTMAX_IMPL_DENSE_FFMA && want != FASTMAX_IMPL_DENSE_TC)
     return fail(FASTMAX_E_UNSUPPORTED, "kernel family %d is not available in this build", want);
   *impl = want;
   return FASTMAX_OK;
+}
+
+// The tensor-core kernels read through TMA, which needs 16-byte aligned base addresses; when the
+// library chose that family itself (AUTO) and a tensor is not aligned, the CUDA-core family
+// serves the call instead of failing it.
+static bool aligned16(std::initializer_list<const void*> ptrs) {
+  for (const void* q : ptrs)
+    if (((uintptr_t)q & 15) != 0) return false;
+  return true;
 }
 
 // Backward workspace: [dots: bh+bhkv floats][delta or dvec: bh*nq floats]
@@ -192,6 +202,22 @@ int fastmax_b200_device_status(int* status, void* stream) {
   return FASTMAX_OK;
 }
 
+int fastmax_b200_device_status_reset(void* stream) {
+  int rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if ((rc = tc_status_reset(s))) return rc;
+  if ((rc = tc_wide_status_reset(s))) return rc;
+  if ((rc = tc_dkdv128_status_reset(s))) return rc;
+  if ((rc = moments_tc_status_reset(s))) return rc;
+  return first_tc_status_reset(s);
+}
+
+int fastmax_b200_wait_selftest(long long limit_clocks, void* stream) {
+  int rc = check_device();
+  if (rc) return rc;
+  return tc_wait_selftest(limit_clocks, (cudaStream_t)stream);
+}
+
 int fastmax_b200_profile_enable(int on) {
   g_prof_on.store(0);
   prof_clear();
@@ -229,14 +255,14 @@ size_t fastmax_b200_forward_workspace_bytes(const fastmax_problem* p) {
   if (validate(p)) return 0;
   int impl;
   if (pick_impl(*p, false, &impl)) return 0;
-  return impl == FASTMAX_IMPL_MOMENTS_FFMA ? fwd_ws_bytes(*p) : 0;
+  return impl == FASTMAX_IMPL_MOMENTS ? fwd_ws_bytes(*p) : 0;
 }
 
 size_t fastmax_b200_backward_workspace_bytes(const fastmax_problem* p) {
   if (validate(p)) return 0;
   int impl;
   if (pick_impl(*p, false, &impl)) return 0;
-  return impl == FASTMAX_IMPL_MOMENTS_FFMA ? bwd_ws_bytes(*p) : bwd_layout(*p).total;
+  return impl == FASTMAX_IMPL_MOMENTS ? bwd_ws_bytes(*p) : bwd_layout(*p).total;
 }
 
 static int forward_impl(const fastmax_problem* prob, const void* q, const void* k, const void* v,
@@ -251,9 +277,11 @@ static int forward_impl(const fastmax_problem* prob, const void* q, const void* 
   if ((rc = check_device())) return rc;
   int impl;
   if ((rc = pick_impl(p, o.out_f32 != 0, &impl))) return rc;
+  if (p.impl == FASTMAX_IMPL_AUTO && impl == FASTMAX_IMPL_DENSE_TC && !aligned16({q, k, v, o.out}))
+    impl = FASTMAX_IMPL_DENSE_FFMA;
   Ctx c{p, (cudaStream_t)stream};
   if (p.normalize && (rc = launch_rowmax(c, q, k, (stat_t*)stats))) return rc;
-  if (impl == FASTMAX_IMPL_MOMENTS_FFMA) {
+  if (impl == FASTMAX_IMPL_MOMENTS) {
     const size_t need = moments_fwd_layout(p).bytes;
     if (!workspace || workspace_bytes < need)
       return fail(FASTMAX_E_WORKSPACE, "forward workspace too small: need %zu bytes, got %zu", need,
@@ -293,14 +321,17 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
   if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the forward's stats buffer");
   int impl;
   if ((rc = pick_impl(p, false, &impl))) return rc;
+  if (p.impl == FASTMAX_IMPL_AUTO && impl == FASTMAX_IMPL_DENSE_TC &&
+      !aligned16({q, k, v, out, grad_out, grad_q, grad_k, grad_v}))
+    impl = FASTMAX_IMPL_DENSE_FFMA;
   BwdWs w = bwd_layout(p);
-  const size_t need = impl == FASTMAX_IMPL_MOMENTS_FFMA ? moments_bwd_layout(p).bytes : w.total;
+  const size_t need = impl == FASTMAX_IMPL_MOMENTS ? moments_bwd_layout(p).bytes : w.total;
   if (need > 0 && (!workspace || workspace_bytes < need))
     return fail(FASTMAX_E_WORKSPACE, "backward workspace too small: need %zu bytes, got %zu", need,
                 workspace_bytes);
   if ((rc = check_device())) return rc;
   Ctx c{p, (cudaStream_t)stream};
-  if (impl == FASTMAX_IMPL_MOMENTS_FFMA)
+  if (impl == FASTMAX_IMPL_MOMENTS)
     return moments_backward(c, q, k, v, out, den, (const stat_t*)stats, grad_out, grad_q, grad_k, grad_v,
                             workspace);
   float* dots = (float*)((char*)workspace + w.dots_off);

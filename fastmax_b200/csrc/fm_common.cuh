@@ -107,8 +107,11 @@ int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,
 int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
                       const float* dvec, const stat_t* stats, float* dots, void* grad_q,
                       void* grad_k, void* grad_v, const ChunkAdd* ca = nullptr);
-// Copies the device-side protocol status word to *out (synchronises the stream).
+// Copies the device-side protocol status word to *out (synchronises the stream); *_reset clears it.
+// wait_selftest launches one warp that waits, with the given clock limit, on a barrier nobody arrives at.
+int tc_wait_selftest(long long limit_clocks, cudaStream_t stream);
 int tc_status(int* out, cudaStream_t stream);
+int tc_status_reset(cudaStream_t stream);
 // Ping-pong kernels for d == 64 (fm_dense_tc_wide.cu): forward, grad_q, and grad_k / grad_v in one kernel.
 bool dense_tc_wide_supports(const fastmax_problem& p);
 int dense_tc_wide_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
@@ -117,12 +120,14 @@ int dense_tc_wide_backward(const Ctx& c, const void* q, const void* k, const voi
 int dense_tc_wide_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
                           void* out, float* den, const ChunkAdd* ca = nullptr);
 int tc_wide_status(int* out, cudaStream_t stream);
+int tc_wide_status_reset(cudaStream_t stream);
 // backward for d == 128: grad_q, and grad_k / grad_v in one kernel (fm_dense_tc_dkdv128.cu)
 bool dense_tc_dkdv128_supports(const fastmax_problem& p);
 int dense_tc_backward128(const Ctx& c, const void* q, const void* k, const void* v, const void* gs,
                          const float* dvec, const stat_t* stats, float* dots, void* grad_q, void* grad_k,
                          void* grad_v, const ChunkAdd* ca = nullptr);
 int tc_dkdv128_status(int* out, cudaStream_t stream);
+int tc_dkdv128_status_reset(cudaStream_t stream);
 
 // Optional coupling of the score-form kernels to the moment-state form: columns are
 // restricted to the row's own chunk of `chunk` tokens (0 = no restriction; needs
@@ -174,6 +179,7 @@ int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int 
                        const void* x, const void* u, const float* uvec, const void* state_bf16,
                        const stat_t* stats, float* out_a, float* den_a, float* out_b);
 int moments_tc_status(int* out, cudaStream_t stream);
+int moments_tc_status_reset(cudaStream_t stream);
 
 // first-order part on tensor cores (fm_first_tc.cu): bf16, d in {64, 128}
 bool first_tc_supports(const fastmax_problem& p);
@@ -186,6 +192,7 @@ int first_tc_readout(const Ctx& c, int type_b, int heads, int n, int chunk, int 
                      const stat_t* stats, float* o_add, float* den_add, int accumulate, int final = 0,
                      void* out_final = nullptr, float* den_final = nullptr, float* dots = nullptr);
 int first_tc_status(int* out, cudaStream_t stream);
+int first_tc_status_reset(cudaStream_t stream);
 // host orchestration of the moment family (fm_moments.cu)
 struct MomFwdWs { size_t states, total, o_add, den_add, s16, bytes; };
 struct MomBwdWs { size_t dots, delta, dvec, gs, states, total, gq_add, gk_add, gv_add, s16, bytes; };

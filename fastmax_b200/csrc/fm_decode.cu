@@ -19,7 +19,7 @@
 // (fastmax_cuda_forward.cu:109, 132-150 with nq = 1).
 //
 // The state is fp32, F = (d^2 +) d + 1 rows of d+1 floats (second-order rows first, the
-// constant row last) after a 4-float header {max |k|^2, tokens, 0, 0} per key/value head.
+// constant row last) after a 4-word header {max |k|^2, token count (int32 bits), 0, 0} per key/value head.
 // A step reads and writes it once: HBM-bound, 2 * 4 * F * (d+1) bytes per key/value head
 // per token, independent of the length.  A thread owns one column c of one block of rows
 // (a CTA's threads cover whole rows, so state accesses are contiguous), keeps the block
@@ -182,7 +182,8 @@ __global__ void __launch_bounds__(DecCfg<D>::THREADS) decode_kernel(const DecArg
   // every CTA of the head holds the same maximum; the first one records it
   if (blockIdx.x == 0 && tid == 0) {
     hs[0] = __int_as_float(s_kmax2_bits);
-    hs[1] += (float)a.n_new;
+    // the token count is an integer bit pattern in the float slot: exact past 2^24 tokens
+    hs[1] = __int_as_float(__float_as_int(hs[1]) + (int)a.n_new);
   }
   if (!READ) return;
 

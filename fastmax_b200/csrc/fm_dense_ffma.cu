@@ -80,9 +80,12 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
   float* cinvd = cdelta + BN;    // [BN]   DKDV
 
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-  // heads on grid.x; causal FWD/DQ tiles are issued longest (latest rows) first
-  const int hr = blockIdx.x;
-  const int tile = (MODE == MODE_DKDV) ? blockIdx.y : gridDim.y - 1 - blockIdx.y;
+  // one-dimensional grid (head-major), so neither heads nor row tiles meet the 65535 limit of
+  // grid.y; causal FWD/DQ tiles are issued longest (latest rows) first
+  const int ntr = (a.nrows + BM - 1) / BM;
+  const int hr = blockIdx.x / ntr;
+  const int tidx = blockIdx.x % ntr;
+  const int tile = (MODE == MODE_DKDV) ? tidx : ntr - 1 - tidx;
   const int r0 = tile * BM;
   const int kvh = (MODE == MODE_DKDV) ? hr : hr / a.ratio;
 
@@ -99,6 +102,9 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
       rinvd[i] = ok ? 1.0f / a.den[(size_t)hr * a.nrows + r] : 0.f;
     }
   }
+
+  // the epilogue reads Xs written by other threads even when the column loop below runs zero times
+  __syncthreads();
 
   float o1[4][NC], o2[4][NC], rsum[4];
 #pragma unroll
@@ -296,7 +302,9 @@ int launch_one(const Ctx& c, const DenseArgs& a, int row_heads) {
   size_t sm = smem_bytes(D, MODE);
   FM_CUDA_TRY(cudaFuncSetAttribute(dense_ffma_kernel<D, MODE, T>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-  dim3 grid(row_heads, (a.nrows + BM - 1) / BM);
+  const long long blocks = (long long)row_heads * ((a.nrows + BM - 1) / BM);
+  if (blocks > 0x7FFFFFFFLL) return fail(FASTMAX_E_ARG, "heads x row tiles = %lld exceeds the grid limit", blocks);
+  dim3 grid((unsigned)blocks);
   static const char* const names[3] = {"fm_dense_ffma_fwd", "fm_dense_ffma_dq", "fm_dense_ffma_dkdv"};
   FM_LAUNCH(names[MODE], c.stream, (dense_ffma_kernel<D, MODE, T><<<grid, 256, sm, c.stream>>>(a)));
   FM_CUDA_TRY(cudaGetLastError());

@@ -590,8 +590,39 @@ int dense_tc_backward(const Ctx& c, const void* q, const void* k, const void* v,
   return launch_tc<OP_A>(c, "fm_dense_tc_dv", k, nullptr, q, gs, p.nk, p.nq, a);
 }
 
+// One warp waits on a barrier that nobody ever arrives at, with the same bounded wait the
+// kernels above use but a caller-chosen limit; when the wait gives up it records code 99 and
+// the kernel returns.  This is how the give-up path is exercised without breaking a real
+// kernel's protocol.
+__global__ void wait_selftest_kernel(long long limit_clocks) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t b = sm100::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(b, 1);
+    sm100::mbar_fence_init();
+  }
+  __syncwarp();
+  if (!sm100::mbar_wait_limit(b, 0, limit_clocks)) {
+    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, 99);
+  }
+}
+
+int tc_wait_selftest(long long limit_clocks, cudaStream_t stream) {
+  if (limit_clocks < 0 || limit_clocks > sm100::kWaitLimitClocks)
+    return fail(FASTMAX_E_ARG, "limit_clocks must lie in [0, %lld]", sm100::kWaitLimitClocks);
+  FM_LAUNCH("fm_wait_selftest", stream, (wait_selftest_kernel<<<1, 32, 0, stream>>>(limit_clocks)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
 int tc_status(int* out, cudaStream_t stream) {
   FM_CUDA_TRY(cudaMemcpyFromSymbolAsync(out, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
+int tc_status_reset(cudaStream_t stream) {
+  const int zero = 0;
+  FM_CUDA_TRY(cudaMemcpyToSymbolAsync(g_tc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream));
   FM_CUDA_TRY(cudaStreamSynchronize(stream));
   return FASTMAX_OK;
 }

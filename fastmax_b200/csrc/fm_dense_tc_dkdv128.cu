@@ -447,5 +447,11 @@ int tc_dkdv128_status(int* out, cudaStream_t stream) {
   FM_CUDA_TRY(cudaStreamSynchronize(stream));
   return FASTMAX_OK;
 }
+int tc_dkdv128_status_reset(cudaStream_t stream) {
+  const int zero = 0;
+  FM_CUDA_TRY(cudaMemcpyToSymbolAsync(g_ktc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
 
 }  // namespace fm

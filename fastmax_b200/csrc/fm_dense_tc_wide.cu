@@ -549,6 +549,12 @@ int tc_wide_status(int* out, cudaStream_t stream) {
   FM_CUDA_TRY(cudaStreamSynchronize(stream));
   return FASTMAX_OK;
 }
+int tc_wide_status_reset(cudaStream_t stream) {
+  const int zero = 0;
+  FM_CUDA_TRY(cudaMemcpyToSymbolAsync(g_wtc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
 
 
 }  // namespace fm

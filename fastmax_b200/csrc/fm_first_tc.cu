@@ -449,13 +449,19 @@ bool first_tc_supports(const fastmax_problem& p) {
     const char* e = getenv("FASTMAX_B200_NO_TC_MOMENTS");
     return e && e[0] == '1';
   }();
-  return !off && p.dtype == FASTMAX_BF16 && (p.d == 64 || p.d == 128) && p.bh == p.bhkv;
+  return !off && p.impl != FASTMAX_IMPL_MOMENTS_FFMA && p.dtype == FASTMAX_BF16 && (p.d == 64 || p.d == 128) && p.bh == p.bhkv;
 }
 
 size_t first_tc_copy_bytes(const fastmax_problem& p, int mats) { return (size_t)mats * p.d * p.d * 2; }
 
 int first_tc_status(int* out, cudaStream_t stream) {
   FM_CUDA_TRY(cudaMemcpyFromSymbolAsync(out, g_ftc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
+int first_tc_status_reset(cudaStream_t stream) {
+  const int zero = 0;
+  FM_CUDA_TRY(cudaMemcpyToSymbolAsync(g_ftc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream));
   FM_CUDA_TRY(cudaStreamSynchronize(stream));
   return FASTMAX_OK;
 }

@@ -582,15 +582,22 @@ int moments_tc_status(int* out, cudaStream_t stream) {
   FM_CUDA_TRY(cudaStreamSynchronize(stream));
   return FASTMAX_OK;
 }
+int moments_tc_status_reset(cudaStream_t stream) {
+  const int zero = 0;
+  FM_CUDA_TRY(cudaMemcpyToSymbolAsync(g_mtc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream));
+  FM_CUDA_TRY(cudaStreamSynchronize(stream));
+  return FASTMAX_OK;
+}
 
-// FASTMAX_B200_NO_TC_MOMENTS=1 in the environment keeps the moment family on the CUDA-core
-// kernels (used by the tests to compare the two implementations of the same stages).
+// impl == FASTMAX_IMPL_MOMENTS_FFMA, or FASTMAX_B200_NO_TC_MOMENTS=1 in the environment, keeps the
+// moment family on the CUDA-core kernels (used by the tests to compare the two implementations of
+// the same stages).
 bool moments_tc_supports(const fastmax_problem& p) {
   static const bool off = [] {
     const char* e = getenv("FASTMAX_B200_NO_TC_MOMENTS");
     return e && e[0] == '1';
   }();
-  return !off && p.dtype == FASTMAX_BF16 && p.d == 64 && p.p == 2 && p.bh == p.bhkv;
+  return !off && p.impl != FASTMAX_IMPL_MOMENTS_FFMA && p.dtype == FASTMAX_BF16 && p.d == 64 && p.p == 2 && p.bh == p.bhkv;
 }
 
 size_t moments_tc_state_bytes(int mats) { return (size_t)mats * NROWS_TP * 64 * 2; }

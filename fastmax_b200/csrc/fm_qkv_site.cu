@@ -219,6 +219,20 @@ __global__ void __launch_bounds__(256) noise_kernel(const T* x, const T* __restr
     stf(y + i, (float)x[i] * (1.0f + dropout * (float)noise[i]));
 }
 
+// The reference's packed forward result (rows of d + 1 floats, the denominator last): the first d
+// channels of every row are scaled by 1 + dropout * noise, the denominator is left alone
+// (reference apply_dropout, fastmax_cuda_forward.cu:271-280).  One thread per element of noise.
+template <typename TN>
+__global__ void __launch_bounds__(256) packed_noise_kernel(float* o, const TN* __restrict__ noise, float dropout,
+                                                           long long rows, int d) {
+  const long long count = rows * d;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / d;
+    o[i + r] *= 1.0f + dropout * ldf(noise + i);
+  }
+}
+
 int grid_for(long long work_items, int* blocks) {
   int dev = 0, sms = 0;
   FM_CUDA_TRY(cudaGetDevice(&dev));
@@ -337,6 +351,26 @@ int fastmax_b200_scale_by_noise(const void* x, const void* noise, void* y, float
     FM_LAUNCH("fm_scale_by_noise", st,
               (noise_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)noise,
                                                                    (__nv_bfloat16*)y, dropout, (long long)count)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+int fastmax_b200_scale_packed_by_noise(float* o_packed, const void* noise, float dropout, long long rows, int d,
+                                       int noise_dtype, void* stream) {
+  if (noise_dtype != FASTMAX_F32 && noise_dtype != FASTMAX_BF16)
+    return fail(FASTMAX_E_ARG, "dtype %d is neither FASTMAX_F32 nor FASTMAX_BF16", noise_dtype);
+  if (rows < 0 || d <= 0) return fail(FASTMAX_E_ARG, "bad shape");
+  if (rows == 0) return FASTMAX_OK;
+  if (!o_packed || !noise) return fail(FASTMAX_E_ARG, "NULL array");
+  int blocks, rc;
+  if ((rc = grid_for(rows * d, &blocks))) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (noise_dtype == FASTMAX_F32)
+    FM_LAUNCH("fm_scale_packed_by_noise", st,
+              (packed_noise_kernel<float><<<blocks, 256, 0, st>>>(o_packed, (const float*)noise, dropout, rows, d)));
+  else
+    FM_LAUNCH("fm_scale_packed_by_noise", st,
+              (packed_noise_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(o_packed, (const __nv_bfloat16*)noise,
+                                                                          dropout, rows, d)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }

@@ -74,15 +74,18 @@ __device__ __forceinline__ uint32_t mbar_try_suspend(uint32_t bar, uint32_t pari
 // a protocol error ends the kernel with an error status instead of hanging it.
 // The clock is read once per 16 suspended tries, so a waiting warp issues few instructions.
 constexpr long long kWaitLimitClocks = 2000000000LL;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, long long limit_clocks) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i)
       if (mbar_try_suspend(bar, parity, 100000u)) return true;
-    if (clock64() - t0 > kWaitLimitClocks) return false;
+    if (clock64() - t0 > limit_clocks) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, kWaitLimitClocks);
 }
 
 // ---- TMA ----------------------------------------------------------------------

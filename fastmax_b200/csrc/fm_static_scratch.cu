@@ -7,8 +7,14 @@
 // on its behalf fails, or succeeds only by evicting cached blocks), and
 // latency-critical loops for which the device-wide synchronisation that
 // cudaMalloc and cudaFree imply is not acceptable.  For them the scratch lives
-// in a file-scope __device__ array: the driver reserves it when the library is
-// loaded on a GPU and it stays reserved until the process exits.
+// in a file-scope __device__ array that the driver reserves on a GPU when this
+// library's code is loaded there, and that stays reserved until the process exits.
+// With CUDA's default lazy module loading that happens at the first call on that
+// GPU, which also looks the array's address up (with that GPU current).  A host
+// that is about to hand the rest of the GPU to its own arena, or to start a stream
+// capture, should therefore make one call first; an empty problem (bh == 0, all
+// pointers NULL) does the set-up and nothing else.  Setting
+// CUDA_MODULE_LOADING=EAGER moves the reservation to library load.
 //
 // Limits.  The array is kStaticScratchBytes (8 MiB) per GPU; a problem whose
 // scratch does not fit is rejected with FASTMAX_E_WORKSPACE.  Every call on a
@@ -68,6 +74,16 @@ int fastmax_b200_backward_static(const fastmax_problem* prob, const void* q, con
   int rc = check_problem(prob);
   if (rc) return rc;
   const fastmax_problem& p = *prob;
+  // The device check and the per-device address lookup come before everything else, so that
+  // a call with an empty problem (bh == 0) is a cheap way to do the one-time set-up early:
+  // under CUDA's lazy module loading it is this lookup that makes the driver reserve the
+  // array on the current GPU.
+  int major = 0, dev = 0;
+  FM_CUDA_TRY(cudaGetDevice(&dev));
+  FM_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10) return fail(FASTMAX_E_DEVICE, "device %d is not compute capability 10.x", dev);
+  void* base = nullptr;
+  if ((rc = static_scratch(&base))) return rc;
   if (p.bh == 0 || (p.nq == 0 && p.nk == 0)) return FASTMAX_OK;
   if (!q || !k || !v || !out || !den || !grad_out || !grad_q || !grad_k || !grad_v)
     return fail(FASTMAX_E_ARG, "NULL tensor pointer");
@@ -82,12 +98,6 @@ int fastmax_b200_backward_static(const fastmax_problem* prob, const void* q, con
                 "this problem needs %zu bytes of scratch but the built-in array holds %zu "
                 "(bh*nq must stay below about %zu); use fastmax_b200_backward with a caller buffer",
                 need, kStaticScratchBytes, (kStaticScratchBytes - dots_bytes) / sizeof(float));
-  void* base = nullptr;
-  if ((rc = static_scratch(&base))) return rc;
-  int major = 0, dev = 0;
-  FM_CUDA_TRY(cudaGetDevice(&dev));
-  FM_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
-  if (major != 10) return fail(FASTMAX_E_DEVICE, "device %d is not compute capability 10.x", dev);
   Ctx c{p, (cudaStream_t)stream};
   float* dots = (float*)base;
   float* delta = (float*)((char*)base + dots_bytes);

@@ -53,9 +53,11 @@ enum {
   FASTMAX_IMPL_AUTO = 0,
   FASTMAX_IMPL_DENSE_FFMA = 1,   /* tiled score form on CUDA cores, fp32 math */
   FASTMAX_IMPL_DENSE_TC = 2,     /* tiled score form on tcgen05 tensor cores (bf16) */
-  FASTMAX_IMPL_MOMENTS_FFMA = 3, /* chunked moment-state form, states on CUDA cores; each chunk's own
-                                    block in score form on the best family for the problem */
-  FASTMAX_IMPL_MOMENTS_TC = 4    /* chunked moment-state form with states on tcgen05 (not built yet) */
+  FASTMAX_IMPL_MOMENTS = 3,      /* chunked moment-state form: states built and read on tcgen05 where a
+                                    kernel exists (bf16: second order at d == 64, first order at d in
+                                    {64, 128}), otherwise on CUDA cores; each chunk's own block in score
+                                    form on the best family for the problem */
+  FASTMAX_IMPL_MOMENTS_FFMA = 4  /* the same with every state kernel on CUDA cores (any d and dtype) */
 };
 
 /* One attention problem.  Mirrors the argument list of the reference's
@@ -102,8 +104,17 @@ int fastmax_b200_profile_get(int i, char* name, int name_len, float* ms);
  * tensor-core kernels bound every wait on a barrier; a wait that gives up stores
  * a non-zero code in a device word and the kernel winds down instead of
  * hanging.  This call synchronises `stream` and copies the word to *status
- * (host pointer): 0 means no kernel of this process ever gave up a wait. */
+ * (host pointer): 0 means no kernel of this process gave up a wait since the last reset. */
 int fastmax_b200_device_status(int* status, void* stream);
+/* Clears the status word (synchronises `stream`), so that a later give-up can be told from
+ * an earlier one. */
+int fastmax_b200_device_status_reset(void* stream);
+/* Exercises the give-up path without disturbing a real kernel: launches one warp that waits,
+ * bounded by limit_clocks SM clocks (at most the kernels' own limit, about a second), on a
+ * barrier that nothing ever completes.  The kernel returns once the limit has passed -- the
+ * wait is re-armed in steps of up to 1.6 ms -- and fastmax_b200_device_status then reports 99.
+ * Nothing faults and the context stays usable. */
+int fastmax_b200_wait_selftest(long long limit_clocks, void* stream);
 
 /* Bytes of the per-head statistics buffer (max row norms and their row
  * indices) that forward writes and backward reads.  Replaces the reference's
@@ -226,7 +237,10 @@ int fastmax_b200_shard_norm_fixup(const fastmax_problem* prob, const void* q, co
  *  - Problems whose scratch does not fit -- roughly bh*nq above 2 million --
  *    return FASTMAX_E_WORKSPACE; use fastmax_b200_backward for those.
  *  - The first call on each GPU looks up the array's device address (with that
- *    GPU current).  Make that first call before starting any stream capture.
+ *    GPU current); under CUDA's lazy module loading that is also when the driver
+ *    reserves the 8 MiB there.  Make that first call before starting any stream
+ *    capture and before your own allocator takes what is left of the GPU: a call
+ *    with an empty problem (bh == 0, every pointer NULL) does just this set-up.
  *  - All calls on a GPU share the one array: calls that overlap on the GPU race,
  *    so keep them on one stream or order them yourself.  Nothing is assumed
  *    about the array's contents between calls; what must start at zero is
@@ -271,6 +285,12 @@ int fastmax_b200_swap_middle_axes(const void* src, void* dst, long long batch, l
                                   int d, int dtype, void* stream);
 int fastmax_b200_scale_by_noise(const void* x, const void* noise, void* y, float dropout, size_t count,
                                 int dtype, void* stream);
+/* The same output dropout on the packed forward result of forward_packed: o_packed is
+ * (rows, d + 1) float32, noise (rows, d) of type noise_dtype; channels 0..d-1 of every row
+ * are scaled in place, the denominator channel is not (reference apply_dropout,
+ * fastmax_cuda_forward.cu:271-280, which runs over the first d channels of o). */
+int fastmax_b200_scale_packed_by_noise(float* o_packed, const void* noise, float dropout, long long rows,
+                                       int d, int noise_dtype, void* stream);
 
 /* ---- decoding against a persistent moment state --------------------------------
  * Replaces the key/value cache of the reference's model (model.py:501-504, 828-852)

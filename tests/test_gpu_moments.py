@@ -22,7 +22,7 @@ def randn(*shape, seed):
 @pytest.mark.parametrize("c", CASES, ids=[c["tag"] for c in CASES])
 def test_reference_vectors_through_the_moment_family(c):
     """Sequences shorter than one chunk: states are built and summed, the score-form part covers everything."""
-    got, _ = run_cabi(c["q"], c["k"], c["v"], c["go"], torch.float32, impl="moments_ffma", chunk=256,
+    got, _ = run_cabi(c["q"], c["k"], c["v"], c["go"], torch.float32, impl="moments", chunk=256,
                       **case_kwargs(c))
     assert_close(got, [c[n + "64"] for n in ("out", "dq", "dk", "dv")], torch.float32, c["tag"])
 
@@ -42,7 +42,7 @@ def test_moment_family_over_several_chunks(cfg, dtype):
     if not norm:
         q, k = q * d ** -0.5, k * d ** -0.5
     kw = dict(mask=mask, normalize=norm, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
-    got, _ = run_cabi(q, k, v, go, dtype, impl="moments_ffma", chunk=chunk, **kw)
+    got, _ = run_cabi(q, k, v, go, dtype, impl="moments", chunk=chunk, **kw)
     assert _cabi.device_status() == 0
     ref = oracle(q, k, v, go, dtype, dense=True, **kw)
     assert_close(got, ref, dtype, str(cfg))
@@ -52,7 +52,7 @@ def test_unmasked_moments_with_more_keys_than_queries():
     q, go = randn(1, 2, 300, 32, seed=1), randn(1, 2, 300, 32, seed=2)
     k, v = randn(1, 2, 777, 32, seed=3), randn(1, 2, 777, 32, seed=4)
     kw = dict(mask=0, normalize=1, p=2, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
-    got, _ = run_cabi(q, k, v, go, torch.float32, impl="moments_ffma", chunk=256, **kw)
+    got, _ = run_cabi(q, k, v, go, torch.float32, impl="moments", chunk=256, **kw)
     ref = oracle(q, k, v, go, torch.float32, dense=True, **kw)
     assert_close(got, ref, torch.float32, "unmasked nq != nk")
 
@@ -98,6 +98,10 @@ def test_shard_stage_calls_reproduce_the_unsharded_result(dtype, d, normalize):
     for a, b, name in zip(got, want, ("out", "dq", "dk", "dv")):
         e = float((a.float() - b.float()).abs().max() / b.float().abs().max())
         assert e < tol, (name, e)
+    # and against the CPU oracle, not only against another CUDA path
+    ref = oracle(*[t.float().cpu()[None] for t in (q, k, v, go)], dtype, dense=True, a0=1.0, a1=1.0, a2=0.5, lim=1.0,
+                 **{n_: int(x_) for n_, x_ in kw.items()})
+    assert_close([t.float().cpu()[None] for t in got], ref, dtype, "shard stages vs oracle")
 
 
 @pytest.mark.parametrize("dtype,d,normalize,p", [(torch.float32, 32, True, 2), (torch.bfloat16, 64, True, 2),
@@ -138,3 +142,7 @@ def test_unmasked_shard_stage_calls_reproduce_the_unsharded_result(dtype, d, nor
     for a, b, name in zip(got, want, ("out", "dq", "dk", "dv")):
         e = float((a.float() - b.float()).abs().max() / b.float().abs().max())
         assert e < tol, (name, e)
+    # and against the CPU oracle, not only against another CUDA path
+    ref = oracle(*[t.float().cpu()[None] for t in (q, k, v, go)], dtype, dense=True, a0=1.0, a1=1.0, a2=0.5, lim=1.0,
+                 **{n_: int(x_) for n_, x_ in kw.items()})
+    assert_close([t.float().cpu()[None] for t in got], ref, dtype, "shard stages vs oracle")

@@ -94,8 +94,8 @@ def test_unsupported_requests_fail_loudly():
     q = torch.randn(2, 64, 64, device="cuda")
     with pytest.raises(RuntimeError):
         _cabi.forward(q, q, q, mask=True, normalize=False, p=2, impl="dense_tc")   # fp32
-    with pytest.raises(RuntimeError):
-        _cabi.forward(q.bfloat16(), q.bfloat16(), q.bfloat16(), mask=True, normalize=False, p=2, impl="moments_tc")
+    with pytest.raises(ValueError):
+        _cabi.forward(q.bfloat16(), q.bfloat16(), q.bfloat16(), mask=True, normalize=False, p=2, impl=7)
 
 
 _NARROW_CHILD = r"""
