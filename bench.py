@@ -1,22 +1,26 @@
 """Fastmax forward+backward throughput on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-A step is one forward + backward pass of Fastmax attention over one batch of
-synthetic N(0,1) inputs.  The workload is the configuration the headline target
-is quoted on: causal, bf16, p=2, B=64, H=16, N=10000, D=64, normalize=True,
-lim=1, a=(1,1,0.5).  With N GPUs every rank runs that workload on its own shard
-of an N-times larger batch (batch*head units are independent; no collective on
-the data path), so `value` is total tokens of all ranks over the slowest rank's
-device time ("weak" scaling); `--scaling strong` splits the single batch's
-batch*head units over the ranks instead.
+A step is one forward + backward pass of Fastmax attention over one batch of synthetic
+N(0,1) inputs.  The default workload is the configuration the headline target is quoted on:
+causal, bf16, p=2, B=64, H=16, N=10000, D=64, normalize=True, lim=1, a=(1,1,0.5).  With N
+GPUs that ONE batch is split: its B*H batch*head units are independent, so each rank takes
+B*H/N of them and nothing is exchanged on the data path (`scaling: strong`; `--scaling weak`
+gives every rank the whole batch instead, and the default run reports that figure too, under
+`weak`).  `value` is tokens of the batch over the slowest rank's device time.
 
-Rank 0 prints one JSON line.  `value` is measured with the inputs resident in
-HBM; `e2e` is the same metric with pinned host buffers through
-fastmax_b200.host.HostPipeline, host<->device copies inside the timed region.  `--impl reference` times
-the CPU restatement of the reference's PyTorch path (oracle/) on the host
-cores, on a bounded sample of the same workload.
+Rank 0 prints one JSON line.  `value` is measured with the inputs resident in HBM; `e2e` is
+the same metric with pinned host buffers through fastmax_b200.host.HostPipeline, host<->device
+copies inside the timed region.  The line of the default workload also carries `c5`: the
+long-context configuration (B=1, H=32, N=262144, D=64) with its sequence split over the same
+N ranks, a few steps, so that the sequence-sharded path is measured by the same command.
+
+`--impl reference` times the reference's own pure-PyTorch path on the host cores: the function
+compiled into oracle/_ref by oracle/make_ref.py when that has been built, else the oracle's
+restatement of it.  It runs the CPU-runnable configuration (B=2, H=8, N=1024, D=32) exactly
+(`c1`) and a bounded sample of the selected workload, extrapolated to the whole job (`value`).
 """
 from __future__ import annotations
 
@@ -40,23 +44,38 @@ WORKLOADS = {
     "c4p2": (32, 32, 16384, 128, "bf16", 0, 2, 0),
     "c4p1": (32, 32, 16384, 128, "bf16", 0, 1, 0),
     "c5": (1, 32, 262144, 64, "bf16", 1, 2, 1),   # long context; sharded along the sequence when N > 1
-    "c5s": (1, 8, 65536, 64, "bf16", 1, 2, 1),    # reduced long-context case
     "c5u": (1, 32, 262144, 128, "bf16", 0, 1, 0), # long unmasked p = 1 sequence, sharded along the sequence when N > 1
-    "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
-    "c4s": (4, 8, 16384, 128, "bf16", 0, 2, 0),   # reduced unmasked d=128 case
-    "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),   # small case for ncu captures (inputs 4 x 67 MB)
-    "prof1": (2, 8, 16384, 128, "bf16", 0, 1, 0),  # small p = 1 case for ncu captures (inputs 4 x 67 MB)
     # decoding against the persistent moment state: one new token per sequence and step (N is not used)
     "decode": (64, 16, 1, 64, "bf16", 1, 2, 1),
-    "decodes": (16, 16, 1, 64, "bf16", 1, 2, 1),   # small case for ncu captures (277 MB of state)
     # the model's call site: packed projection -> rotary embedding -> attention -> (B, T, H*hs), and back
     "site": (8, 32, 4096, 64, "bf16", 1, 1, 1),
 }
+# Reduced shapes for profiler captures (--profile-case NAME): inputs larger than L2, a few hundred MB in all.
+PROFILE_CASES = {
+    "tiny": (2, 4, 1024, 64, "bf16", 1, 2, 1),
+    "prof": (8, 16, 4096, 64, "bf16", 1, 2, 1),      # inputs 4 x 67 MB
+    "prof1": (2, 8, 16384, 128, "bf16", 0, 1, 0),    # p = 1, inputs 4 x 67 MB
+    "c4s": (4, 8, 16384, 128, "bf16", 0, 2, 0),      # unmasked d = 128
+    "c5s": (1, 8, 65536, 64, "bf16", 1, 2, 1),       # long context
+    "c2s": (16, 8, 1000, 32, "fp32", 1, 2, 1),       # fp32 CUDA-core family
+    "decodes": (16, 16, 1, 64, "bf16", 1, 2, 1),     # 277 MB of decode state
+}
 A = dict(a0=1.0, a1=1.0, a2=0.5, lim=1.0)
+L2_BYTES = 126e6
+# FP32 FFMA peak for the fp32 workloads (no measured figure exists): 148 SMs x 128 lanes x 2 FLOP x 1.965 GHz
+FFMA_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12
+# Version of the library the DRAM-traffic figures below were captured on; another version reports none.
+TRAFFIC_LIB_VERSION = 100
+# ncu DRAM bytes (read + write) per token-head, bf16, D = 64, small case scaled by heads x tokens
+NCU_BYTES_PER_TOKEN_HEAD = {"fm_dense_tc_fwd": 483.2, "fm_dense_tc_dq": 621.3, "fm_dense_tc_dkdv": 723.8}
+
+
+def cfg_of(name):
+    return WORKLOADS[name] if name in WORKLOADS else PROFILE_CASES[name]
 
 
 def describe(name):
-    B, H, N, D, dt, mask, p, norm = WORKLOADS[name]
+    B, H, N, D, dt, mask, p, norm = cfg_of(name)
     return (f"{name}: {'causal' if mask else 'unmasked'} {dt} p={p} B={B} H={H} N={N} D={D} "
             f"normalize={bool(norm)} lim=1 a=(1,1,0.5)")
 
@@ -69,7 +88,11 @@ def alg_flops_per_token_head(D, p):
     return 4 * u, 4 * u, 6 * u
 
 
-KERNEL_FLOP_SHARE = {"fwd": "fwd", "dq": "dq", "dkdv": "dkdv", "dk": "dk", "dv": "dv"}
+def l2_note(nbytes_inputs, flushed):
+    if flushed:
+        return ("inputs (%.1f MB per GPU) fit the 126 MB L2: a 256 MB buffer is rewritten between timed steps"
+                % (nbytes_inputs / 1e6))
+    return "inputs (%.2f GB per GPU) larger than the 126 MB L2" % (nbytes_inputs / 1e9)
 
 
 class ClockSampler:
@@ -298,47 +321,76 @@ def load_peaks():
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_sample(name, steps, warmup):
-    """Time the oracle (CPU restatement of the reference's PyTorch path) on one
-    head of the workload at a sequence length it can hold in memory; the
-    factorised evaluation is linear in n, so tokens/s per head carries over."""
-    import torch
+def _cpu_function():
+    """(function, kind): the reference's own fastmax_function from oracle/_ref, else the oracle's port."""
+    from oracle.make_ref import load
 
+    fn = load()
+    if fn is not None:
+        return fn, "reference"
     from oracle.fastmax_oracle import fastmax_moments
 
-    B, H, N, D, dt, mask, p, norm = WORKLOADS[name]
-    n = min(N, 1024 if D >= 64 else 2048)
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    g = torch.Generator().manual_seed(1234)
-    q, k, v, go = [torch.randn(1, 1, n, D, generator=g) for _ in range(4)]
-    if dt == "bf16":
-        q, k, v, go = [t.bfloat16().float() for t in (q, k, v, go)]
-    times = []
+    return fastmax_moments, "port"
+
+
+def _cpu_time(fn, q, k, v, go, steps, warmup, budget_s, **kw):
+    """Median seconds of forward + backward(go); stops early when `budget_s` is used up."""
+    times, t_start = [], time.perf_counter()
     for it in range(warmup + steps):
         qq, kk, vv = [t.clone().requires_grad_(True) for t in (q, k, v)]
         t0 = time.perf_counter()
-        out = fastmax_moments(qq, kk, vv, mask=mask, normalize=norm, p=p, **A)
-        out.backward(go)
+        out = fn(qq, kk, vv, **kw)
+        out.backward(go.to(out.dtype))
         dtm = time.perf_counter() - t0
         if it >= warmup:
             times.append(dtm)
-    t = statistics.median(times)
-    # whole-job tokens/s: a token counts once for all H heads
-    value = (n / t) / H
-    return {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": f"1 of {B * H} batch*head units, first {n} of {N} tokens, fp32 math, "
-                      f"median of {steps} fwd+bwd ({t:.2f} s each), scaled by 1/H"}, t
+        if times and time.perf_counter() - t_start > budget_s:
+            break
+    return statistics.median(times), len(times)
+
+
+def cpu_arm(name, steps, warmup, budget_s=120.0):
+    """The CPU implementation on all host cores: (i) BASELINE configuration 1 exactly, (ii) one
+    batch*head unit of workload `name` at a length the cumulative-moment evaluation can hold in
+    memory (it is linear in n, so tokens/s per head carries over), scaled to whole-job tokens/s."""
+    import torch
+
+    fn, kind = _cpu_function()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(1234)
+    # (i) configuration 1, exactly as stated: fp32, unmasked, p = 2, normalize, B=2 H=8 N=1024 D=32
+    B1, H1, N1, D1 = WORKLOADS["c1"][:4]
+    q, k, v, go = [torch.randn(B1, H1, N1, D1, generator=g) for _ in range(4)]
+    t1, n1 = _cpu_time(fn, q, k, v, go, min(steps, 5), 1, budget_s / 4, mask=0, normalize=1, p=2, **A)
+    c1 = {"seconds_per_step": t1, "tokens_per_s": B1 * N1 / t1, "steps": n1,
+          "config": describe("c1") + ", the whole configuration"}
+    if name == "c1":
+        return {"value": c1["tokens_per_s"], "unit": "tokens/s", "cores": cores, "kind": kind,
+                "sample": f"the whole configuration, fp32, median of {n1} fwd+bwd ({t1:.2f} s each)", "c1": c1}, t1, n1
+    # (ii) a bounded sample of the selected workload
+    B, H, N, D, dt, mask, p, norm = cfg_of(name)
+    n = min(N, 1024 if D >= 64 else 2048)
+    q, k, v, go = [torch.randn(1, 1, n, D, generator=g) for _ in range(4)]
+    if dt == "bf16":
+        q, k, v, go = [t.bfloat16().float() for t in (q, k, v, go)]
+    if not norm:
+        q, k = q * D ** -0.5, k * D ** -0.5
+    t, ns = _cpu_time(fn, q, k, v, go, steps, warmup, budget_s, mask=mask, normalize=norm, p=p, **A)
+    value = (n / t) / H          # whole-job tokens/s: a token counts once for all H heads
+    return {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "extrapolated": True,
+            "sample": f"1 of {B * H} batch*head units, first {n} of {N} tokens, fp32 math, median of {ns} "
+                      f"fwd+bwd ({t:.2f} s each), scaled by 1/H to the whole job", "c1": c1}, t, ns
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cb, t = cpu_sample(args.workload, max(1, min(args.steps, 5)), max(1, min(args.warmup, 1)))
+    cb, t, ns = cpu_arm(args.workload, max(1, args.steps), max(1, min(args.warmup, 1)), budget_s=150.0)
     line = {"impl": "reference", "metric": "fastmax_fwd_bwd_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
-            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+            "n_gpus": args.gpus, "steps": ns, "steps_requested": args.steps, "warmup": max(1, min(args.warmup, 1)),
+            "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": {"workload": describe(args.workload)},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -346,242 +398,309 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------- GPU arm
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
+def _per_kernel(recs):
+    per = {}
+    for name, t in recs:
+        c, s = per.get(name, (0, 0.0))
+        per[name] = (c + 1, s + t)
+    return per
 
-    import fastmax_b200
+
+def _kernel_table(per):
+    tot = sum(x[1] for x in per.values()) or 1.0
+    return {n: {"launches": c, "ms_total": round(s, 3), "share": round(s / tot, 4)}
+            for n, (c, s) in sorted(per.items(), key=lambda kv: -kv[1][1])}
+
+
+class Harness:
+    """Process-group plumbing shared by the timed legs."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        t = self.torch.tensor([x], device=self.dev, dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def timed_region(hz, step, steps, warmup, flush_l2=False, sample_clocks=False):
+    """`warmup` untimed steps, then exactly `steps` timed ones between barriers; device time by CUDA events
+    on the launching stream, max over ranks.  With flush_l2 every step is timed on its own and a 256 MB
+    buffer is rewritten in between (outside the events)."""
+    torch = hz.torch
     from fastmax_b200 import _cabi
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    B, H, N, D, dt, mask, p, norm = WORKLOADS[args.workload]
-    dtype = torch.bfloat16 if dt == "bf16" else torch.float32
-    bh_total = B * H
-    seq_mode = args.workload.startswith("c5")   # one long sequence, split along n over the ranks
-    if seq_mode:
-        return run_seq(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
-    if args.workload.startswith("decode"):
-        return run_decode(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
-    if args.workload == "site":
-        return run_site(args, world, rank, dev, (B, H, N, D, dt, mask, p, norm))
-    if args.scaling == "strong":
-        bh = bh_total // world + (1 if rank < bh_total % world else 0)
-        tokens_job = B * N
+    for _ in range(warmup):
+        step()
+    hz.barrier()
+    sampler = ClockSampler(hz.local)
+    if sample_clocks and hz.rank == 0:
+        sampler.start()
+    _cabi.profile(True)
+    n0 = _cabi.launch_count()
+    hz.barrier()
+    if flush_l2:
+        junk = torch.empty(256 << 20, dtype=torch.uint8, device=hz.dev)
+        evs = []
+        for _ in range(steps):
+            junk.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            evs.append((e0, e1))
+        hz.barrier()
+        ms = sum(a.elapsed_time(b) for a, b in evs)
     else:
-        bh = bh_total
-        tokens_job = B * N * world
-    kw = dict(mask=bool(mask), normalize=bool(norm), p=p, impl=args.family, chunk=args.chunk, **A)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        hz.barrier()
+        ms = e0.elapsed_time(e1)
+    launches = _cabi.launch_count() - n0
+    recs = _cabi.profile_records()
+    _cabi.profile(False)
+    clocks = sampler.stop() if (sample_clocks and hz.rank == 0) else None
+    return {"ms": hz.max_over_ranks(ms), "launches": int(launches), "per": _per_kernel(recs), "clocks": clocks}
 
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    q, k, v, go = [torch.randn(bh, N, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4)]
+
+def bh_leg(hz, args, cfg, bh, steps, warmup, sample_clocks):
+    """Forward + backward on `bh` batch*head units resident in HBM, through the C ABI."""
+    torch = hz.torch
+    from fastmax_b200 import _cabi
+
+    B, H, N, D, dt, mask, p, norm = cfg
+    dtype = torch.bfloat16 if dt == "bf16" else torch.float32
+    kw = dict(mask=bool(mask), normalize=bool(norm), p=p, impl=args.family, chunk=args.chunk, **A)
+    g = torch.Generator(device=hz.dev).manual_seed(1234 + hz.rank)
+    q, k, v, go = [torch.randn(bh, N, D, generator=g, device=hz.dev, dtype=torch.float32).to(dtype) for _ in range(4)]
+    if not norm:   # unnormalised configurations scale q and k by 1/sqrt(D)
+        q, k = q * D ** -0.5, k * D ** -0.5
+    in_bytes = 4 * q.numel() * q.element_size()
+    flush = in_bytes < 2 * L2_BYTES
 
     def step():
         out, den, stats = _cabi.forward(q, k, v, **kw)
         return out, _cabi.backward(q, k, v, out, den, stats, go, **kw)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    _cabi.profile(True)
-    n0 = _cabi.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        res = step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = _cabi.launch_count() - n0
-    recs = _cabi.profile_records()
-    _cabi.profile(False)
-    clocks = sampler.stop() if rank == 0 else None
-    tms = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    ms = float(tms.item())
-    value = tokens_job * args.steps / (ms * 1e-3)
-
-    # ---- end to end with host buffers: fastmax_b200.host.HostPipeline streams groups of heads
-    # through the GPU (copy-in, forward+backward, copy-out overlapped) ----------------------
-    from fastmax_b200.host import HostPipeline, prefer_gpu_numa_node
-
-    numa_node = prefer_gpu_numa_node(dev)     # pinned buffers below land next to this rank's GPU
-
-    del res
-    host_in = [t.cpu().pin_memory() for t in (q, k, v, go)]
-    host_out = [torch.empty_like(h).pin_memory() for h in host_in]
-    del q, k, v, go
-    torch.cuda.empty_cache()
-    pipe = HostPipeline(bh, N, D, dtype, dev, heads_per_group=args.e2e_group, **kw)
-
-    def e2e_step():
-        pipe.run(*host_in, *host_out)
-
-    e2e_steps = max(1, min(args.steps, 3))
-    e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    e2e_ms = float(tms.item()) / e2e_steps
-    nbytes = sum(h.numel() * h.element_size() for h in host_in)
-
-    if rank == 0:
-        per = {}
-        for name, t in recs:
-            c, s = per.get(name, (0, 0.0))
-            per[name] = (c + 1, s + t)
-        dom = max(per, key=lambda n: per[n][1]) if per else None
-        peaks = load_peaks()
-        ff, fq, fkv = alg_flops_per_token_head(D, p)
-        flops_of = {"fwd": ff, "dq": fq, "dkdv": fkv, "dk": fkv * 2 // 3, "dv": fkv // 3}
-        roof = None
-        if dom is not None:
-            cnt, tot = per[dom]
-            kind = dom.rsplit("_", 1)[-1]
-            # DRAM bytes per token-head of the score kernels (bf16, d = 64), from the ncu capture of the
-            # small case summarised under profiles/: heads are processed one after another, so every
-            # re-read of a head's tiles hits L2 and the traffic grows in proportion to heads x tokens
-            ncu_bytes = {"fm_dense_tc_fwd": 483.2, "fm_dense_tc_dq": 621.3, "fm_dense_tc_dkdv": 723.8}
-            traffic = ncu_bytes[dom] * bh * N if (dom in ncu_bytes and D == 64 and dt == "bf16") else None
-            if kind in flops_of:
-                achieved = flops_of[kind] * bh * N / (tot / cnt * 1e-3) / 1e12
-                roof = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
-                        "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": traffic,
-                        "traffic_source": "ncu dram bytes of a small case scaled by heads x tokens" if traffic else None,
-                        "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "ms_per_launch": tot / cnt,
-                        "alg_flops_per_launch": flops_of[kind] * bh * N}
-            else:
-                nb = 2 * bh * N * D * (2 if dt == "bf16" else 4)
-                achieved = nb / (tot / cnt * 1e-3) / 1e9
-                roof = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
-        total_alg = (ff + fq + fkv) * bh * N * args.steps * (world if args.scaling != "strong" else 1)
-        line = {
-            "metric": "fastmax_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": dt, "data": "synthetic",
-            "config": {"workload": describe(args.workload), "global_batch": B * (world if args.scaling != "strong" else 1),
-                       "batch_heads_per_gpu": bh, "parallelism": f"batch*head sharded x{world}, no collective",
-                       "l2": "inputs (4 x %.2f GB per GPU) larger than the 126 MB L2" % (bh * N * D * (2 if dt == "bf16" else 4) / 1e9)},
-            "clocks": clocks, "gpu_launches": int(launches),
-            "alg_tflops_whole_step": total_alg / world / (ms * 1e-3) / 1e12,
-            "kernels": {n: {"launches": c, "ms_total": round(s, 3), "share": round(s / sum(x[1] for x in per.values()), 4)}
-                        for n, (c, s) in sorted(per.items(), key=lambda kv: -kv[1][1])},
-            "roofline": roof,
-            "e2e": {"value": tokens_job / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
-                    "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "host_numa_node_rank0": numa_node},
-        }
-        if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_sample(args.workload, 2, 1)[0]
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    r = timed_region(hz, step, steps, warmup, flush_l2=flush, sample_clocks=sample_clocks)
+    r.update(in_bytes=in_bytes, flushed=flush, tensors=(q, k, v, go), kw=kw, dtype=dtype)
+    return r
 
 
-def run_seq(args, world, rank, dev, cfg):
-    """Long-context workload: the sequence is split into `world` contiguous shards (one per GPU, all heads
-    on every GPU); per pass the ranks exchange the per-shard moment totals (all-gather) and the
-    normalisation statistics (all-reduce).  Total work is fixed, so this is strong scaling."""
-    import torch
-    import torch.distributed as dist
-
+def seq_leg(hz, args, cfg, steps, warmup, sample_clocks=False):
+    """One long sequence split into `world` contiguous shards (all heads on every GPU); per pass the ranks
+    exchange the per-shard moment totals and the normalisation statistics.  Total work is fixed."""
+    torch = hz.torch
     import fastmax_b200
-    from fastmax_b200 import _cabi
     from fastmax_b200.sharded import fastmax_sequence_parallel
 
     B, H, N, D, dt, mask, p, norm = cfg
     dtype = torch.bfloat16 if dt == "bf16" else torch.float32
-    nl = N // world
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    q, k, v, go = [torch.randn(B * H, nl, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4)]
-    if not norm:   # unnormalised configurations scale q and k by 1/sqrt(D)
+    nl = N // hz.world
+    g = torch.Generator(device=hz.dev).manual_seed(1234 + hz.rank)
+    q, k, v, go = [torch.randn(B * H, nl, D, generator=g, device=hz.dev, dtype=torch.float32).to(dtype) for _ in range(4)]
+    if not norm:
         q, k = q * D ** -0.5, k * D ** -0.5
     mod = fastmax_b200.FASTMultiHeadAttention()
 
     def step():
         qd, kd, vd = [t.detach().requires_grad_(True) for t in (q, k, v)]
-        if world > 1:
+        if hz.world > 1:
             out = fastmax_sequence_parallel(qd, kd, vd, mask=bool(mask), normalize=bool(norm), p=p, chunk=args.chunk, **A)
         else:
             out = mod(qd, kd, vd, None, bool(mask), 0.0, bool(norm), 1.0, A["a0"], A["a1"], A["a2"], A["lim"], p)
         out.backward(go)
         return out
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    r = timed_region(hz, step, steps, warmup, sample_clocks=sample_clocks)
+    ff, fq, fkv = alg_flops_per_token_head(D, p)
+    ms_step = r["ms"] / steps
+    in_kernels = sum(s for _, s in r["per"].values()) / steps
+    r.update(ms_per_step=ms_step, tokens_per_s=B * N / (ms_step * 1e-3), tokens_per_gpu=nl,
+             alg_tflops_per_gpu=(ff + fq + fkv) * B * H * nl / (ms_step * 1e-3) / 1e12,
+             ms_in_library_kernels=in_kernels, ms_outside_library_kernels=max(ms_step - in_kernels, 0.0))
+    del q, k, v, go
+    torch.cuda.empty_cache()
+    return r
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(dev.index)
-    if rank == 0:
-        sampler.start()
-    _cabi.profile(True)
-    n0 = _cabi.launch_count()
+
+def roofline_of(per, cfg, bh, peaks, lib_version):
+    """Roofline record of the kernel with the largest share of the timed region."""
+    B, H, N, D, dt, mask, p, norm = cfg
+    if not per:
+        return None
+    dom = max(per, key=lambda n: per[n][1])
+    cnt, tot = per[dom]
+    ms = tot / cnt
+    ff, fq, fkv = alg_flops_per_token_head(D, p)
+    flops_of = {"fwd": ff, "dq": fq, "dkdv": fkv, "dk": fkv * 2 // 3, "dv": fkv // 3}
+    kind = dom.rsplit("_", 1)[-1]
+    es = 2 if dt == "bf16" else 4
+    if kind in flops_of and (p == 2 or dt != "bf16"):
+        flops = flops_of[kind] * bh * N
+        achieved = flops / (ms * 1e-3) / 1e12
+        if dt == "bf16":
+            peak, src, bound = peaks["bf16_tflops_sustained"], peaks["source"] + " (sustained cuBLAS bf16)", "tensor"
+        else:
+            peak, src, bound = FFMA_TFLOPS_NOMINAL, "nominal FP32 FFMA at the maximum SM clock (no measured figure)", "fp32-ffma"
+        traffic = None
+        if dom in NCU_BYTES_PER_TOKEN_HEAD and D == 64 and dt == "bf16" and lib_version == TRAFFIC_LIB_VERSION:
+            traffic = NCU_BYTES_PER_TOKEN_HEAD[dom] * bh * N
+        return {"bound": bound, "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": traffic,
+                "traffic_source": "ncu dram bytes of a small case scaled by heads x tokens" if traffic else None,
+                "peak_source": src, "ms_per_launch": ms, "alg_flops_per_launch": flops}
+    nb = 2 * bh * N * D * es     # a streaming kernel of the p = 1 path reads two token tensors once
+    achieved = nb / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+            "ms_per_launch": ms, "alg_bytes_per_launch": nb}
+
+
+def run_ours(args):
+    hz = Harness()
+    torch = hz.torch
+    from fastmax_b200 import _cabi
+
+    world, rank, dev = hz.world, hz.rank, hz.dev
+    cfg = cfg_of(args.workload)
+    B, H, N, D, dt, mask, p, norm = cfg
+    if args.workload.startswith("c5"):
+        return run_seq(hz, args, cfg)
+    if args.workload.startswith("decode"):
+        return run_decode(args, world, rank, dev, cfg)
+    if args.workload == "site":
+        return run_site(args, world, rank, dev, cfg)
+    bh_total = B * H
+    strong = args.scaling == "strong"
+    bh = (bh_total // world + (1 if rank < bh_total % world else 0)) if strong else bh_total
+    tokens_job = B * N * (1 if strong else world)
+
+    main = bh_leg(hz, args, cfg, bh, args.steps, args.warmup, sample_clocks=True)
+    ms = main["ms"]
+    value = tokens_job * args.steps / (ms * 1e-3)
+    q, k, v, go = main.pop("tensors")
+    kw, dtype = main["kw"], main["dtype"]
+
+    # ---- end to end with host buffers: fastmax_b200.host.HostPipeline streams groups of heads
+    # through the GPU (copy-in, forward+backward, copy-out overlapped) ----------------------
+    from fastmax_b200.host import HostPipeline, prefer_gpu_numa_node
+
+    numa_node = prefer_gpu_numa_node(dev)     # pinned buffers below land next to this rank's GPU
+    host_in = [t.cpu().pin_memory() for t in (q, k, v, go)]
+    host_out = [torch.empty_like(h).pin_memory() for h in host_in]
+    del q, k, v, go
+    torch.cuda.empty_cache()
+    pipe = HostPipeline(bh, N, D, dtype, dev, heads_per_group=args.e2e_group, **kw)
+    pipe.run(*host_in, *host_out)
+    hz.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
     e0.record()
     for _ in range(args.steps):
-        step()
+        pipe.run(*host_in, *host_out)
     e1.record()
-    barrier()
-    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    launches = _cabi.launch_count() - n0
-    recs = _cabi.profile_records()
-    _cabi.profile(False)
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    ms = float(tms.item())
+    hz.barrier()
+    e2e_ms = hz.max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    nbytes = sum(h.numel() * h.element_size() for h in host_in)
+    del pipe, host_in, host_out
+    torch.cuda.empty_cache()
+
+    # ---- extra legs of the default workload --------------------------------------------------
+    weak = c5 = None
+    if args.workload == "c3" and not args.no_extras:
+        if world > 1 and strong:
+            w = bh_leg(hz, args, cfg, bh_total, min(args.steps, 5), 3, sample_clocks=False)
+            w.pop("tensors")
+            torch.cuda.empty_cache()
+            ws = min(args.steps, 5)
+            weak = {"value": B * N * world * ws / (w["ms"] * 1e-3), "unit": "tokens/s", "ms_per_step": w["ms"] / ws,
+                    "steps": ws, "global_batch": B * world, "batch_heads_per_gpu": bh_total}
+        s = seq_leg(hz, args, WORKLOADS["c5"], 5, 3)
+        c5 = {"workload": describe("c5"), "n_gpus": world, "steps": 5, "warmup": 3, "scaling": "strong",
+              "ms_per_step": s["ms_per_step"], "tokens_per_s": s["tokens_per_s"], "tokens_per_gpu": s["tokens_per_gpu"],
+              "alg_tflops_per_gpu": s["alg_tflops_per_gpu"],
+              "ms_outside_library_kernels": s["ms_outside_library_kernels"],
+              "parallelism": (f"sequence sharded x{world}: all-gather of per-shard moment totals, all-reduce of "
+                              "normalisation statistics") if world > 1 else "one GPU, no exchange",
+              "kernels": _kernel_table(s["per"])}
+
     if rank == 0:
-        per = {}
-        for name, t in recs:
-            c, s = per.get(name, (0, 0.0))
-            per[name] = (c + 1, s + t)
+        peaks = load_peaks()
         ff, fq, fkv = alg_flops_per_token_head(D, p)
-        tot = sum(x[1] for x in per.values())
+        lib_version = int(_cabi.lib().fastmax_b200_version())
         line = {
-            "metric": "fastmax_fwd_bwd_tokens_per_s", "value": B * N * args.steps / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "metric": "fastmax_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": describe(args.workload), "global_batch": B * (1 if strong else world),
+                       "batch_heads_per_gpu": bh,
+                       "parallelism": f"batch*head units {'split' if strong else 'replicated'} x{world}, no collective",
+                       "l2": l2_note(main["in_bytes"], main["flushed"])},
+            "clocks": main["clocks"], "gpu_launches": main["launches"],
+            "alg_tflops_per_gpu": (ff + fq + fkv) * bh * N * args.steps / (ms * 1e-3) / 1e12,
+            "kernels": _kernel_table(main["per"]),
+            "roofline": roofline_of(main["per"], cfg, bh, peaks, lib_version),
+            "e2e": {"value": tokens_job / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
+                    "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": args.steps,
+                    "host_numa_node_rank0": numa_node},
+        }
+        if weak:
+            line["weak"] = weak
+        if c5:
+            line["c5"] = c5
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_arm(args.workload, 2, 1, budget_s=30.0)[0]
+        print(json.dumps(line), flush=True)
+    hz.close()
+
+
+def run_seq(hz, args, cfg):
+    """`--workload c5` / `c5u`: the long-context configurations as the whole line."""
+    B, H, N, D, dt, mask, p, norm = cfg
+    world = hz.world
+    s = seq_leg(hz, args, cfg, args.steps, args.warmup, sample_clocks=True)
+    if hz.rank == 0:
+        line = {
+            "metric": "fastmax_fwd_bwd_tokens_per_s", "value": s["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": s["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dt, "data": "synthetic",
-            "config": {"workload": describe(args.workload), "tokens_per_gpu": nl,
+            "config": {"workload": describe(args.workload), "tokens_per_gpu": s["tokens_per_gpu"],
                        "parallelism": f"sequence sharded x{world}; "
                                       + ("all-gather" if mask else "all-reduce") + " of per-shard moment totals, "
                                       "all-reduce of normalisation statistics",
                        "l2": "inputs larger than the 126 MB L2"},
-            "clocks": clocks, "gpu_launches": int(launches),
-            "alg_tflops_per_gpu": (ff + fq + fkv) * B * H * nl * args.steps / (ms * 1e-3) / 1e12,
-            "kernels": {n: {"launches": c, "ms_total": round(s, 3), "share": round(s / tot, 4)}
-                        for n, (c, s) in sorted(per.items(), key=lambda kv: -kv[1][1])},
+            "clocks": s["clocks"], "gpu_launches": s["launches"],
+            "alg_tflops_per_gpu": s["alg_tflops_per_gpu"],
+            "ms_outside_library_kernels": s["ms_outside_library_kernels"],
+            "kernels": _kernel_table(s["per"]),
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    hz.close()
 
 
 def main():
@@ -591,14 +710,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--profile-case", default=None, choices=sorted(PROFILE_CASES),
+                    help="run a reduced shape meant for profiler captures instead of a workload")
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the weak-scaling and long-context legs of c3")
     ap.add_argument("--family", default="auto", choices=["auto", "dense_ffma", "dense_tc", "moments", "moments_ffma"],
                     help="kernel family to force (default: the library's own choice)")
     ap.add_argument("--chunk", type=int, default=0, help="moment family: tokens per chunk (0 = default)")
     ap.add_argument("--e2e-group", type=int, default=32,
                     help="batch*head units per group of the host-buffer pipeline of the e2e leg")
     args = ap.parse_args()
+    if args.profile_case:
+        args.workload, args.no_cpu, args.no_extras = args.profile_case, True, True
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":

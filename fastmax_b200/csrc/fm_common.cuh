@@ -99,7 +99,7 @@ struct FwdOut {
 int launch_gprep(const Ctx& c, const void* grad_out, const void* out, const float* den, void* gs,
                  float* dvec);
 
-// Tensor-core score-form family (bf16, head dimension 64, bh == bhkv).
+// Tensor-core score-form family (bf16, head dimension 64 or 128, bh a multiple of bhkv).
 bool dense_tc_supports(const fastmax_problem& p);
 struct ChunkAdd;
 int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,

@@ -138,3 +138,24 @@ def test_moment_state_recurrence_equals_dense_rows(p, normalize):
         want = fastmax_dense(q[None, :, t:t + 1], k[None, :, :t + 1], v[None, :, :t + 1], mask=1,
                              normalize=normalize, p=p, a0=0.7, a1=1.3, a2=0.4, lim=1.5)[0]
         assert rel_err(got, want) < 1e-12
+
+
+def test_restatement_matches_the_compiled_reference_function():
+    """Where oracle/_ref has been built from a reference tree (oracle/make_ref.py), the oracle is held
+    against the reference's own function directly, on fresh seeded inputs."""
+    from oracle.make_ref import load
+    ref = load()
+    if ref is None:
+        pytest.skip("oracle/_ref has not been built")
+    g = torch.Generator().manual_seed(41)
+    for mask in (0, 1):
+        for p in (1, 2):
+            for norm in (0, 1):
+                q, k, v, go = [torch.randn(2, 2, 37, 8, generator=g, dtype=torch.float64) * 0.5 for _ in range(4)]
+                kw = dict(mask=mask, normalize=norm, a0=1.0, a1=1.2, a2=0.4, lim=1.1, p=p)
+                qr, kr, vr = [t.clone().requires_grad_(True) for t in (q, k, v)]
+                out = ref(qr, kr, vr, **kw)
+                out.backward(go)
+                got = fastmax_fwd_bwd(q, k, v, go, **kw)
+                for a, b, name in zip(got, (out.detach(), qr.grad, kr.grad, vr.grad), ("out", "dq", "dk", "dv")):
+                    assert rel_err(a, b) < 1e-11, (mask, p, norm, name)
