@@ -28,6 +28,7 @@ EXPORTS = (
     "fastmax_b200_shard_forward_workspace_bytes", "fastmax_b200_shard_backward_workspace_bytes",
     "fastmax_b200_shard_rowmax", "fastmax_b200_shard_kv_state", "fastmax_b200_shard_forward",
     "fastmax_b200_shard_qg_state", "fastmax_b200_shard_backward", "fastmax_b200_shard_norm_fixup",
+    "fastmax_b200_shard_dq_far", "fastmax_b200_shard_sum_totals",
     "fastmax_b200_static_scratch_bytes", "fastmax_b200_backward_static",
     "fastmax_b200_qkv_split_rope", "fastmax_b200_qkv_merge_rope_grad", "fastmax_b200_swap_middle_axes",
     "fastmax_b200_scale_by_noise", "fastmax_b200_scale_packed_by_noise",
@@ -77,7 +78,9 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_shard_kv_state.argtypes = [pp, vp, vp, vp, vp, vp]
         L.fastmax_b200_shard_forward.argtypes = [pp] + [vp] * 9 + [sz, vp]
         L.fastmax_b200_shard_qg_state.argtypes = [pp] + [vp] * 8 + [sz, vp]
-        L.fastmax_b200_shard_backward.argtypes = [pp] + [vp] * 16 + [sz, vp]
+        L.fastmax_b200_shard_backward.argtypes = [pp] + [vp] * 15 + [i32, vp, sz, vp]
+        L.fastmax_b200_shard_dq_far.argtypes = [pp] + [vp] * 7 + [sz, vp]
+        L.fastmax_b200_shard_sum_totals.argtypes = [vp, i32, i32, i32, sz, vp, vp]
         L.fastmax_b200_shard_norm_fixup.argtypes = [pp, vp, vp, vp, vp, i32, vp, vp, vp]
         L.fastmax_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), vp]
         L.fastmax_b200_device_status_reset.argtypes = [vp]

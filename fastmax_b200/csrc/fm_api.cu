@@ -245,8 +245,18 @@ int fastmax_b200_profile_get(int i, char* name, int name_len, float* ms) {
   return FASTMAX_OK;
 }
 
+// Unmasked problems on the moment family leave the total key/value state behind the statistic
+// words, so that the backward pass does not have to rebuild it from k and v.
+static size_t stats_words_bytes(const fastmax_problem& p) {
+  return align_up(sizeof(stat_t) * (size_t)(p.bh + p.bhkv), 256);
+}
+static bool keeps_total(const fastmax_problem& p, int impl) { return impl == FASTMAX_IMPL_MOMENTS && !p.mask; }
+
 size_t fastmax_b200_stats_bytes(const fastmax_problem* p) {
   if (!p || p->bh < 0 || p->bhkv < 0) return 0;
+  int impl;
+  if (validate(p) == FASTMAX_OK && p->bh > 0 && pick_impl(*p, false, &impl) == FASTMAX_OK && keeps_total(*p, impl))
+    return stats_words_bytes(*p) + moment_total_bytes(*p);
   return sizeof(stat_t) * (size_t)(p->bh + p->bhkv);
 }
 
@@ -286,7 +296,8 @@ static int forward_impl(const fastmax_problem* prob, const void* q, const void* 
     if (!workspace || workspace_bytes < need)
       return fail(FASTMAX_E_WORKSPACE, "forward workspace too small: need %zu bytes, got %zu", need,
                   workspace_bytes);
-    return moments_forward(c, q, k, v, (const stat_t*)stats, o, workspace);
+    float* keep = (stats && keeps_total(p, impl)) ? (float*)((char*)stats + stats_words_bytes(p)) : nullptr;
+    return moments_forward(c, q, k, v, (const stat_t*)stats, o, workspace, keep);
   }
   if (impl == FASTMAX_IMPL_DENSE_TC)
     return dense_tc_forward(c, q, k, v, (const stat_t*)stats, o.out, o.den);
@@ -333,7 +344,9 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
   Ctx c{p, (cudaStream_t)stream};
   if (impl == FASTMAX_IMPL_MOMENTS)
     return moments_backward(c, q, k, v, out, den, (const stat_t*)stats, grad_out, grad_q, grad_k, grad_v,
-                            workspace);
+                            workspace,
+                            (stats && keeps_total(p, impl)) ? (const float*)((const char*)stats + stats_words_bytes(p))
+                                                            : nullptr);
   float* dots = (float*)((char*)workspace + w.dots_off);
   float* delta = (float*)((char*)workspace + w.delta_off);
   if (p.normalize)
@@ -476,7 +489,7 @@ int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, cons
                                 const void* stats, const void* grad_out, const float* delta,
                                 const float* kv_states, float* qg_states, const float* r_base,
                                 float* dots, void* grad_q, void* grad_k, void* grad_v,
-                                void* workspace, size_t workspace_bytes, void* stream) {
+                                int32_t dq_far_done, void* workspace, size_t workspace_bytes, void* stream) {
   int rc = validate_shard(prob);
   if (rc) return rc;
   const fastmax_problem& p = *prob;
@@ -496,7 +509,9 @@ int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, cons
   FM_CUDA_TRY(cudaMemsetAsync(dots, 0, sizeof(float) * (size_t)(p.bh + p.bhkv), c.stream));
   float* dvec = (float*)(ws + w.dvec);
   void* gs = ws + w.gs;
-  if (dense_tc_supports(p) && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
+  // gs and dvec are still in the workspace when shard_dq_far ran on it
+  if (!(dq_far_done && p.mask) && dense_tc_supports(p) && (rc = launch_gprep(c, grad_out, out, den, gs, dvec)))
+    return rc;
   if (!p.mask)   // kv_states holds the key/value total of all shards, r_base the query/gradient total
     return moments_backward_total(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dvec, gs, kv_states,
                                   r_base, (float*)(ws + w.gq), (float*)(ws + w.gk), (float*)(ws + w.gv),
@@ -504,7 +519,33 @@ int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, cons
   return moments_backward_finish(c, q, k, v, den, (const stat_t*)stats, grad_out, delta, dvec, gs,
                                  kv_states, qg_states, r_base, (float*)(ws + w.gq), (float*)(ws + w.gk),
                                  (float*)(ws + w.gv), ws + w.s16, p.normalize ? dots : nullptr, grad_q, grad_k,
-                                 grad_v);
+                                 grad_v, dq_far_done != 0);
+}
+
+int fastmax_b200_shard_dq_far(const fastmax_problem* prob, const void* q, const float* den, const void* stats,
+                              const void* grad_out, const float* delta, const float* kv_states, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  int rc = validate_shard(prob);
+  if (rc) return rc;
+  const fastmax_problem& p = *prob;
+  if (!p.mask) return fail(FASTMAX_E_ARG, "shard_dq_far applies to causal shards only");
+  if (!q || !den || !grad_out || !delta || !kv_states) return fail(FASTMAX_E_ARG, "NULL tensor pointer");
+  if (p.normalize && !stats) return fail(FASTMAX_E_ARG, "normalize needs the reduced stats buffer");
+  const ShardBwdWs w = shard_bwd_layout(p);
+  if (!workspace || workspace_bytes < w.bytes)
+    return fail(FASTMAX_E_WORKSPACE, "shard backward workspace too small: need %zu bytes, got %zu", w.bytes,
+                workspace_bytes);
+  Ctx c{p, (cudaStream_t)stream};
+  char* ws = (char*)workspace;
+  return moments_backward_dq_far(c, q, den, (const stat_t*)stats, grad_out, delta, (const float*)(ws + w.dvec),
+                                 ws + w.gs, kv_states, (float*)(ws + w.gq), ws + w.s16);
+}
+
+int fastmax_b200_shard_sum_totals(const float* gathered, int32_t world, int32_t rank, int32_t reverse,
+                                  size_t floats_per_shard, float* out, void* stream) {
+  if (!gathered || !out || world <= 0 || rank < 0 || rank >= world)
+    return fail(FASTMAX_E_ARG, "bad arguments to shard_sum_totals");
+  return launch_sum_totals(gathered, world, rank, reverse, floats_per_shard, out, (cudaStream_t)stream);
 }
 
 int fastmax_b200_shard_norm_fixup(const fastmax_problem* prob, const void* q, const void* k,

@@ -218,23 +218,24 @@ __global__ void __launch_bounds__(256) gprep_kernel(const __nv_bfloat16* __restr
   for (int t = 0; t < STEPS; ++t) {
     const size_t row = row0 + (size_t)t * RPW;
     const uint32_t gw[4] = {g[t].x, g[t].y, g[t].z, g[t].w}, ow[4] = {o[t].x, o[t].y, o[t].z, o[t].w};
-    float gf[8], s = 0.f;
+    // dvec is formed from the ROUNDED gs values: the gradient kernels subtract it from gs . v, and with
+    // both built from the same bf16 numbers the difference is gs . (v - out) exactly, so the rounding of
+    // gs acts like a 2^-9 relative change of grad_out instead of an absolute error that survives the
+    // cancellation (early causal rows, where out is close to the few values seen, showed it)
+    const float inv = (row < rows) ? 1.0f / __ldg(den + row) : 0.f;
+    uint32_t gr[4];
+    float s = 0.f;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      gf[2 * e] = __uint_as_float(gw[e] << 16);
-      gf[2 * e + 1] = __uint_as_float(gw[e] & 0xFFFF0000u);
-      s = fmaf(gf[2 * e], __uint_as_float(ow[e] << 16), s);
-      s = fmaf(gf[2 * e + 1], __uint_as_float(ow[e] & 0xFFFF0000u), s);
+      gr[e] = pack_bf16x2(__uint_as_float(gw[e] << 16) * inv, __uint_as_float(gw[e] & 0xFFFF0000u) * inv);
+      s = fmaf(__uint_as_float(gr[e] << 16), __uint_as_float(ow[e] << 16), s);
+      s = fmaf(__uint_as_float(gr[e] & 0xFFFF0000u), __uint_as_float(ow[e] & 0xFFFF0000u), s);
     }
 #pragma unroll
     for (int m = LPR / 2; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
     if (row < rows) {
-      const float inv = 1.0f / __ldg(den + row);
-      uint4 w;
-      w.x = pack_bf16x2(gf[0] * inv, gf[1] * inv); w.y = pack_bf16x2(gf[2] * inv, gf[3] * inv);
-      w.z = pack_bf16x2(gf[4] * inv, gf[5] * inv); w.w = pack_bf16x2(gf[6] * inv, gf[7] * inv);
-      ((uint4*)(gs + row * D))[part] = w;
-      if (part == 0) dvec[row] = s * inv;
+      ((uint4*)(gs + row * D))[part] = make_uint4(gr[0], gr[1], gr[2], gr[3]);
+      if (part == 0) dvec[row] = s;
     }
   }
 }
@@ -309,6 +310,36 @@ int launch_norm_fixup(const Ctx& c, const void* q, const void* k, const stat_t* 
               (norm_fixup_kernel<__nv_bfloat16><<<heads, 128, 0, c.stream>>>(
                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, stats, dots, (__nv_bfloat16*)gq,
                   (__nv_bfloat16*)gk, p.bh, p.nq, p.nk, p.d, row_offset)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Sequence sharding: after an all-gather of the per-shard moment totals into (world, floats), a shard
+// needs the sum over the shards before it (forward, grad_q) or after it (grad_k, grad_v).  HBM-bound:
+// reads (number of shards summed) x floats, writes floats; 16-byte accesses, grid-stride.
+__global__ void __launch_bounds__(256) sum_totals_kernel(const float4* __restrict__ gathered, int first, int last,
+                                                         size_t quads, float4* __restrict__ out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = first; r < last; ++r) {
+      const float4 v = __ldg(gathered + (size_t)r * quads + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    out[i] = acc;
+  }
+}
+
+int launch_sum_totals(const float* gathered, int world, int rank, int reverse, size_t floats, float* out,
+                      cudaStream_t stream) {
+  const int first = reverse ? rank + 1 : 0, last = reverse ? world : rank;
+  if (floats == 0) return FASTMAX_OK;
+  if (floats % 4 != 0 || (((uintptr_t)gathered | (uintptr_t)out) & 15) != 0)
+    return fail(FASTMAX_E_ARG, "totals must be 16-byte aligned and a multiple of 4 floats long");
+  const size_t quads = floats / 4;
+  const unsigned blocks = (unsigned)((quads + 255) / 256 < 148 * 8 ? (quads + 255) / 256 : 148 * 8);
+  FM_LAUNCH("fm_sum_totals", stream,
+            (sum_totals_kernel<<<blocks, 256, 0, stream>>>((const float4*)gathered, first, last, quads, (float4*)out)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }

@@ -204,7 +204,7 @@ size_t state16_bytes(const fastmax_problem& p, int n);   // bf16 operand copies 
 MomFwdWs moments_fwd_layout(const fastmax_problem& p);
 MomBwdWs moments_bwd_layout(const fastmax_problem& p);
 int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
-                    const FwdOut& o, void* workspace);
+                    const FwdOut& o, void* workspace, float* total_keep = nullptr);
 int moments_forward_finish(const Ctx& c, const void* q, const void* k, const void* v,
                            const stat_t* stats, float* kv_states, const float* s_base,
                            float* o_add, float* den_add, void* s16, const FwdOut& o);
@@ -214,13 +214,19 @@ int moments_build_states(const Ctx& c, int n, const void* y, const void* z, cons
                          const float* delta, int ext, const void* gs, const float* dvec, float* states);
 int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* out,
                      const float* den, const stat_t* stats, const void* grad_out, void* grad_q,
-                     void* grad_k, void* grad_v, void* workspace);
+                     void* grad_k, void* grad_v, void* workspace, const float* kv_total_kept = nullptr);
 int moments_backward_finish(const Ctx& c, const void* q, const void* k, const void* v,
                             const float* den, const stat_t* stats, const void* grad_out,
                             const float* delta, const float* dvec, const void* gs,
                             const float* s_states, float* r_states, const float* r_base,
                             float* gq_add, float* gk_add, float* gv_add, void* s16, float* dots,
-                            void* grad_q, void* grad_k, void* grad_v);
+                            void* grad_q, void* grad_k, void* grad_v, bool dq_far_done = false);
+int moments_backward_dq_far(const Ctx& c, const void* q, const float* den, const stat_t* stats,
+                            const void* grad_out, const float* delta, const float* dvec, const void* gs,
+                            const float* s_states, float* gq_add, void* s16);
+// out[i] = sum of gathered[r][i] over r < rank (r > rank when reverse); gathered is (world, floats)
+int launch_sum_totals(const float* gathered, int world, int rank, int reverse, size_t floats, float* out,
+                      cudaStream_t stream);
 // unmasked passes from given total states (this device's, or the sum over all sequence shards)
 int moments_forward_total(const Ctx& c, const void* q, const stat_t* stats, const float* total, float* o_add,
                           float* den_add, void* s16, const FwdOut& o);

@@ -348,8 +348,12 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
               }
               pv[h] = (col > limcol || col < lowcol) ? 0.f : v;
             }
-            if (MODE == OP_A) rs2[e & 3] = add2(rs2[e & 3], pack2(pv[0], pv[1]));
             pk[e] = pack_bf16(pv[0], pv[1]);
+            // Tiles on the causal diagonal (and ragged last tiles) hold most of what an early row sees, so
+            // their share of the row sum is taken from the ROUNDED values the product will use: numerator
+            // and denominator then carry the same rounding, and a row with one key returns its value exactly.
+            if (MODE == OP_A)
+              rs2[e & 3] = add2(rs2[e & 3], pack2(__uint_as_float(pk[e] << 16), __uint_as_float(pk[e] & 0xFFFF0000u)));
           }
         }
         // P(t-1) must have been consumed by its MMA before it is overwritten

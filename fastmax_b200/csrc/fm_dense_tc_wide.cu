@@ -86,7 +86,12 @@ struct WCfg {
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_wtc_status, 0, code); }
 
-template <int MODE, bool GQ>   // GQ: grouped k/v heads (bh > bhkv); the plain case compiles without the head walk
+// GQ: grouped k/v heads (bh > bhkv); the plain case compiles without the head walk.
+// SQ (MODE_DKDV without grouped heads, a2 > 0): the polynomial in completed-square form,
+//   f(s) = A2 ((s + b)^2 + c),  f'(s) = 2 A2 (s + b),  b = A1 / (2 A2),  c = A0 / A2 - b^2,
+// so that a pair of scores costs t = s + b, P' = t t + c, E' = t (w - dvec): four packed operations
+// instead of five.  The factors A2 (grad_v) and 2 A2 (grad_k) multiply the accumulators in the epilogue.
+template <int MODE, bool GQ, bool SQ = false>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                      const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
@@ -265,6 +270,8 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     const uint64_t A0v = pack2(A0, A0);
     using coef_t = typename std::conditional<GQ, uint64_t, const uint64_t>::type;   // fixed unless heads are grouped
     coef_t A1v = pack2(A1, A1), A2v = pack2(A2, A2), A2d = pack2(2.f * A2, 2.f * A2);
+    const float sq_b = SQ ? A1 / (2.f * A2) : 0.f, sq_c = SQ ? A0 / A2 - sq_b * sq_b : 0.f;
+    const uint64_t Bv = pack2(sq_b, sq_b), Cv = pack2(sq_c, sq_c);
     int limcol = a.ncols - 1, lowcol = 0;   // columns kept for this row: lowcol <= col <= limcol
     if (a.mask) {
       if (rev) lowcol = row - a.off;
@@ -360,8 +367,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
               unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
               v0 = (col > limcol || col < lowcol) ? 0.f : v0;
               v1 = (col + 1 > limcol || col + 1 < lowcol) ? 0.f : v1;
-              rs2[e & 3] = add2(rs2[e & 3], pack2(v0, v1));
               pe[e] = pack_bf16(v0, v1);
+              // Tiles on the causal diagonal (and ragged last tiles) hold most of what an early row sees, so
+              // their share of the row sum is taken from the ROUNDED values the product will use: numerator
+              // and denominator then carry the same rounding, and a row with one key returns its value exactly.
+              rs2[e & 3] = add2(rs2[e & 3], pack2(__uint_as_float(pe[e] << 16), __uint_as_float(pe[e] & 0xFFFF0000u)));
             }
           }
         } else if (!need_mask) {
@@ -370,8 +380,14 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             const uint64_t s2 = pack2u(sv[2 * e], sv[2 * e + 1]);
             if (rev && (e & 1) == 0) nd2 = lds_v2(vec_s + (e >> 1) * 16);   // four column values per load
             const uint64_t ndl = rev ? ((e & 1) ? nd2.y : nd2.x) : ndl_row;
-            pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
-            if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+            if constexpr (SQ) {
+              const uint64_t t2 = add2(s2, Bv);
+              pe[e] = pack_bf16_2(mul2(t2, add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
+              pp[e] = pack_bf16_2(fma2(t2, t2, Cv));
+            } else {
+              pe[e] = pack_bf16_2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)));
+              if (FUSED) pp[e] = pack_bf16_2(fma2(fma2(A2v, s2, A1v), s2, A0v));
+            }
           }
         } else {
 #pragma unroll
@@ -382,10 +398,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             const int col = c0 + 2 * e;
             const bool z0 = col > limcol || col < lowcol, z1 = col + 1 > limcol || col + 1 < lowcol;
             float v0, v1;
-            unpack2(mul2(fma2(A2d, s2, A1v), add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
+            const uint64_t t2 = SQ ? add2(s2, Bv) : fma2(A2d, s2, A1v);
+            unpack2(mul2(t2, add2(pack2u(wv[2 * e], wv[2 * e + 1]), ndl)), v0, v1);
             pe[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
             if (FUSED) {
-              unpack2(fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
+              unpack2(SQ ? fma2(t2, t2, Cv) : fma2(fma2(A2v, s2, A1v), s2, A0v), v0, v1);
               pp[e] = pack_bf16(z0 ? 0.f : v0, z1 ? 0.f : v1);
             }
           }
@@ -428,10 +445,11 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const int cc = (part4 & 1) * 32;
       const bool dots_here = !FWD && !second && a.dots != nullptr;
       const float* add = second ? a.o2_add : a.o_add;
+      const float pre = SQ ? (second ? A2 : 2.f * A2) : 1.f;   // completed square: the factor left out of E' and P'
       const float part = store_row<32>(tl + (second ? T_O2 : T_O) + cc, row_ok,
                                        (__nv_bfloat16*)(second ? a.o2 : a.o) + grow * D + cc,
                                        add ? add + grow * D + cc : nullptr,
-                                       dots_here ? (const __nv_bfloat16*)a.x + grow * D + cc : nullptr, scale);
+                                       dots_here ? (const __nv_bfloat16*)a.x + grow * D + cc : nullptr, scale, pre);
       if (FWD && part4 == 0 && row_ok) a.den_out[grow] = rowsum;
       if (dots_here) {
         float sum = part;
@@ -469,7 +487,13 @@ int launch_wide(const Ctx& c, const char* name, const void* x, const void* u, co
   a.x = x;
   a.ntr = (nrows + BM - 1) / BM;
   dim3 grid((unsigned)((size_t)heads * a.ntr));
-  if (kv_ratio > 1) {
+  if (MODE == MODE_DKDV && kv_ratio == 1 && a.a2 > 0.f) {
+    FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE, false, MODE == MODE_DKDV>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, WCfg<MODE>::SMEM));
+    FM_LAUNCH(name, c.stream,
+              (dense_tc_wide_kernel<MODE, false, MODE == MODE_DKDV><<<grid, kThreads, WCfg<MODE>::SMEM, c.stream>>>(
+                  tx, tu, ty, tz, a, kv_ratio)));
+  } else if (kv_ratio > 1) {
     FM_CUDA_TRY(cudaFuncSetAttribute(dense_tc_wide_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      WCfg<MODE>::SMEM));
     FM_LAUNCH(name, c.stream,

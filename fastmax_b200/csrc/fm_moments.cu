@@ -163,14 +163,15 @@ int moments_forward_finish(const Ctx& c, const void* q, const void* k, const voi
   return dense_ffma_forward(c, q, k, v, stats, o, ca);
 }
 
+// total_keep (unmasked only, may be null): where the total key/value state is left for the backward pass
 int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
-                    const FwdOut& o, void* workspace) {
+                    const FwdOut& o, void* workspace, float* total_keep) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   const MomFwdWs w = moments_fwd_layout(p);
   char* ws = (char*)workspace;
   float* states = (float*)(ws + w.states);
-  float* total = (float*)(ws + w.total);
+  float* total = (!p.mask && total_keep) ? total_keep : (float*)(ws + w.total);
   float* o_add = (float*)(ws + w.o_add);
   float* den_add = (float*)(ws + w.den_add);
   int rc;
@@ -199,6 +200,16 @@ int moments_forward_total(const Ctx& c, const void* q, const stat_t* stats, cons
 }
 
 // ---- backward ----------------------------------------------------------------------
+// The part of grad_q that reads the key/value prefixes (everything before a token's own chunk).  It
+// depends on nothing from later shards, so a sequence shard issues it while the query/gradient
+// totals are being exchanged.
+int moments_backward_dq_far(const Ctx& c, const void* q, const float* den, const stat_t* stats,
+                            const void* grad_out, const float* delta, const float* dvec, const void* gs,
+                            const float* s_states, float* gq_add, void* s16) {
+  return read_states(c, 1, c.p.nq, 1, q, grad_out, den, delta, 1, gs, dvec, s_states, s16, stats, nullptr,
+                     nullptr, gq_add);
+}
+
 // s_states: exclusive prefixes of the (k, v) chunk states (as left by the forward finish);
 // r_states: raw chunk states of (q, grad_out/den | -delta/den); r_base: sum of the totals of
 // all later shards or null.  Writes the three gradients without the normalisation row fix.
@@ -207,14 +218,14 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
                             const float* delta, const float* dvec, const void* gs,
                             const float* s_states, float* r_states, const float* r_base,
                             float* gq_add, float* gk_add, float* gv_add, void* s16, float* dots,
-                            void* grad_q, void* grad_k, void* grad_v) {
+                            void* grad_q, void* grad_k, void* grad_v, bool dq_far_done) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   const int nchunk = (p.nq + L - 1) / L;
   int rc;
   // grad_q reads the key/value prefixes with u = [grad_out/den | -delta/den]
-  if ((rc = read_states(c, 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec, s_states, s16, stats, nullptr,
-                        nullptr, gq_add)))
+  if (!dq_far_done &&
+      (rc = moments_backward_dq_far(c, q, den, stats, grad_out, delta, dvec, gs, s_states, gq_add, s16)))
     return rc;
   // grad_k and grad_v read the suffix sums of the query/gradient states
   if ((rc = moments_prefix(c, p.bh, nchunk, r_states, r_base, nullptr, 1, 1))) return rc;
@@ -231,9 +242,11 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
   return dense_ffma_backward(c, q, k, v, den, stats, grad_out, delta, dots, grad_q, grad_k, grad_v, ca);
 }
 
+// kv_total_kept (unmasked only, may be null): the total key/value state the forward left behind; without
+// it the state is rebuilt from k and v
 int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* out,
                      const float* den, const stat_t* stats, const void* grad_out, void* grad_q,
-                     void* grad_k, void* grad_v, void* workspace) {
+                     void* grad_k, void* grad_v, void* workspace, const float* kv_total_kept) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   const MomBwdWs w = moments_bwd_layout(p);
@@ -251,8 +264,11 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
   int rc;
   if (p.normalize)
     FM_CUDA_TRY(cudaMemsetAsync(dots, 0, sizeof(float) * (size_t)(p.bh + p.bhkv), c.stream));
-  if ((rc = launch_delta(c, grad_out, out, delta))) return rc;
   const bool tc = dense_tc_supports(p);
+  // the plain row dots feed the CUDA-core kernels only; when every stage runs on tensor cores they
+  // all read gs / dvec and the pass over grad_out and out is skipped
+  const bool all_tc = tc && first_tc_supports(p) && (p.p == 1 || moments_tc_supports(p));
+  if (!all_tc && (rc = launch_delta(c, grad_out, out, delta))) return rc;
   if (tc && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
   const int nck = (p.nk + L - 1) / L, ncq = (p.nq + L - 1) / L;
   if (p.mask) {
@@ -279,9 +295,12 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
   } else {
     // unmasked: totals only, no score-form part.  The two totals share one buffer, so grad_q is
     // read out before the query/gradient total replaces the key/value total.
-    if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
-    if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, total, 0, 0))) return rc;
-    if ((rc = moments_backward_total(c, q, k, v, den, stats, grad_out, delta, dvec, gs, total, nullptr, gq_add,
+    if (!kv_total_kept) {
+      if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
+      if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, total, 0, 0))) return rc;
+    }
+    if ((rc = moments_backward_total(c, q, k, v, den, stats, grad_out, delta, dvec, gs,
+                                     kv_total_kept ? kv_total_kept : total, nullptr, gq_add,
                                      gk_add, gv_add, s16, dots, grad_q, nullptr, nullptr)))
       return rc;
     if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;

@@ -408,10 +408,12 @@ __device__ __forceinline__ ulonglong2 lds_v2(uint32_t saddr) {
 }
 
 // One thread's accumulator row segment (NC fp32 columns from TMEM column tcol) -> bf16 global
-// row, with the optional fp32 addend; returns the dot product with the x row when wanted.
+// row: (accumulator * pre + optional fp32 addend) * scale; returns the dot product of what was
+// stored (before rounding) with the x row when wanted.
 template <int NC>
 __device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfloat16* dst,
-                                           const float* add, const __nv_bfloat16* xr, float scale) {
+                                           const float* add, const __nv_bfloat16* xr, float scale,
+                                           float pre = 1.f) {
   float part = 0.f;
 #pragma unroll
   for (int c0 = 0; c0 < NC; c0 += 32) {
@@ -423,7 +425,7 @@ __device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfl
       for (int v8 = 0; v8 < 4; ++v8) {
         float f[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[v8 * 8 + e]);
+        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[v8 * 8 + e]) * pre;   // pre scales the accumulator only
         if (add) {
           const float4 a0 = __ldg((const float4*)(add + c0) + 2 * v8);
           const float4 a1 = __ldg((const float4*)(add + c0) + 2 * v8 + 1);

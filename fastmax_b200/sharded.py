@@ -33,6 +33,55 @@ from . import _cabi
 __all__ = ["CudaShardBackend", "SequenceShardedFastmax", "fastmax_sequence_parallel", "exclusive_rank_sum"]
 
 
+class _Exchange:
+    """Exchange of per-shard totals on CUDA without staging copies.
+
+    One persistent ``(world, floats)`` buffer per (device, kind): the state kernels write this
+    rank's total straight into its row, an in-place ``all_gather_into_tensor`` issued on a side
+    stream fills the other rows while the caller's stream keeps computing, and one library
+    kernel (``fastmax_b200_shard_sum_totals``) adds up the rows of the earlier (or later) ranks.
+    """
+
+    _buffers = {}
+    _streams = {}
+
+    @classmethod
+    def buffer(cls, kind, device, world, floats):
+        key = (kind, device, world, floats)
+        buf = cls._buffers.get(key)
+        if buf is None:
+            buf = torch.empty(world, floats, dtype=torch.float32, device=device)
+            cls._buffers[key] = buf
+            cls._buffers[key + ("sum",)] = torch.empty(floats, dtype=torch.float32, device=device)
+        return buf
+
+    @classmethod
+    def start(cls, gathered, rank, group):
+        """Begin the all-gather of row ``rank`` of ``gathered`` into all rows; returns a handle."""
+        dev = gathered.device
+        side = cls._streams.get(dev)
+        if side is None:
+            side = cls._streams[dev] = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))        # the row has been written
+        with torch.cuda.stream(side):
+            return dist.all_gather_into_tensor(gathered, gathered[rank], group=group, async_op=True)
+
+    @classmethod
+    def finish(cls, kind, work, gathered, rank, reverse):
+        """Wait (on the current stream) for the gather and return the sum over the ranks before
+        ``rank`` (after it when ``reverse``), or None when there are none."""
+        work.wait()
+        world, floats = gathered.shape
+        if (rank == world - 1) if reverse else (rank == 0):
+            return None
+        out = cls._buffers[(kind, gathered.device, world, floats, "sum")]
+        with torch.cuda.device(gathered.device):
+            _cabi._check(_cabi.lib().fastmax_b200_shard_sum_totals(
+                gathered.data_ptr(), world, rank, int(reverse), floats, out.data_ptr(), _cabi._stream(gathered)),
+                "shard_sum_totals")
+        return out
+
+
 def exclusive_rank_sum(total: torch.Tensor, group=None, reverse: bool = False):
     """Sum of ``total`` over the ranks before this one (after it when ``reverse``); None if there are none."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -70,10 +119,14 @@ class CudaShardBackend:
                                                  stats.data_ptr(), _cabi._stream(q)), "shard_rowmax")
         return stats
 
-    def kv_state(self, k, v):
+    def total_floats(self, k):
+        return _cabi.lib().fastmax_b200_moment_total_bytes(self._prob(k, k)) // 4
+
+    def kv_state(self, k, v, total_out=None):
         L, prob = _cabi.lib(), self._prob(k, k)
         states = torch.empty(L.fastmax_b200_moment_state_bytes(prob) // 4, dtype=torch.float32, device=k.device)
-        total = torch.empty(L.fastmax_b200_moment_total_bytes(prob) // 4, dtype=torch.float32, device=k.device)
+        total = total_out if total_out is not None else \
+            torch.empty(L.fastmax_b200_moment_total_bytes(prob) // 4, dtype=torch.float32, device=k.device)
         _cabi._check(L.fastmax_b200_shard_kv_state(prob, k.data_ptr(), v.data_ptr(), states.data_ptr(),
                                                    total.data_ptr(), _cabi._stream(k)), "shard_kv_state")
         return states, total
@@ -90,11 +143,12 @@ class CudaShardBackend:
                      "shard_forward")
         return out, den
 
-    def qg_state(self, q, out, den, go):
+    def qg_state(self, q, out, den, go, total_out=None):
         L, prob = _cabi.lib(), self._prob(q, q)
         delta = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
         states = torch.empty(L.fastmax_b200_moment_state_bytes(prob) // 4, dtype=torch.float32, device=q.device)
-        total = torch.empty(L.fastmax_b200_moment_total_bytes(prob) // 4, dtype=torch.float32, device=q.device)
+        total = total_out if total_out is not None else \
+            torch.empty(L.fastmax_b200_moment_total_bytes(prob) // 4, dtype=torch.float32, device=q.device)
         wsb = L.fastmax_b200_shard_backward_workspace_bytes(prob)
         self._bwd_ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)   # reused by backward()
         _cabi._check(L.fastmax_b200_shard_qg_state(prob, q.data_ptr(), out.data_ptr(), den.data_ptr(), go.data_ptr(),
@@ -102,7 +156,16 @@ class CudaShardBackend:
                                                    self._bwd_ws.data_ptr(), wsb, _cabi._stream(q)), "shard_qg_state")
         return delta, states, total
 
-    def backward(self, q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base):
+    def dq_far(self, q, den, stats, go, delta, kv_states):
+        """The part of grad_q that needs nothing from later shards (see ``fastmax_b200_shard_dq_far``); its
+        result stays in the workspace that ``qg_state`` made and ``backward`` reuses."""
+        L, prob = _cabi.lib(), self._prob(q, q)
+        ws = self._bwd_ws
+        _cabi._check(L.fastmax_b200_shard_dq_far(prob, q.data_ptr(), den.data_ptr(), self._ptr(stats), go.data_ptr(),
+                                                 delta.data_ptr(), kv_states.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                 _cabi._stream(q)), "shard_dq_far")
+
+    def backward(self, q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base, dq_far_done=False):
         L, prob = _cabi.lib(), self._prob(q, k)
         gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dots = torch.empty(q.shape[0] + k.shape[0], dtype=torch.float32, device=q.device)
@@ -113,7 +176,8 @@ class CudaShardBackend:
         _cabi._check(L.fastmax_b200_shard_backward(
             prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), den.data_ptr(), self._ptr(stats),
             go.data_ptr(), delta.data_ptr(), kv_states.data_ptr(), self._ptr(qg_states), self._ptr(r_base),
-            dots.data_ptr(), gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), ws.data_ptr(), wsb, _cabi._stream(q)),
+            dots.data_ptr(), gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), int(bool(dq_far_done)), ws.data_ptr(), wsb,
+            _cabi._stream(q)),
             "shard_backward")
         return gq, gk, gv, dots
 
@@ -140,6 +204,20 @@ class SequenceShardedFastmax(torch.autograd.Function):
         if normalize:
             stats = backend.rowmax(q, k, row_offset)
             dist.all_reduce(stats, op=dist.ReduceOp.MAX, group=group)
+        fused = q.is_cuda and isinstance(backend, CudaShardBackend) and getattr(backend, "mask", True)
+        if fused:
+            # this rank's total is written straight into its row of the gather buffer
+            world = dist.get_world_size(group)
+            gathered = _Exchange.buffer("kv", q.device, world, backend.total_floats(k))
+            kv_states, kv_total = backend.kv_state(k, v, total_out=gathered[rank])
+            work = _Exchange.start(gathered, rank, group)
+            s_base = _Exchange.finish("kv", work, gathered, rank, reverse=False)
+            out, den = backend.forward(q, k, v, stats, kv_states, s_base)
+            ctx.fused = True
+            ctx.backend, ctx.group, ctx.normalize, ctx.row_offset = backend, group, normalize, row_offset
+            ctx.save_for_backward(q, k, v, out, den, kv_states, *([stats] if normalize else []))
+            return out
+        ctx.fused = False
         kv_states, kv_total = backend.kv_state(k, v)
         if getattr(backend, "mask", True):
             s_base = exclusive_rank_sum(kv_total, group)
@@ -159,6 +237,19 @@ class SequenceShardedFastmax(torch.autograd.Function):
         stats = rest[0] if rest else None
         backend, group = ctx.backend, ctx.group
         go = grad_out.contiguous().to(q.dtype)
+        if ctx.fused:
+            rank, world = dist.get_rank(group), dist.get_world_size(group)
+            gathered = _Exchange.buffer("qg", q.device, world, backend.total_floats(q))
+            delta, qg_states, _ = backend.qg_state(q, out, den, go, total_out=gathered[rank])
+            work = _Exchange.start(gathered, rank, group)
+            backend.dq_far(q, den, stats, go, delta, kv_states)       # runs while the totals travel
+            r_base = _Exchange.finish("qg", work, gathered, rank, reverse=True)
+            gq, gk, gv, dots = backend.backward(q, k, v, out, den, stats, go, delta, kv_states, qg_states, r_base,
+                                                dq_far_done=True)
+            if ctx.normalize:
+                dist.all_reduce(dots, op=dist.ReduceOp.SUM, group=group)
+                backend.norm_fixup(q, k, stats, dots, ctx.row_offset, gq, gk)
+            return gq, gk, gv, None, None, None
         delta, qg_states, qg_total = backend.qg_state(q, out, den, go)
         if getattr(backend, "mask", True):
             r_base = exclusive_rank_sum(qg_total, group, reverse=True)

@@ -116,8 +116,12 @@ int fastmax_b200_device_status_reset(void* stream);
  * Nothing faults and the context stays usable. */
 int fastmax_b200_wait_selftest(long long limit_clocks, void* stream);
 
-/* Bytes of the per-head statistics buffer (max row norms and their row
- * indices) that forward writes and backward reads.  Replaces the reference's
+/* Bytes of the per-head statistics buffer that forward writes and backward
+ * reads: the max row norms and their row indices and, for unmasked problems
+ * that run on the moment family, the total key/value moment state (so that
+ * backward need not rebuild it).  backward must be given the buffer the
+ * forward call of the same problem filled; with normalize == 0 it may be NULL,
+ * and backward then recomputes what it needs.  Replaces the reference's
  * qnorms/knorms/qmaxes/kmaxes temporaries (reference fastmax_cuda_forward.cu:
  * 349-358), which it needs because it rescales q and k in place. */
 size_t fastmax_b200_stats_bytes(const fastmax_problem* prob);
@@ -215,7 +219,20 @@ int fastmax_b200_shard_backward(const fastmax_problem* prob, const void* q, cons
                                 const void* stats, const void* grad_out, const float* delta,
                                 const float* kv_states, float* qg_states, const float* r_base,
                                 float* dots, void* grad_q, void* grad_k, void* grad_v,
-                                void* workspace, size_t workspace_bytes, void* stream);
+                                int32_t dq_far_done, void* workspace, size_t workspace_bytes, void* stream);
+/* Optional split of shard_backward for causal shards, so that the exchange of the query/gradient
+ * totals can overlap compute: shard_dq_far evaluates the part of grad_q that reads the key/value
+ * prefixes -- it needs nothing from later shards -- into the workspace.  Call it after
+ * shard_qg_state on the same workspace (whose gs / dvec it uses) while the exchange is in flight,
+ * then pass dq_far_done = 1 to shard_backward, again with the same, untouched workspace. */
+int fastmax_b200_shard_dq_far(const fastmax_problem* prob, const void* q, const float* den, const void* stats,
+                              const void* grad_out, const float* delta, const float* kv_states,
+                              void* workspace, size_t workspace_bytes, void* stream);
+/* After an all-gather of every shard's total into gathered (world, floats_per_shard): out = sum of
+ * the totals of the shards before `rank` (after it when reverse != 0).  With no such shard out is
+ * zero-filled; pass NULL as s_base / r_base instead of calling this. */
+int fastmax_b200_shard_sum_totals(const float* gathered, int32_t world, int32_t rank, int32_t reverse,
+                                  size_t floats_per_shard, float* out, void* stream);
 int fastmax_b200_shard_norm_fixup(const fastmax_problem* prob, const void* q, const void* k,
                                   const void* stats, const float* dots, int32_t row_offset,
                                   void* grad_q, void* grad_k, void* stream);

@@ -87,6 +87,23 @@ def test_shard_stage_calls_reproduce_the_unsharded_result(dtype, d, normalize):
     for r in range(G):
         base = sum(qg[j][2] for j in range(r + 1, G)) if r < G - 1 else None
         grads.append(be.backward(qs[r], ks[r], vs[r], outs[r], dens[r], st, gs[r], qg[r][0], kv[r][0], qg[r][1], base))
+    # the split backward (grad_q's far part issued early, as the multi-GPU driver does while the totals
+    # travel) and the library's sum over gathered totals give the same numbers
+    gathered = torch.stack([x[2] for x in qg])
+    for r in range(G):
+        delta_r, states_r, _ = be.qg_state(qs[r], outs[r], dens[r], gs[r])
+        be.dq_far(qs[r], dens[r], st, gs[r], delta_r, kv[r][0])
+        base = None
+        if r < G - 1:
+            base = torch.empty_like(gathered[0])
+            _cabi._check(_cabi.lib().fastmax_b200_shard_sum_totals(gathered.data_ptr(), G, r, 1, gathered.shape[1],
+                                                                   base.data_ptr(), _cabi._stream(base)), "sum_totals")
+            want_base = sum(qg[j][2] for j in range(r + 1, G))
+            assert torch.allclose(base, want_base, rtol=1e-6, atol=1e-6)
+        split = be.backward(qs[r], ks[r], vs[r], outs[r], dens[r], st, gs[r], delta_r, kv[r][0], states_r, base,
+                            dq_far_done=True)
+        for a, b, name in zip(split, grads[r], ("dq", "dk", "dv", "dots")):
+            assert torch.allclose(a.float(), b.float(), rtol=1e-5, atol=1e-6), (r, name)
     if normalize:
         dots = sum(gr[3] for gr in grads)
         for r in range(G):

@@ -65,6 +65,16 @@ def test_other_coefficients_and_lim():
     assert_close(got, ref, torch.bfloat16, "coefficients")
 
 
+def test_negative_second_order_coefficient_takes_the_general_polynomial_path():
+    """With a2 > 0 the fused grad_k + grad_v kernel evaluates the polynomial in completed-square form; a
+    negative a2 (still a positive kernel for |s| <= lim^2) must go through the general form."""
+    q, k, v, go = [randn(1, 2, 400, 64, seed=s) for s in (11, 12, 13, 14)]
+    kw = dict(mask=1, normalize=1, p=2, a0=1.0, a1=0.8, a2=-0.1, lim=1.0)
+    got, _ = run_cabi(q, k, v, go, torch.bfloat16, impl="dense_tc", **kw)
+    ref = oracle(q, k, v, go, torch.bfloat16, dense=True, **kw)
+    assert_close(got, ref, torch.bfloat16, "negative a2")
+
+
 def test_auto_dispatch_picks_tensor_cores_and_matches_cuda_core_family():
     """Both families on the same device inputs at a size the CPU oracle would take long on."""
     dev = torch.device("cuda", 0)
