@@ -611,23 +611,25 @@ def run_ours(args):
     # through the GPU (copy-in, forward+backward, copy-out overlapped) ----------------------
     from fastmax_b200.host import HostPipeline, prefer_gpu_numa_node
 
-    numa_node = prefer_gpu_numa_node(dev)     # pinned buffers below land next to this rank's GPU
-    host_in = [t.cpu().pin_memory() for t in (q, k, v, go)]
-    host_out = [torch.empty_like(h).pin_memory() for h in host_in]
-    del q, k, v, go
-    torch.cuda.empty_cache()
-    pipe = HostPipeline(bh, N, D, dtype, dev, heads_per_group=args.e2e_group, **kw)
-    pipe.run(*host_in, *host_out)
-    hz.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
+    numa_node, e2e_ms, nbytes = -1, None, 0
+    if args.profile_case is None:              # profiler captures stop after the device-resident leg
+        numa_node = prefer_gpu_numa_node(dev)     # pinned buffers below land next to this rank's GPU
+        host_in = [t.cpu().pin_memory() for t in (q, k, v, go)]
+        host_out = [torch.empty_like(h).pin_memory() for h in host_in]
+        del q, k, v, go
+        torch.cuda.empty_cache()
+        pipe = HostPipeline(bh, N, D, dtype, dev, heads_per_group=args.e2e_group, **kw)
         pipe.run(*host_in, *host_out)
-    e1.record()
-    hz.barrier()
-    e2e_ms = hz.max_over_ranks(e0.elapsed_time(e1)) / args.steps
-    nbytes = sum(h.numel() * h.element_size() for h in host_in)
-    del pipe, host_in, host_out
+        hz.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            pipe.run(*host_in, *host_out)
+        e1.record()
+        hz.barrier()
+        e2e_ms = hz.max_over_ranks(e0.elapsed_time(e1)) / args.steps
+        nbytes = sum(h.numel() * h.element_size() for h in host_in)
+        del pipe, host_in, host_out
     torch.cuda.empty_cache()
 
     # ---- extra legs of the default workload --------------------------------------------------
@@ -665,7 +667,8 @@ def run_ours(args):
             "alg_tflops_per_gpu": (ff + fq + fkv) * bh * N * args.steps / (ms * 1e-3) / 1e12,
             "kernels": _kernel_table(main["per"]),
             "roofline": roofline_of(main["per"], cfg, bh, peaks, lib_version),
-            "e2e": {"value": tokens_job / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
+            "e2e": None if e2e_ms is None else
+                   {"value": tokens_job / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
                     "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": args.steps,
                     "host_numa_node_rank0": numa_node},
         }

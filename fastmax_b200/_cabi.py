@@ -21,6 +21,7 @@ EXPORTS = (
     "fastmax_b200_version", "fastmax_b200_last_error", "fastmax_b200_stats_bytes",
     "fastmax_b200_forward_workspace_bytes", "fastmax_b200_backward_workspace_bytes",
     "fastmax_b200_forward", "fastmax_b200_forward_packed", "fastmax_b200_backward",
+    "fastmax_b200_forward_bt", "fastmax_b200_backward_bt", "fastmax_b200_bt_layout_supported",
     "fastmax_b200_launch_count", "fastmax_b200_profile_enable", "fastmax_b200_profile_count",
     "fastmax_b200_profile_get", "fastmax_b200_device_status", "fastmax_b200_device_status_reset",
     "fastmax_b200_wait_selftest",
@@ -69,6 +70,9 @@ def lib() -> ctypes.CDLL:
         L.fastmax_b200_forward_packed.argtypes = [pp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.fastmax_b200_backward.restype = ctypes.c_int
         L.fastmax_b200_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
+        L.fastmax_b200_forward_bt.argtypes = [pp, vp, vp, vp, vp, vp, vp, ctypes.c_int32, vp, sz, vp]
+        L.fastmax_b200_backward_bt.argtypes = [pp] + [vp] * 7 + [ctypes.c_int32] + [vp] * 4 + [sz, vp]
+        L.fastmax_b200_bt_layout_supported.argtypes = [pp, ctypes.c_int32]
         for f in ("moment_state_bytes", "moment_total_bytes", "shard_forward_workspace_bytes",
                   "shard_backward_workspace_bytes"):
             fn = getattr(L, "fastmax_b200_" + f)
@@ -223,6 +227,56 @@ def forward(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0, a2=0.5
                                     den.data_ptr(), stats.data_ptr(), ws.data_ptr(), wsb, _stream(q))
     _check(rc, "fastmax_b200_forward")
     return out, den, stats
+
+
+def bt_layout_supported(q, k, heads_per_batch, **kw) -> bool:
+    """Whether ``forward_bt`` / ``backward_bt`` can serve a problem of these shapes."""
+    prob = make_problem(q, k, kw["mask"], kw["normalize"], kw.get("temperature", 1.0), kw.get("a0", 1.0),
+                        kw.get("a1", 1.0), kw.get("a2", 0.5), kw.get("lim", 1.0), kw.get("p", 2),
+                        kw.get("impl", "auto"), kw.get("chunk", 0))
+    return bool(lib().fastmax_b200_bt_layout_supported(prob, int(heads_per_batch)))
+
+
+def forward_bt(q, k, v, heads_per_batch, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0,
+               p=2, impl="auto", chunk=0):
+    """As ``forward`` but the result is (batch, nq, heads_per_batch, d) -- what the model's output projection
+    takes after a ``view`` -- written in that layout by the attention kernel itself."""
+    _require(q, k, v)
+    L = lib()
+    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl, chunk)
+    bh, nq, d = q.shape
+    with torch.cuda.device(q.device):
+        wsb = L.fastmax_b200_forward_workspace_bytes(prob)
+        out = torch.empty(bh // heads_per_batch, nq, heads_per_batch, d, dtype=q.dtype, device=q.device)
+        den = torch.empty(bh, nq, dtype=torch.float32, device=q.device)
+        stats = torch.empty(max(L.fastmax_b200_stats_bytes(prob), 8), dtype=torch.uint8, device=q.device)
+        ws = _workspace(wsb, q.device)
+        rc = L.fastmax_b200_forward_bt(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                       den.data_ptr(), stats.data_ptr(), int(heads_per_batch), ws.data_ptr(), wsb,
+                                       _stream(q))
+    _check(rc, "fastmax_b200_forward_bt")
+    return out, den, stats
+
+
+def backward_bt(q, k, v, out_bt, den, stats, grad_out_bt, heads_per_batch, *, mask, normalize, temperature=1.0,
+                a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2, impl="auto", chunk=0):
+    """Gradients from ``forward_bt``'s result and an upstream gradient in the same (batch, nq, heads, d) layout."""
+    _require(q, k, v)
+    for t in (out_bt, grad_out_bt):
+        if t.device != q.device or t.dtype != q.dtype or not t.is_contiguous() or t.numel() != q.numel():
+            raise ValueError("out and grad_out must be contiguous (batch, nq, heads, d) tensors of q's dtype")
+    L = lib()
+    prob = make_problem(q, k, mask, normalize, temperature, a0, a1, a2, lim, p, impl, chunk)
+    with torch.cuda.device(q.device):
+        wsb = L.fastmax_b200_backward_workspace_bytes(prob)
+        gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ws = _workspace(wsb, q.device)
+        rc = L.fastmax_b200_backward_bt(prob, q.data_ptr(), k.data_ptr(), v.data_ptr(), out_bt.data_ptr(),
+                                        den.data_ptr(), stats.data_ptr(), grad_out_bt.data_ptr(),
+                                        int(heads_per_batch), gq.data_ptr(), gk.data_ptr(), gv.data_ptr(),
+                                        ws.data_ptr(), wsb, _stream(q))
+    _check(rc, "fastmax_b200_backward_bt")
+    return gq, gk, gv
 
 
 def forward_packed(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0,

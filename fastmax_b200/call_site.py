@@ -7,12 +7,16 @@ expands k and v to the query head count, applies rotary embeddings
 ``.contiguous()`` and calls the attention (``model.py:557-575``); the result is
 transposed back (``model.py:603``) and flattened to (B, T, H*hs) by the caller.
 
-``fastmax_attention_from_qkv`` does the same with four kernel passes around the
+``fastmax_attention_from_qkv`` does the same with two kernel passes around the
 attention kernels instead of a dozen elementwise ones: one that reads the
 projection once and writes rotated per-head q, k, v (k and v stay at G heads;
-the attention kernels take grouped heads natively), one that turns (B, H, T, hs)
-into (B, T, H, hs), and the two mirror images in the backward pass.  Every pass
-goes through the C ABI; nothing here computes on the CPU.
+the attention kernels take grouped heads natively) and its mirror image in the
+backward pass.  The transposition to (B, T, H, hs) costs no pass where the
+tensor-core kernels run (bf16, head size 64 or 128): the forward kernel writes
+its result in that layout and the backward's preparation pass reads the
+incoming gradient from it.  Other problems (fp32, small heads) swap the axes
+with one more pass each way.  Every pass goes through the C ABI; nothing here
+computes on the CPU.
 """
 from __future__ import annotations
 
@@ -29,9 +33,14 @@ class _FromQKV(torch.autograd.Function):
         b, n, g, total, d = qkv5.shape
         heads = g * (total - 2)
         q, k, v = _cabi.qkv_split_rope(qkv5, cos, sin, rope_n)
+        ctx.kw, ctx.rope_n, ctx.dims = kw, rope_n, (b, n, heads, d)
+        ctx.bt = _cabi.bt_layout_supported(q, k, heads, **kw)
+        if ctx.bt:      # the attention kernel writes (B, T, H, hs) itself
+            out, den, stats = _cabi.forward_bt(q, k, v, heads, **kw)
+            ctx.save_for_backward(q, k, v, out, den, stats, cos, sin)
+            return out.view(b, n, heads * d)
         out, den, stats = _cabi.forward(q, k, v, **kw)
         ctx.save_for_backward(q, k, v, out, den, stats, cos, sin)
-        ctx.kw, ctx.rope_n, ctx.dims = kw, rope_n, (b, n, heads, d)
         return _cabi.swap_middle_axes(out.view(b, heads, n, d)).view(b, n, heads * d)
 
     @staticmethod
@@ -39,8 +48,11 @@ class _FromQKV(torch.autograd.Function):
         q, k, v, out, den, stats, cos, sin = ctx.saved_tensors
         b, n, heads, d = ctx.dims
         gy = grad_y.to(q.dtype).contiguous().view(b, n, heads, d)
-        go = _cabi.swap_middle_axes(gy).view(b * heads, n, d)
-        gq, gk, gv = _cabi.backward(q, k, v, out, den, stats, go, **ctx.kw)
+        if ctx.bt:
+            gq, gk, gv = _cabi.backward_bt(q, k, v, out, den, stats, gy, heads, **ctx.kw)
+        else:
+            go = _cabi.swap_middle_axes(gy).view(b * heads, n, d)
+            gq, gk, gv = _cabi.backward(q, k, v, out, den, stats, go, **ctx.kw)
         t = ctx.kw["temperature"]
         if t != 1.0:
             gk = gk / t               # as the reference wrapper does (example.py:80)

@@ -275,9 +275,24 @@ size_t fastmax_b200_backward_workspace_bytes(const fastmax_problem* p) {
   return impl == FASTMAX_IMPL_MOMENTS ? bwd_ws_bytes(*p) : bwd_layout(*p).total;
 }
 
+// Whether a problem can take its result and upstream gradient in the (batch, n, heads, d) layout:
+// the last kernel of the forward must be a tensor-core score kernel and grad_out / out must be read
+// by the gradient preparation pass alone.
+static int bt_layout_ok(const fastmax_problem& p, int heads_per_batch, int impl) {
+  if (heads_per_batch <= 0 || p.bh % heads_per_batch != 0)
+    return fail(FASTMAX_E_ARG, "heads_per_batch=%d does not divide bh=%d", heads_per_batch, p.bh);
+  const bool ok = dense_tc_supports(p) &&
+                  (impl == FASTMAX_IMPL_DENSE_TC || (impl == FASTMAX_IMPL_MOMENTS && p.mask && moments_all_tc(p)));
+  if (!ok)
+    return fail(FASTMAX_E_UNSUPPORTED,
+                "the (batch, n, heads, d) layout needs the tensor-core kernels (bf16, d in {64, 128}; the moment "
+                "family only when causal); use the plain layout and swap the axes");
+  return FASTMAX_OK;
+}
+
 static int forward_impl(const fastmax_problem* prob, const void* q, const void* k, const void* v,
                         const FwdOut& o, void* stats, void* workspace, size_t workspace_bytes,
-                        void* stream) {
+                        void* stream, int heads_per_batch = 0) {
   int rc = validate(prob);
   if (rc) return rc;
   const fastmax_problem& p = *prob;
@@ -289,7 +304,9 @@ static int forward_impl(const fastmax_problem* prob, const void* q, const void* 
   if ((rc = pick_impl(p, o.out_f32 != 0, &impl))) return rc;
   if (p.impl == FASTMAX_IMPL_AUTO && impl == FASTMAX_IMPL_DENSE_TC && !aligned16({q, k, v, o.out}))
     impl = FASTMAX_IMPL_DENSE_FFMA;
+  if (heads_per_batch && (rc = bt_layout_ok(p, heads_per_batch, impl))) return rc;
   Ctx c{p, (cudaStream_t)stream};
+  c.out_heads = heads_per_batch;
   if (p.normalize && (rc = launch_rowmax(c, q, k, (stat_t*)stats))) return rc;
   if (impl == FASTMAX_IMPL_MOMENTS) {
     const size_t need = moments_fwd_layout(p).bytes;
@@ -311,6 +328,21 @@ int fastmax_b200_forward(const fastmax_problem* prob, const void* q, const void*
   return forward_impl(prob, q, k, v, o, stats, workspace, workspace_bytes, stream);
 }
 
+int fastmax_b200_forward_bt(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                            void* out_bt, float* den, void* stats, int32_t heads_per_batch, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  if (heads_per_batch <= 0) return fail(FASTMAX_E_ARG, "heads_per_batch must be positive");
+  FwdOut o{out_bt, den, prob ? prob->d : 0, 1, 0};
+  return forward_impl(prob, q, k, v, o, stats, workspace, workspace_bytes, stream, heads_per_batch);
+}
+
+int fastmax_b200_bt_layout_supported(const fastmax_problem* prob, int32_t heads_per_batch) {
+  if (validate(prob)) return 0;
+  int impl;
+  if (pick_impl(*prob, false, &impl)) return 0;
+  return bt_layout_ok(*prob, heads_per_batch, impl) == FASTMAX_OK;
+}
+
 int fastmax_b200_forward_packed(const fastmax_problem* prob, const void* q, const void* k,
                                 const void* v, float* o_packed, void* stats, void* workspace,
                                 size_t workspace_bytes, void* stream) {
@@ -319,10 +351,10 @@ int fastmax_b200_forward_packed(const fastmax_problem* prob, const void* q, cons
   return forward_impl(prob, q, k, v, o, stats, workspace, workspace_bytes, stream);
 }
 
-int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void* k, const void* v,
-                          const void* out, const float* den, const void* stats,
-                          const void* grad_out, void* grad_q, void* grad_k, void* grad_v,
-                          void* workspace, size_t workspace_bytes, void* stream) {
+static int backward_impl(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                         const void* out, const float* den, const void* stats,
+                         const void* grad_out, void* grad_q, void* grad_k, void* grad_v,
+                         void* workspace, size_t workspace_bytes, void* stream, int heads_per_batch) {
   int rc = validate(prob);
   if (rc) return rc;
   const fastmax_problem& p = *prob;
@@ -335,6 +367,7 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
   if (p.impl == FASTMAX_IMPL_AUTO && impl == FASTMAX_IMPL_DENSE_TC &&
       !aligned16({q, k, v, out, grad_out, grad_q, grad_k, grad_v}))
     impl = FASTMAX_IMPL_DENSE_FFMA;
+  if (heads_per_batch && (rc = bt_layout_ok(p, heads_per_batch, impl))) return rc;
   BwdWs w = bwd_layout(p);
   const size_t need = impl == FASTMAX_IMPL_MOMENTS ? moments_bwd_layout(p).bytes : w.total;
   if (need > 0 && (!workspace || workspace_bytes < need))
@@ -342,6 +375,7 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
                 workspace_bytes);
   if ((rc = check_device())) return rc;
   Ctx c{p, (cudaStream_t)stream};
+  c.out_heads = heads_per_batch;
   if (impl == FASTMAX_IMPL_MOMENTS)
     return moments_backward(c, q, k, v, out, den, (const stat_t*)stats, grad_out, grad_q, grad_k, grad_v,
                             workspace,
@@ -368,6 +402,22 @@ int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void
   return FASTMAX_OK;
 }
 
+int fastmax_b200_backward(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                          const void* out, const float* den, const void* stats,
+                          const void* grad_out, void* grad_q, void* grad_k, void* grad_v,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  return backward_impl(prob, q, k, v, out, den, stats, grad_out, grad_q, grad_k, grad_v, workspace, workspace_bytes,
+                       stream, 0);
+}
+
+int fastmax_b200_backward_bt(const fastmax_problem* prob, const void* q, const void* k, const void* v,
+                             const void* out_bt, const float* den, const void* stats, const void* grad_out_bt,
+                             int32_t heads_per_batch, void* grad_q, void* grad_k, void* grad_v, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  if (heads_per_batch <= 0) return fail(FASTMAX_E_ARG, "heads_per_batch must be positive");
+  return backward_impl(prob, q, k, v, out_bt, den, stats, grad_out_bt, grad_q, grad_k, grad_v, workspace,
+                       workspace_bytes, stream, heads_per_batch);
+}
 
 // ---- sequence sharding ------------------------------------------------------------------
 static int validate_shard(const fastmax_problem* prob) {

@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(256) gprep_kernel(const __nv_bfloat16* __restr
                                                     const __nv_bfloat16* __restrict__ out,
                                                     const float* __restrict__ den, size_t rows,
                                                     __nv_bfloat16* __restrict__ gs,
-                                                    float* __restrict__ dvec) {
+                                                    float* __restrict__ dvec, int n, int out_heads) {
   constexpr int LPR = D / 8;        // lanes per row, 16 bytes (8 elements) each
   constexpr int RPW = 32 / LPR;     // rows per warp and step
   constexpr int STEPS = 2;          // independent steps per warp: more bytes in flight
@@ -207,8 +207,10 @@ __global__ void __launch_bounds__(256) gprep_kernel(const __nv_bfloat16* __restr
   for (int t = 0; t < STEPS; ++t) {
     const size_t row = row0 + (size_t)t * RPW;
     if (row < rows) {
-      g[t] = __ldg((const uint4*)(go + row * D) + part);
-      o[t] = __ldg((const uint4*)(out + row * D) + part);
+      // grad_out and out may be (batch, n, heads, D) arrays; gs, dvec and den are always (heads, n, .)
+      const size_t src = out_heads > 0 ? out_row((int)(row / n), (int)(row % n), n, out_heads) : row;
+      g[t] = __ldg((const uint4*)(go + src * D) + part);
+      o[t] = __ldg((const uint4*)(out + src * D) + part);
     } else {
       g[t] = make_uint4(0u, 0u, 0u, 0u);
       o[t] = g[t];
@@ -255,12 +257,12 @@ int launch_gprep(const Ctx& c, const void* go, const void* out, const float* den
     FM_LAUNCH("fm_gprep", c.stream,
               (gprep_kernel<64><<<blocks, 256, 0, c.stream>>>((const __nv_bfloat16*)go,
                                                               (const __nv_bfloat16*)out, den, rows,
-                                                              (__nv_bfloat16*)gs, dvec)));
+                                                              (__nv_bfloat16*)gs, dvec, c.p.nq, c.out_heads)));
   else
     FM_LAUNCH("fm_gprep", c.stream,
               (gprep_kernel<128><<<blocks, 256, 0, c.stream>>>((const __nv_bfloat16*)go,
                                                                (const __nv_bfloat16*)out, den, rows,
-                                                               (__nv_bfloat16*)gs, dvec)));
+                                                               (__nv_bfloat16*)gs, dvec, c.p.nq, c.out_heads)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }

@@ -71,7 +71,16 @@ int check_problem(const fastmax_problem* p);
 struct Ctx {
   fastmax_problem p;
   cudaStream_t stream;
+  // > 0: the forward's result and the upstream gradient are (batch, n, out_heads, d) arrays -- the
+  // layout the model's output projection consumes -- instead of (batch * out_heads, n, d); only the
+  // tensor-core score kernels and the gradient preparation pass honour it (see fastmax_b200_forward_bt)
+  int out_heads = 0;
 };
+// Row of head `head`, token `row` in a (heads, n, .) array, or in a (batch, n, out_heads, .) array
+__host__ __device__ __forceinline__ size_t out_row(int head, int row, int n, int out_heads) {
+  return out_heads > 0 ? ((size_t)(head / out_heads) * n + row) * out_heads + head % out_heads
+                       : (size_t)head * n + row;
+}
 
 // Row statistics of q and k into `stats` (zeroes it first).
 // row_offset is added to the row indices that are recorded (a sequence shard's first token).
@@ -98,6 +107,9 @@ struct FwdOut {
 // gs[h,i,:] = grad_out[h,i,:] / den[h,i]  (bf16) and dvec[h,i] = (grad_out[h,i,:] . out[h,i,:]) / den[h,i]
 int launch_gprep(const Ctx& c, const void* grad_out, const void* out, const float* den, void* gs,
                  float* dvec);
+// true when every stage of the moment family runs on tensor cores for this problem (then grad_out
+// and out are read by the gradient preparation pass only)
+bool moments_all_tc(const fastmax_problem& p);
 
 // Tensor-core score-form family (bf16, head dimension 64 or 128, bh a multiple of bhkv).
 bool dense_tc_supports(const fastmax_problem& p);

@@ -58,6 +58,7 @@ struct TcArgs {
   int chunk;             // > 0: only the columns of the row pair's own chunk
   const float* o_add;    // fp32 (heads, nrows, d) added to the accumulator row
   const float* den_add;  // OP_A with fwd_div: added to the row sum
+  int o_heads;           // OP_A with fwd_div: > 0 writes out as (batch, nrows, o_heads, d)
 };
 
 constexpr int BM = 128;
@@ -388,7 +389,8 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           tmem_ld64(tg + C::T_O + hc * 64, ov);
           tmem_wait_ld();
           if (row_ok) {
-            uint4* dst = (uint4*)((__nv_bfloat16*)a.o + grow * D + hc * 64);
+            const size_t orow = (MODE == OP_A && a.fwd_div) ? out_row(head, row, a.nrows, a.o_heads) : grow;
+            uint4* dst = (uint4*)((__nv_bfloat16*)a.o + orow * D + hc * 64);
             const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * D + hc * 64);
             const float4* addr = a.o_add ? (const float4*)(a.o_add + grow * D + hc * 64) : nullptr;
 #pragma unroll
@@ -556,6 +558,7 @@ int dense_tc_forward(const Ctx& c, const void* q, const void* k, const void* v,
   a.den_out = den;
   a.fwd_div = 1;
   a.rev = 0;
+  a.o_heads = c.out_heads;
   if (ca) { a.chunk = ca->chunk; a.o_add = ca->out_add; a.den_add = ca->den_add; }
   return launch_tc<OP_A>(c, "fm_dense_tc_fwd", q, nullptr, k, v, c.p.nq, c.p.nk, a);
 }

@@ -54,6 +54,7 @@ struct WArgs {
   const stat_t* stat_k;
   int nrows, ncols, off, mask, ntr, chunk;
   float a0, a1, a2, lim;
+  int o_heads;           // MODE_FWD: > 0 writes out as (batch, nrows, o_heads, 64)
 };
 
 enum { MODE_DQ = 0, MODE_DKDV = 1, MODE_FWD = 2 };
@@ -446,8 +447,9 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const bool dots_here = !FWD && !second && a.dots != nullptr;
       const float* add = second ? a.o2_add : a.o_add;
       const float pre = SQ ? (second ? A2 : 2.f * A2) : 1.f;   // completed square: the factor left out of E' and P'
+      const size_t orow = FWD ? out_row(head, row_ok ? row : 0, a.nrows, a.o_heads) : grow;
       const float part = store_row<32>(tl + (second ? T_O2 : T_O) + cc, row_ok,
-                                       (__nv_bfloat16*)(second ? a.o2 : a.o) + grow * D + cc,
+                                       (__nv_bfloat16*)(second ? a.o2 : a.o) + orow * D + cc,
                                        add ? add + grow * D + cc : nullptr,
                                        dots_here ? (const __nv_bfloat16*)a.x + grow * D + cc : nullptr, scale, pre);
       if (FWD && part4 == 0 && row_ok) a.den_out[grow] = rowsum;
@@ -564,6 +566,7 @@ int dense_tc_wide_forward(const Ctx& c, const void* q, const void* k, const void
   a.lim = p.lim;
   a.o = out;
   a.den_out = den;
+  a.o_heads = c.out_heads;
   if (ca) { a.chunk = ca->chunk; a.o_add = ca->out_add; a.den_add = ca->den_add; }
   return launch_wide<MODE_FWD>(c, "fm_dense_tc_fwd", q, nullptr, k, v, p.nq, p.nk, a);
 }

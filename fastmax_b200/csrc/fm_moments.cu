@@ -38,6 +38,10 @@ size_t state16_bytes(const fastmax_problem& p, int n) {
   return state16_second(p, mats) + (first_tc_supports(p) ? up256(first_tc_copy_bytes(p, mats)) : 0);
 }
 
+bool moments_all_tc(const fastmax_problem& p) {
+  return dense_tc_supports(p) && first_tc_supports(p) && (p.p == 1 || moments_tc_supports(p));
+}
+
 bool moments_supports(const fastmax_problem& p) {
   return p.bh == p.bhkv && (!p.mask || p.nq == p.nk);
 }
@@ -267,7 +271,7 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
   const bool tc = dense_tc_supports(p);
   // the plain row dots feed the CUDA-core kernels only; when every stage runs on tensor cores they
   // all read gs / dvec and the pass over grad_out and out is skipped
-  const bool all_tc = tc && first_tc_supports(p) && (p.p == 1 || moments_tc_supports(p));
+  const bool all_tc = moments_all_tc(p);
   if (!all_tc && (rc = launch_delta(c, grad_out, out, delta))) return rc;
   if (tc && (rc = launch_gprep(c, grad_out, out, den, gs, dvec))) return rc;
   const int nck = (p.nk + L - 1) / L, ncq = (p.nq + L - 1) / L;

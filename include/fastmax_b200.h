@@ -141,6 +141,26 @@ int fastmax_b200_forward(const fastmax_problem* prob,
                          void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* The same passes with the result and the upstream gradient in the layout the model's output
+ * projection works on: out_bt and grad_out_bt are (batch, nq, heads_per_batch, d) arrays with
+ * batch * heads_per_batch == bh, i.e. the reference's `o.transpose(1, 2)` (model.py:603) and its
+ * inverse (the `.contiguous()` on the incoming gradient) are folded into the kernels that write
+ * and read those tensors.  q, k, v, den and the gradients keep the (heads, n, d) layout.
+ * Served by the tensor-core kernels only (bf16, d 64 or 128; the moment family when causal):
+ * bt_layout_supported returns 1 when the problem qualifies, otherwise the calls return
+ * FASTMAX_E_UNSUPPORTED and the caller swaps the axes itself (fastmax_b200_swap_middle_axes). */
+int fastmax_b200_bt_layout_supported(const fastmax_problem* prob, int32_t heads_per_batch);
+int fastmax_b200_forward_bt(const fastmax_problem* prob,
+                            const void* q, const void* k, const void* v,
+                            void* out_bt, float* den, void* stats, int32_t heads_per_batch,
+                            void* workspace, size_t workspace_bytes, void* stream);
+int fastmax_b200_backward_bt(const fastmax_problem* prob,
+                             const void* q, const void* k, const void* v,
+                             const void* out_bt, const float* den, const void* stats,
+                             const void* grad_out_bt, int32_t heads_per_batch,
+                             void* grad_q, void* grad_k, void* grad_v,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Forward pass in the reference's packed layout: o is (bh, nq, d+1) float32
  * whose channels 0..d-1 hold the divided output and channel d the denominator
  * (reference fastmax_cuda_forward.cu:347, 199-210; the reference wrapper

@@ -114,6 +114,7 @@ def test_noise_scaling_matches_oracle_and_runs_in_place(count, dtype):
 FULL = [
     # batch, tokens, heads, groups, head size, rotated features, mask, p
     (2, 70, 4, 2, 32, 8, 1, 1), (1, 150, 4, 4, 64, 64, 1, 2), (2, 33, 6, 2, 16, 16, 0, 2), (1, 300, 4, 1, 64, 32, 1, 1),
+    (2, 200, 2, 1, 128, 128, 1, 2), (1, 4400, 2, 2, 64, 64, 1, 1), (2, 140, 4, 2, 64, 64, 0, 2),
 ]
 
 
@@ -127,9 +128,17 @@ def test_call_site_forward_and_backward_against_oracle(cfg, dtype):
     ang = torch.outer(torch.arange(t, dtype=torch.float32), 1.0 / (10000 ** (torch.arange(0, r, 2) / r)))
     cos, sin = torch.cos(ang).repeat(1, 2), torch.sin(ang).repeat(1, 2)
     xq = qkv.cuda().requires_grad_(True)
+    _cabi.profile(True)
     y = fastmax_attention_from_qkv(xq, cos, sin, heads, groups, hs, r, mask=bool(mask), normalize=True, p=p)
     assert y.shape == (b, t, heads * hs) and y.dtype == dtype
     y.backward(gy.cuda())
+    names = [n for n, _ in _cabi.profile_records()]
+    _cabi.profile(False)
+    if dtype == torch.bfloat16 and hs in (64, 128):
+        # the tensor-core kernels write and read the (B, T, H, hs) layout themselves: no transposition pass
+        assert "fm_swap_axes" not in names, names
+    else:
+        assert names.count("fm_swap_axes") == 2, names
     x = qkv.double().requires_grad_(True)
     want = call_site(x, cos.double(), sin.double(), heads, groups, hs, r, round_dtype=dtype, mask=mask,
                      normalize=1, p=p, a0=1.0, a1=1.0, a2=0.5, lim=1.0)
