@@ -65,9 +65,10 @@ L2_BYTES = 126e6
 # FP32 FFMA peak for the fp32 workloads (no measured figure exists): 148 SMs x 128 lanes x 2 FLOP x 1.965 GHz
 FFMA_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12
 # Version of the library the DRAM-traffic figures below were captured on; another version reports none.
-TRAFFIC_LIB_VERSION = 100
-# ncu DRAM bytes (read + write) per token-head, bf16, D = 64, small case scaled by heads x tokens
-NCU_BYTES_PER_TOKEN_HEAD = {"fm_dense_tc_fwd": 483.2, "fm_dense_tc_dq": 621.3, "fm_dense_tc_dkdv": 723.8}
+TRAFFIC_LIB_VERSION = 200
+# ncu DRAM bytes (read + write) per token-head, bf16, D = 64: the capture of the small case summarised in
+# profiles/dense_tc_small_case_ncu_full.md, scaled by heads x tokens
+NCU_BYTES_PER_TOKEN_HEAD = {"fm_dense_tc_fwd": 487.0, "fm_dense_tc_dq": 622.7, "fm_dense_tc_dkdv": 722.1}
 
 
 def cfg_of(name):

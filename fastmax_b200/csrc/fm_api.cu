@@ -182,7 +182,7 @@ using namespace fm;
 
 extern "C" {
 
-int fastmax_b200_version(void) { return 100; }
+int fastmax_b200_version(void) { return 200; }
 
 const char* fastmax_b200_last_error(void) { return g_err; }
 
