@@ -26,7 +26,7 @@ namespace fm {
 namespace {
 
 enum { MODE_FWD = 0, MODE_DQ = 1, MODE_DKDV = 2 };
-constexpr int BM = 64, BN = 64, LP = BN + 1;
+constexpr int BM = 64, BN = 64, LP = BN + 4;   // LP: row stride of the P / E tiles (16-byte aligned rows)
 
 struct DenseArgs {
   const void* x;  // row operand: q (FWD, DQ) or k (DKDV)          [row heads][nrows][D]
@@ -50,12 +50,46 @@ struct DenseArgs {
   const float* den_add;   // FWD: added to the row sum
 };
 
+// 64 rows of D elements -> fp32 tile with row stride D + 4 (rows stay 16-byte aligned, and the odd
+// number of 16-byte units per row keeps 128-bit reads of eight consecutive rows free of bank
+// conflicts).  Four elements per access where the source is aligned for it, else element by element.
+__device__ __forceinline__ float4 ld4(const float* p) { return __ldg((const float4*)p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 w = __ldg((const uint2*)p);
+  return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xFFFF0000u), __uint_as_float(w.y << 16),
+                     __uint_as_float(w.y & 0xFFFF0000u));
+}
 template <int D, typename T>
 __device__ __forceinline__ void load_tile(float* dst, const T* src, int r0, int n) {
-  constexpr int LD = D + 1;
-  for (int idx = threadIdx.x; idx < 64 * D; idx += 256) {
-    int r = idx / D, c = idx % D;
-    dst[r * LD + c] = (r0 + r < n) ? ldf(src + (size_t)(r0 + r) * D + c) : 0.f;
+  constexpr int LD = D + 4, Q = D / 4;
+  if ((reinterpret_cast<uintptr_t>(src) & (4 * sizeof(T) - 1)) == 0) {
+    for (int idx = threadIdx.x; idx < 64 * Q; idx += 256) {
+      const int r = idx / Q, c = (idx % Q) * 4;
+      const float4 v = (r0 + r < n) ? ld4(src + (size_t)(r0 + r) * D + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      *(float4*)(dst + r * LD + c) = v;
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < 64 * D; idx += 256) {
+      const int r = idx / D, c = idx % D;
+      dst[r * LD + c] = (r0 + r < n) ? ldf(src + (size_t)(r0 + r) * D + c) : 0.f;
+    }
+  }
+}
+
+// N consecutive floats of shared memory (N in {1, 2, 4, 8}; p is N-float aligned) with the widest reads
+template <int N>
+__device__ __forceinline__ void ld_vec(float (&r)[N], const float* p) {
+  if constexpr (N == 1) {
+    r[0] = p[0];
+  } else if constexpr (N == 2) {
+    const float2 v = *(const float2*)p;
+    r[0] = v.x; r[1] = v.y;
+  } else {
+#pragma unroll
+    for (int q = 0; q < N / 4; ++q) {
+      const float4 v = *(const float4*)(p + 4 * q);
+      r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
+    }
   }
 }
 
@@ -65,11 +99,12 @@ __device__ __forceinline__ void store_any(void* base, size_t idx, float v, int f
   else stf((T*)base + idx, v);
 }
 
+// Two CTAs per SM up to d = 64 (128 registers, at most 105 KB of shared memory each); d = 128 runs one.
 template <int D, int MODE, typename T>
-__global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
-  constexpr int LD = D + 1;
+__global__ void __launch_bounds__(256, (D <= 64) ? 2 : 1) dense_ffma_kernel(const DenseArgs a) {
+  constexpr int LD = D + 4;
   constexpr int NC = (D + 15) / 16;
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   float* Xs = smem;          // [BM][LD]
   float* Ys = Xs + BM * LD;  // [BN][LD]
   float* Zs = Ys + BN * LD;  // [BN][LD]
@@ -150,25 +185,42 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) { s[i][j] = 0.f; w[i][j] = 0.f; }
-#pragma unroll 4
-      for (int kk = 0; kk < D; ++kk) {
-        float xr[4], yc[4], ur[4], zc[4];
+      // four features per step, one 128-bit shared-memory read per row and step: a thread's four rows
+      // (ty + 16 i) are broadcast within a quarter warp, its four columns (tx + 16 j) lie in rows whose
+      // stride (D + 4 floats) spreads eight neighbours over all banks
+#pragma unroll 2
+      for (int kk = 0; kk < D; kk += 4) {
+        float4 xr[4], yc[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          xr[i] = Xs[(ty + 16 * i) * LD + kk];
-          yc[i] = Ys[(tx + 16 * i) * LD + kk];
-          if (MODE != MODE_FWD) {
-            ur[i] = Us[(ty + 16 * i) * LD + kk];
-            zc[i] = Zs[(tx + 16 * i) * LD + kk];
-          }
+          xr[i] = *(const float4*)(Xs + (ty + 16 * i) * LD + kk);
+          yc[i] = *(const float4*)(Ys + (tx + 16 * i) * LD + kk);
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            s[i][j] = fmaf(xr[i], yc[j], s[i][j]);
-            if (MODE != MODE_FWD) w[i][j] = fmaf(ur[i], zc[j], w[i][j]);
+            s[i][j] = fmaf(xr[i].x, yc[j].x, s[i][j]);
+            s[i][j] = fmaf(xr[i].y, yc[j].y, s[i][j]);
+            s[i][j] = fmaf(xr[i].z, yc[j].z, s[i][j]);
+            s[i][j] = fmaf(xr[i].w, yc[j].w, s[i][j]);
           }
+        if (MODE != MODE_FWD) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            xr[i] = *(const float4*)(Us + (ty + 16 * i) * LD + kk);
+            yc[i] = *(const float4*)(Zs + (tx + 16 * i) * LD + kk);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              w[i][j] = fmaf(xr[i].x, yc[j].x, w[i][j]);
+              w[i][j] = fmaf(xr[i].y, yc[j].y, w[i][j]);
+              w[i][j] = fmaf(xr[i].z, yc[j].z, w[i][j]);
+              w[i][j] = fmaf(xr[i].w, yc[j].w, w[i][j]);
+            }
+        }
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -197,32 +249,39 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
       }
       __syncthreads();
 
+      // four score columns per step: the P (and E) values of a thread's rows come as 128-bit reads
 #pragma unroll 2
-      for (int j = 0; j < BN; ++j) {
-        float pr[4], er[4];
+      for (int j4 = 0; j4 < BN; j4 += 4) {
+        float4 pr4[4], er4[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          pr[i] = Ps[(ty + 16 * i) * LP + j];
-          if (MODE == MODE_DKDV) er[i] = Es[(ty + 16 * i) * LP + j];
+          pr4[i] = *(const float4*)(Ps + (ty + 16 * i) * LP + j4);
+          if (MODE == MODE_DKDV) er4[i] = *(const float4*)(Es + (ty + 16 * i) * LP + j4);
         }
 #pragma unroll
-        for (int m = 0; m < NC; ++m) {
-          const int cidx = tx + 16 * m;
-          if (D % 16 == 0 || cidx < D) {
-            if (MODE == MODE_FWD) {
-              const float zv = Zs[j * LD + cidx];
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = j4 + jj;
+          float pr[4], er[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) o1[i][m] = fmaf(pr[i], zv, o1[i][m]);
-            } else if (MODE == MODE_DQ) {
-              const float yv = Ys[j * LD + cidx];
+          for (int i = 0; i < 4; ++i) {
+            pr[i] = jj == 0 ? pr4[i].x : jj == 1 ? pr4[i].y : jj == 2 ? pr4[i].z : pr4[i].w;
+            if (MODE == MODE_DKDV) er[i] = jj == 0 ? er4[i].x : jj == 1 ? er4[i].y : jj == 2 ? er4[i].z : er4[i].w;
+          }
+          // the thread's NC features of row j of Y and / or Z: one vector read each
+          float yv[NC], zv[NC];
+          if (D % 16 == 0 || tx * NC < D) {
+            if (MODE != MODE_FWD) ld_vec<NC>(yv, Ys + j * LD + tx * NC);
+            if (MODE != MODE_DQ) ld_vec<NC>(zv, Zs + j * LD + tx * NC);
 #pragma unroll
-              for (int i = 0; i < 4; ++i) o1[i][m] = fmaf(pr[i], yv, o1[i][m]);
-            } else {
-              const float yv = Ys[j * LD + cidx], zv = Zs[j * LD + cidx];
+            for (int m = 0; m < NC; ++m) {
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                o1[i][m] = fmaf(er[i], yv, o1[i][m]);
-                o2[i][m] = fmaf(pr[i], zv, o2[i][m]);
+                if (MODE == MODE_FWD) o1[i][m] = fmaf(pr[i], zv[m], o1[i][m]);
+                else if (MODE == MODE_DQ) o1[i][m] = fmaf(pr[i], yv[m], o1[i][m]);
+                else {
+                  o1[i][m] = fmaf(er[i], yv[m], o1[i][m]);
+                  o2[i][m] = fmaf(pr[i], zv[m], o2[i][m]);
+                }
               }
             }
           }
@@ -245,7 +304,7 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
         if (tx == 0) a.den_out[grow * a.den_stride] = dsum;
 #pragma unroll
         for (int m = 0; m < NC; ++m) {
-          const int cidx = tx + 16 * m;
+          const int cidx = tx * NC + m;   // a thread's output features are contiguous
           if (D % 16 == 0 || cidx < D) {
             const float num = o1[i][m] + (a.o1_add ? a.o1_add[grow * D + cidx] : 0.f);
             store_any<T>(a.o1, grow * a.o_stride + cidx, num * inv, a.out_f32);
@@ -262,7 +321,7 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
         const size_t grow = (size_t)hr * a.nrows + r;
 #pragma unroll
         for (int m = 0; m < NC; ++m) {
-          const int cidx = tx + 16 * m;
+          const int cidx = tx * NC + m;   // a thread's output features are contiguous
           if (D % 16 == 0 || cidx < D) {
             const float g1 = o1[i][m] + (a.o1_add ? a.o1_add[grow * D + cidx] : 0.f);
             stf((T*)a.o1 + grow * D + cidx, g1);
@@ -289,7 +348,7 @@ __global__ void __launch_bounds__(256) dense_ffma_kernel(const DenseArgs a) {
 }
 
 size_t smem_bytes(int d, int mode) {
-  size_t ld = d + 1;
+  size_t ld = d + 4;
   size_t f = 3 * 64 * ld + 64 * LP;
   if (mode != MODE_FWD) f += 64 * ld;
   if (mode == MODE_DKDV) f += 64 * LP + 2 * BN;
