@@ -45,8 +45,13 @@ struct F1StateArgs {
 template <int DD>
 struct F1S {
   static constexpr int NSUB = DD / 64;
-  static constexpr int NS = (DD == 128) ? 2 : 4;
-  static constexpr int TILE = NSUB * 128 * 128;   // one operand tile: 128 tokens x DD bf16
+  // Tokens per tile and ring depth are chosen so that a CTA needs 96 KB of shared memory: two CTAs per SM,
+  // each with two of its three 32 KB stages in flight while the third is consumed, keep enough bytes on the
+  // way from HBM (one CTA with two 64 KB stages reached 58 % of the copy bandwidth).
+  static constexpr int TOK = (DD == 128) ? 64 : 128;
+  static constexpr int NS = 3;
+  static constexpr int SUBTILE = TOK * 128;       // TOK tokens x 64 bf16
+  static constexpr int TILE = NSUB * SUBTILE;     // one operand tile: TOK tokens x DD bf16
   static constexpr int STAGE = 2 * TILE;          // Y then Z
   static constexpr int OFF_VEC = NS * STAGE;      // float sv[DD], se[DD], s_e, pad, e[128]
   static constexpr int OFF_BAR = OFF_VEC + (2 * DD + 4 + 128) * 4;
@@ -56,7 +61,7 @@ struct F1S {
 };
 
 template <int DD>
-__global__ void __launch_bounds__(F1_THREADS, 1)
+__global__ void __launch_bounds__(F1_THREADS, 2)
 first_state_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmZ,
                    const F1StateArgs a) {
   using C = F1S<DD>;
@@ -73,7 +78,8 @@ first_state_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constan
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hc = blockIdx.x, head = hc / a.nchunk, chunk = hc % a.nchunk;
   const int t_begin = chunk * a.chunk, t_end = min(a.n, t_begin + a.chunk);
-  const int nblk = (t_end - t_begin + 127) / 128;
+  constexpr int TOK = C::TOK;
+  const int nblk = (t_end - t_begin + TOK - 1) / TOK;
 
   if (tid == 0) {
     // a stage is free when the MMAs that read it are done and the vector sums have read it
@@ -97,8 +103,8 @@ first_state_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constan
         mbar_expect_tx(BAR_FULL(s), C::STAGE);
         const uint32_t dst = sbase + s * C::STAGE;
         for (int sub = 0; sub < C::NSUB; ++sub) {
-          tma_load_3d(dst + sub * 16384, &tmY, BAR_FULL(s), sub * 64, t_begin + k * 128, head);
-          tma_load_3d(dst + C::TILE + sub * 16384, &tmZ, BAR_FULL(s), sub * 64, t_begin + k * 128, head);
+          tma_load_3d(dst + sub * C::SUBTILE, &tmY, BAR_FULL(s), sub * 64, t_begin + k * TOK, head);
+          tma_load_3d(dst + C::TILE + sub * C::SUBTILE, &tmZ, BAR_FULL(s), sub * 64, t_begin + k * TOK, head);
         }
       }
     }
@@ -112,9 +118,9 @@ first_state_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constan
         const int s = k % C::NS;
         if (!mbar_wait(BAR_FULL(s), (uint32_t)((k / C::NS) & 1))) { report(42); ok = false; break; }
         tc_fence_after();
-        const uint32_t y_lo = desc_lo(sbase + s * C::STAGE, 16384);
-        const uint32_t z_lo = desc_lo(sbase + s * C::STAGE + C::TILE, 16384);
-        umma_ss_mn_steps<8>(tmem, y_lo, z_lo, idesc, k > 0 ? 1u : 0u);
+        const uint32_t y_lo = desc_lo(sbase + s * C::STAGE, C::SUBTILE);
+        const uint32_t z_lo = desc_lo(sbase + s * C::STAGE + C::TILE, C::SUBTILE);
+        umma_ss_mn_steps<TOK / 16>(tmem, y_lo, z_lo, idesc, k > 0 ? 1u : 0u);
         umma_commit(BAR_EMPTY(s));
       }
       if (ok) umma_commit(BAR_DONE());
@@ -135,14 +141,14 @@ first_state_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constan
     bool ok = true;
     for (int k = 0; k < nblk; ++k) {
       const int s = k % C::NS;
-      const int tok0 = t_begin + k * 128;
-      ebuf[t] = (tok0 + t < t_end) ? (dv ? -__ldg(dv + tok0 + t) : 1.f) : 0.f;
+      const int tok0 = t_begin + k * TOK;
+      if (t < TOK) ebuf[t] = (tok0 + t < t_end) ? (dv ? -__ldg(dv + tok0 + t) : 1.f) : 0.f;
       if (!mbar_wait(BAR_FULL(s), (uint32_t)((k / C::NS) & 1))) { report(46); ok = false; break; }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      const uint8_t* yt = smem + s * C::STAGE + sub * 16384;
+      const uint8_t* yt = smem + s * C::STAGE + sub * C::SUBTILE;
       const uint8_t* zt = yt + C::TILE;
 #pragma unroll 4
-      for (int r = part; r < 128; r += NPART) {
+      for (int r = part; r < TOK; r += NPART) {
         const uint32_t off = r * 128 + ((((uint32_t)cc >> 3) ^ (r & 7)) << 4) + (cc & 7) * 2;
         const float e = ebuf[r];                  // 0 for rows past the end of the chunk
         const float2 zv = __bfloat1622float2(*(const __nv_bfloat162*)(zt + off));
@@ -264,7 +270,9 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
     mbar_init(BAR_SF, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(BAR_TF(b), 1);
-      mbar_init(BAR_TE(b), 1);
+      // a stage is free once the product that read it is done and, where the epilogue reads x from it for
+      // the normaliser dot (type A), once its four warps have done so
+      mbar_init(BAR_TE(b), (!a.type_b && (a.den_add || a.final == 1)) ? 5 : 1);
       mbar_init(BAR_AF(b), 1);
       mbar_init(BAR_AE(b), 4);
     }
@@ -334,6 +342,11 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
     for (int i = t; i < 2 * DD + 1; i += 128)
       ncol[i] = (i < DD) ? __ldg(st + (size_t)i * a.dvp + DD) : __ldg(st + (size_t)DD * a.dvp + (i - DD));
     asm volatile("bar.sync 1, 128;" ::: "memory");
+    // type A adds a0 * (constant row) to every element: scaled once here (the value column DD stays raw);
+    // the loops below read these vectors four values per shared-memory access
+    if (!a.type_b)
+      for (int i = t; i < DD; i += 128) crow[i] *= a.a0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
     float part = 0.f;
     bool ok = true;
     for (int i = 0; i < nt; ++i) {
@@ -345,20 +358,30 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
       if (a.type_b) {
         extra = tok_ok ? (a.uvec ? -a.uvec[grow] : 1.f) : 0.f;
       } else if (a.den_add || a.final == 1) {
-        const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * DD);
+        // x_i . (normaliser column): the row is read from the token tile TMA delivered (128-byte rows of a
+        // 64-column sub-tile, 16-byte pieces XOR-swizzled by the row), not from global memory again
+        if (!mbar_wait(BAR_TF(b), (uint32_t)((i >> 1) & 1))) { report(49); ok = false; break; }
+        const int r = qd * 32 + lane;
+        const uint8_t* trow = smem + b * C::TILE + r * 128;
         float dot = 0.f;
-        if (tok_ok)
-#pragma unroll 4
-          for (int v8 = 0; v8 < DD / 8; ++v8) {
-            const uint4 xv = __ldg(xr + v8);
+#pragma unroll
+        for (int sb = 0; sb < C::NSUB; ++sb)
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) {
+            const uint4 xv = *(const uint4*)(trow + sb * 16384 + ((pc ^ (r & 7)) << 4));
             const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+            const float4 n0 = *(const float4*)(ncol + sb * 64 + 8 * pc), n1 = *(const float4*)(ncol + sb * 64 + 8 * pc + 4);
+            const float nc[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              dot = fmaf(__uint_as_float(xw[e] << 16), ncol[8 * v8 + 2 * e], dot);
-              dot = fmaf(__uint_as_float(xw[e] & 0xFFFF0000u), ncol[8 * v8 + 2 * e + 1], dot);
+              dot = fmaf(__uint_as_float(xw[e] << 16), nc[2 * e], dot);
+              dot = fmaf(__uint_as_float(xw[e] & 0xFFFF0000u), nc[2 * e + 1], dot);
             }
           }
         extra = A1 * dot + a.a0 * crow[DD];
+        // this warp is done with the stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_TE(b));
       }
       if (!mbar_wait(BAR_AF(b), (uint32_t)((i >> 1) & 1))) { report(45); ok = false; break; }
       tc_fence_after();
@@ -377,11 +400,13 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
 #pragma unroll
           for (int v8 = 0; v8 < 8; ++v8) {
             float r[8];
+            const float* vecp = (a.type_b ? ncol : crow) + hcol * 64 + 8 * v8;
+            const float4 c0 = *(const float4*)vecp, c1 = *(const float4*)(vecp + 4);
+            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              const int col = hcol * 64 + 8 * v8 + e;
               const float acc = __uint_as_float(tv[8 * v8 + e]);
-              r[e] = a.type_b ? A1 * fmaf(extra, ncol[col], acc) : fmaf(A1, acc, a.a0 * crow[col]);
+              r[e] = a.type_b ? A1 * fmaf(extra, cv[e], acc) : fmaf(A1, acc, cv[e]);
             }
             if (a.final) {
               uint4 w;
@@ -475,8 +500,9 @@ int first_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* 
   const int nchunk = (n + chunk - 1) / chunk;
   CUtensorMap ty, tz;
   int rc;
-  if ((rc = tma_map_bf16(&ty, y, heads, n, p.d, 128))) return rc;
-  if ((rc = tma_map_bf16(&tz, z, heads, n, p.d, 128))) return rc;
+  const int tok = p.d == 128 ? F1S<128>::TOK : F1S<64>::TOK;
+  if ((rc = tma_map_bf16(&ty, y, heads, n, p.d, tok))) return rc;
+  if ((rc = tma_map_bf16(&tz, z, heads, n, p.d, tok))) return rc;
   F1StateArgs a;
   a.y = y; a.z = z; a.dvec = dvec; a.state = state;
   a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.dvp = m.dvp; a.rows = m.f; a.f_lin = p.d * p.d - m.f0;
@@ -527,13 +553,17 @@ int first_tc_readout(const Ctx& c, int type_b, int heads, int n, int chunk, int 
   a.f_lin = p.d * p.d - m.f0; a.type_b = type_b; a.accumulate = accumulate;
   a.final = final; a.out_final = out_final; a.den_final = den_final; a.dots = dots;
   // runs of up to 8 tiles that never cross a chunk (chunks are multiples of 256 tokens)
-  int run = 8;
+  // a CTA pays for loading the state copy and the vector terms once per run, so runs are as long as
+  // the chunk allows (a run never crosses a chunk; chunks are multiples of 256 tokens), at most 32 tiles --
+  // shortened while that would leave the GPU short of CTAs
+  const int tiles = (n + 127) / 128;
+  int run = 32;
   if (per_chunk) {
     const int tpc = chunk / 128;
     while (tpc % run) run >>= 1;
   }
+  while (run > 8 && (size_t)heads * ((tiles + run - 1) / run) < 4 * 148) run >>= 1;
   a.run = run;
-  const int tiles = (n + 127) / 128;
   const unsigned grid = (unsigned)((size_t)heads * ((tiles + run - 1) / run));
   const char* name = type_b ? "fm_first_tc_readout_b" : "fm_first_tc_readout_a";
   if (p.d == 128) {
