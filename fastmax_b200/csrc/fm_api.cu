@@ -245,18 +245,30 @@ int fastmax_b200_profile_get(int i, char* name, int name_len, float* ms) {
   return FASTMAX_OK;
 }
 
-// Unmasked problems on the moment family leave the total key/value state behind the statistic
-// words, so that the backward pass does not have to rebuild it from k and v.
+// Problems on the moment family leave behind the statistic words what the backward pass would otherwise
+// rebuild from k and v: unmasked, the total key/value state; causal, the exclusive prefixes of the key/value
+// chunk states -- the latter only while they are no larger than twice the tensors autograd holds anyway
+// (q, k, v, out), which is the case for the tensor-core configurations (1.1 MB of state per 2048-token chunk
+// and head at d = 64 against 1 MB of tokens).
 static size_t stats_words_bytes(const fastmax_problem& p) {
   return align_up(sizeof(stat_t) * (size_t)(p.bh + p.bhkv), 256);
 }
-static bool keeps_total(const fastmax_problem& p, int impl) { return impl == FASTMAX_IMPL_MOMENTS && !p.mask; }
+static size_t kept_bytes(const fastmax_problem& p) {
+  if (!p.mask) return moment_total_bytes(p);
+  const size_t states = moment_state_bytes(p, p.nk);
+  const size_t es = p.dtype == FASTMAX_BF16 ? 2 : 4;
+  const size_t held = es * (size_t)p.d * (2 * (size_t)p.bh * p.nq + 2 * (size_t)p.bhkv * p.nk);
+  return states <= 2 * held ? states : 0;
+}
+static bool keeps_total(const fastmax_problem& p, int impl) {
+  return impl == FASTMAX_IMPL_MOMENTS && kept_bytes(p) > 0;
+}
 
 size_t fastmax_b200_stats_bytes(const fastmax_problem* p) {
   if (!p || p->bh < 0 || p->bhkv < 0) return 0;
   int impl;
   if (validate(p) == FASTMAX_OK && p->bh > 0 && pick_impl(*p, false, &impl) == FASTMAX_OK && keeps_total(*p, impl))
-    return stats_words_bytes(*p) + moment_total_bytes(*p);
+    return stats_words_bytes(*p) + kept_bytes(*p);
   return sizeof(stat_t) * (size_t)(p->bh + p->bhkv);
 }
 

@@ -167,14 +167,15 @@ int moments_forward_finish(const Ctx& c, const void* q, const void* k, const voi
   return dense_ffma_forward(c, q, k, v, stats, o, ca);
 }
 
-// total_keep (unmasked only, may be null): where the total key/value state is left for the backward pass
+// total_keep (may be null): where the forward leaves what the backward would otherwise rebuild from k and v --
+// unmasked: the total key/value state; causal: the exclusive prefixes of the key/value chunk states
 int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
                     const FwdOut& o, void* workspace, float* total_keep) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   const MomFwdWs w = moments_fwd_layout(p);
   char* ws = (char*)workspace;
-  float* states = (float*)(ws + w.states);
+  float* states = (p.mask && total_keep) ? total_keep : (float*)(ws + w.states);
   float* total = (!p.mask && total_keep) ? total_keep : (float*)(ws + w.total);
   float* o_add = (float*)(ws + w.o_add);
   float* den_add = (float*)(ws + w.den_add);
@@ -246,8 +247,8 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
   return dense_ffma_backward(c, q, k, v, den, stats, grad_out, delta, dots, grad_q, grad_k, grad_v, ca);
 }
 
-// kv_total_kept (unmasked only, may be null): the total key/value state the forward left behind; without
-// it the state is rebuilt from k and v
+// kv_total_kept (may be null): what the forward left behind (unmasked: the total key/value state; causal: the
+// exclusive prefixes of the key/value chunk states); without it the states are rebuilt from k and v
 int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, const void* out,
                      const float* den, const stat_t* stats, const void* grad_out, void* grad_q,
                      void* grad_k, void* grad_v, void* workspace, const float* kv_total_kept) {
@@ -278,10 +279,12 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
   if (p.mask) {
     // the key/value prefixes are rebuilt (the forward does not keep them), used for grad_q,
     // then the buffer is reused for the query/gradient states
-    if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
-    if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, nullptr, 0, 1))) return rc;
-    if ((rc = read_states(c, 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec, states, s16, stats, nullptr,
-                          nullptr, gq_add)))
+    if (!kv_total_kept) {
+      if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
+      if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, nullptr, 0, 1))) return rc;
+    }
+    if ((rc = read_states(c, 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec,
+                          kv_total_kept ? kv_total_kept : states, s16, stats, nullptr, nullptr, gq_add)))
       return rc;
     if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
     if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, nullptr, 1, 1))) return rc;
