@@ -56,7 +56,7 @@ struct RtArgs {
                        // 2: one token tile, group 0 type A and group 1 type B
 };
 
-constexpr int RT_THREADS = 320;   // warps 0-3 group 0, 4-7 group 1, 8 TMA producer, 9 MMA issuer
+constexpr int RT_THREADS = 352;   // warps 0-3 group 0, 4-7 group 1, 8 TMA producer, 9 and 10 MMA issuers
 constexpr int RT_NS = 4;          // state-tile ring stages
 constexpr int RT_TILE = 128 * D * 2;
 constexpr int RT_OFF_X = 0;                         // two token tiles
@@ -96,7 +96,7 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
   if (tid == 0) {
     mbar_init(BAR_X(), 1);
-    for (int s = 0; s < RT_NS; ++s) { mbar_init(BAR_FULL(s), 1); mbar_init(BAR_EMPTY(s), 1); }
+    for (int s = 0; s < RT_NS; ++s) { mbar_init(BAR_FULL(s), 1); mbar_init(BAR_EMPTY(s), a.mode == 2 ? 1 : ntile); }
     for (int t = 0; t < 2; ++t)
       for (int b = 0; b < 2; ++b) { mbar_init(BAR_TFULL(t, b), 1); mbar_init(BAR_TFREE(t, b), readers); }
     mbar_fence_init();
@@ -123,29 +123,33 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         tma_load_3d(sbase + RT_OFF_ST + s * RT_TILE, &tmS, BAR_FULL(s), 0, n * 128, srow);
       }
     }
-  } else if (warp == 9) {
-    // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
-    {
+  } else if (warp >= 9) {
+    // ---------------- MMA issuers: the whole warp runs the loop, one elected lane issues ----------------
+    // Two warps, so that the barrier checks of one overlap the products of the other (the
+    // tensor pipe's queue is short: a single issuer leaves it idle between slices).  With two
+    // token tiles issuer w owns tile w; with one tile the issuers take alternate slices, so
+    // each owns one T buffer and the ring stages of its parity.
+    const int w = warp - 9;
+    const bool one_tile = a.mode == 2;
+    if (one_tile || w < ntile) {
       constexpr uint32_t idesc = idesc_bf16(128, 128, 0, 0);
       bool ok = mbar_wait_warp(BAR_X(), 0);
       if (!ok) report(22);
       tc_fence_after();
       const uint32_t st0 = desc_lo(sbase + RT_OFF_ST, 16);
-      for (int n = 0; ok && n < RT_NT; ++n) {
+      const int t = one_tile ? 0 : w;
+      const uint32_t x_lo = desc_lo(sbase + RT_OFF_X + t * RT_TILE, 16);
+      for (int n = one_tile ? w : 0; ok && n < RT_NT; n += one_tile ? 2 : 1) {
         const int s = n % RT_NS, buf = n & 1;
-        if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((n / RT_NS) & 1))) { report(23); ok = false; break; }
-        for (int t = 0; t < ntile; ++t) {
-          // the buffer was last used by slice n-2
-          if (n >= 2 && !mbar_wait_warp(BAR_TFREE(t, buf), (uint32_t)(((n >> 1) - 1) & 1))) { report(24); ok = false; break; }
-          tc_fence_after();
-          if (elect_one()) {
-            umma_ss_k64(tmem + t * 256 + buf * 128, desc_lo(sbase + RT_OFF_X + t * RT_TILE, 16),
-                        st0 + (uint32_t)s * (RT_TILE >> 4), idesc);
-            umma_commit(BAR_TFULL(t, buf));
-          }
-          __syncwarp();
+        if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((n / RT_NS) & 1))) { report(23); break; }
+        // the buffer was last used by slice n-2
+        if (n >= 2 && !mbar_wait_warp(BAR_TFREE(t, buf), (uint32_t)(((n >> 1) - 1) & 1))) { report(24); break; }
+        tc_fence_after();
+        if (elect_one()) {
+          umma_ss_k64(tmem + t * 256 + buf * 128, x_lo, st0 + (uint32_t)s * (RT_TILE >> 4), idesc);
+          umma_commit(BAR_TFULL(t, buf));
+          umma_commit(BAR_EMPTY(s));
         }
-        if (ok && elect_one()) umma_commit(BAR_EMPTY(s));
         __syncwarp();
       }
     }
@@ -162,9 +166,10 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const float c = stat_scale(a.stat_q, head, a.lim) * stat_scale(a.stat_k, head, a.lim);
       const float A2 = a.a2 * c * c;
       const uint32_t tbase = tmem + t * 256 + ((uint32_t)(qd * 32) << 16);
-      // this thread's token row, as 32 packed fp32 pairs
-      uint64_t x2[32];
-      {
+      // 32 packed fp32 pairs per thread: type A keeps its token row here, type B its 64 running sums
+      // (one array for both, so that neither kind carries the other's registers through the loop)
+      uint64_t xa[32];
+      if (!type_b) {
         const uint4* xr = (const uint4*)((const __nv_bfloat16*)a.x + grow * D);
 #pragma unroll
         for (int v8 = 0; v8 < 8; ++v8) {
@@ -172,11 +177,10 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            x2[v8 * 4 + e] = pack2(__uint_as_float(ww[e] << 16), __uint_as_float(ww[e] & 0xFFFF0000u));
+            xa[v8 * 4 + e] = pack2(__uint_as_float(ww[e] << 16), __uint_as_float(ww[e] & 0xFFFF0000u));
         }
       }
       float* ut = (float*)(smem + RT_OFF_UT) + ((size_t)g * 128 + qd * 32 + lane) * RT_UT_LD;
-      uint64_t acc2[32];
       if (type_b) {
         // ut row = [u_0 .. u_63 | e]; only this thread reads it back
         const uint4* ur = (const uint4*)((const __nv_bfloat16*)a.u + grow * D);
@@ -192,7 +196,7 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
         ut[64] = tok_ok ? (a.uvec ? -a.uvec[grow] : 1.0f) : 0.f;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) acc2[e] = pack2(0.f, 0.f);
+        for (int e = 0; e < 32; ++e) xa[e] = pack2(0.f, 0.f);
       }
       bool ok = true;
       for (int n = 0; n < RT_NT; ++n) {
@@ -212,20 +216,17 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           }
           if (cidx > 64) continue;            // padding rows of the last slice
           if (!type_b) {
-            uint64_t s2 = pack2(0.f, 0.f), s3 = s2;
+            uint64_t s4[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              s2 = fma2(x2[e], pack2u(tv[2 * e], tv[2 * e + 1]), s2);
-              s3 = fma2(x2[e + 1], pack2u(tv[2 * e + 2], tv[2 * e + 3]), s3);
-            }
+            for (int e = 0; e < 32; ++e) s4[e & 3] = fma2(xa[e], pack2u(tv[2 * e], tv[2 * e + 1]), s4[e & 3]);
             float lo, hi;
-            unpack2(add2(s2, s3), lo, hi);
+            unpack2(add2(add2(s4[0], s4[1]), add2(s4[2], s4[3])), lo, hi);
             ut[cidx] = A2 * (lo + hi);      // staged in this thread's row, written out at the end
           } else {
             const float uc = ut[cidx];
             const uint64_t u2 = pack2(uc, uc);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) acc2[e] = fma2(u2, pack2u(tv[2 * e], tv[2 * e + 1]), acc2[e]);
+            for (int e = 0; e < 32; ++e) xa[e] = fma2(u2, pack2u(tv[2 * e], tv[2 * e + 1]), xa[e]);
           }
         }
       }
@@ -241,8 +242,8 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           float f0, f1, f2, f3;
-          unpack2(acc2[2 * e], f0, f1);
-          unpack2(acc2[2 * e + 1], f2, f3);
+          unpack2(xa[2 * e], f0, f1);
+          unpack2(xa[2 * e + 1], f2, f3);
           dst[e] = make_float4(k2 * f0, k2 * f1, k2 * f2, k2 * f3);
         }
       }
