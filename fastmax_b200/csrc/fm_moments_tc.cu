@@ -37,6 +37,15 @@ constexpr int NROWS_T = 65 * 64;          // rows (c, b) of the transposed bf16 
 constexpr int NROWS_TP = 33 * 128;        // padded to whole 128-row tiles
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_mtc_status, 0, code); }
+// 16 bytes from / 4 bytes to shared memory by shared-window address (keeps the access off the generic path)
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(saddr));
+  return r;
+}
+__device__ __forceinline__ void sts32(uint32_t saddr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
+}
 
 // =====================================================================================
 // readout
@@ -284,12 +293,22 @@ __global__ void __launch_bounds__(256) state_to_bf16t_kernel(const float* __rest
 
 // =====================================================================================
 // state build: T2[(a,b)][c] = sum_j y_j[a] y_j[b] z_j[c],  c < 64
-// One CTA owns 16 values of a (8 accumulator tiles of 2 a x 64 b rows, 64 columns each =
-// all 512 TMEM columns) for one chunk of one head and walks the chunk in blocks of 128
-// tokens.  Two groups of 128 threads (one token each) write the feature tiles
-// A[m][(a,b)][token] = y[a] y[b] as bf16 into a ring of shared-memory buffers in the
-// 128-byte-swizzled MN-major layout; one thread issues, per tile, 8 K=16 MMAs against the
-// value tile that TMA delivered (MN-major B).
+// One CTA owns 8 values of a -- four accumulator tiles of (2 a x 64 b) rows by 64 columns,
+// TMEM columns 0..255 -- for one chunk of one head and walks the chunk in blocks of 128
+// tokens.  The feature tiles are the A operand and live in tensor memory, never in shared
+// memory: TMEM lane (a, b) of tile m holds y[a] y[b] for the block's 128 tokens as 64 packed
+// bf16 pairs (columns 256 + 64 m ..), written by the threads that own the lane, and the
+// value tile that TMA delivered is the MN-major B operand of eight K=16 products per tile.
+//   The sixteen generator warps form two independent halves, one per 64 tokens of the block
+// (warps 0-7 and 8-15), each with its own named barrier, feature-buffer columns, mbarriers
+// and MMA issuer warp, so that the latency chain of one half (transpose, barrier, row reads,
+// TMEM stores, hand-off) overlaps that of the other.  A half first transposes its y rows
+// into shared memory (yT[feature][token]), so that a thread reads its own row b once, as
+// 16-byte vectors, and the row a of each tile as a broadcast; warp w covers the TMEM lane
+// quarter w % 4 and 32 tokens.  Shared-memory traffic per block is the transposition, 32 KB
+// of row reads and the tensor core's 64 KB of value-tile reads, a quarter of what feature
+// tiles staged in shared memory cost.  The y rows come straight from global memory into
+// registers two blocks ahead; the producer warp asks for them in L2 earlier still.
 // =====================================================================================
 struct StArgs {
   const void* y;     // (heads, n, 64) bf16 feature source
@@ -298,17 +317,23 @@ struct StArgs {
   size_t per_state;
 };
 
-constexpr int ST_THREADS = 320;       // warps 0-3, 4-7: generator groups; 8: TMA; 9: MMA issuer
-constexpr int ST_NA = 4;              // feature-tile ring
-constexpr int ST_NZ = 2;              // value-tile ring
-constexpr int ST_ATILE = 2 * 128 * 128;   // two 64-feature blocks of 128 tokens x 128 bytes
+constexpr int ST_GEN_WARPS = 16;
+constexpr int ST_THREADS = (ST_GEN_WARPS + 3) * 32;   // warps 0-15: generators; 16: TMA; 17, 18: MMA issuers
+constexpr int ST_TILES = 4;           // accumulator tiles (and feature buffers) per CTA
+constexpr int ST_SPLIT = 64 / (2 * ST_TILES);   // CTAs per (head, chunk)
+constexpr int ST_NZ = 3;              // value-tile ring
 constexpr int ST_ZTILE = 128 * 128;
-constexpr int ST_OFF_A = 0;
-constexpr int ST_OFF_Z = ST_NA * ST_ATILE;
-constexpr int ST_OFF_BAR = ST_OFF_Z + ST_NZ * ST_ZTILE;
-constexpr int ST_NBAR = 2 * ST_NA + 2 * ST_NZ + 1;
+constexpr int ST_YT_LD = 272;         // bytes per yT row: 128 tokens + 16 (conflict-free 16-byte reads down a column)
+constexpr int ST_YT = 64 * ST_YT_LD;
+constexpr int ST_OFF_Z = 0;
+constexpr int ST_OFF_YT = ST_NZ * ST_ZTILE;          // two transposed blocks
+constexpr int ST_OFF_BAR = ST_OFF_YT + 2 * ST_YT;
+constexpr int ST_NBAR = 4 * ST_TILES + 2 * ST_NZ + 1;
 constexpr int ST_OFF_TMEM = ST_OFF_BAR + ST_NBAR * 8;
 constexpr int ST_SMEM = ST_OFF_TMEM + 16 + 1024;
+constexpr int ST_TM_A = 64 * ST_TILES;               // first TMEM column of the feature buffers
+constexpr int ST_L2_AHEAD = 5;                       // blocks between the L2 request and the use of y rows
+static_assert(ST_TILES == 4 && ST_GEN_WARPS == 16, "the epilogue gives one tile to each group of four warps");
 
 __global__ void __launch_bounds__(ST_THREADS, 1)
 state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
@@ -316,37 +341,50 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + ST_OFF_BAR;
-  auto BAR_AFULL = [&](int b) { return bar0 + 8u * b; };
-  auto BAR_AEMPTY = [&](int b) { return bar0 + 8u * (ST_NA + b); };
-  auto BAR_ZFULL = [&](int s) { return bar0 + 8u * (2 * ST_NA + s); };
-  auto BAR_ZEMPTY = [&](int s) { return bar0 + 8u * (2 * ST_NA + ST_NZ + s); };
-  auto BAR_DONE = [&]() { return bar0 + 8u * (2 * ST_NA + 2 * ST_NZ); };
+  // barriers: a_full[tile][half] | a_empty[tile][half] | z_full[NZ] | z_empty[NZ] | done
+  auto BAR_AFULL = [&](int m, int h) { return bar0 + 8u * (2 * m + h); };
+  auto BAR_AEMPTY = [&](int m, int h) { return bar0 + 8u * (2 * ST_TILES + 2 * m + h); };
+  auto BAR_ZFULL = [&](int s) { return bar0 + 8u * (4 * ST_TILES + s); };
+  auto BAR_ZEMPTY = [&](int s) { return bar0 + 8u * (4 * ST_TILES + ST_NZ + s); };
+  auto BAR_DONE = [&]() { return bar0 + 8u * (4 * ST_TILES + 2 * ST_NZ); };
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + ST_OFF_TMEM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int quarter = blockIdx.x & 3;
-  const int hc = blockIdx.x >> 2;                 // head * nchunk + chunk
+  const int part = blockIdx.x % ST_SPLIT;
+  const int hc = blockIdx.x / ST_SPLIT;           // head * nchunk + chunk
   const int head = hc / a.nchunk, chunk = hc % a.nchunk;
   const int t_begin = chunk * a.chunk, t_end = min(a.n, t_begin + a.chunk);
   const int nblk = (t_end - t_begin + 127) / 128;
-  const int a0 = quarter * 16;
+  const int a0 = part * 2 * ST_TILES;
+  const __nv_bfloat16* ybase = (const __nv_bfloat16*)a.y + (size_t)head * a.n * D;
 
   if (tid == 0) {
-    for (int b = 0; b < ST_NA; ++b) { mbar_init(BAR_AFULL(b), 4); mbar_init(BAR_AEMPTY(b), 1); }
-    for (int s = 0; s < ST_NZ; ++s) { mbar_init(BAR_ZFULL(s), 1); mbar_init(BAR_ZEMPTY(s), 1); }
-    mbar_init(BAR_DONE(), 1);
+    for (int m = 0; m < ST_TILES; ++m)
+      for (int h = 0; h < 2; ++h) { mbar_init(BAR_AFULL(m, h), ST_GEN_WARPS / 2); mbar_init(BAR_AEMPTY(m, h), 1); }
+    for (int s = 0; s < ST_NZ; ++s) { mbar_init(BAR_ZFULL(s), 1); mbar_init(BAR_ZEMPTY(s), 2); }
+    mbar_init(BAR_DONE(), 2);
     mbar_fence_init();
   }
-  if (warp == 9) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+  if (warp == ST_GEN_WARPS + 1) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == ST_GEN_WARPS) {
+    // ---- producer: value tiles by TMA, and L2 requests for the y rows of later blocks ----
     if (lane == 0) tma_prefetch_desc(&tmZ);
+    auto ask_l2 = [&](int k) {
+      if (k >= nblk) return;
+      for (int i = lane; i < 128; i += 32) {
+        const int tok = t_begin + k * 128 + i;
+        if (tok < t_end) asm volatile("prefetch.global.L2 [%0];" ::"l"(ybase + (size_t)tok * D));
+      }
+    };
+    for (int k = 2; k < ST_L2_AHEAD; ++k) ask_l2(k);
     for (int k = 0; k < nblk; ++k) {
       const int s = k % ST_NZ;
+      ask_l2(k + ST_L2_AHEAD);
       if (!mbar_wait(BAR_ZEMPTY(s), (((k / ST_NZ) & 1) ^ 1))) { report(31); break; }
       if (lane == 0) {
         mbar_expect_tx(BAR_ZFULL(s), ST_ZTILE);
@@ -355,77 +393,122 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
         tma_load_3d(sbase + ST_OFF_Z + s * ST_ZTILE, &tmZ, BAR_ZFULL(s), 0, t_begin + k * 128, head);
       }
     }
-  } else if (warp == 9) {
-    {   // the whole warp runs the loop, one elected lane issues
-      constexpr uint32_t idesc = idesc_bf16(128, 64, 1, 1);
-      bool ok = true;
-      for (int k = 0; ok && k < nblk; ++k) {
-        const int s = k % ST_NZ;
-        if (!mbar_wait_warp(BAR_ZFULL(s), (uint32_t)((k / ST_NZ) & 1))) { report(32); ok = false; break; }
-        const uint32_t z_lo = desc_lo(sbase + ST_OFF_Z + s * ST_ZTILE, ST_ZTILE);
-        for (int m = 0; m < 8; ++m) {
-          const int q = k * 8 + m, b = q % ST_NA;
-          if (!mbar_wait_warp(BAR_AFULL(b), (uint32_t)((q / ST_NA) & 1))) { report(33); ok = false; break; }
-          tc_fence_after();
-          if (elect_one()) {
-            umma_ss_mn_steps<8>(tmem + m * 64, desc_lo(sbase + ST_OFF_A + b * ST_ATILE, ST_ATILE / 2), z_lo,
-                                idesc, k > 0 ? 1u : 0u);
-            umma_commit(BAR_AEMPTY(b));
-          }
-          __syncwarp();
-        }
-        if (ok && elect_one()) umma_commit(BAR_ZEMPTY(s));
-        __syncwarp();
-      }
-      if (ok && elect_one()) umma_commit(BAR_DONE());
-    }
-    __syncwarp();
-  } else {
-    const int g = warp >> 2, j = (warp & 3) * 32 + lane;   // group, token within the block
-    const __nv_bfloat16* ybase = (const __nv_bfloat16*)a.y + (size_t)head * a.n * D;
+  } else if (warp > ST_GEN_WARPS) {
+    // Issuer warp w serves token half w of every block: the whole warp runs the loop, one elected
+    // lane issues four K=16 products per tile.  Both halves add into the same accumulators; in the
+    // first block half 1 lets half 0's product of a tile complete first, because that one starts
+    // the accumulator.
+    const int w = warp - ST_GEN_WARPS - 1;
+    constexpr uint32_t idesc = idesc_bf16(128, 64, 0, 1);
     bool ok = true;
     for (int k = 0; ok && k < nblk; ++k) {
-      const int tok = t_begin + k * 128 + j;
-      __nv_bfloat162 yp[32];
-      {
-        const uint4* yr = (const uint4*)(ybase + (size_t)tok * D);
+      const int s = k % ST_NZ;
+      if (!mbar_wait_warp(BAR_ZFULL(s), (uint32_t)((k / ST_NZ) & 1))) { report(32); ok = false; break; }
+      const uint32_t z_lo = desc_lo(sbase + ST_OFF_Z + s * ST_ZTILE, ST_ZTILE) + (uint32_t)w * (4 * 128);
+      for (int m = 0; m < ST_TILES; ++m) {
+        if (!mbar_wait_warp(BAR_AFULL(m, w), (uint32_t)(k & 1))) { report(33); ok = false; break; }
+        if (k == 0 && w == 1 && !mbar_wait_warp(BAR_AEMPTY(m, 0), 0)) { report(36); ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {
+          umma_ts_steps<4>(tmem + m * 64, tmem + ST_TM_A + m * 64 + w * 32, z_lo, idesc, (k > 0 || w == 1) ? 1u : 0u);
+          umma_commit(BAR_AEMPTY(m, w));
+        }
+        __syncwarp();
+      }
+      if (ok && elect_one()) umma_commit(BAR_ZEMPTY(s));
+      __syncwarp();
+    }
+    if (ok && elect_one()) umma_commit(BAR_DONE());
+    __syncwarp();
+  } else {
+    const int h = warp >> 3, tq = (warp >> 2) & 1, qd = warp & 3;   // token half, 32-token quarter in it, TMEM lane quarter
+    const int b = (qd & 1) * 32 + lane;             // this thread's feature row b (the same in every tile)
+    const int a_sub = qd >> 1;                      // which of the tile's two a values
+    const int tok_off = h * 64 + tq * 32;           // first of this warp's 32 tokens in the block
+    // transposition duty inside the half: token pair jp (of 32) and 8 features from fg * 8
+    const int jp = tid & 31, fg = (tid >> 5) & 7;
+    auto load_rows = [&](int k, uint4 (&r)[2]) {
+      const int tok = t_begin + k * 128 + h * 64 + 2 * jp;
 #pragma unroll
-        for (int v8 = 0; v8 < 8; ++v8) {
-          uint4 w = (tok < t_end) ? __ldg(yr + v8) : make_uint4(0, 0, 0, 0);
-          yp[v8 * 4 + 0] = *reinterpret_cast<__nv_bfloat162*>(&w.x);
-          yp[v8 * 4 + 1] = *reinterpret_cast<__nv_bfloat162*>(&w.y);
-          yp[v8 * 4 + 2] = *reinterpret_cast<__nv_bfloat162*>(&w.z);
-          yp[v8 * 4 + 3] = *reinterpret_cast<__nv_bfloat162*>(&w.w);
+      for (int t = 0; t < 2; ++t)
+        r[t] = (k < nblk && tok + t < t_end) ? __ldg((const uint4*)(ybase + (size_t)(tok + t) * D + fg * 8))
+                                             : make_uint4(0, 0, 0, 0);
+    };
+    uint4 rows[2], rows_next[2];
+    load_rows(0, rows);
+    load_rows(1, rows_next);
+    const uint32_t ta = tmem + ST_TM_A + h * 32 + tq * 16 + ((uint32_t)(qd * 32) << 16);   // this warp's part of feature buffer 0
+    bool ok = true;
+    for (int k = 0; k < nblk; ++k) {   // every generator thread takes part in every block's barrier
+      const uint32_t yt = sbase + ST_OFF_YT + (k & 1) * ST_YT;
+      {
+        // word (feature f, token pair) = two consecutive tokens of feature f
+        const uint32_t t0[4] = {rows[0].x, rows[0].y, rows[0].z, rows[0].w};
+        const uint32_t t1[4] = {rows[1].x, rows[1].y, rows[1].z, rows[1].w};
+        const uint32_t col = yt + (fg * 8) * ST_YT_LD + (h * 32 + jp) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          sts32(col + (2 * e) * ST_YT_LD, __byte_perm(t0[e], t1[e], 0x5410));
+          sts32(col + (2 * e + 1) * ST_YT_LD, __byte_perm(t0[e], t1[e], 0x7632));
         }
       }
+      rows[0] = rows_next[0];
+      rows[1] = rows_next[1];
+      load_rows(k + 2, rows_next);                  // two blocks ahead
+      if (h == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
+      // Reuse of a yT buffer two blocks later needs no second barrier: a thread that writes block
+      // k + 2 has passed the barrier of block k + 1, which every thread of its half reaches only
+      // after its reads of block k (a half reads only the token columns it wrote).
+      if (!ok) continue;
+      uint32_t yb[16];
+      {
+        const uint32_t rb = yt + b * ST_YT_LD + tok_off * 2;
 #pragma unroll
-      for (int mm = 0; mm < 4; ++mm) {
-        const int m = 2 * mm + g;              // this group's accumulator tiles: g, g+2, g+4, g+6
-        const int q = k * 8 + m, b = q % ST_NA;
-        if (!mbar_wait(BAR_AEMPTY(b), (((q / ST_NA) & 1) ^ 1))) { report(34); ok = false; break; }
-        uint8_t* abuf = smem + ST_OFF_A + b * ST_ATILE;
+        for (int v = 0; v < 4; ++v) {
+          const uint4 w4 = lds128(rb + v * 16);
+          yb[4 * v] = w4.x; yb[4 * v + 1] = w4.y; yb[4 * v + 2] = w4.z; yb[4 * v + 3] = w4.w;
+        }
+      }
+      // products of one tile: row a of the tile (a broadcast read) times this thread's row b
+      auto products = [&](int m, uint32_t (&pr)[16]) {
+        const uint32_t ra = yt + (a0 + 2 * m + a_sub) * ST_YT_LD + tok_off * 2;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int aa = a0 + 2 * m + half;    // value of a for this 64-feature block
-          // y[aa] broadcast to both halves of a bf16 pair; re-read from memory (a cache hit)
-          // because aa is not a compile-time index into the register copy of the row
-          const __nv_bfloat16 ys = (tok < t_end) ? ybase[(size_t)tok * D + aa] : __float2bfloat16_rn(0.f);
-          const __nv_bfloat162 ya = __halves2bfloat162(ys, ys);
-          uint4* row = (uint4*)(abuf + half * (ST_ATILE / 2) + (j >> 3) * 1024 + (j & 7) * 128);
+        for (int v = 0; v < 4; ++v) {
+          const uint4 w4 = lds128(ra + v * 16);
+          const uint32_t ya[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            __nv_bfloat162 p0 = __hmul2(yp[ch * 4 + 0], ya), p1 = __hmul2(yp[ch * 4 + 1], ya);
-            __nv_bfloat162 p2 = __hmul2(yp[ch * 4 + 2], ya), p3 = __hmul2(yp[ch * 4 + 3], ya);
-            uint4 w;
-            w.x = *reinterpret_cast<uint32_t*>(&p0); w.y = *reinterpret_cast<uint32_t*>(&p1);
-            w.z = *reinterpret_cast<uint32_t*>(&p2); w.w = *reinterpret_cast<uint32_t*>(&p3);
-            row[ch ^ (j & 7)] = w;
+          for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 pv = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&yb[4 * v + e]),
+                                              *reinterpret_cast<const __nv_bfloat162*>(&ya[e]));
+            pr[4 * v + e] = *reinterpret_cast<const uint32_t*>(&pv);
           }
         }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(BAR_AFULL(b));
-      }
+      };
+      // Tiles go two at a time, and the stores of one pair complete while the products of the next
+      // are formed.  A feature buffer is free once the product that read it one block ago is done;
+      // products complete in order, so the later tile's barrier covers the earlier one's too.
+      uint32_t p0[16], p1[16], p2[16], p3[16];
+      products(0, p0);
+      products(1, p1);
+      if (!mbar_wait(BAR_AEMPTY(1, h), (uint32_t)((k & 1) ^ 1))) { report(34); ok = false; continue; }
+      tc_fence_after();
+      tmem_st16(ta, p0);
+      tmem_st16(ta + 64, p1);
+      products(2, p2);
+      products(3, p3);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(BAR_AFULL(0, h)); mbar_arrive(BAR_AFULL(1, h)); }
+      if (!mbar_wait(BAR_AEMPTY(3, h), (uint32_t)((k & 1) ^ 1))) { report(34); ok = false; continue; }
+      tc_fence_after();
+      tmem_st16(ta + 128, p2);
+      tmem_st16(ta + 192, p3);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(BAR_AFULL(2, h)); mbar_arrive(BAR_AFULL(3, h)); }
     }
     // ---- epilogue: accumulator rows -> fp32 state (columns 0..63); the normaliser column and the
     // padding are zeroed here, state_ecol_kernel then adds its partial sums into column 64 ----
@@ -433,26 +516,22 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
     tc_fence_after();
     if (ok) {
       float* st = a.state + (size_t)hc * a.per_state;
-      const int l = (warp & 3) * 32 + lane;    // TMEM lane = row of the accumulator tile
-#pragma unroll 1
-      for (int mm = 0; mm < 4; ++mm) {
-        const int m = 2 * mm + g;
-        uint32_t tv[64];
-        tmem_ld64(tmem + m * 64 + ((uint32_t)((warp & 3) * 32) << 16), tv);
-        tmem_wait_ld();
-        const int f = (a0 + 2 * m + (l >> 6)) * 64 + (l & 63);
-        float4* dst = (float4*)(st + (size_t)f * a.dvp);
+      const int m = warp >> 2;                       // one tile per group of four warps
+      uint32_t tv[64];
+      tmem_ld64(tmem + m * 64 + ((uint32_t)(qd * 32) << 16), tv);
+      tmem_wait_ld();
+      const int f = (a0 + 2 * m + a_sub) * 64 + b;
+      float4* dst = (float4*)(st + (size_t)f * a.dvp);
 #pragma unroll
-        for (int e = 0; e < 16; ++e)
-          dst[e] = make_float4(__uint_as_float(tv[4 * e]), __uint_as_float(tv[4 * e + 1]),
-                               __uint_as_float(tv[4 * e + 2]), __uint_as_float(tv[4 * e + 3]));
-        dst[16] = make_float4(0.f, 0.f, 0.f, 0.f);   // columns 64..67 (dvp == 68 at d == 64)
-      }
+      for (int e = 0; e < 16; ++e)
+        dst[e] = make_float4(__uint_as_float(tv[4 * e]), __uint_as_float(tv[4 * e + 1]),
+                             __uint_as_float(tv[4 * e + 2]), __uint_as_float(tv[4 * e + 3]));
+      dst[16] = make_float4(0.f, 0.f, 0.f, 0.f);   // columns 64..67 (dvp == 68 at d == 64)
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == ST_GEN_WARPS + 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -630,7 +709,7 @@ int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void
   a.per_state = (size_t)m.f * m.dvp;
   FM_CUDA_TRY(cudaFuncSetAttribute(state_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM));
   FM_LAUNCH("fm_moments_tc_state", c.stream,
-            (state_tc_kernel<<<(unsigned)((size_t)heads * nchunk * 4), ST_THREADS, ST_SMEM, c.stream>>>(tz, a)));
+            (state_tc_kernel<<<(unsigned)((size_t)heads * nchunk * ST_SPLIT), ST_THREADS, ST_SMEM, c.stream>>>(tz, a)));
   FM_CUDA_TRY(cudaGetLastError());
   FM_LAUNCH("fm_moments_state_ecol", c.stream,
             (state_ecol_kernel<<<dim3((unsigned)((size_t)heads * nchunk), 2), 256, 0, c.stream>>>(
