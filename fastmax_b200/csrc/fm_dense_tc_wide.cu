@@ -64,6 +64,7 @@ constexpr int kProducerWarp = 16, kIssuerWarp = 17, kAccIssuerWarp = 19, kComput
 constexpr int ROW_TILE = BM * 128;
 constexpr int OFF_X = 0, OFF_U = ROW_TILE;
 constexpr int T_S = 0, T_W = 128, T_E = 256, T_P = 320, T_O = 384, T_O2 = 448;
+constexpr int T_X = T_P;   // MODE_DQ (no P): the row operands x (32 columns) and u (32 columns) as TMEM A operands
 template <int MODE>
 struct WCfg {
   static constexpr int BN = (MODE == MODE_FWD) ? 128 : 64;   // columns per tile
@@ -80,7 +81,7 @@ struct WCfg {
   static constexpr int OFF_ST = (MODE == MODE_FWD ? 1 : 2) * ROW_TILE;   // the forward has no U tile
   static constexpr int OFF_VEC = OFF_ST + NS * STAGE;      // per compute warp 2 x 32 floats
   static constexpr int OFF_BAR = OFF_VEC + kComputeWarps * 2 * 32 * 4;
-  static constexpr int NBAR = 2 + 2 * NS + 8;
+  static constexpr int NBAR = 2 + 2 * NS + 9;
   static constexpr int OFF_TMEM = OFF_BAR + NBAR * 8;
   static constexpr int SMEM = OFF_TMEM + 16 + 1024;
 };
@@ -102,6 +103,9 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   constexpr int BN = C::BN, NS = C::NS, COL_TILE = C::COL_TILE, STAGE = C::STAGE;
   constexpr int OFF_ST = C::OFF_ST, OFF_VEC = C::OFF_VEC, OFF_BAR = C::OFF_BAR, OFF_TMEM = C::OFF_TMEM;
   constexpr bool PV_EARLY = MODE == MODE_DQ;
+  // grad_q has 64 TMEM columns to spare: its row operands are copied there once, so that the S / W
+  // products read only the column tile from shared memory (32.6 instead of 48.6 cycles per K=16 step)
+  constexpr bool XT = MODE == MODE_DQ;
   constexpr int HB = BN / 2;          // columns of one compute warp = packed bf16 columns of one group
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -115,6 +119,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   auto BAR_SFREE = [&](int g) { return bar0 + 8u * (4 + 2 * NS + g); };
   auto BAR_P = [&](int g) { return bar0 + 8u * (6 + 2 * NS + g); };
   auto BAR_PV = [&](int g) { return bar0 + 8u * (8 + 2 * NS + g); };
+  const uint32_t BAR_XT = bar0 + 8u * (10 + 2 * NS);
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + OFF_TMEM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -163,6 +168,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       mbar_init(BAR_FULL(s), 1);
       mbar_init(BAR_EMPTY(s), 1);
     }
+    mbar_init(BAR_XT, kComputeWarps);
     for (int g = 0; g < 2; ++g) {
       mbar_init(BAR_S(g), 1);
       mbar_init(BAR_SFREE(g), kComputeWarps / 2);
@@ -210,7 +216,7 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const uint32_t x_lo = desc_lo(sbase + OFF_X, 16);
       const uint32_t u_lo = desc_lo(sbase + OFF_U, 16);
       const uint32_t st_k = desc_lo(sbase + OFF_ST, 16);         // stage 0, K-major view
-      bool ok = mbar_wait_warp(BAR_X, 0);
+      bool ok = mbar_wait_warp(XT ? BAR_XT : BAR_X, 0);
       if (!ok) report(2);
       tc_fence_after();
       const int g = warp - kIssuerWarp;
@@ -223,8 +229,13 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         tc_fence_after();
         const uint32_t y_lo = st_k + (uint32_t)s * (STAGE >> 4);
         if (elect_one()) {
-          umma_ss_k64(tmem + T_S + g * BN, x_lo, y_lo, idescS);
-          if (!FWD) umma_ss_k64(tmem + T_W + g * BN, u_lo, y_lo + (COL_TILE >> 4), idescS);
+          if constexpr (XT) {
+            umma_ts_k64(tmem + T_S + g * BN, tmem + T_X, y_lo, idescS);
+            umma_ts_k64(tmem + T_W + g * BN, tmem + T_X + 32, y_lo + (COL_TILE >> 4), idescS);
+          } else {
+            umma_ss_k64(tmem + T_S + g * BN, x_lo, y_lo, idescS);
+            if (!FWD) umma_ss_k64(tmem + T_W + g * BN, u_lo, y_lo + (COL_TILE >> 4), idescS);
+          }
           umma_commit(BAR_S(g));
         }
         __syncwarp();
@@ -290,6 +301,25 @@ dense_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const int col = tile_of(j, cp) * BN + cpart * 32 + lane;
       return (j < J && col < a.ncols) ? -__ldg(a.dvec + (size_t)head_of(cp) * a.ncols + col) : 0.f;
     };
+    if (XT && J > 0) {
+      // copy this warp's 32 rows x 16 bf16 pairs of x (warps 0-7) or u (warps 8-15) from the swizzled
+      // row tile to TMEM: word c of a row is (element 2c, element 2c + 1), the A operand's layout
+      if (!mbar_wait(BAR_X, 0)) report(11);
+      const int cq = warp >> 2, r = qd * 32 + lane;
+      const uint32_t src = sbase + (cq < 2 ? OFF_X : OFF_U) + r * 128;
+      uint32_t xw[16];
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const ulonglong2 w2 = lds_v2(src + (((4 * (cq & 1) + v) ^ (r & 7)) << 4));
+        xw[4 * v] = (uint32_t)w2.x; xw[4 * v + 1] = (uint32_t)(w2.x >> 32);
+        xw[4 * v + 2] = (uint32_t)w2.y; xw[4 * v + 3] = (uint32_t)(w2.y >> 32);
+      }
+      tmem_st16(tl + T_X + cq * 16, xw);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_XT);
+    }
     ColPos pc = pos0;                     // position of this group's current tile
     advance(pc, gp);
     float nxt = rev ? fetch_vec(gp, pc) : 0.f;

@@ -257,6 +257,36 @@ __device__ __forceinline__ void umma_ss_k64(uint32_t d_tmem, uint32_t a_lo, uint
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four K-steps of D[tmem] = A[tmem] B[smem]^T with B K-major (one 128-byte swizzle row of 64
+// bf16 per MN index: 32 bytes per step) and A advancing 8 columns per step.  The first step
+// overwrites D unless `accumulate` is set.
+__device__ __forceinline__ void umma_ts_k64(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                            uint32_t idesc, uint32_t accumulate = 0) {
+  asm volatile(
+      "{\n"
+      ".reg .b64 db;\n"
+      ".reg .b32 a, b;\n"
+      ".reg .pred pf, pt;\n"
+      "setp.ne.b32 pf, %5, 0;\n"
+      "setp.eq.b32 pt, 0, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, pf;\n"
+      "add.u32 a, %1, 8;\n"
+      "add.u32 b, %2, 2;\n"
+      "mov.b64 db, {b, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n"
+      "add.u32 a, %1, 16;\n"
+      "add.u32 b, %2, 4;\n"
+      "mov.b64 db, {b, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n"
+      "add.u32 a, %1, 24;\n"
+      "add.u32 b, %2, 6;\n"
+      "mov.b64 db, {b, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // NK K-steps of D[tmem] (+)= A[tmem] B[smem] with B MN-major (16 K rows = 2048
 // bytes per step) and A advancing 8 columns per step.  `accumulate` applies to the
 // first step; later steps always accumulate.
