@@ -18,8 +18,9 @@
 //   MN-major A operand, the value tile is the MN-major B operand delivered by TMA,
 //   and the accumulators stay in tensor memory for the whole chunk.
 //
-// The first-order and constant rows of the state and the normaliser column of the
-// state build stay on the CUDA-core kernels of fm_moments_ffma.cu.
+// The normaliser column of the state build is a third, small tensor-core kernel here; the
+// first-order and constant rows of the state stay on the kernels of fm_first_tc.cu and
+// fm_moments_ffma.cu.
 #include <cstdlib>
 
 #include "fm_common.cuh"
@@ -510,8 +511,8 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       __syncwarp();
       if (lane == 0) { mbar_arrive(BAR_AFULL(2, h)); mbar_arrive(BAR_AFULL(3, h)); }
     }
-    // ---- epilogue: accumulator rows -> fp32 state (columns 0..63); the normaliser column and the
-    // padding are zeroed here, state_ecol_kernel then adds its partial sums into column 64 ----
+    // ---- epilogue: accumulator rows -> fp32 state (columns 0..63), the normaliser column from the
+    // block state_ecol_tc_kernel left in the first-order rows, zero padding ----
     if (ok && !mbar_wait(BAR_DONE(), 0)) { report(35); ok = false; }
     tc_fence_after();
     if (ok) {
@@ -526,7 +527,7 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       for (int e = 0; e < 16; ++e)
         dst[e] = make_float4(__uint_as_float(tv[4 * e]), __uint_as_float(tv[4 * e + 1]),
                              __uint_as_float(tv[4 * e + 2]), __uint_as_float(tv[4 * e + 3]));
-      dst[16] = make_float4(0.f, 0.f, 0.f, 0.f);   // columns 64..67 (dvp == 68 at d == 64)
+      dst[16] = make_float4(st[(size_t)4096 * a.dvp + f], 0.f, 0.f, 0.f);   // columns 64..67 (dvp == 68 at d == 64)
     }
   }
   tc_fence_before();
@@ -537,92 +538,139 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
   }
 }
 
-// Normaliser column of the second-order rows on the CUDA cores:
-//   state[(a,b)][64] += sum_j e_j y_j[a] y_j[b]   (e = 1, or -dvec)
-// over this CTA's slice of the chunk's tokens (blockIdx.y of gridDim.y slices); the column was
-// zeroed by state_tc_kernel, which runs before on the same stream.  Four groups of 64 threads
-// take every fourth token of a 32-token stage; a thread owns an 8 x 8 block of (a, b), so a
-// token costs it four 16-byte shared-memory loads per 64 FMAs.
-__global__ void __launch_bounds__(256) state_ecol_kernel(const __nv_bfloat16* __restrict__ y,
-                                                         const float* __restrict__ dvec,
-                                                         float* __restrict__ state, int n, int chunk,
-                                                         int nchunk, int dvp, size_t per_state) {
-  __shared__ __align__(16) float stage[2][32][64];
-  float (*ys)[64] = stage[0], (*ye)[64] = stage[1];
+// Normaliser column of the second-order rows on the tensor cores:
+//   state[(a,b)][64] = E[a][b] = sum_j e_j y_j[a] y_j[b] = (Y^T (e o Y))[a][b]   (e = 1, or -dvec)
+// One CTA per (head, chunk).  A 128-token tile of y, as TMA delivers it, is at once the MN-major A
+// operand (features along M) and -- when e = 1 -- the MN-major B operand; with e = -dvec four warps
+// write the scaled rows e_j y_j (rounded to bf16 once, from the fp32 product) into a second tile
+// with the same swizzled offsets.  An M = 128 operand has two 64-wide blocks; the second one is
+// simply the 16 KB that follow the tile in shared memory (the next ring stage, or the first scaled
+// tile after the last stage), so TMEM lanes 64..127 receive products of whatever lies there and are
+// never read; lane a < 64, column b of the accumulator is E[a][b].  The result is left as a dense
+// 64 x 64 block in the state matrix's own first-order rows (4096.. of 4161, 17.7 KB), which nothing has
+// written yet: state_tc_kernel, next on the stream, copies E[a][b] into column 64 of the row (a, b) it
+// writes anyway (4-byte stores scattered over 4096 rows cost more than the whole product), and the
+// first-order state kernels then overwrite the block with the real rows.
+constexpr int EC_THREADS = 192;       // warps 0-3: scaled copy and epilogue; 4: TMA; 5: MMA issuer
+constexpr int EC_NS = 4;              // y-tile ring
+constexpr int EC_STAGE = ST_ZTILE;
+constexpr int EC_OFF_B = EC_NS * EC_STAGE;           // two scaled tiles
+constexpr int EC_OFF_BAR = EC_OFF_B + 2 * ST_ZTILE;
+constexpr int EC_NBAR = 2 * EC_NS + 4 + 1;
+constexpr int EC_OFF_TMEM = EC_OFF_BAR + EC_NBAR * 8;
+constexpr int EC_SMEM = EC_OFF_TMEM + 16 + 1024;
+
+__global__ void __launch_bounds__(EC_THREADS, 2)
+state_ecol_tc_kernel(const __grid_constant__ CUtensorMap tmY, const float* __restrict__ dvec,
+                     float* __restrict__ state, int n, int chunk, int nchunk, int dvp, size_t per_state) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + EC_OFF_BAR;
+  // barriers: y_full[NS] | y_empty[NS] | b_full[2] | b_empty[2] | done
+  auto BAR_YFULL = [&](int s) { return bar0 + 8u * s; };
+  auto BAR_YEMPTY = [&](int s) { return bar0 + 8u * (EC_NS + s); };
+  auto BAR_BFULL = [&](int b) { return bar0 + 8u * (2 * EC_NS + b); };
+  auto BAR_BEMPTY = [&](int b) { return bar0 + 8u * (2 * EC_NS + 2 + b); };
+  const uint32_t BAR_DONE = bar0 + 8u * (2 * EC_NS + 4);
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + EC_OFF_TMEM);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hc = blockIdx.x, head = hc / nchunk, ck = hc % nchunk;
-  const int slice = ((chunk + (int)gridDim.y - 1) / (int)gridDim.y + 31) / 32 * 32;
-  const int t_begin = ck * chunk + (int)blockIdx.y * slice;
-  const int t_end = min(min(n, ck * chunk + chunk), t_begin + slice);
-  if (t_begin >= t_end) return;
-  const int grp = threadIdx.x >> 6, w = threadIdx.x & 63;
-  const int a0 = (w >> 3) * 8, b0 = (w & 7) * 8;
-  float acc[8][8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int jj = 0; jj < 8; ++jj) acc[i][jj] = 0.f;
-  const __nv_bfloat16* yb = y + (size_t)head * n * 64;
-  // 32 tokens x 64 values per stage, 8 bf16 per thread; the next stage's values are fetched into
-  // registers while the current stage is being multiplied
-  const int lr = threadIdx.x >> 3, c8 = (threadIdx.x & 7) * 8;
-  auto fetch = [&](int t0, uint4& v, float& e) {
-    const int tok = t0 + lr;
-    v = make_uint4(0u, 0u, 0u, 0u);
-    e = 0.f;
-    if (tok < t_end) {
-      v = __ldg((const uint4*)(yb + (size_t)tok * 64 + c8));
-      e = dvec ? -__ldg(dvec + (size_t)head * n + tok) : 1.f;
-    }
-  };
-  uint4 v;
-  float e;
-  fetch(t_begin, v, e);
-  for (int t0 = t_begin; t0 < t_end; t0 += 32) {
-    __syncthreads();
-    {
-      const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float lo = __uint_as_float(vw[q] << 16), hi = __uint_as_float(vw[q] & 0xFFFF0000u);
-        ys[lr][c8 + 2 * q] = lo;
-        ys[lr][c8 + 2 * q + 1] = hi;
-        ye[lr][c8 + 2 * q] = lo * e;
-        ye[lr][c8 + 2 * q + 1] = hi * e;
+  const int t_begin = ck * chunk, t_end = min(n, t_begin + chunk);
+  const int nblk = (t_end - t_begin + 127) / 128;
+  const bool scaled = dvec != nullptr;
+
+  if (tid == 0) {
+    for (int s = 0; s < EC_NS; ++s) { mbar_init(BAR_YFULL(s), 1); mbar_init(BAR_YEMPTY(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(BAR_BFULL(b), 4); mbar_init(BAR_BEMPTY(b), 1); }
+    mbar_init(BAR_DONE, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) tmem_alloc(smem_u32((const void*)tmem_slot), 64);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) tma_prefetch_desc(&tmY);
+    for (int k = 0; k < nblk; ++k) {
+      const int s = k % EC_NS;
+      if (!mbar_wait(BAR_YEMPTY(s), (((k / EC_NS) & 1) ^ 1))) { report(41); break; }
+      if (lane == 0) {
+        mbar_expect_tx(BAR_YFULL(s), EC_STAGE);
+        // rows past the end of the sequence are zero-filled; chunks are whole multiples of 128 tokens
+        tma_load_3d(sbase + s * EC_STAGE, &tmY, BAR_YFULL(s), 0, t_begin + k * 128, head);
       }
     }
-    __syncthreads();
-    if (t0 + 32 < t_end) fetch(t0 + 32, v, e);
-#pragma unroll 2
-    for (int r = grp; r < 32; r += 4) {
-      const float4 xa0 = *(const float4*)&ye[r][a0], xa1 = *(const float4*)&ye[r][a0 + 4];
-      const float4 xb0 = *(const float4*)&ys[r][b0], xb1 = *(const float4*)&ys[r][b0 + 4];
-      const float xa[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
-      const float xb[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) acc[i][jj] = fmaf(xa[i], xb[jj], acc[i][jj]);
+  } else if (warp == 5) {
+    constexpr uint32_t idesc = idesc_bf16(128, 64, 1, 1);
+    bool ok = true;
+    for (int k = 0; ok && k < nblk; ++k) {
+      const int s = k % EC_NS, bb = k & 1;
+      if (!mbar_wait_warp(BAR_YFULL(s), (uint32_t)((k / EC_NS) & 1))) { report(42); ok = false; break; }
+      if (scaled && !mbar_wait_warp(BAR_BFULL(bb), (uint32_t)((k >> 1) & 1))) { report(43); ok = false; break; }
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t a_lo = desc_lo(sbase + s * EC_STAGE, ST_ZTILE);
+        const uint32_t b_lo = scaled ? desc_lo(sbase + EC_OFF_B + bb * ST_ZTILE, ST_ZTILE) : a_lo;
+        umma_ss_mn_steps<8>(tmem, a_lo, b_lo, idesc, k > 0 ? 1u : 0u);
+        umma_commit(BAR_YEMPTY(s));
+        if (scaled) umma_commit(BAR_BEMPTY(bb));
+      }
+      __syncwarp();
     }
-  }
-  // the four groups' partial sums are added up in shared memory (the staging arrays are free now),
-  // so the CTA issues one atomic per (a, b)
-  float* red = &stage[0][0][0];
-  static_assert(sizeof(stage) == 4096 * sizeof(float), "the staging arrays must hold one 64 x 64 block");
-  for (int gsel = 0; gsel < 4; ++gsel) {
-    __syncthreads();
-    if (grp == gsel) {
+    if (ok && elect_one()) umma_commit(BAR_DONE);
+    __syncwarp();
+  } else {
+    bool ok = true;
+    if (scaled) {
+      // thread j owns token row j of the block: the eight 16-byte pieces of the row keep their
+      // (swizzled) offsets, so the copy never has to know which piece is which
+      for (int k = 0; ok && k < nblk; ++k) {
+        const int s = k % EC_NS, bb = k & 1;
+        const int tok = t_begin + k * 128 + tid;
+        const float e = (tok < t_end) ? -__ldg(dvec + (size_t)head * n + tok) : 0.f;
+        if (!mbar_wait(BAR_YFULL(s), (uint32_t)((k / EC_NS) & 1))) { report(44); ok = false; break; }
+        if (!mbar_wait(BAR_BEMPTY(bb), (uint32_t)(((k >> 1) & 1) ^ 1))) { report(45); ok = false; break; }
+        const uint32_t src = sbase + s * EC_STAGE + tid * 128, dst = sbase + EC_OFF_B + bb * ST_ZTILE + tid * 128;
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+        for (int c = 0; c < 8; ++c) {
+          const uint4 w = lds128(src + c * 16);
+          const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+          uint32_t o[4];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          float* dst = red + (a0 + i) * 64 + b0 + jj;
-          *dst = (gsel == 0) ? acc[i][jj] : *dst + acc[i][jj];
+          for (int q = 0; q < 4; ++q)
+            o[q] = pack_bf16(e * __uint_as_float(in[q] << 16), e * __uint_as_float(in[q] & 0xFFFF0000u));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + c * 16), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                       "r"(o[3]) : "memory");
         }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_BFULL(bb));
+      }
+    }
+    if (ok && !mbar_wait(BAR_DONE, 0)) { report(46); ok = false; }
+    tc_fence_after();
+    if (ok && warp < 2) {
+      uint32_t tv[64];
+      tmem_ld64(tmem + ((uint32_t)(warp * 32) << 16), tv);
+      tmem_wait_ld();
+      // E[a][0..63] as one contiguous row of the scratch block (see the header comment)
+      float4* row = (float4*)(state + (size_t)hc * per_state + (size_t)4096 * dvp + (size_t)(warp * 32 + lane) * 64);
+#pragma unroll
+      for (int e = 0; e < 16; ++e)
+        row[e] = make_float4(__uint_as_float(tv[4 * e]), __uint_as_float(tv[4 * e + 1]),
+                             __uint_as_float(tv[4 * e + 2]), __uint_as_float(tv[4 * e + 3]));
     }
   }
+  tc_fence_before();
   __syncthreads();
-  float* st = state + (size_t)hc * per_state;
-  for (int i = threadIdx.x; i < 4096; i += 256) atomicAdd(st + (size_t)i * dvp + 64, red[i]);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 64);
+  }
 }
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -693,9 +741,11 @@ int moments_tc_convert(const Ctx& c, int mats, const float* state, void* state_b
   return FASTMAX_OK;
 }
 
-// Second-order rows of the chunk states of (y, z | e): columns 0..63 on the tensor cores,
-// the e column (e = 1 when dvec is null, else -dvec) on the CUDA cores.  The first-order and
-// constant rows are left to moments_chunk_state with p = 1 row range.
+// Second-order rows of the chunk states of (y, z | e) on the tensor cores: columns 0..63 by
+// state_tc_kernel, the e column (e = 1 when dvec is null, else -dvec) by state_ecol_tc_kernel.
+// The first-order and constant rows are NOT valid afterwards (they held the e column's scratch
+// block): the caller builds them next, with first_tc_chunk_state or moments_chunk_state's p = 1
+// row range, both of which write every element of those rows.
 int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
                            const float* dvec, float* state) {
   if (heads == 0 || n == 0) return FASTMAX_OK;
@@ -707,13 +757,17 @@ int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void
   StArgs a;
   a.y = y; a.state = state; a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.dvp = m.dvp;
   a.per_state = (size_t)m.f * m.dvp;
+  // the normaliser column first: the state kernel picks it up in its epilogue
+  CUtensorMap ty;
+  if ((rc = make_map(&ty, y, heads, n))) return rc;
+  FM_CUDA_TRY(cudaFuncSetAttribute(state_ecol_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, EC_SMEM));
+  FM_LAUNCH("fm_moments_state_ecol", c.stream,
+            (state_ecol_tc_kernel<<<(unsigned)((size_t)heads * nchunk), EC_THREADS, EC_SMEM, c.stream>>>(
+                ty, dvec, state, n, chunk, nchunk, m.dvp, a.per_state)));
+  FM_CUDA_TRY(cudaGetLastError());
   FM_CUDA_TRY(cudaFuncSetAttribute(state_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM));
   FM_LAUNCH("fm_moments_tc_state", c.stream,
             (state_tc_kernel<<<(unsigned)((size_t)heads * nchunk * ST_SPLIT), ST_THREADS, ST_SMEM, c.stream>>>(tz, a)));
-  FM_CUDA_TRY(cudaGetLastError());
-  FM_LAUNCH("fm_moments_state_ecol", c.stream,
-            (state_ecol_kernel<<<dim3((unsigned)((size_t)heads * nchunk), 2), 256, 0, c.stream>>>(
-                (const __nv_bfloat16*)y, dvec, state, n, chunk, nchunk, m.dvp, a.per_state)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }
