@@ -222,7 +222,41 @@ struct F1ReadArgs {
   void* out_final;
   float* den_final;
   float* dots;
+  int wide_io;          // out_final / o_add / x are 32-byte aligned: 32-byte accesses in the epilogue
 };
+
+// 16 bytes from shared memory by shared-window address (keeps the epilogue's vector reads off the generic path)
+__device__ __forceinline__ uint4 lds128u(uint32_t saddr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(saddr));
+  return r;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t saddr) {
+  float4 r;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(saddr));
+  return r;
+}
+
+// 32 bytes to / from global memory in one access where the address allows it (one full sector per lane:
+// a thread owns a whole row here, so its accesses never coalesce with its neighbours'), else two of 16.
+__device__ __forceinline__ void stg32(void* p, const uint32_t (&w)[8], bool wide) {
+  if (wide) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+  } else {
+    ((uint4*)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    ((uint4*)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+__device__ __forceinline__ void ldg32(const void* p, uint32_t (&w)[8], bool wide) {
+  if (wide) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]),
+                 "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(p));
+  } else {
+    const uint4 a = ((const uint4*)p)[0], b = ((const uint4*)p)[1];
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  }
+}
 
 template <int DD>
 struct F1R {
@@ -258,6 +292,7 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + C::OFF_TMEM);
   float* ncol = (float*)(smem + C::OFF_VEC);       // S1[a][DD], a < DD
   float* crow = ncol + DD;                         // constant row, DD + 1 values
+  const uint32_t ncol_s = sbase + C::OFF_VEC;      // the same vectors by shared-window address
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tiles = (a.n + 127) / 128;
   const int runs = (tiles + a.run - 1) / a.run;
@@ -362,15 +397,15 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
         // 64-column sub-tile, 16-byte pieces XOR-swizzled by the row), not from global memory again
         if (!mbar_wait(BAR_TF(b), (uint32_t)((i >> 1) & 1))) { report(49); ok = false; break; }
         const int r = qd * 32 + lane;
-        const uint8_t* trow = smem + b * C::TILE + r * 128;
+        const uint32_t trow = sbase + b * C::TILE + r * 128;
         float dot = 0.f;
 #pragma unroll
         for (int sb = 0; sb < C::NSUB; ++sb)
 #pragma unroll
           for (int pc = 0; pc < 8; ++pc) {
-            const uint4 xv = *(const uint4*)(trow + sb * 16384 + ((pc ^ (r & 7)) << 4));
+            const uint4 xv = lds128u(trow + sb * 16384 + ((pc ^ (r & 7)) << 4));
             const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-            const float4 n0 = *(const float4*)(ncol + sb * 64 + 8 * pc), n1 = *(const float4*)(ncol + sb * 64 + 8 * pc + 4);
+            const float4 n0 = lds128f(ncol_s + (sb * 64 + 8 * pc) * 4), n1 = lds128f(ncol_s + (sb * 64 + 8 * pc + 4) * 4);
             const float nc[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -397,41 +432,50 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
           if (lane == 0) mbar_arrive(BAR_AE(b));
         }
         if (tok_ok) {
+          const bool wide = a.wide_io != 0;
 #pragma unroll
-          for (int v8 = 0; v8 < 8; ++v8) {
-            float r[8];
-            const float* vecp = (a.type_b ? ncol : crow) + hcol * 64 + 8 * v8;
-            const float4 c0 = *(const float4*)vecp, c1 = *(const float4*)(vecp + 4);
-            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          for (int v16 = 0; v16 < 4; ++v16) {
+            float r[16];
+            const uint32_t vecp = (a.type_b ? ncol_s : ncol_s + DD * 4) + (hcol * 64 + 16 * v16) * 4;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float acc = __uint_as_float(tv[8 * v8 + e]);
-              r[e] = a.type_b ? A1 * fmaf(extra, cv[e], acc) : fmaf(A1, acc, cv[e]);
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const float4 c4 = lds128f(vecp + 16 * q4);
+              const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float acc = __uint_as_float(tv[16 * v16 + 4 * q4 + e]);
+                r[4 * q4 + e] = a.type_b ? A1 * fmaf(extra, cv[e], acc) : fmaf(A1, acc, cv[e]);
+              }
             }
             if (a.final) {
-              uint4 w;
-              w.x = pack_bf16(r[0] * scale, r[1] * scale); w.y = pack_bf16(r[2] * scale, r[3] * scale);
-              w.z = pack_bf16(r[4] * scale, r[5] * scale); w.w = pack_bf16(r[6] * scale, r[7] * scale);
-              ((uint4*)((__nv_bfloat16*)a.out_final + grow * DD + hcol * 64))[v8] = w;
-              if (a.dots) {
-                const uint4 xv = __ldg((const uint4*)((const __nv_bfloat16*)a.x + grow * DD + hcol * 64) + v8);
-                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+              uint32_t w[8];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
+              for (int e = 0; e < 8; ++e) w[e] = pack_bf16(r[2 * e] * scale, r[2 * e + 1] * scale);
+              stg32((__nv_bfloat16*)a.out_final + grow * DD + hcol * 64 + 16 * v16, w, wide);
+              if (a.dots) {
+                uint32_t xw[8];
+                ldg32((const __nv_bfloat16*)a.x + grow * DD + hcol * 64 + 16 * v16, xw, wide);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
                   part = fmaf(r[2 * e], __uint_as_float(xw[e] << 16), part);
                   part = fmaf(r[2 * e + 1], __uint_as_float(xw[e] & 0xFFFF0000u), part);
                 }
               }
             } else {
-              float4* dst = (float4*)(a.o_add + grow * DD + hcol * 64) + 2 * v8;
-              float4 w0 = make_float4(r[0], r[1], r[2], r[3]), w1 = make_float4(r[4], r[5], r[6], r[7]);
-              if (a.accumulate) {
-                const float4 o0 = dst[0], o1 = dst[1];
-                w0.x += o0.x; w0.y += o0.y; w0.z += o0.z; w0.w += o0.w;
-                w1.x += o1.x; w1.y += o1.y; w1.z += o1.z; w1.w += o1.w;
+#pragma unroll
+              for (int h8 = 0; h8 < 2; ++h8) {
+                float* dst = a.o_add + grow * DD + hcol * 64 + 16 * v16 + 8 * h8;
+                uint32_t w[8];
+                if (a.accumulate) {
+                  ldg32(dst, w, wide);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) w[e] = __float_as_uint(r[8 * h8 + e] + __uint_as_float(w[e]));
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) w[e] = __float_as_uint(r[8 * h8 + e]);
+                }
+                stg32(dst, w, wide);
               }
-              dst[0] = w0;
-              dst[1] = w1;
             }
           }
         }
@@ -552,6 +596,7 @@ int first_tc_readout(const Ctx& c, int type_b, int heads, int n, int chunk, int 
   a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.per_chunk = per_chunk; a.dvp = m.dvp; a.rows = m.f;
   a.f_lin = p.d * p.d - m.f0; a.type_b = type_b; a.accumulate = accumulate;
   a.final = final; a.out_final = out_final; a.den_final = den_final; a.dots = dots;
+  a.wide_io = (((uintptr_t)out_final | (uintptr_t)o_add | (uintptr_t)x) & 31) == 0;
   // runs of up to 8 tiles that never cross a chunk (chunks are multiples of 256 tokens)
   // a CTA pays for loading the state copy and the vector terms once per run, so runs are as long as
   // the chunk allows (a run never crosses a chunk; chunks are multiples of 256 tokens), at most 32 tiles --
