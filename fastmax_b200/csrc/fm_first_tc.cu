@@ -237,27 +237,6 @@ __device__ __forceinline__ float4 lds128f(uint32_t saddr) {
   return r;
 }
 
-// 32 bytes to / from global memory in one access where the address allows it (one full sector per lane:
-// a thread owns a whole row here, so its accesses never coalesce with its neighbours'), else two of 16.
-__device__ __forceinline__ void stg32(void* p, const uint32_t (&w)[8], bool wide) {
-  if (wide) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-  } else {
-    ((uint4*)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    ((uint4*)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-  }
-}
-__device__ __forceinline__ void ldg32(const void* p, uint32_t (&w)[8], bool wide) {
-  if (wide) {
-    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]),
-                 "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(p));
-  } else {
-    const uint4 a = ((const uint4*)p)[0], b = ((const uint4*)p)[1];
-    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-  }
-}
-
 template <int DD>
 struct F1R {
   static constexpr int NSUB = DD / 64;

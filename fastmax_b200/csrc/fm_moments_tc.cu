@@ -62,6 +62,7 @@ struct RtArgs {
   const stat_t* stat_k;
   float a2, lim;
   int n, chunk, nchunk, state_per_chunk;
+  int wide_io;         // out_a / out_b are 32-byte aligned
   int mode;            // 0: type A on two token tiles, 1: type B on two token tiles,
                        // 2: one token tile, group 0 type A and group 1 type B
 };
@@ -241,20 +242,31 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
       }
       if (ok && !type_b && tok_ok) {
-        float4* dst = (float4*)(a.out_a + grow * D);
+        // a thread owns its 256-byte row: 32-byte stores write whole sectors
+        float* dst = a.out_a + grow * D;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) dst[e] = make_float4(ut[4 * e], ut[4 * e + 1], ut[4 * e + 2], ut[4 * e + 3]);
+        for (int e = 0; e < 8; ++e) {
+          uint32_t w[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) w[q] = __float_as_uint(ut[8 * e + q]);
+          stg32(dst + 8 * e, w, a.wide_io != 0);
+        }
         if (a.den_a) a.den_a[grow] = ut[64];
       }
       if (ok && type_b && tok_ok) {
         const float k2 = 2.f * A2;
-        float4* dst = (float4*)(a.out_b + grow * D);
+        float* dst = a.out_b + grow * D;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float f0, f1, f2, f3;
-          unpack2(xa[2 * e], f0, f1);
-          unpack2(xa[2 * e + 1], f2, f3);
-          dst[e] = make_float4(k2 * f0, k2 * f1, k2 * f2, k2 * f3);
+        for (int e = 0; e < 8; ++e) {
+          uint32_t w[8];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float f0, f1;
+            unpack2(xa[4 * e + q], f0, f1);
+            w[2 * q] = __float_as_uint(k2 * f0);
+            w[2 * q + 1] = __float_as_uint(k2 * f1);
+          }
+          stg32(dst + 8 * e, w, a.wide_io != 0);
         }
       }
     }
@@ -790,6 +802,7 @@ int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int 
   a.stat_k = p.normalize ? stats + p.bh : nullptr;
   a.a2 = p.a2; a.lim = p.lim;
   a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.state_per_chunk = state_per_chunk; a.mode = mode;
+  a.wide_io = (((uintptr_t)out_a | (uintptr_t)out_b) & 31) == 0;
   const int per_cta = (mode == 2) ? 128 : 256;
   const unsigned grid = (unsigned)((size_t)heads * ((n + per_cta - 1) / per_cta));
   FM_CUDA_TRY(cudaFuncSetAttribute(readout_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));

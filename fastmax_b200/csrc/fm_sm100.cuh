@@ -429,6 +429,27 @@ __device__ __forceinline__ uint32_t pack_bf16_2(uint64_t v) {
   return pack_bf16(lo, hi);
 }
 
+// 32 bytes to / from global memory in one access where the address allows it (one full sector per lane:
+// a thread owns a whole row here, so its accesses never coalesce with its neighbours'), else two of 16.
+__device__ __forceinline__ void stg32(void* p, const uint32_t (&w)[8], bool wide) {
+  if (wide) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+  } else {
+    ((uint4*)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    ((uint4*)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+__device__ __forceinline__ void ldg32(const void* p, uint32_t (&w)[8], bool wide) {
+  if (wide) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]),
+                 "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(p));
+  } else {
+    const uint4 a = ((const uint4*)p)[0], b = ((const uint4*)p)[1];
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  }
+}
+
 // ---- helpers shared by the score kernels ------------------------------------------------------
 // 16 bytes from shared memory by shared-window address (keeps the load off the generic path)
 __device__ __forceinline__ ulonglong2 lds_v2(uint32_t saddr) {
@@ -445,6 +466,9 @@ __device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfl
                                            const float* add, const __nv_bfloat16* xr, float scale,
                                            float pre = 1.f) {
   float part = 0.f;
+  // a thread owns its row segment, so neighbouring lanes never share a sector: 32-byte accesses
+  // (whole sectors) where the three addresses allow them
+  const bool wide = (((uintptr_t)dst | (uintptr_t)add | (uintptr_t)xr) & 31) == 0;
 #pragma unroll
   for (int c0 = 0; c0 < NC; c0 += 32) {
     uint32_t ov[32];
@@ -452,27 +476,32 @@ __device__ __forceinline__ float store_row(uint32_t taddr, bool row_ok, __nv_bfl
     tmem_wait_ld();
     if (row_ok) {
 #pragma unroll
-      for (int v8 = 0; v8 < 4; ++v8) {
-        float f[8];
+      for (int v16 = 0; v16 < 2; ++v16) {
+        float f[16];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[v8 * 8 + e]) * pre;   // pre scales the accumulator only
+        for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(ov[v16 * 16 + e]) * pre;   // pre scales the accumulator only
         if (add) {
-          const float4 a0 = __ldg((const float4*)(add + c0) + 2 * v8);
-          const float4 a1 = __ldg((const float4*)(add + c0) + 2 * v8 + 1);
-          f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
-          f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t aw[8];
+            ldg32(add + c0 + 16 * v16 + 8 * h, aw, wide);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[8 * h + e] += __uint_as_float(aw[e]);
+          }
         }
+        uint32_t w[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] *= scale;
-        uint4 w;
-        w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]);
-        w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
-        ((uint4*)(dst + c0))[v8] = w;
+        for (int e = 0; e < 8; ++e) {
+          f[2 * e] *= scale;
+          f[2 * e + 1] *= scale;
+          w[e] = pack_bf16(f[2 * e], f[2 * e + 1]);
+        }
+        stg32(dst + c0 + 16 * v16, w, wide);
         if (xr) {
-          const uint4 xv = __ldg((const uint4*)(xr + c0) + v8);
-          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+          uint32_t xw[8];
+          ldg32(xr + c0 + 16 * v16, xw, wide);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+          for (int e = 0; e < 8; ++e) {
             part = fmaf(f[2 * e], __uint_as_float(xw[e] << 16), part);
             part = fmaf(f[2 * e + 1], __uint_as_float(xw[e] & 0xFFFF0000u), part);
           }
