@@ -255,7 +255,7 @@ static size_t stats_words_bytes(const fastmax_problem& p) {
 }
 static size_t kept_bytes(const fastmax_problem& p) {
   if (!p.mask) return moment_total_bytes(p);
-  const size_t states = moment_state_bytes(p, p.nk);
+  const size_t states = moment_state_bytes(p, p.nk) + moment_kept16_bytes(p);
   const size_t es = p.dtype == FASTMAX_BF16 ? 2 : 4;
   const size_t held = es * (size_t)p.d * (2 * (size_t)p.bh * p.nq + 2 * (size_t)p.bhkv * p.nk);
   return states <= 2 * held ? states : 0;

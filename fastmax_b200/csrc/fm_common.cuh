@@ -173,9 +173,10 @@ MomentDims moment_dims(int d, int p = 2);
 int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
                         const float* den, const float* delta, int ext, float* state,
                         int first_order_only = 0);
-// exclusive running sum over chunks (reverse = suffix), started from base; total = own sum
+// exclusive running sum over chunks (reverse = suffix), started from base; total = own sum; state rows
+// before first_row are neither read nor written
 int moments_prefix(const Ctx& c, int heads, int nchunk, float* state, const float* base, float* total,
-                   int reverse, int write);
+                   int reverse, int write, int first_row = 0);
 int moments_readout(const Ctx& c, int mode_b, int heads, int n, int chunk, int state_per_chunk,
                     const void* x, const void* u, const float* den, const float* delta, int ext,
                     const float* state, const stat_t* stats, float* o_add, float* den_add,
@@ -187,6 +188,8 @@ size_t moments_tc_state_bytes(int mats);
 int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y, const void* z,
                            const float* dvec, float* state);
 int moments_tc_convert(const Ctx& c, int mats, const float* state, void* state_bf16);
+int moments_tc_prefix_convert(const Ctx& c, int heads, int nchunk, const float* state, const float* base,
+                              float* total, int reverse, void* state_bf16);
 int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int state_per_chunk,
                        const void* x, const void* u, const float* uvec, const void* state_bf16,
                        const stat_t* stats, float* out_a, float* den_a, float* out_b);
@@ -213,13 +216,15 @@ bool moments_supports(const fastmax_problem& p);
 size_t moment_state_bytes(const fastmax_problem& p, int n);
 size_t moment_total_bytes(const fastmax_problem& p);
 size_t state16_bytes(const fastmax_problem& p, int n);   // bf16 operand copies of the states of n tokens
+size_t moment_kept16_bytes(const fastmax_problem& p);    // bf16 second-order copies kept beside the fp32 states
 MomFwdWs moments_fwd_layout(const fastmax_problem& p);
 MomBwdWs moments_bwd_layout(const fastmax_problem& p);
 int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
                     const FwdOut& o, void* workspace, float* total_keep = nullptr);
 int moments_forward_finish(const Ctx& c, const void* q, const void* k, const void* v,
                            const stat_t* stats, float* kv_states, const float* s_base,
-                           float* o_add, float* den_add, void* s16, const FwdOut& o);
+                           float* o_add, float* den_add, void* s16, const FwdOut& o,
+                           void* second16 = nullptr);
 // chunk states of (y, z | e) with the best kernels for the problem; gs/dvec are the bf16
 // gradient rows and grad_out.out/den when ext == 1 and the tensor-core path is used
 int moments_build_states(const Ctx& c, int n, const void* y, const void* z, const float* den,

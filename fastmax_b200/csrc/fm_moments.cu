@@ -38,6 +38,12 @@ size_t state16_bytes(const fastmax_problem& p, int n) {
   return state16_second(p, mats) + (first_tc_supports(p) ? up256(first_tc_copy_bytes(p, mats)) : 0);
 }
 
+// second-order bf16 copies of the key/value chunk prefixes that a causal forward leaves for the backward
+size_t moment_kept16_bytes(const fastmax_problem& p) {
+  const int L = moments_chunk(p);
+  return state16_second(p, p.bh * ((p.nk + L - 1) / L));
+}
+
 bool moments_all_tc(const fastmax_problem& p) {
   return dense_tc_supports(p) && first_tc_supports(p) && (p.p == 1 || moments_tc_supports(p));
 }
@@ -92,10 +98,11 @@ int moments_build_states(const Ctx& c, int n, const void* y, const void* z, cons
 }
 
 // read-out of prefix (or total) states for n tokens; mode 0: type A, 1: type B, 2: both on x
+// second16 (may be null): second-order bf16 copies that exist already (prefix_states, or kept by the forward)
 static int read_states(const Ctx& c, int mode, int n, int per_chunk, const void* x, const void* u,
                        const float* den, const float* delta, int ext, const void* gs, const float* dvec,
                        const float* states, void* s16, const stat_t* stats, float* out_a, float* den_a,
-                       float* out_b) {
+                       float* out_b, const void* second16 = nullptr) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   int rc;
@@ -103,9 +110,9 @@ static int read_states(const Ctx& c, int mode, int n, int per_chunk, const void*
   const bool tc1 = first_tc_supports(p) && (p.p == 1 || tc2);
   const int mats = p.bh * (per_chunk ? (n + L - 1) / L : 1);
   if (tc2) {
-    if ((rc = moments_tc_convert(c, mats, states, s16))) return rc;
-    if ((rc = moments_tc_readout(c, mode, p.bh, n, L, per_chunk, x, ext ? gs : u, ext ? dvec : nullptr, s16,
-                                 stats, out_a, den_a, out_b)))
+    if (!second16 && (rc = moments_tc_convert(c, mats, states, s16))) return rc;
+    if ((rc = moments_tc_readout(c, mode, p.bh, n, L, per_chunk, x, ext ? gs : u, ext ? dvec : nullptr,
+                                 second16 ? second16 : s16, stats, out_a, den_a, out_b)))
       return rc;
   }
   if (tc1) {
@@ -145,19 +152,35 @@ static int read_first_final(const Ctx& c, int type_b, int n, const void* tile, c
                           nullptr, 0, final, out, den_out, dots);
 }
 
+// Exclusive running sums over the chunks of every head (per-chunk mode).  With `fuse` and the tensor-core
+// second-order part, the second-order rows go straight to their bf16 transposed copies at `second16` in one
+// pass over the raw states and stay raw in `states` (nothing else reads them); only the first-order rows are
+// summed in place.  *ready tells whether `second16` holds the copies.
+static int prefix_states(const Ctx& c, int nchunk, float* states, const float* base, int reverse, bool fuse,
+                         void* second16, bool* ready) {
+  const fastmax_problem& p = c.p;
+  *ready = fuse && p.p == 2 && moments_tc_supports(p);
+  if (!*ready) return moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1);
+  int rc;
+  if ((rc = moments_tc_prefix_convert(c, p.bh, nchunk, states, base, nullptr, reverse, second16))) return rc;
+  return moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1, p.d * p.d);
+}
+
 // ---- forward -----------------------------------------------------------------------
 // kv_states: raw chunk states of (k, v) for this shard (already built); s_base: sum of the
 // totals of all earlier shards or null.  Turns the states into prefixes in place.
 int moments_forward_finish(const Ctx& c, const void* q, const void* k, const void* v,
                            const stat_t* stats, float* kv_states, const float* s_base,
-                           float* o_add, float* den_add, void* s16, const FwdOut& o) {
+                           float* o_add, float* den_add, void* s16, const FwdOut& o, void* second16) {
   const fastmax_problem& p = c.p;
   const int L = moments_chunk(p);
   const int nchunk = (p.nk + L - 1) / L;
   int rc;
-  if ((rc = moments_prefix(c, p.bh, nchunk, kv_states, s_base, nullptr, 0, 1))) return rc;
+  // second16 != null: the caller does not need the fp32 second-order prefixes (see prefix_states)
+  bool ready;
+  if ((rc = prefix_states(c, nchunk, kv_states, s_base, 0, second16 != nullptr, second16, &ready))) return rc;
   if ((rc = read_states(c, 0, p.nq, 1, q, nullptr, nullptr, nullptr, 0, nullptr, nullptr, kv_states, s16,
-                        stats, o_add, den_add, nullptr)))
+                        stats, o_add, den_add, nullptr, ready ? second16 : nullptr)))
     return rc;
   ChunkAdd ca;
   ca.chunk = L;
@@ -168,7 +191,9 @@ int moments_forward_finish(const Ctx& c, const void* q, const void* k, const voi
 }
 
 // total_keep (may be null): where the forward leaves what the backward would otherwise rebuild from k and v --
-// unmasked: the total key/value state; causal: the exclusive prefixes of the key/value chunk states
+// unmasked: the total key/value state; causal: the chunk states of the keys and values (first-order rows as
+// exclusive prefixes; with the tensor-core second-order part those rows stay raw and their prefixes follow
+// as bf16 transposed copies, moment_kept16_bytes)
 int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, const stat_t* stats,
                     const FwdOut& o, void* workspace, float* total_keep) {
   const fastmax_problem& p = c.p;
@@ -182,7 +207,12 @@ int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, c
   int rc;
   void* s16 = ws + w.s16;
   if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
-  if (p.mask) return moments_forward_finish(c, q, k, v, stats, states, nullptr, o_add, den_add, s16, o);
+  if (p.mask) {
+    // second-order prefixes go straight to their bf16 copies: behind the kept fp32 states when the
+    // backward will want them again, else in the workspace
+    void* second16 = total_keep ? (void*)((char*)total_keep + moment_state_bytes(p, p.nk)) : s16;
+    return moments_forward_finish(c, q, k, v, stats, states, nullptr, o_add, den_add, s16, o, second16);
+  }
   // unmasked: every query reads the total of all keys
   const int nchunk = (p.nk + L - 1) / L;
   if ((rc = moments_prefix(c, p.bh, nchunk, states, nullptr, total, 0, 0))) return rc;
@@ -279,17 +309,22 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
   if (p.mask) {
     // the key/value prefixes are rebuilt (the forward does not keep them), used for grad_q,
     // then the buffer is reused for the query/gradient states
+    bool ready = false;
+    const void* kv16 = nullptr;   // second-order bf16 copies of the key/value prefixes, where they exist already
     if (!kv_total_kept) {
       if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
-      if ((rc = moments_prefix(c, p.bh, nck, states, nullptr, nullptr, 0, 1))) return rc;
+      if ((rc = prefix_states(c, nck, states, nullptr, 0, true, s16, &ready))) return rc;
+      if (ready) kv16 = s16;
+    } else if (moment_kept16_bytes(p) > 0) {
+      kv16 = (const char*)kv_total_kept + moment_state_bytes(p, p.nk);
     }
     if ((rc = read_states(c, 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec,
-                          kv_total_kept ? kv_total_kept : states, s16, stats, nullptr, nullptr, gq_add)))
+                          kv_total_kept ? kv_total_kept : states, s16, stats, nullptr, nullptr, gq_add, kv16)))
       return rc;
     if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
-    if ((rc = moments_prefix(c, p.bh, ncq, states, nullptr, nullptr, 1, 1))) return rc;
+    if ((rc = prefix_states(c, ncq, states, nullptr, 1, true, s16, &ready))) return rc;
     if ((rc = read_states(c, 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr, states, s16, stats,
-                          gv_add, nullptr, gk_add)))
+                          gv_add, nullptr, gk_add, ready ? s16 : nullptr)))
       return rc;
     ChunkAdd ca;
     ca.chunk = L;

@@ -397,11 +397,11 @@ int moments_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* y
 }
 
 int moments_prefix(const Ctx& c, int heads, int nchunk, float* state, const float* base, float* total,
-                   int reverse, int write) {
+                   int reverse, int write, int first_row) {
   if (heads == 0 || nchunk == 0) return FASTMAX_OK;
   const MomentDims m = moment_dims(c.p.d, c.p.p);
   const size_t per = (size_t)m.f * m.dvp;
-  const size_t first = 0;
+  const size_t first = (size_t)first_row * m.dvp;   // rows before it are left alone (dvp is a multiple of 4)
   if ((((uintptr_t)state | (uintptr_t)base | (uintptr_t)total) & 15) != 0)
     return fail(FASTMAX_E_ARG, "moment states and totals must be 16-byte aligned");
   dim3 grid((unsigned)((per - first + 1023) / 1024), heads);   // four elements per thread

@@ -305,6 +305,88 @@ __global__ void __launch_bounds__(256) state_to_bf16t_kernel(const float* __rest
 }
 
 // =====================================================================================
+// Running sum over the chunks of a head and the bf16 transposed copy in one pass, second-order
+// rows only:  out[m][c*64 + b][a] = bf16( base[(b*64 + a)][c] + sum of state[m'][(b*64 + a)][c] over
+// the chunks m' before m (after m when reverse) ).  One CTA per (head, b) keeps its 64 x 68 block of
+// the running sum in registers, in fp32, walks the chunks in order and reads every raw chunk state
+// once; the fp32 states are left as they are.  `total` (may be null) gets the sum over this head's
+// chunks without the base.  The block with b == 64 zeroes the padding rows of every copy.
+// =====================================================================================
+__global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restrict__ state,
+                                                           const float* __restrict__ base,
+                                                           float* __restrict__ total,
+                                                           __nv_bfloat16* __restrict__ out, int nchunk, int dvp,
+                                                           size_t per_state, int reverse) {
+  __shared__ float blk[64][69];
+  const int head = blockIdx.y, b = blockIdx.x, t = threadIdx.x;
+  if (b == 64) {
+    for (int i = 0; i < nchunk; ++i) {
+      uint32_t* o = (uint32_t*)(out + ((size_t)(head * nchunk + i) * NROWS_TP + NROWS_T) * 64);
+      for (int w = t; w < (NROWS_TP - NROWS_T) * 32; w += 256) o[w] = 0u;
+    }
+    return;
+  }
+  constexpr int NV = 64 * 68 / 4;                    // float4 pieces of the block (dvp == 68)
+  const size_t blk_off = (size_t)b * 64 * dvp;       // rows (b, a = 0..63) are contiguous
+  float4 run[5], nxt[5];
+#pragma unroll
+  for (int u = 0; u < 5; ++u) {
+    const int v = t + u * 256;
+    run[u] = (base && v < NV) ? *(const float4*)(base + (size_t)head * per_state + blk_off + 4 * v)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float4 start[5];
+#pragma unroll
+  for (int u = 0; u < 5; ++u) start[u] = run[u];
+  auto load = [&](int i, float4 (&r)[5]) {
+    const int c = reverse ? nchunk - 1 - i : i;
+    const float* src = state + (size_t)(head * nchunk + c) * per_state + blk_off;
+#pragma unroll
+    for (int u = 0; u < 5; ++u) {
+      const int v = t + u * 256;
+      r[u] = (i < nchunk && v < NV) ? __ldcs((const float4*)(src + 4 * v)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  load(0, nxt);
+  for (int i = 0; i < nchunk; ++i) {
+    const int c = reverse ? nchunk - 1 - i : i;
+    // the exclusive running sum of this chunk, transposed through shared memory
+#pragma unroll
+    for (int u = 0; u < 5; ++u) {
+      const int v = t + u * 256;
+      if (v < NV) {
+        const int e = 4 * v, aa = e / 68, cc = e % 68;   // 68 is a multiple of 4: a piece never straddles rows
+        blk[aa][cc] = run[u].x; blk[aa][cc + 1] = run[u].y; blk[aa][cc + 2] = run[u].z; blk[aa][cc + 3] = run[u].w;
+      }
+    }
+    float4 cur[5];
+#pragma unroll
+    for (int u = 0; u < 5; ++u) cur[u] = nxt[u];
+    load(i + 1, nxt);                                  // in flight during the transposed write
+    __syncthreads();
+    uint32_t* o = (uint32_t*)(out + (size_t)(head * nchunk + c) * NROWS_TP * 64);
+    for (int w = t; w < 65 * 32; w += 256) {
+      const int cc = w >> 5, ap = (w & 31) * 2;
+      o[((size_t)cc * 64 + b) * 32 + (w & 31)] = pack_bf16(blk[ap][cc], blk[ap + 1][cc]);
+    }
+#pragma unroll
+    for (int u = 0; u < 5; ++u) {
+      run[u].x += cur[u].x; run[u].y += cur[u].y; run[u].z += cur[u].z; run[u].w += cur[u].w;
+    }
+    __syncthreads();
+  }
+  if (total) {
+#pragma unroll
+    for (int u = 0; u < 5; ++u) {
+      const int v = t + u * 256;
+      if (v < NV)
+        *(float4*)(total + (size_t)head * per_state + blk_off + 4 * v) =
+            make_float4(run[u].x - start[u].x, run[u].y - start[u].y, run[u].z - start[u].z, run[u].w - start[u].w);
+    }
+  }
+}
+
+// =====================================================================================
 // state build: T2[(a,b)][c] = sum_j y_j[a] y_j[b] z_j[c],  c < 64
 // One CTA owns 8 values of a -- four accumulator tiles of (2 a x 64 b) rows by 64 columns,
 // TMEM columns 0..255 -- for one chunk of one head and walks the chunk in blocks of 128
@@ -749,6 +831,23 @@ int moments_tc_convert(const Ctx& c, int mats, const float* state, void* state_b
   FM_LAUNCH("fm_moments_state_bf16", c.stream,
             (state_to_bf16t_kernel<<<grid, 256, 0, c.stream>>>(state, (__nv_bfloat16*)state_bf16, m.dvp,
                                                                (size_t)m.f * m.dvp)));
+  FM_CUDA_TRY(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+// Exclusive running sums over chunks (from `base`, per head, may be null) of the second-order rows,
+// written as the read-out's bf16 transposed copies; the fp32 states stay raw.  `total` as in
+// moments_prefix.  The first-order rows are the caller's business (moments_prefix with a row range).
+int moments_tc_prefix_convert(const Ctx& c, int heads, int nchunk, const float* state, const float* base,
+                              float* total, int reverse, void* state_bf16) {
+  if (heads == 0 || nchunk == 0) return FASTMAX_OK;
+  const MomentDims m = moment_dims(64);
+  if ((((uintptr_t)state | (uintptr_t)base | (uintptr_t)total) & 15) != 0)
+    return fail(FASTMAX_E_ARG, "moment states and totals must be 16-byte aligned");
+  dim3 grid(65, heads);
+  FM_LAUNCH("fm_moments_prefix_bf16", c.stream,
+            (prefix_bf16t_kernel<<<grid, 256, 0, c.stream>>>(state, base, total, (__nv_bfloat16*)state_bf16, nchunk,
+                                                             m.dvp, (size_t)m.f * m.dvp, reverse)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }

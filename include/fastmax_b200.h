@@ -119,8 +119,9 @@ int fastmax_b200_wait_selftest(long long limit_clocks, void* stream);
 /* Bytes of the per-head statistics buffer that forward writes and backward
  * reads: the max row norms and their row indices and, for problems that run on
  * the moment family, the key/value moment states backward would otherwise
- * rebuild (unmasked: their total; causal: the per-chunk prefixes, about the
- * size of q + k + v + out at d = 64).  backward must be given the buffer the
+ * rebuild (unmasked: their total; causal: the per-chunk states and the bf16
+ * copies of their running sums that the read-out multiplies, about 1.6 times
+ * the size of q + k + v + out at d = 64).  backward must be given the buffer the
  * forward call of the same problem filled; with normalize == 0 it may be NULL,
  * and backward then recomputes what it needs.  Replaces the reference's
  * qnorms/knorms/qmaxes/kmaxes temporaries (reference fastmax_cuda_forward.cu:
