@@ -616,12 +616,34 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       tmem_ld64(tmem + m * 64 + ((uint32_t)(qd * 32) << 16), tv);
       tmem_wait_ld();
       const int f = (a0 + 2 * m + a_sub) * 64 + b;
-      float4* dst = (float4*)(st + (size_t)f * a.dvp);
+      float* dst = st + (size_t)f * a.dvp;
+      const uint32_t ecol = __float_as_uint(st[(size_t)4096 * a.dvp + f]);   // column 64; 65..67 are padding (dvp == 68)
+      // A thread owns its 272-byte row, so its stores share no sector with its neighbours': 32-byte stores
+      // (whole sectors) wherever the row allows.  A row that starts on a 32-byte boundary is 8 x 32 + 16
+      // bytes, one that starts 16 bytes past a boundary is 16 + 8 x 32 (rows and matrices are 16-byte multiples).
+      if (((uintptr_t)dst & 16) != 0) {
+        *(float4*)dst = make_float4(__uint_as_float(tv[0]), __uint_as_float(tv[1]), __uint_as_float(tv[2]),
+                                    __uint_as_float(tv[3]));
 #pragma unroll
-      for (int e = 0; e < 16; ++e)
-        dst[e] = make_float4(__uint_as_float(tv[4 * e]), __uint_as_float(tv[4 * e + 1]),
-                             __uint_as_float(tv[4 * e + 2]), __uint_as_float(tv[4 * e + 3]));
-      dst[16] = make_float4(st[(size_t)4096 * a.dvp + f], 0.f, 0.f, 0.f);   // columns 64..67 (dvp == 68 at d == 64)
+        for (int e = 0; e < 8; ++e) {
+          uint32_t w[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int col = 4 + 8 * e + q;
+            w[q] = col < 64 ? tv[col < 64 ? col : 0] : (col == 64 ? ecol : 0u);
+          }
+          stg32(dst + 4 + 8 * e, w, true);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          uint32_t w[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) w[q] = tv[8 * e + q];
+          stg32(dst + 8 * e, w, true);
+        }
+        *(float4*)(dst + 64) = make_float4(__uint_as_float(ecol), 0.f, 0.f, 0.f);
+      }
     }
   }
   tc_fence_before();
