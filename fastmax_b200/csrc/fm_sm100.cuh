@@ -287,6 +287,20 @@ __device__ __forceinline__ void umma_ts_k64(uint32_t d_tmem, uint32_t a_tmem, ui
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One K=16 step of D[tmem] (+)= A[tmem] B[smem] with the low descriptor word given.
+__device__ __forceinline__ void umma_ts_1(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .b64 db;\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // NK K-steps of D[tmem] (+)= A[tmem] B[smem] with B MN-major (16 K rows = 2048
 // bytes per step) and A advancing 8 columns per step.  `accumulate` applies to the
 // first step; later steps always accumulate.
