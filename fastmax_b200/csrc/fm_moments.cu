@@ -263,9 +263,11 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
       (rc = moments_backward_dq_far(c, q, den, stats, grad_out, delta, dvec, gs, s_states, gq_add, s16)))
     return rc;
   // grad_k and grad_v read the suffix sums of the query/gradient states
-  if ((rc = moments_prefix(c, p.bh, nchunk, r_states, r_base, nullptr, 1, 1))) return rc;
+  // (nothing reads r_states after this call, so their second-order rows may stay raw: prefix_states)
+  bool ready;
+  if ((rc = prefix_states(c, nchunk, r_states, r_base, 1, true, s16, &ready))) return rc;
   if ((rc = read_states(c, 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr, r_states, s16, stats,
-                        gv_add, nullptr, gk_add)))
+                        gv_add, nullptr, gk_add, ready ? s16 : nullptr)))
     return rc;
   ChunkAdd ca;
   ca.chunk = L;

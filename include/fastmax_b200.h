@@ -209,7 +209,8 @@ int fastmax_b200_backward(const fastmax_problem* prob,
  *                     shard_backward will be given (shard_backward_workspace_bytes)
  *   shard_backward    r_base = sum of later shards' qg_total (NULL on the last);
  *                     writes the gradients without the normalisation row and the
- *                     per-head dots (bh + bhkv floats, zeroed here)
+ *                     per-head dots (bh + bhkv floats, zeroed here); consumes qg_states
+ *                     (their contents are undefined afterwards)
  *   shard_norm_fixup  after dots were summed over shards: corrects the max-norm row
  *                     on the shard that owns it
  * Unmasked shards (mask = 0): every token reads the totals of ALL shards, so the caller
