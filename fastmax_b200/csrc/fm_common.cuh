@@ -189,7 +189,7 @@ int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void
                            const float* dvec, float* state);
 int moments_tc_convert(const Ctx& c, int mats, const float* state, void* state_bf16);
 int moments_tc_prefix_convert(const Ctx& c, int heads, int nchunk, const float* state, const float* base,
-                              float* total, int reverse, void* state_bf16);
+                              int reverse, void* state_bf16);
 int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int state_per_chunk,
                        const void* x, const void* u, const float* uvec, const void* state_bf16,
                        const stat_t* stats, float* out_a, float* den_a, float* out_b);

@@ -162,7 +162,7 @@ static int prefix_states(const Ctx& c, int nchunk, float* states, const float* b
   *ready = fuse && p.p == 2 && moments_tc_supports(p);
   if (!*ready) return moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1);
   int rc;
-  if ((rc = moments_tc_prefix_convert(c, p.bh, nchunk, states, base, nullptr, reverse, second16))) return rc;
+  if ((rc = moments_tc_prefix_convert(c, p.bh, nchunk, states, base, reverse, second16))) return rc;
   return moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1, p.d * p.d);
 }
 

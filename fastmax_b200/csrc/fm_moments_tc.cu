@@ -309,12 +309,11 @@ __global__ void __launch_bounds__(256) state_to_bf16t_kernel(const float* __rest
 // rows only:  out[m][c*64 + b][a] = bf16( base[(b*64 + a)][c] + sum of state[m'][(b*64 + a)][c] over
 // the chunks m' before m (after m when reverse) ).  One CTA per (head, b) keeps its 64 x 68 block of
 // the running sum in registers, in fp32, walks the chunks in order and reads every raw chunk state
-// once; the fp32 states are left as they are.  `total` (may be null) gets the sum over this head's
-// chunks without the base.  The block with b == 64 zeroes the padding rows of every copy.
+// once; the fp32 states are left as they are.  The block with b == 64 zeroes the padding rows of
+// every copy.
 // =====================================================================================
 __global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restrict__ state,
                                                            const float* __restrict__ base,
-                                                           float* __restrict__ total,
                                                            __nv_bfloat16* __restrict__ out, int nchunk, int dvp,
                                                            size_t per_state, int reverse) {
   __shared__ float blk[64][69];
@@ -335,9 +334,6 @@ __global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restri
     run[u] = (base && v < NV) ? *(const float4*)(base + (size_t)head * per_state + blk_off + 4 * v)
                               : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  float4 start[5];
-#pragma unroll
-  for (int u = 0; u < 5; ++u) start[u] = run[u];
   auto load = [&](int i, float4 (&r)[5]) {
     const int c = reverse ? nchunk - 1 - i : i;
     const float* src = state + (size_t)(head * nchunk + c) * per_state + blk_off;
@@ -374,15 +370,6 @@ __global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restri
       run[u].x += cur[u].x; run[u].y += cur[u].y; run[u].z += cur[u].z; run[u].w += cur[u].w;
     }
     __syncthreads();
-  }
-  if (total) {
-#pragma unroll
-    for (int u = 0; u < 5; ++u) {
-      const int v = t + u * 256;
-      if (v < NV)
-        *(float4*)(total + (size_t)head * per_state + blk_off + 4 * v) =
-            make_float4(run[u].x - start[u].x, run[u].y - start[u].y, run[u].z - start[u].z, run[u].w - start[u].w);
-    }
   }
 }
 
@@ -858,17 +845,17 @@ int moments_tc_convert(const Ctx& c, int mats, const float* state, void* state_b
 }
 
 // Exclusive running sums over chunks (from `base`, per head, may be null) of the second-order rows,
-// written as the read-out's bf16 transposed copies; the fp32 states stay raw.  `total` as in
-// moments_prefix.  The first-order rows are the caller's business (moments_prefix with a row range).
+// written as the read-out's bf16 transposed copies; the fp32 states stay raw.  The first-order rows
+// are the caller's business (moments_prefix with a row range).
 int moments_tc_prefix_convert(const Ctx& c, int heads, int nchunk, const float* state, const float* base,
-                              float* total, int reverse, void* state_bf16) {
+                              int reverse, void* state_bf16) {
   if (heads == 0 || nchunk == 0) return FASTMAX_OK;
   const MomentDims m = moment_dims(64);
-  if ((((uintptr_t)state | (uintptr_t)base | (uintptr_t)total) & 15) != 0)
+  if ((((uintptr_t)state | (uintptr_t)base) & 15) != 0)
     return fail(FASTMAX_E_ARG, "moment states and totals must be 16-byte aligned");
   dim3 grid(65, heads);
   FM_LAUNCH("fm_moments_prefix_bf16", c.stream,
-            (prefix_bf16t_kernel<<<grid, 256, 0, c.stream>>>(state, base, total, (__nv_bfloat16*)state_bf16, nchunk,
+            (prefix_bf16t_kernel<<<grid, 256, 0, c.stream>>>(state, base, (__nv_bfloat16*)state_bf16, nchunk,
                                                              m.dvp, (size_t)m.f * m.dvp, reverse)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
