@@ -112,9 +112,10 @@ static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   const double d = p.d, F = d + (p.p == 2 ? d * d : 0.0);
   // Constants fitted to this library's kernels on a B200 (bf16, d = 64, p = 2, causal): the score family takes
   // 5.6 ns per token and head at 10^4 keys; the moment family 5.0 ns for its states and read-outs plus 2.0 ns
-  // for the score kernels of a 2048-token chunk (short rows run at 0.58 of the long-row rate).  The two
-  // families then break even at 12.3 k keys, as measured (10240: 23.0 against 27.4 ms; 12288: 27.7 against
-  // 28.1; 16384: 38.1 against 29.9 for the same number of token-heads).
+  // for the score kernels of a 2048-token chunk (short rows run at 0.58 of the long-row rate), the former
+  // times the share of chunks that build and read states.  The two families then break even near 11 k keys,
+  // as measured (10240: 22.5 against 24.5 ms; 12288: 27.7 against 25.8; 16384: 37.8 against 28.0 for the
+  // same number of token-heads).
   const double rate_score = tc_ok ? 800e12 : 25e12;
   const double rate_state = p.p == 2 ? (moments_tc_supports(p) ? 760e12 : 20e12) : (first_tc_supports(p) ? 450e12 : 20e12);
   const double rate_chunk = tc_ok ? 0.58 * rate_score : rate_score;
@@ -122,7 +123,10 @@ static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   const double chunk_keys = p.mask ? 0.5 * moments_chunk(p) : 0.0;
   const double per_key = 14.0 * (d + 0.5);
   const double t_score = keys * per_key / rate_score;
-  const double t_mom = 14.0 * F * (d + 1) / rate_state + chunk_keys * per_key / rate_chunk;
+  // causal: one chunk in nchunk builds no state and one reads none (see Ctx::skip_chunk, zero_chunk)
+  const int L = moments_chunk(p);
+  const double used = p.mask ? 1.0 - 1.0 / (double)((p.nk + L - 1) / L) : 1.0;
+  const double t_mom = used * 14.0 * F * (d + 1) / rate_state + chunk_keys * per_key / rate_chunk;
   return t_mom < t_score && p.nk > moments_chunk(p);
 }
 

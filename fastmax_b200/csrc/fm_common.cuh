@@ -75,6 +75,12 @@ struct Ctx {
   // layout the model's output projection consumes -- instead of (batch * out_heads, n, d); only the
   // tensor-core score kernels and the gradient preparation pass honour it (see fastmax_b200_forward_bt)
   int out_heads = 0;
+  // Causal moment family, one call for the whole sequence: the chunk whose state nothing reads (the last
+  // one in scan order: no later chunk exists and no total is asked for) is not built, and the tokens of
+  // the chunk whose running sum is empty (the first in scan order, when no base is added) get zeros
+  // without a read-out.  -1: no such chunk.  Honoured by the tensor-core moment kernels.
+  int skip_chunk = -1;
+  int zero_chunk = -1;
 };
 // Row of head `head`, token `row` in a (heads, n, .) array, or in a (batch, n, out_heads, .) array
 __host__ __device__ __forceinline__ size_t out_row(int head, int row, int n, int out_heads) {

@@ -40,6 +40,7 @@ struct F1StateArgs {
   const float* dvec;   // e_j = -dvec[j] when not null, else 1
   float* state;        // (heads, nchunk, rows, DVP) fp32; rows f_lin .. f_lin + D are written
   int n, chunk, nchunk, dvp, rows, f_lin;   // f_lin: stored index of the first first-order row
+  int skip_chunk;      // this chunk's state is not wanted (-1: none)
 };
 
 template <int DD>
@@ -77,6 +78,7 @@ first_state_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constan
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hc = blockIdx.x, head = hc / a.nchunk, chunk = hc % a.nchunk;
+  if (chunk == a.skip_chunk) return;
   const int t_begin = chunk * a.chunk, t_end = min(a.n, t_begin + a.chunk);
   constexpr int TOK = C::TOK;
   const int nblk = (t_end - t_begin + TOK - 1) / TOK;
@@ -223,6 +225,7 @@ struct F1ReadArgs {
   float* den_final;
   float* dots;
   int wide_io;          // out_final / o_add / x are 32-byte aligned: 32-byte accesses in the epilogue
+  int zero_chunk;       // per-chunk mode: the tokens of this chunk read an empty state (-1: none)
 };
 
 // 16 bytes from shared memory by shared-window address (keeps the epilogue's vector reads off the generic path)
@@ -279,6 +282,17 @@ first_readout_kernel(const __grid_constant__ CUtensorMap tmT, const __grid_const
   const int tile0 = (blockIdx.x % runs) * a.run;
   const int nt = min(a.run, tiles - tile0);        // tiles of this run
   const int mat = head * (a.per_chunk ? a.nchunk : 1) + (a.per_chunk ? (tile0 * 128) / a.chunk : 0);
+  if (a.per_chunk && (tile0 * 128) / a.chunk == a.zero_chunk) {
+    // the run lies in one chunk, whose state is empty: the result is zero -- nothing to add, or zeros to write
+    if (!a.accumulate) {
+      const int row0 = tile0 * 128, rows = min(nt * 128, a.n - row0);
+      for (int i = tid; i < rows * (DD / 4); i += F1_THREADS)
+        *(float4*)(a.o_add + ((size_t)head * a.n + row0) * DD + (size_t)i * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!a.type_b && a.den_add)
+        for (int i = tid; i < rows; i += F1_THREADS) a.den_add[(size_t)head * a.n + row0 + i] = 0.f;
+    }
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(BAR_SF, 1);
@@ -529,6 +543,7 @@ int first_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void* 
   F1StateArgs a;
   a.y = y; a.z = z; a.dvec = dvec; a.state = state;
   a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.dvp = m.dvp; a.rows = m.f; a.f_lin = p.d * p.d - m.f0;
+  a.skip_chunk = c.skip_chunk;
   const unsigned grid = (unsigned)((size_t)heads * nchunk);
   if (p.d == 128) {
     FM_CUDA_TRY(cudaFuncSetAttribute(first_state_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, F1S<128>::SMEM));
@@ -576,6 +591,7 @@ int first_tc_readout(const Ctx& c, int type_b, int heads, int n, int chunk, int 
   a.f_lin = p.d * p.d - m.f0; a.type_b = type_b; a.accumulate = accumulate;
   a.final = final; a.out_final = out_final; a.den_final = den_final; a.dots = dots;
   a.wide_io = (((uintptr_t)out_final | (uintptr_t)o_add | (uintptr_t)x) & 31) == 0;
+  a.zero_chunk = (per_chunk && !final) ? c.zero_chunk : -1;
   // runs of up to 8 tiles that never cross a chunk (chunks are multiples of 256 tokens)
   // a CTA pays for loading the state copy and the vector terms once per run, so runs are as long as
   // the chunk allows (a run never crosses a chunk; chunks are multiples of 256 tokens), at most 32 tiles --

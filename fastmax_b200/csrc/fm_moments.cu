@@ -166,6 +166,11 @@ static int prefix_states(const Ctx& c, int nchunk, float* states, const float* b
   return moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1, p.d * p.d);
 }
 
+// Copies of the context that tell the tensor-core moment kernels which chunk's state nothing will read,
+// and whose tokens read an empty running sum (see Ctx).
+static Ctx skipping(const Ctx& c, int chunk) { Ctx r = c; r.skip_chunk = chunk; return r; }
+static Ctx zeroing(const Ctx& c, int chunk) { Ctx r = c; r.zero_chunk = chunk; return r; }
+
 // ---- forward -----------------------------------------------------------------------
 // kv_states: raw chunk states of (k, v) for this shard (already built); s_base: sum of the
 // totals of all earlier shards or null.  Turns the states into prefixes in place.
@@ -179,8 +184,9 @@ int moments_forward_finish(const Ctx& c, const void* q, const void* k, const voi
   // second16 != null: the caller does not need the fp32 second-order prefixes (see prefix_states)
   bool ready;
   if ((rc = prefix_states(c, nchunk, kv_states, s_base, 0, second16 != nullptr, second16, &ready))) return rc;
-  if ((rc = read_states(c, 0, p.nq, 1, q, nullptr, nullptr, nullptr, 0, nullptr, nullptr, kv_states, s16,
-                        stats, o_add, den_add, nullptr, ready ? second16 : nullptr)))
+  // without a base the tokens of the first chunk have nothing before them
+  if ((rc = read_states(zeroing(c, s_base ? -1 : 0), 0, p.nq, 1, q, nullptr, nullptr, nullptr, 0, nullptr, nullptr,
+                        kv_states, s16, stats, o_add, den_add, nullptr, ready ? second16 : nullptr)))
     return rc;
   ChunkAdd ca;
   ca.chunk = L;
@@ -206,7 +212,11 @@ int moments_forward(const Ctx& c, const void* q, const void* k, const void* v, c
   float* den_add = (float*)(ws + w.den_add);
   int rc;
   void* s16 = ws + w.s16;
-  if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
+  // causal: nothing comes after the last chunk, so its state is not built
+  const int last = (p.nk + L - 1) / L - 1;
+  if ((rc = moments_build_states(p.mask ? skipping(c, last) : c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr,
+                                 states)))
+    return rc;
   if (p.mask) {
     // second-order prefixes go straight to their bf16 copies: behind the kept fp32 states when the
     // backward will want them again, else in the workspace
@@ -266,8 +276,8 @@ int moments_backward_finish(const Ctx& c, const void* q, const void* k, const vo
   // (nothing reads r_states after this call, so their second-order rows may stay raw: prefix_states)
   bool ready;
   if ((rc = prefix_states(c, nchunk, r_states, r_base, 1, true, s16, &ready))) return rc;
-  if ((rc = read_states(c, 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr, r_states, s16, stats,
-                        gv_add, nullptr, gk_add, ready ? s16 : nullptr)))
+  if ((rc = read_states(zeroing(c, r_base ? -1 : nchunk - 1), 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr,
+                        r_states, s16, stats, gv_add, nullptr, gk_add, ready ? s16 : nullptr)))
     return rc;
   ChunkAdd ca;
   ca.chunk = L;
@@ -314,19 +324,22 @@ int moments_backward(const Ctx& c, const void* q, const void* k, const void* v, 
     bool ready = false;
     const void* kv16 = nullptr;   // second-order bf16 copies of the key/value prefixes, where they exist already
     if (!kv_total_kept) {
-      if ((rc = moments_build_states(c, p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states))) return rc;
+      if ((rc = moments_build_states(skipping(c, nck - 1), p.nk, k, v, nullptr, nullptr, 0, nullptr, nullptr, states)))
+        return rc;
       if ((rc = prefix_states(c, nck, states, nullptr, 0, true, s16, &ready))) return rc;
       if (ready) kv16 = s16;
     } else if (moment_kept16_bytes(p) > 0) {
       kv16 = (const char*)kv_total_kept + moment_state_bytes(p, p.nk);
     }
-    if ((rc = read_states(c, 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec,
+    // grad_q: the first chunk's tokens have no keys before their chunk; grad_k, grad_v: the last chunk's
+    // tokens no queries after theirs, and nothing reads the query/gradient state of the first chunk
+    if ((rc = read_states(zeroing(c, 0), 1, p.nq, 1, q, grad_out, den, delta, 1, gs, dvec,
                           kv_total_kept ? kv_total_kept : states, s16, stats, nullptr, nullptr, gq_add, kv16)))
       return rc;
-    if ((rc = moments_build_states(c, p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
+    if ((rc = moments_build_states(skipping(c, 0), p.nq, q, grad_out, den, delta, 1, gs, dvec, states))) return rc;
     if ((rc = prefix_states(c, ncq, states, nullptr, 1, true, s16, &ready))) return rc;
-    if ((rc = read_states(c, 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr, states, s16, stats,
-                          gv_add, nullptr, gk_add, ready ? s16 : nullptr)))
+    if ((rc = read_states(zeroing(c, ncq - 1), 2, p.nk, 1, k, v, nullptr, nullptr, 0, nullptr, nullptr, states, s16,
+                          stats, gv_add, nullptr, gk_add, ready ? s16 : nullptr)))
       return rc;
     ChunkAdd ca;
     ca.chunk = L;

@@ -154,8 +154,10 @@ __global__ void __launch_bounds__(256) prefix_kernel(float* state,
     for (int u = 0; u < 8; ++u) {
       const int i = i0 + u;
       const int c = reverse ? nchunk - 1 - i : i;
-      v[u] = (i < nchunk) ? __ldcs((const float4*)(state + ((size_t)head * nchunk + c) * per + e))
-                          : make_float4(0.f, 0.f, 0.f, 0.f);
+      // without a total the last chunk in scan order is added to nothing that is kept (and may not have been built)
+      v[u] = (i < nchunk && (total || i + 1 < nchunk))
+                 ? __ldcs((const float4*)(state + ((size_t)head * nchunk + c) * per + e))
+                 : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {

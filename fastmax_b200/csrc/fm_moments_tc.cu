@@ -63,6 +63,7 @@ struct RtArgs {
   float a2, lim;
   int n, chunk, nchunk, state_per_chunk;
   int wide_io;         // out_a / out_b are 32-byte aligned
+  int zero_chunk;      // tokens of this chunk read an empty state: zeros are written, nothing is multiplied (-1: none)
   int mode;            // 0: type A on two token tiles, 1: type B on two token tiles,
                        // 2: one token tile, group 0 type A and group 1 type B
 };
@@ -104,6 +105,18 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   const int chunk = a.state_per_chunk ? tok0 / a.chunk : 0;
   const int srow = head * (a.state_per_chunk ? a.nchunk : 1) + chunk;   // index of the state matrix
   const int readers = (a.mode == 2) ? 8 : 4;                            // warps that read each T buffer
+  if (a.state_per_chunk && chunk == a.zero_chunk) {
+    // the whole CTA lies in one chunk (chunks are multiples of 256 tokens): zero rows, no products
+    const int rows = min(128 * tiles_per_cta, a.n - tok0);
+    for (int i = tid; i < rows * (D / 4); i += RT_THREADS) {
+      const size_t e = ((size_t)head * a.n + tok0) * D + (size_t)i * 4;
+      if (a.mode != 1) *(float4*)(a.out_a + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a.mode != 0) *(float4*)(a.out_b + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (a.mode != 1 && a.den_a)
+      for (int i = tid; i < rows; i += RT_THREADS) a.den_a[(size_t)head * a.n + tok0 + i] = 0.f;
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(BAR_X(), 1);
@@ -340,7 +353,8 @@ __global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restri
 #pragma unroll
     for (int u = 0; u < 5; ++u) {
       const int v = t + u * 256;
-      r[u] = (i < nchunk && v < NV) ? __ldcs((const float4*)(src + 4 * v)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      // the last chunk in scan order is never added to anything that is written (and may not have been built)
+      r[u] = (i + 1 < nchunk && v < NV) ? __ldcs((const float4*)(src + 4 * v)) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   };
   load(0, nxt);
@@ -397,6 +411,7 @@ struct StArgs {
   float* state;      // (heads, nchunk, F, DVP) fp32; rows a*64+b, columns 0..63 are written
   int n, chunk, nchunk, dvp;
   size_t per_state;
+  int skip_chunk;    // this chunk's state is not wanted (-1: none)
 };
 
 constexpr int ST_GEN_WARPS = 16;
@@ -435,6 +450,7 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
   const int part = blockIdx.x % ST_SPLIT;
   const int hc = blockIdx.x / ST_SPLIT;           // head * nchunk + chunk
   const int head = hc / a.nchunk, chunk = hc % a.nchunk;
+  if (chunk == a.skip_chunk) return;
   const int t_begin = chunk * a.chunk, t_end = min(a.n, t_begin + a.chunk);
   const int nblk = (t_end - t_begin + 127) / 128;
   const int a0 = part * 2 * ST_TILES;
@@ -665,7 +681,8 @@ constexpr int EC_SMEM = EC_OFF_TMEM + 16 + 1024;
 
 __global__ void __launch_bounds__(EC_THREADS, 2)
 state_ecol_tc_kernel(const __grid_constant__ CUtensorMap tmY, const float* __restrict__ dvec,
-                     float* __restrict__ state, int n, int chunk, int nchunk, int dvp, size_t per_state) {
+                     float* __restrict__ state, int n, int chunk, int nchunk, int dvp, size_t per_state,
+                     int skip_chunk) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -680,6 +697,7 @@ state_ecol_tc_kernel(const __grid_constant__ CUtensorMap tmY, const float* __res
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hc = blockIdx.x, head = hc / nchunk, ck = hc % nchunk;
+  if (ck == skip_chunk) return;
   const int t_begin = ck * chunk, t_end = min(n, t_begin + chunk);
   const int nblk = (t_end - t_begin + 127) / 128;
   const bool scaled = dvec != nullptr;
@@ -877,13 +895,14 @@ int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void
   StArgs a;
   a.y = y; a.state = state; a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.dvp = m.dvp;
   a.per_state = (size_t)m.f * m.dvp;
+  a.skip_chunk = c.skip_chunk;
   // the normaliser column first: the state kernel picks it up in its epilogue
   CUtensorMap ty;
   if ((rc = make_map(&ty, y, heads, n))) return rc;
   FM_CUDA_TRY(cudaFuncSetAttribute(state_ecol_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, EC_SMEM));
   FM_LAUNCH("fm_moments_state_ecol", c.stream,
             (state_ecol_tc_kernel<<<(unsigned)((size_t)heads * nchunk), EC_THREADS, EC_SMEM, c.stream>>>(
-                ty, dvec, state, n, chunk, nchunk, m.dvp, a.per_state)));
+                ty, dvec, state, n, chunk, nchunk, m.dvp, a.per_state, a.skip_chunk)));
   FM_CUDA_TRY(cudaGetLastError());
   FM_CUDA_TRY(cudaFuncSetAttribute(state_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM));
   FM_LAUNCH("fm_moments_tc_state", c.stream,
@@ -911,6 +930,7 @@ int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int 
   a.a2 = p.a2; a.lim = p.lim;
   a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.state_per_chunk = state_per_chunk; a.mode = mode;
   a.wide_io = (((uintptr_t)out_a | (uintptr_t)out_b) & 31) == 0;
+  a.zero_chunk = state_per_chunk ? c.zero_chunk : -1;
   const int per_cta = (mode == 2) ? 128 : 256;
   const unsigned grid = (unsigned)((size_t)heads * ((n + per_cta - 1) / per_cta));
   FM_CUDA_TRY(cudaFuncSetAttribute(readout_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));
