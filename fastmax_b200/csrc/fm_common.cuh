@@ -198,7 +198,8 @@ int moments_tc_prefix_convert(const Ctx& c, int heads, int nchunk, const float* 
                               int reverse, void* state_bf16);
 int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int state_per_chunk,
                        const void* x, const void* u, const float* uvec, const void* state_bf16,
-                       const stat_t* stats, float* out_a, float* den_a, float* out_b);
+                       const stat_t* stats, float* out_a, float* den_a, float* out_b,
+                       const float* state_f32 = nullptr);
 int moments_tc_status(int* out, cudaStream_t stream);
 int moments_tc_status_reset(cudaStream_t stream);
 

@@ -111,15 +111,16 @@ static int read_states(const Ctx& c, int mode, int n, int per_chunk, const void*
   const int mats = p.bh * (per_chunk ? (n + L - 1) / L : 1);
   if (tc2) {
     if (!second16 && (rc = moments_tc_convert(c, mats, states, s16))) return rc;
+    // type A comes out complete (first-order and constant terms included), type B second-order only
     if ((rc = moments_tc_readout(c, mode, p.bh, n, L, per_chunk, x, ext ? gs : u, ext ? dvec : nullptr,
-                                 second16 ? second16 : s16, stats, out_a, den_a, out_b)))
+                                 second16 ? second16 : s16, stats, out_a, den_a, out_b, states)))
       return rc;
   }
   if (tc1) {
     // first-order part on tensor cores; it adds to the second-order part when there is one
     void* s1b = (char*)s16 + state16_second(p, mats);
     if ((rc = first_tc_convert(c, mats, states, s1b))) return rc;
-    if (mode == 0 || mode == 2)
+    if ((mode == 0 || mode == 2) && !tc2)
       if ((rc = first_tc_readout(c, 0, p.bh, n, L, per_chunk, x, x, nullptr, states, s1b, stats, out_a, den_a,
                                  tc2)))
         return rc;
@@ -129,7 +130,7 @@ static int read_states(const Ctx& c, int mode, int n, int per_chunk, const void*
         return rc;
     return FASTMAX_OK;
   }
-  if (mode == 0 || mode == 2)
+  if ((mode == 0 || mode == 2) && !tc2)
     if ((rc = moments_readout(c, 0, p.bh, n, L, per_chunk, x, nullptr, nullptr, nullptr, 0, states, stats,
                               out_a, den_a, tc2)))
       return rc;
@@ -162,8 +163,9 @@ static int prefix_states(const Ctx& c, int nchunk, float* states, const float* b
   *ready = fuse && p.p == 2 && moments_tc_supports(p);
   if (!*ready) return moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1);
   int rc;
-  if ((rc = moments_tc_prefix_convert(c, p.bh, nchunk, states, base, reverse, second16))) return rc;
-  return moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1, p.d * p.d);
+  // first the first-order rows in place: the copies carry them too (their last 64 rows)
+  if ((rc = moments_prefix(c, p.bh, nchunk, states, base, nullptr, reverse, 1, p.d * p.d))) return rc;
+  return moments_tc_prefix_convert(c, p.bh, nchunk, states, base, reverse, second16);
 }
 
 // Copies of the context that tell the tensor-core moment kernels which chunk's state nothing will read,

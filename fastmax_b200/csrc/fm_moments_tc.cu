@@ -64,6 +64,12 @@ struct RtArgs {
   int n, chunk, nchunk, state_per_chunk;
   int wide_io;         // out_a / out_b are 32-byte aligned
   int zero_chunk;      // tokens of this chunk read an empty state: zeros are written, nothing is multiplied (-1: none)
+  // Type A also adds the first-order and constant terms when state_f32 is given: x . S1 comes out of the last
+  // slice (the copy's rows 65*64..), the constant row and S1's normaliser column are read from the fp32 state.
+  const float* state_f32;
+  size_t per_state;
+  int dvp;
+  float a0, a1;
   int mode;            // 0: type A on two token tiles, 1: type B on two token tiles,
                        // 2: one token tile, group 0 type A and group 1 type B
 };
@@ -78,7 +84,9 @@ constexpr int RT_UT_LD = 66;
 constexpr int RT_OFF_BAR = RT_OFF_UT + 2 * 128 * RT_UT_LD * 4;
 constexpr int RT_NBAR = 1 + 2 * RT_NS + 8;
 constexpr int RT_OFF_TMEM = RT_OFF_BAR + RT_NBAR * 8;
-constexpr int RT_SMEM = RT_OFF_TMEM + 16 + 1024;
+constexpr int RT_OFF_VEC = RT_OFF_TMEM + 16;        // per type-A group: constant row [65] | S1 normaliser column [64]
+constexpr int RT_VEC = 132;
+constexpr int RT_SMEM = RT_OFF_VEC + 2 * RT_VEC * 4 + 1024;
 constexpr int RT_NT = NROWS_TP / 128;               // 33 slices of 128 columns of T
 
 __global__ void __launch_bounds__(RT_THREADS, 1)
@@ -222,6 +230,19 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 32; ++e) xa[e] = pack2(0.f, 0.f);
       }
+      const bool first_too = !type_b && a.state_f32 != nullptr;
+      const float A1f = a.a1 * c;
+      float* vec = (float*)(smem + RT_OFF_VEC) + g * RT_VEC;   // crow[0..64] | ncol[0..63]
+      if (first_too) {
+        // the group's 128 threads stage the two vectors of this CTA's state (all of them reach the barrier:
+        // a group is of one kind)
+        const float* fs = a.state_f32 + (size_t)srow * a.per_state + (size_t)(64 * 64) * a.dvp;   // first-order rows
+        const int i = qd * 32 + lane;
+        if (i < 65) vec[i] = __ldg(fs + (size_t)64 * a.dvp + i);               // constant row
+        if (i < 64) vec[65 + i] = __ldg(fs + (size_t)i * a.dvp + 64);           // S1[a][64]
+        if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
       bool ok = true;
       for (int n = 0; n < RT_NT; ++n) {
         const int buf = n & 1;
@@ -238,7 +259,20 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_TFREE(t, buf));
           }
-          if (cidx > 64) continue;            // padding rows of the last slice
+          if (cidx > 64) {                    // the last 64 rows of the copy: the first-order block
+            if (first_too) {
+              // T1[c] = x . S1[:, c] in this half; the normaliser column's first-order part is a dot on the CUDA cores
+#pragma unroll
+              for (int cc = 0; cc < 64; ++cc) ut[cc] += fmaf(A1f, __uint_as_float(tv[cc]), a.a0 * vec[cc]);
+              uint64_t s4[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
+#pragma unroll
+              for (int e = 0; e < 32; ++e) s4[e & 3] = fma2(xa[e], pack2(vec[65 + 2 * e], vec[66 + 2 * e]), s4[e & 3]);
+              float lo, hi;
+              unpack2(add2(add2(s4[0], s4[1]), add2(s4[2], s4[3])), lo, hi);
+              ut[64] += fmaf(A1f, lo + hi, a.a0 * vec[64]);
+            }
+            continue;
+          }
           if (!type_b) {
             uint64_t s4[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
@@ -295,16 +329,31 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 // =====================================================================================
 // bf16 transposed copy of the second-order block of fp32 prefix states:
 //   out[m][c*64 + b][a] = state[m][(b*64 + a)][c]      (S2 is symmetric in a, b)
-// one CTA per (state matrix m, b); rows past 65*64 are zero.
+// one CTA per (state matrix m, b).  The 64 rows past 65*64 hold the first-order block the same way,
+//   out[m][65*64 + c][a] = state[m][64*64 + a][c],  c < 64
+// so that the read-out's last slice yields x . S1 beside the normaliser column's second-order part.
 // =====================================================================================
+// rows 65*64 .. 65*64 + 63 of one copy from the (summed) first-order rows of its fp32 state
+__device__ __forceinline__ void first_rows_to_bf16t(const float* __restrict__ st, __nv_bfloat16* __restrict__ o,
+                                                    int dvp, float (*blk)[69], int t) {
+  const float* src = st + (size_t)64 * 64 * dvp;     // rows 4096 + a, a = 0..63
+  for (int i = t; i < 64 * dvp; i += 256) blk[i / dvp][i % dvp] = src[i];
+  __syncthreads();
+  uint32_t* ow = (uint32_t*)(o + (size_t)NROWS_T * 64);
+  for (int w = t; w < 64 * 32; w += 256) {
+    const int cc = w >> 5, ap = (w & 31) * 2;
+    ow[cc * 32 + (w & 31)] = pack_bf16(blk[ap][cc], blk[ap + 1][cc]);
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(256) state_to_bf16t_kernel(const float* __restrict__ state,
                                                              __nv_bfloat16* __restrict__ out, int dvp,
                                                              size_t per_state) {
   __shared__ float blk[64][69];
   const int m = blockIdx.y, b = blockIdx.x;
-  if (b == 64) {  // zero the padding rows
-    __nv_bfloat16* o = out + ((size_t)m * NROWS_TP + NROWS_T) * 64;
-    for (int i = threadIdx.x; i < (NROWS_TP - NROWS_T) * 64; i += 256) o[i] = __float2bfloat16_rn(0.f);
+  if (b == 64) {  // the first-order rows (the fp32 state holds running sums already)
+    first_rows_to_bf16t(state + (size_t)m * per_state, out + (size_t)m * NROWS_TP * 64, dvp, blk, threadIdx.x);
     return;
   }
   const float* src = state + (size_t)m * per_state + (size_t)b * 64 * dvp;   // rows (b, a = 0..63)
@@ -322,8 +371,8 @@ __global__ void __launch_bounds__(256) state_to_bf16t_kernel(const float* __rest
 // rows only:  out[m][c*64 + b][a] = bf16( base[(b*64 + a)][c] + sum of state[m'][(b*64 + a)][c] over
 // the chunks m' before m (after m when reverse) ).  One CTA per (head, b) keeps its 64 x 68 block of
 // the running sum in registers, in fp32, walks the chunks in order and reads every raw chunk state
-// once; the fp32 states are left as they are.  The block with b == 64 zeroes the padding rows of
-// every copy.
+// once; the fp32 states are left as they are.  The block with b == 64 copies the first-order rows
+// (already summed in place) into the last 64 rows of every copy.
 // =====================================================================================
 __global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restrict__ state,
                                                            const float* __restrict__ base,
@@ -332,10 +381,10 @@ __global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restri
   __shared__ float blk[64][69];
   const int head = blockIdx.y, b = blockIdx.x, t = threadIdx.x;
   if (b == 64) {
-    for (int i = 0; i < nchunk; ++i) {
-      uint32_t* o = (uint32_t*)(out + ((size_t)(head * nchunk + i) * NROWS_TP + NROWS_T) * 64);
-      for (int w = t; w < (NROWS_TP - NROWS_T) * 32; w += 256) o[w] = 0u;
-    }
+    // the first-order rows: their running sums were formed in place in the fp32 states before this launch
+    for (int i = 0; i < nchunk; ++i)
+      first_rows_to_bf16t(state + (size_t)(head * nchunk + i) * per_state,
+                          out + (size_t)(head * nchunk + i) * NROWS_TP * 64, dvp, blk, t);
     return;
   }
   constexpr int NV = 64 * 68 / 4;                    // float4 pieces of the block (dvp == 68)
@@ -912,10 +961,11 @@ int moments_tc_chunk_state(const Ctx& c, int heads, int n, int chunk, const void
 }
 
 // mode 0: type A on x -> out_a (+ den_a);  mode 1: type B on (x, u, uvec) -> out_b;
-// mode 2: both on the same tokens.  Results overwrite; they hold the second-order part only.
+// mode 2: both on the same tokens.  Results overwrite; type B holds the second-order part only, type A the
+// whole result when state_f32 (the fp32 states with summed first-order rows) is given.
 int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int state_per_chunk,
                        const void* x, const void* u, const float* uvec, const void* state_bf16,
-                       const stat_t* stats, float* out_a, float* den_a, float* out_b) {
+                       const stat_t* stats, float* out_a, float* den_a, float* out_b, const float* state_f32) {
   if (heads == 0 || n == 0) return FASTMAX_OK;
   const fastmax_problem& p = c.p;
   const int nchunk = (n + chunk - 1) / chunk;
@@ -931,6 +981,8 @@ int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int 
   a.n = n; a.chunk = chunk; a.nchunk = nchunk; a.state_per_chunk = state_per_chunk; a.mode = mode;
   a.wide_io = (((uintptr_t)out_a | (uintptr_t)out_b) & 31) == 0;
   a.zero_chunk = state_per_chunk ? c.zero_chunk : -1;
+  const MomentDims md = moment_dims(64);
+  a.state_f32 = state_f32; a.per_state = (size_t)md.f * md.dvp; a.dvp = md.dvp; a.a0 = p.a0; a.a1 = p.a1;
   const int per_cta = (mode == 2) ? 128 : 256;
   const unsigned grid = (unsigned)((size_t)heads * ((n + per_cta - 1) / per_cta));
   FM_CUDA_TRY(cudaFuncSetAttribute(readout_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));
