@@ -119,14 +119,20 @@ static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   const double rate_score = tc_ok ? 800e12 : 25e12;
   const double rate_state = p.p == 2 ? (moments_tc_supports(p) ? 760e12 : 20e12) : (first_tc_supports(p) ? 450e12 : 20e12);
   const double rate_chunk = tc_ok ? 0.58 * rate_score : rate_score;
-  const double keys = p.mask ? 0.5 * p.nk : (double)p.nk;
+  // Unmasked with nq != nk: the score form costs nq * nk pairs, the moment form one state per key and one
+  // read-out per query row (and the mirror image backward), so per token of the mean length the score form
+  // sees nq * nk / mean(nq, nk) keys.  Few query rows against many keys therefore stay on the score family.
+  const double keys = p.mask ? 0.5 * p.nk : (double)p.nq * p.nk / (0.5 * ((double)p.nq + p.nk));
   const double chunk_keys = p.mask ? 0.5 * moments_chunk(p) : 0.0;
   const double per_key = 14.0 * (d + 0.5);
   const double t_score = keys * per_key / rate_score;
   // causal: one chunk in nchunk builds no state and one reads none (see Ctx::skip_chunk, zero_chunk)
   const int L = moments_chunk(p);
   const double used = p.mask ? 1.0 - 1.0 / (double)((p.nk + L - 1) / L) : 1.0;
-  const double t_mom = used * 14.0 * F * (d + 1) / rate_state + chunk_keys * per_key / rate_chunk;
+  double t_mom = used * 14.0 * F * (d + 1) / rate_state + chunk_keys * per_key / rate_chunk;
+  // unmasked: the fp32 result rows take one more pass (5.5 ns per token and head measured), and each head
+  // pays about a third of a chunk's time once, for its totals (break-even measured near 5 500 keys)
+  if (!p.mask) t_mom *= 1.1 * (1.0 + 0.33 * L / (0.5 * ((double)p.nq + p.nk)));
   return t_mom < t_score && p.nk > moments_chunk(p);
 }
 

@@ -343,9 +343,18 @@ __global__ void __launch_bounds__(256) finalize_kernel(const float* __restrict__
     stf(out + g, v);
   }
   if (mode == 1 && dots) {
+    // one atomic per CTA: thousands of them on one address per head serialise in L2
+    __shared__ float warp_part[8];
 #pragma unroll
     for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
-    if ((threadIdx.x & 31) == 0) atomicAdd(dots + head, part);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += warp_part[w];
+      atomicAdd(dots + head, s);
+    }
   }
 }
 
@@ -460,7 +469,10 @@ int moments_finalize(const Ctx& c, int heads, int n, const float* r, const float
                      void* out, float* den_out, float* dots, int mode) {
   if (heads == 0 || n == 0) return FASTMAX_OK;
   const int d = c.p.d;
-  dim3 grid((unsigned)min((size_t)1024, ((size_t)n * d + 255) / 256), heads);
+  // enough CTAs to fill the device a few times over; with the per-head dot, few CTAs per head
+  // when there are many heads, since each ends in an atomic on the head's word
+  const size_t most = dots ? (size_t)max(8, (4096 + heads - 1) / heads) : (size_t)1024;
+  dim3 grid((unsigned)min(most, ((size_t)n * d + 255) / 256), heads);
   if (c.p.dtype == FASTMAX_F32)
     FM_LAUNCH("fm_moments_finalize", c.stream,
               (finalize_kernel<float><<<grid, 256, 0, c.stream>>>(r, den_in, (const float*)x, (float*)out,
