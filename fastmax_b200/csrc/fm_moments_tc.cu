@@ -466,7 +466,7 @@ struct StArgs {
 constexpr int ST_GEN_WARPS = 16;
 constexpr int ST_THREADS = (ST_GEN_WARPS + 3) * 32;   // warps 0-15: generators; 16: TMA; 17, 18: MMA issuers
 constexpr int ST_TILES = 4;           // accumulator tiles (and feature buffers) per CTA
-constexpr int ST_SPLIT = 64 / (2 * ST_TILES);   // CTAs per (head, chunk)
+constexpr int ST_SPLIT = 5;            // CTAs per (head, chunk): four of four tiles and one of one tile
 constexpr int ST_NZ = 3;              // value-tile ring
 constexpr int ST_ZTILE = 128 * 128;
 constexpr int ST_YT_LD = 272;         // bytes per yT row: 128 tokens + 16 (conflict-free 16-byte reads down a column)
@@ -474,7 +474,7 @@ constexpr int ST_YT = 64 * ST_YT_LD;
 constexpr int ST_OFF_Z = 0;
 constexpr int ST_OFF_YT = ST_NZ * ST_ZTILE;          // two transposed blocks
 constexpr int ST_OFF_BAR = ST_OFF_YT + 2 * ST_YT;
-constexpr int ST_NBAR = 4 * ST_TILES + 2 * ST_NZ + 1;
+constexpr int ST_NBAR = 5 * ST_TILES + 2 * ST_NZ + 1;
 constexpr int ST_OFF_TMEM = ST_OFF_BAR + ST_NBAR * 8;
 constexpr int ST_SMEM = ST_OFF_TMEM + 16 + 1024;
 constexpr int ST_TM_A = 64 * ST_TILES;               // first TMEM column of the feature buffers
@@ -493,6 +493,9 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
   auto BAR_ZFULL = [&](int s) { return bar0 + 8u * (4 * ST_TILES + s); };
   auto BAR_ZEMPTY = [&](int s) { return bar0 + 8u * (4 * ST_TILES + ST_NZ + s); };
   auto BAR_DONE = [&]() { return bar0 + 8u * (4 * ST_TILES + 2 * ST_NZ); };
+  // completes once, when half 0's first product of tile m is done (a_empty[m][0] completes every block, and a
+  // late waiter on one parity of it could see two completions as none)
+  auto BAR_START = [&](int m) { return bar0 + 8u * (4 * ST_TILES + 2 * ST_NZ + 1 + m); };
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + ST_OFF_TMEM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -502,12 +505,13 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
   if (chunk == a.skip_chunk) return;
   const int t_begin = chunk * a.chunk, t_end = min(a.n, t_begin + a.chunk);
   const int nblk = (t_end - t_begin + 127) / 128;
-  const int a0 = part * 2 * ST_TILES;
+  const int ntile = part == 4 ? 1 : ST_TILES;
   const __nv_bfloat16* ybase = (const __nv_bfloat16*)a.y + (size_t)head * a.n * D;
 
   if (tid == 0) {
     for (int m = 0; m < ST_TILES; ++m)
       for (int h = 0; h < 2; ++h) { mbar_init(BAR_AFULL(m, h), ST_GEN_WARPS / 2); mbar_init(BAR_AEMPTY(m, h), 1); }
+    for (int m = 0; m < ST_TILES; ++m) mbar_init(BAR_START(m), 1);
     for (int s = 0; s < ST_NZ; ++s) { mbar_init(BAR_ZFULL(s), 1); mbar_init(BAR_ZEMPTY(s), 2); }
     mbar_init(BAR_DONE(), 2);
     mbar_fence_init();
@@ -552,13 +556,14 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       const int s = k % ST_NZ;
       if (!mbar_wait_warp(BAR_ZFULL(s), (uint32_t)((k / ST_NZ) & 1))) { report(32); ok = false; break; }
       const uint32_t z_lo = desc_lo(sbase + ST_OFF_Z + s * ST_ZTILE, ST_ZTILE) + (uint32_t)w * (4 * 128);
-      for (int m = 0; m < ST_TILES; ++m) {
+      for (int m = 0; m < ntile; ++m) {
         if (!mbar_wait_warp(BAR_AFULL(m, w), (uint32_t)(k & 1))) { report(33); ok = false; break; }
-        if (k == 0 && w == 1 && !mbar_wait_warp(BAR_AEMPTY(m, 0), 0)) { report(36); ok = false; break; }
+        if (k == 0 && w == 1 && !mbar_wait_warp(BAR_START(m), 0)) { report(36); ok = false; break; }
         tc_fence_after();
         if (elect_one()) {
           umma_ts_steps<4>(tmem + m * 64, tmem + ST_TM_A + m * 64 + w * 32, z_lo, idesc, (k > 0 || w == 1) ? 1u : 0u);
           umma_commit(BAR_AEMPTY(m, w));
+          if (k == 0 && w == 0) umma_commit(BAR_START(m));
         }
         __syncwarp();
       }
@@ -569,8 +574,22 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
     __syncwarp();
   } else {
     const int h = warp >> 3, tq = (warp >> 2) & 1, qd = warp & 3;   // token half, 32-token quarter in it, TMEM lane quarter
-    const int b = (qd & 1) * 32 + lane;             // this thread's feature row b (the same in every tile)
-    const int a_sub = qd >> 1;                      // which of the tile's two a values
+    // This thread's lane of tile m holds the unordered pair {b, other(m)}: b is the thread's own feature
+    // (the same in every tile, so its row is read once per block), other(m) the tile's.
+    //   part 0: b = lane,      other = (lane + s) % 32,      s = 4 m + quarter = 0..15   (pairs inside features 0..31)
+    //   part 1: b = 32 + lane, other = 4 m + quarter                                     (features 32..63 x 0..15)
+    //   part 2: b = 32 + lane, other = 16 + 4 m + quarter                                (features 32..63 x 16..31)
+    //   part 3: b = 32 + lane, other = 32 + (lane + s) % 32                              (pairs inside 32..63)
+    //   part 4: one tile; quarter 0: b = lane, quarter 1: b = 32 + lane, other = b's partner at distance 16, of
+    //           which lanes 0..15 are new pairs; quarters 2 and 3 repeat them and are not stored.
+    // Distances 0..15 around the ring of 32 give every pair inside a group of 32 once, distance 16 gives the
+    // remaining sixteen; 2080 pairs in 17 tiles of 128 lanes instead of 4096 ordered ones in 32.
+    const int grp = part == 0 ? 0 : (part < 4 ? 1 : (qd & 1));
+    const int b = grp * 32 + lane;
+    const int o_off = (part == 3 || part == 4) ? grp * 32 : 0;
+    const int o_lane = (part == 1 || part == 2) ? 0 : lane;
+    const int o_c0 = part == 4 ? 16 : (part == 2 ? 16 + qd : qd);
+    auto other = [&](int m) { return o_off + ((o_lane + o_c0 + 4 * m) & 31); };
     const int tok_off = h * 64 + tq * 32;           // first of this warp's 32 tokens in the block
     // transposition duty inside the half: token pair jp (of 32) and 8 features from fg * 8
     const int jp = tid & 31, fg = (tid >> 5) & 7;
@@ -619,7 +638,7 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       }
       // products of one tile: row a of the tile (a broadcast read) times this thread's row b
       auto products = [&](int m, uint32_t (&pr)[16]) {
-        const uint32_t ra = yt + (a0 + 2 * m + a_sub) * ST_YT_LD + tok_off * 2;
+        const uint32_t ra = yt + other(m) * ST_YT_LD + tok_off * 2;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           const uint4 w4 = lds128(ra + v * 16);
@@ -637,6 +656,16 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       // products complete in order, so the later tile's barrier covers the earlier one's too.
       uint32_t p0[16], p1[16], p2[16], p3[16];
       products(0, p0);
+      if (ntile == 1) {
+        if (!mbar_wait(BAR_AEMPTY(0, h), (uint32_t)((k & 1) ^ 1))) { report(34); ok = false; continue; }
+        tc_fence_after();
+        tmem_st16(ta, p0);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_AFULL(0, h));
+        continue;
+      }
       products(1, p1);
       if (!mbar_wait(BAR_AEMPTY(1, h), (uint32_t)((k & 1) ^ 1))) { report(34); ok = false; continue; }
       tc_fence_after();
@@ -664,10 +693,17 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
     if (ok) {
       float* st = a.state + (size_t)hc * a.per_state;
       const int m = warp >> 2;                       // one tile per group of four warps
+      const int o = other(m);
+      const bool warp_mine = m < ntile && (part < 4 || qd < 2);   // the TMEM read is a whole-warp instruction
+      const bool mine = warp_mine && (part < 4 || lane < 16);
       uint32_t tv[64];
-      tmem_ld64(tmem + m * 64 + ((uint32_t)(qd * 32) << 16), tv);
-      tmem_wait_ld();
-      const int f = (a0 + 2 * m + a_sub) * 64 + b;
+      if (warp_mine) {
+        tmem_ld64(tmem + m * 64 + ((uint32_t)(qd * 32) << 16), tv);
+        tmem_wait_ld();
+      }
+      // the pair's row goes to both of its places in the state, (b, other) and (other, b)
+      for (int side = 0; mine && side < (o == b ? 1 : 2); ++side) {
+      const int f = side == 0 ? b * 64 + o : o * 64 + b;
       float* dst = st + (size_t)f * a.dvp;
       const uint32_t ecol = __float_as_uint(st[(size_t)4096 * a.dvp + f]);   // column 64; 65..67 are padding (dvp == 68)
       // A thread owns its 272-byte row, so its stores share no sector with its neighbours': 32-byte stores
@@ -695,6 +731,7 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
           stg32(dst + 8 * e, w, true);
         }
         *(float4*)(dst + 64) = make_float4(__uint_as_float(ecol), 0.f, 0.f, 0.f);
+      }
       }
     }
   }
