@@ -68,7 +68,9 @@ FFMA_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12
 TRAFFIC_LIB_VERSION = 200
 # ncu DRAM bytes (read + write) per token-head, bf16, D = 64: the capture of the small case summarised in
 # profiles/dense_tc_small_case_ncu_full.md, scaled by heads x tokens
-NCU_BYTES_PER_TOKEN_HEAD = {"fm_dense_tc_fwd": 487.0, "fm_dense_tc_dq": 622.7, "fm_dense_tc_dkdv": 722.1}
+NCU_BYTES_PER_TOKEN_HEAD = {"fm_dense_tc_fwd": 487.0, "fm_dense_tc_dq": 622.7, "fm_dense_tc_dkdv": 722.1,
+                            # per token whose chunk builds a state (profiles/moments_tc_small_case_ncu_full.md)
+                            "fm_moments_tc_state": 717.5}
 
 
 def cfg_of(name):
@@ -550,7 +552,24 @@ def seq_leg(hz, args, cfg, steps, warmup, sample_clocks=False):
     return r
 
 
-def roofline_of(per, cfg, bh, peaks, lib_version):
+def moment_kernel_flops(name, D, N, mask, chunk):
+    """Products one launch of a tensor-core moment kernel needs, per batch*head unit (None: another kernel).
+    The state build forms each unordered pair of features once: D (D + 1) / 2 feature rows by D value columns
+    per token (the normaliser column comes from another kernel).  A read-out contracts a token's D x D features
+    with D + 1 columns.  Causal: one chunk builds no state and one reads none."""
+    L = chunk or 2048
+    nchunk = -(-N // L)
+    if name == "fm_moments_tc_state":
+        tokens = min(N, (nchunk - 1) * L) if mask else N
+        return 2 * (D * (D + 1) // 2) * D * tokens
+    reads = {"fm_moments_tc_readout_a": 1, "fm_moments_tc_readout_b": 1, "fm_moments_tc_readout_ab": 2}
+    if name in reads:
+        tokens = max(N - L, 0) if mask else N
+        return reads[name] * 2 * D * D * (D + 1) * tokens
+    return None
+
+
+def roofline_of(per, cfg, bh, peaks, lib_version, chunk=0):
     """Roofline record of the kernel with the largest share of the timed region."""
     B, H, N, D, dt, mask, p, norm = cfg
     if not per:
@@ -558,6 +577,19 @@ def roofline_of(per, cfg, bh, peaks, lib_version):
     dom = max(per, key=lambda n: per[n][1])
     cnt, tot = per[dom]
     ms = tot / cnt
+    mf = moment_kernel_flops(dom, D, N, mask, chunk) if (dt == "bf16" and p == 2) else None
+    if mf is not None:
+        flops = mf * bh
+        achieved = flops / (ms * 1e-3) / 1e12
+        traffic = None
+        if dom in NCU_BYTES_PER_TOKEN_HEAD and D == 64 and lib_version == TRAFFIC_LIB_VERSION:
+            traffic = NCU_BYTES_PER_TOKEN_HEAD[dom] * flops / moment_kernel_flops(dom, D, 1, 0, 1)
+        return {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
+                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": traffic,
+                "traffic_source": "ncu dram bytes of a small case scaled by heads x tokens" if traffic else None,
+                "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "ms_per_launch": ms,
+                "alg_flops_per_launch": flops,
+                "note": "useful products of this kernel alone; the step's rate is alg_tflops_per_gpu"}
     ff, fq, fkv = alg_flops_per_token_head(D, p)
     flops_of = {"fwd": ff, "dq": fq, "dkdv": fkv, "dk": fkv * 2 // 3, "dv": fkv // 3}
     kind = dom.rsplit("_", 1)[-1]
@@ -667,7 +699,7 @@ def run_ours(args):
             "clocks": main["clocks"], "gpu_launches": main["launches"],
             "alg_tflops_per_gpu": (ff + fq + fkv) * bh * N * args.steps / (ms * 1e-3) / 1e12,
             "kernels": _kernel_table(main["per"]),
-            "roofline": roofline_of(main["per"], cfg, bh, peaks, lib_version),
+            "roofline": roofline_of(main["per"], cfg, bh, peaks, lib_version, args.chunk),
             "e2e": None if e2e_ms is None else
                    {"value": tokens_job / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
                     "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": args.steps,

@@ -111,13 +111,14 @@ static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   if (!moments_supports(p)) return false;
   const double d = p.d, F = d + (p.p == 2 ? d * d : 0.0);
   // Constants fitted to this library's kernels on a B200 (bf16, d = 64, p = 2, causal): the score family takes
-  // 5.6 ns per token and head at 10^4 keys; the moment family 5.0 ns for its states and read-outs plus 2.0 ns
+  // 5.6 ns per token and head at 10^4 keys; the moment family 4.2 ns for its states and read-outs plus 2.0 ns
   // for the score kernels of a 2048-token chunk (short rows run at 0.58 of the long-row rate), the former
-  // times the share of chunks that build and read states.  The two families then break even near 11 k keys,
-  // as measured (10240: 22.5 against 24.5 ms; 12288: 27.7 against 25.8; 16384: 37.8 against 28.0 for the
-  // same number of token-heads).
+  // times the share of chunks that build and read states.  The two families then break even near 9 500 keys,
+  // as measured (score against moment family for the same number of token-heads, 8192 keys: 20.3 / 23.8 ms;
+  // 9216: 22.6 / 24.0; 10000: 60.8 / 57.5; 12288: 27.7 / 25.8 and 16384: 37.8 / 28.0 before the state build
+  // halved its products).
   const double rate_score = tc_ok ? 800e12 : 25e12;
-  const double rate_state = p.p == 2 ? (moments_tc_supports(p) ? 760e12 : 20e12) : (first_tc_supports(p) ? 450e12 : 20e12);
+  const double rate_state = p.p == 2 ? (moments_tc_supports(p) ? 900e12 : 20e12) : (first_tc_supports(p) ? 450e12 : 20e12);
   const double rate_chunk = tc_ok ? 0.58 * rate_score : rate_score;
   // Unmasked with nq != nk: the score form costs nq * nk pairs, the moment form one state per key and one
   // read-out per query row (and the mirror image backward), so per token of the mean length the score form
@@ -130,9 +131,9 @@ static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   const int L = moments_chunk(p);
   const double used = p.mask ? 1.0 - 1.0 / (double)((p.nk + L - 1) / L) : 1.0;
   double t_mom = used * 14.0 * F * (d + 1) / rate_state + chunk_keys * per_key / rate_chunk;
-  // unmasked: the fp32 result rows take one more pass (5.5 ns per token and head measured), and each head
+  // unmasked: the fp32 result rows take one more pass (5.5 ns per token and head in all), and each head
   // pays about a third of a chunk's time once, for its totals (break-even measured near 5 500 keys)
-  if (!p.mask) t_mom *= 1.1 * (1.0 + 0.33 * L / (0.5 * ((double)p.nq + p.nk)));
+  if (!p.mask) t_mom *= 1.3 * (1.0 + 0.33 * L / (0.5 * ((double)p.nq + p.nk)));
   return t_mom < t_score && p.nk > moments_chunk(p);
 }
 

@@ -556,6 +556,20 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       const int s = k % ST_NZ;
       if (!mbar_wait_warp(BAR_ZFULL(s), (uint32_t)((k / ST_NZ) & 1))) { report(32); ok = false; break; }
       const uint32_t z_lo = desc_lo(sbase + ST_OFF_Z + s * ST_ZTILE, ST_ZTILE) + (uint32_t)w * (4 * 128);
+      if (ntile == 1) {
+        // one tile: its four feature buffers are a ring over blocks, so that the threads that form the
+        // features run ahead of the products instead of waiting for each one
+        const int fb = k & 3;
+        if (!mbar_wait_warp(BAR_AFULL(fb, w), (uint32_t)((k >> 2) & 1))) { report(33); ok = false; break; }
+        if (k == 0 && w == 1 && !mbar_wait_warp(BAR_START(0), 0)) { report(36); ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {
+          umma_ts_steps<4>(tmem, tmem + ST_TM_A + fb * 64 + w * 32, z_lo, idesc, (k > 0 || w == 1) ? 1u : 0u);
+          umma_commit(BAR_AEMPTY(fb, w));
+          if (k == 0 && w == 0) umma_commit(BAR_START(0));
+        }
+        __syncwarp();
+      } else
       for (int m = 0; m < ntile; ++m) {
         if (!mbar_wait_warp(BAR_AFULL(m, w), (uint32_t)(k & 1))) { report(33); ok = false; break; }
         if (k == 0 && w == 1 && !mbar_wait_warp(BAR_START(m), 0)) { report(36); ok = false; break; }
@@ -657,13 +671,14 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       uint32_t p0[16], p1[16], p2[16], p3[16];
       products(0, p0);
       if (ntile == 1) {
-        if (!mbar_wait(BAR_AEMPTY(0, h), (uint32_t)((k & 1) ^ 1))) { report(34); ok = false; continue; }
+        const int fb = k & 3;                       // feature buffer of this block (a ring over blocks)
+        if (!mbar_wait(BAR_AEMPTY(fb, h), (uint32_t)(((k >> 2) & 1) ^ 1))) { report(34); ok = false; continue; }
         tc_fence_after();
-        tmem_st16(ta, p0);
+        tmem_st16(ta + 64 * fb, p0);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(BAR_AFULL(0, h));
+        if (lane == 0) mbar_arrive(BAR_AFULL(fb, h));
         continue;
       }
       products(1, p1);
@@ -688,14 +703,20 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
     }
     // ---- epilogue: accumulator rows -> fp32 state (columns 0..63), the normaliser column from the
     // block state_ecol_tc_kernel left in the first-order rows, zero padding ----
+    float* st = a.state + (size_t)hc * a.per_state;
+    const int m = warp >> 2;                       // one tile per group of four warps
+    const int o = other(m);
+    const bool warp_mine = m < ntile && (part < 4 || qd < 2);   // the TMEM read is a whole-warp instruction
+    const bool mine = warp_mine && (part < 4 || lane < 16);
+    // column 64 of the pair's two rows (65..67 are padding, dvp == 68), asked for before the wait for the products
+    uint32_t ecols[2] = {0u, 0u};
+    if (ok && mine) {
+      ecols[0] = __float_as_uint(st[(size_t)4096 * a.dvp + b * 64 + o]);
+      ecols[1] = __float_as_uint(st[(size_t)4096 * a.dvp + o * 64 + b]);
+    }
     if (ok && !mbar_wait(BAR_DONE(), 0)) { report(35); ok = false; }
     tc_fence_after();
     if (ok) {
-      float* st = a.state + (size_t)hc * a.per_state;
-      const int m = warp >> 2;                       // one tile per group of four warps
-      const int o = other(m);
-      const bool warp_mine = m < ntile && (part < 4 || qd < 2);   // the TMEM read is a whole-warp instruction
-      const bool mine = warp_mine && (part < 4 || lane < 16);
       uint32_t tv[64];
       if (warp_mine) {
         tmem_ld64(tmem + m * 64 + ((uint32_t)(qd * 32) << 16), tv);
@@ -705,7 +726,7 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
       for (int side = 0; mine && side < (o == b ? 1 : 2); ++side) {
       const int f = side == 0 ? b * 64 + o : o * 64 + b;
       float* dst = st + (size_t)f * a.dvp;
-      const uint32_t ecol = __float_as_uint(st[(size_t)4096 * a.dvp + f]);   // column 64; 65..67 are padding (dvp == 68)
+      const uint32_t ecol = ecols[side];
       // A thread owns its 272-byte row, so its stores share no sector with its neighbours': 32-byte stores
       // (whole sectors) wherever the row allows.  A row that starts on a 32-byte boundary is 8 x 32 + 16
       // bytes, one that starts 16 bytes past a boundary is 16 + 8 x 32 (rows and matrices are 16-byte multiples).
