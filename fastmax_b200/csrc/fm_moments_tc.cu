@@ -438,26 +438,30 @@ __global__ void __launch_bounds__(256) prefix_bf16t_kernel(const float* __restri
 
 // =====================================================================================
 // state build: T2[(a,b)][c] = sum_j y_j[a] y_j[b] z_j[c],  c < 64
-// One CTA owns 8 values of a -- four accumulator tiles of (2 a x 64 b) rows by 64 columns,
-// TMEM columns 0..255 -- for one chunk of one head and walks the chunk in blocks of 128
-// tokens.  The feature tiles are the A operand and live in tensor memory, never in shared
-// memory: TMEM lane (a, b) of tile m holds y[a] y[b] for the block's 128 tokens as 64 packed
-// bf16 pairs (columns 256 + 64 m ..), written by the threads that own the lane, and the
-// value tile that TMA delivered is the MN-major B operand of eight K=16 products per tile.
+// T2 is symmetric in (a, b), so each of the 2080 unordered pairs is formed once and its row is
+// written to both of its places: 17 tiles of 128 pairs instead of 32 tiles of ordered ones.
+// Five CTAs share one chunk of one head; four own four accumulator tiles of 128 pairs by 64
+// columns (TMEM columns 0..255), the fifth one tile (see the pair table in the kernel), and each
+// walks the chunk in blocks of 128 tokens.  The feature tiles are the A operand and live in
+// tensor memory, never in shared memory: a TMEM lane of tile m holds its pair's product
+// y[b] y[other] for the block's 128 tokens as 64 packed bf16 pairs (columns 256 + 64 m ..),
+// written by the threads that own the lane, and the value tile that TMA delivered is the
+// MN-major B operand of eight K=16 products per tile.
 //   The sixteen generator warps form two independent halves, one per 64 tokens of the block
 // (warps 0-7 and 8-15), each with its own named barrier, feature-buffer columns, mbarriers
 // and MMA issuer warp, so that the latency chain of one half (transpose, barrier, row reads,
 // TMEM stores, hand-off) overlaps that of the other.  A half first transposes its y rows
 // into shared memory (yT[feature][token]), so that a thread reads its own row b once, as
-// 16-byte vectors, and the row a of each tile as a broadcast; warp w covers the TMEM lane
-// quarter w % 4 and 32 tokens.  Shared-memory traffic per block is the transposition, 32 KB
-// of row reads and the tensor core's 64 KB of value-tile reads, a quarter of what feature
-// tiles staged in shared memory cost.  The y rows come straight from global memory into
+// 16-byte vectors, and the tile's other row per tile (one row for the whole warp where the pair
+// is feature x fixed feature, the warp's 32 rows rotated where it is a distance around the
+// ring); warp w covers the TMEM lane quarter w % 4 and 32 tokens.  Shared-memory traffic per
+// block is the transposition, the row reads and the tensor core's reads of the value tile, a
+// fraction of what feature tiles staged in shared memory cost.  The y rows come straight from global memory into
 // registers two blocks ahead; the producer warp asks for them in L2 earlier still.
 // =====================================================================================
 struct StArgs {
   const void* y;     // (heads, n, 64) bf16 feature source
-  float* state;      // (heads, nchunk, F, DVP) fp32; rows a*64+b, columns 0..63 are written
+  float* state;      // (heads, nchunk, F, DVP) fp32; rows a*64+b and b*64+a of each pair, columns 0..64 and padding
   int n, chunk, nchunk, dvp;
   size_t per_state;
   int skip_chunk;    // this chunk's state is not wanted (-1: none)
