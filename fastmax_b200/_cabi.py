@@ -18,7 +18,7 @@ F32, BF16 = 0, 1
 IMPL = {"auto": 0, "dense_ffma": 1, "dense_tc": 2, "moments": 3, "moments_ffma": 4}
 
 EXPORTS = (
-    "fastmax_b200_version", "fastmax_b200_last_error", "fastmax_b200_stats_bytes",
+    "fastmax_b200_version", "fastmax_b200_last_error", "fastmax_b200_stats_bytes", "fastmax_b200_selected_impl",
     "fastmax_b200_forward_workspace_bytes", "fastmax_b200_backward_workspace_bytes",
     "fastmax_b200_forward", "fastmax_b200_forward_packed", "fastmax_b200_backward",
     "fastmax_b200_forward_bt", "fastmax_b200_backward_bt", "fastmax_b200_bt_layout_supported",
@@ -64,6 +64,8 @@ def lib() -> ctypes.CDLL:
         for f in ("stats_bytes", "forward_workspace_bytes", "backward_workspace_bytes"):
             fn = getattr(L, "fastmax_b200_" + f)
             fn.restype, fn.argtypes = sz, [pp]
+        L.fastmax_b200_selected_impl.restype = ctypes.c_int
+        L.fastmax_b200_selected_impl.argtypes = [pp, ctypes.POINTER(ctypes.c_int32)]
         L.fastmax_b200_forward.restype = ctypes.c_int
         L.fastmax_b200_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.fastmax_b200_forward_packed.restype = ctypes.c_int
@@ -294,6 +296,15 @@ def forward_packed(q, k, v, *, mask, normalize, temperature=1.0, a0=1.0, a1=1.0,
                                            stats.data_ptr(), ws.data_ptr(), wsb, _stream(q))
     _check(rc, "fastmax_b200_forward_packed")
     return o, stats
+
+
+def selected_impl(prob: Problem) -> str:
+    """Name of the kernel family a call with this problem runs (host arithmetic only, no device needed)."""
+    got = ctypes.c_int32(0)
+    rc = lib().fastmax_b200_selected_impl(prob, ctypes.byref(got))
+    if rc:
+        raise RuntimeError(lib().fastmax_b200_last_error().decode())
+    return {v: k for k, v in IMPL.items()}[got.value]
 
 
 def workspace_bytes(q, k, **kw):

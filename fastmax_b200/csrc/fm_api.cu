@@ -289,6 +289,16 @@ size_t fastmax_b200_stats_bytes(const fastmax_problem* p) {
   return sizeof(stat_t) * (size_t)(p->bh + p->bhkv);
 }
 
+int fastmax_b200_selected_impl(const fastmax_problem* p, int32_t* impl) {
+  if (!impl) return fail(FASTMAX_E_ARG, "null impl pointer");
+  int rc = validate(p);
+  if (rc) return rc;
+  int got = 0;
+  if ((rc = pick_impl(*p, false, &got))) return rc;
+  *impl = got;
+  return FASTMAX_OK;
+}
+
 // Sized for the family the call will run: the moment family needs room for its states.
 size_t fastmax_b200_forward_workspace_bytes(const fastmax_problem* p) {
   if (validate(p)) return 0;

@@ -46,6 +46,35 @@ def test_version_and_size_queries_need_no_gpu():
     assert ctypes.sizeof(_cabi.Problem) == 64
 
 
+def test_family_selection_follows_the_measured_break_even_points():
+    """The library's choice of kernel family (host arithmetic, no device): tensor-core score kernels for short
+    rows, the moment family where it was measured faster -- causal bf16 p=2 d=64 from about 9 500 keys on (the
+    headline shape has 10 000), unmasked from about 5 500, p=1 at almost any length -- and never for a few
+    query rows against many keys; fp32 stays on the CUDA-core score kernels."""
+    def pick(**kw):
+        base = dict(dtype=_cabi.BF16, bh=1024, bhkv=1024, nq=10000, nk=10000, d=64, mask=1, normalize=1, p=2,
+                    impl=0, a0=1, a1=1, a2=0.5, lim=1, temperature=1)
+        base.update(kw)
+        return _cabi.selected_impl(_cabi.Problem(**base))
+
+    assert pick() == "moments"                                           # the headline shape
+    assert pick(nq=8192, nk=8192) == "dense_tc"
+    assert pick(nq=9216, nk=9216) == "dense_tc"
+    assert pick(nq=12288, nk=12288) == "moments"
+    assert pick(bh=32, bhkv=32, nq=262144, nk=262144) == "moments"       # the long-context configuration
+    assert pick(mask=0, nq=4096, nk=4096) == "dense_tc"
+    assert pick(mask=0, nq=6144, nk=6144) == "moments"
+    assert pick(mask=0, nq=256, nk=6000) == "dense_tc"                   # few query rows, many keys
+    assert pick(mask=0, nq=1, nk=100000) == "dense_tc"
+    assert pick(mask=0, p=1, d=128, nq=16384, nk=16384, normalize=0) == "moments"
+    assert pick(mask=0, d=128, nq=16384, nk=16384, normalize=0) == "dense_tc"
+    assert pick(dtype=_cabi.F32, d=32, nq=1000, nk=1000) == "dense_ffma"
+    assert pick(impl=_cabi.IMPL["dense_tc"]) == "dense_tc"               # a forced family is reported as such
+    assert pick(impl=_cabi.IMPL["moments_ffma"]) == "moments"
+    with pytest.raises(RuntimeError):
+        pick(impl=_cabi.IMPL["dense_tc"], dtype=_cabi.F32, d=32)
+
+
 def test_bad_arguments_are_rejected_before_any_launch():
     L = _cabi.lib()
     prob = _cabi.Problem(dtype=0, bh=2, bhkv=2, nq=4, nk=4, d=32, mask=1, normalize=0, p=3, impl=0,
