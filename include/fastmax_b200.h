@@ -132,9 +132,9 @@ size_t fastmax_b200_stats_bytes(const fastmax_problem* prob);
  * launching anything: one of FASTMAX_IMPL_DENSE_FFMA, FASTMAX_IMPL_DENSE_TC,
  * FASTMAX_IMPL_MOMENTS in *impl (prob->impl AUTO: the library's choice from its
  * rate model; a forced family: that family, or an error where it cannot serve the
- * problem).  Pure host arithmetic; needs no device.  The reference has one kernel
- * per mask/p combination and no such choice (reference fastmax_cuda_forward.cu:
- * 388-433). */
+ * problem).  Pure host arithmetic; needs no device.  The reference has one pair
+ * of kernels per mask setting and no such choice (reference
+ * fastmax_cuda_forward.cu:384-391). */
 int fastmax_b200_selected_impl(const fastmax_problem* prob, int32_t* impl);
 
 /* Bytes of scratch the forward / backward pass needs (may be 0). */
