@@ -163,3 +163,32 @@ def test_unmasked_shard_stage_calls_reproduce_the_unsharded_result(dtype, d, nor
     ref = oracle(*[t.float().cpu()[None] for t in (q, k, v, go)], dtype, dense=True, a0=1.0, a1=1.0, a2=0.5, lim=1.0,
                  **{n_: int(x_) for n_, x_ in kw.items()})
     assert_close([t.float().cpu()[None] for t in got], ref, dtype, "shard stages vs oracle")
+
+
+def test_second_order_state_rows_are_mirrored_and_match_the_definition():
+    """The tensor-core state build forms each unordered feature pair {a, b} once and writes the row to
+    both (a, b) and (b, a): the two rows must be bit-identical, every row must be written (ragged last
+    chunk included), and the total must equal sum_j k_j[a] k_j[b] v_j[c] -- with the products of two
+    bf16 values rounded to bf16, as the kernel forms them."""
+    dev = torch.device("cuda", 0)
+    bh, n, d = 3, 1000, 64
+    g = torch.Generator(device=dev).manual_seed(21)
+    k, v = [torch.randn(bh, n, d, generator=g, device=dev).bfloat16() for _ in range(2)]
+    be = CudaShardBackend(normalize=False, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2, chunk=256)
+    _, total = be.kv_state(k, v)
+    dvp, rows = 68, d * d + d + 1
+    assert total.numel() >= bh * rows * dvp                          # the size query rounds up to 256 bytes
+    t = total[:bh * rows * dvp].view(bh, rows, dvp)
+    s2 = t[:, :d * d, :d].reshape(bh, d, d, d)                     # [a][b][c]
+    assert torch.equal(s2, s2.transpose(1, 2))
+    e2 = t[:, :d * d, d].reshape(bh, d, d)                          # normaliser column
+    kf, vf = k.float(), v.float()
+    feat = (kf[:, :, :, None] * kf[:, :, None, :]).bfloat16().float()      # (bh, n, a, b), rounded like the kernel's
+    want = torch.einsum("hjab,hjc->habc", feat, vf)
+    scale = want.abs().max()
+    assert float((s2 - want).abs().max() / scale) < 2e-3
+    want_e = torch.einsum("hja,hjb->hab", kf, kf)
+    assert float((e2 - want_e).abs().max() / want_e.abs().max()) < 1e-2
+    s1 = t[:, d * d:d * d + d, :d]                                  # first-order rows
+    want1 = torch.einsum("hja,hjc->hac", kf, vf)
+    assert float((s1 - want1).abs().max() / want1.abs().max()) < 2e-3
