@@ -70,7 +70,13 @@ TRAFFIC_LIB_VERSION = 200
 # profiles/dense_tc_small_case_ncu_full.md, scaled by heads x tokens
 NCU_BYTES_PER_TOKEN_HEAD = {"fm_dense_tc_fwd": 487.0, "fm_dense_tc_dq": 622.7, "fm_dense_tc_dkdv": 722.1,
                             # per token whose chunk builds a state (profiles/moments_tc_small_case_ncu_full.md)
-                            "fm_moments_tc_state": 717.5}
+                            "fm_moments_tc_state": 717.5,
+                            # per token that is read out (same file, section on the read-outs' traffic)
+                            "fm_moments_tc_readout_a": 611.9, "fm_moments_tc_readout_b": 734.8,
+                            "fm_moments_tc_readout_ab": 972.2}
+# Labels that are launches of one kernel function: the roofline record is of the function with the largest share.
+KERNEL_OF_LABEL = {"fm_moments_tc_readout_a": "readout_tc_kernel", "fm_moments_tc_readout_b": "readout_tc_kernel",
+                   "fm_moments_tc_readout_ab": "readout_tc_kernel"}
 
 
 def cfg_of(name):
@@ -574,22 +580,32 @@ def roofline_of(per, cfg, bh, peaks, lib_version, chunk=0):
     B, H, N, D, dt, mask, p, norm = cfg
     if not per:
         return None
-    dom = max(per, key=lambda n: per[n][1])
-    cnt, tot = per[dom]
+    share = {}
+    for label, (c_, t_) in per.items():
+        fn = KERNEL_OF_LABEL.get(label, label)
+        share[fn] = share.get(fn, 0.0) + t_
+    dom = max(share, key=share.get)
+    labels = [n for n in per if KERNEL_OF_LABEL.get(n, n) == dom]
+    cnt, tot = sum(per[n][0] for n in labels), sum(per[n][1] for n in labels)
     ms = tot / cnt
-    mf = moment_kernel_flops(dom, D, N, mask, chunk) if (dt == "bf16" and p == 2) else None
-    if mf is not None:
-        flops = mf * bh
+    mfs = {n: moment_kernel_flops(n, D, N, mask, chunk) for n in labels} if (dt == "bf16" and p == 2) else {}
+    if mfs and all(v is not None for v in mfs.values()):
+        # per launch: the average over this function's launches of the step, of FLOPs and of time alike
+        flops = sum(per[n][0] * mfs[n] for n in labels) * bh / cnt
         achieved = flops / (ms * 1e-3) / 1e12
         traffic = None
-        if dom in NCU_BYTES_PER_TOKEN_HEAD and D == 64 and lib_version == TRAFFIC_LIB_VERSION:
-            traffic = NCU_BYTES_PER_TOKEN_HEAD[dom] * flops / moment_kernel_flops(dom, D, 1, 0, 1)
+        if all(n in NCU_BYTES_PER_TOKEN_HEAD for n in labels) and D == 64 and lib_version == TRAFFIC_LIB_VERSION:
+            traffic = sum(per[n][0] * NCU_BYTES_PER_TOKEN_HEAD[n] * mfs[n] / moment_kernel_flops(n, D, 1, 0, 1)
+                          for n in labels) * bh / cnt
+        if len(labels) > 1:
+            dom = dom + " (" + ", ".join(sorted(labels)) + ")"
         return {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": traffic,
                 "traffic_source": "ncu dram bytes of a small case scaled by heads x tokens" if traffic else None,
                 "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "ms_per_launch": ms,
                 "alg_flops_per_launch": flops,
-                "note": "useful products of this kernel alone; the step's rate is alg_tflops_per_gpu"}
+                "note": "products this kernel's own formulation needs (read-out: ordered feature pairs; state build: "
+                        "unordered ones), averaged over its launches of the step; the step's rate is alg_tflops_per_gpu"}
     ff, fq, fkv = alg_flops_per_token_head(D, p)
     flops_of = {"fwd": ff, "dq": fq, "dkdv": fkv, "dk": fkv * 2 // 3, "dv": fkv // 3}
     kind = dom.rsplit("_", 1)[-1]
