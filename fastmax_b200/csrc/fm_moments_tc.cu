@@ -14,9 +14,9 @@
 //   backward loops) by a GEMM of the raw token tile against the state.
 //
 // state    -- T2[(a,b)][c] = sum_j y_j[a] y_j[b] z_j[c] over the tokens of a chunk: the
-//   features y_a y_b are generated on the CUDA cores into shared memory as the
-//   MN-major A operand, the value tile is the MN-major B operand delivered by TMA,
-//   and the accumulators stay in tensor memory for the whole chunk.
+//   features y_a y_b (each unordered pair once) are formed on the CUDA cores and written
+//   to tensor memory as the A operand, the value tile is the MN-major B operand delivered
+//   by TMA, and the accumulators stay in tensor memory for the whole chunk.
 //
 // The normaliser column of the state build is a third, small tensor-core kernel here; the
 // first-order and constant rows of the state stay on the kernels of fm_first_tc.cu and
@@ -605,9 +605,8 @@ state_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const StArgs a) {
     const int grp = part == 0 ? 0 : (part < 4 ? 1 : (qd & 1));
     const int b = grp * 32 + lane;
     const int o_off = (part == 3 || part == 4) ? grp * 32 : 0;
-    const int o_lane = (part == 1 || part == 2) ? 0 : lane;
-    const int o_c0 = part == 4 ? 16 : (part == 2 ? 16 + qd : qd);
-    auto other = [&](int m) { return o_off + ((o_lane + o_c0 + 4 * m) & 31); };
+    const int o_sum = ((part == 1 || part == 2) ? 0 : lane) + (part == 4 ? 16 : (part == 2 ? 16 + qd : qd));
+    auto other = [&](int m) { return o_off + ((o_sum + 4 * m) & 31); };
     const int tok_off = h * 64 + tq * 32;           // first of this warp's 32 tokens in the block
     // transposition duty inside the half: token pair jp (of 32) and 8 features from fg * 8
     const int jp = tid & 31, fg = (tid >> 5) & 7;
