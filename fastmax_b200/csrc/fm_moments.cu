@@ -111,10 +111,9 @@ static int read_states(const Ctx& c, int mode, int n, int per_chunk, const void*
   const int mats = p.bh * (per_chunk ? (n + L - 1) / L : 1);
   if (tc2) {
     if (!second16 && (rc = moments_tc_convert(c, mats, states, s16))) return rc;
-    // type A comes out complete (first-order and constant terms included), type B second-order only
-    if ((rc = moments_tc_readout(c, mode, p.bh, n, L, per_chunk, x, ext ? gs : u, ext ? dvec : nullptr,
-                                 second16 ? second16 : s16, stats, out_a, den_a, out_b, states)))
-      return rc;
+    // both kinds come out complete: the first-order and constant terms ride on the copy's last rows
+    return moments_tc_readout(c, mode, p.bh, n, L, per_chunk, x, ext ? gs : u, ext ? dvec : nullptr,
+                              second16 ? second16 : s16, stats, out_a, den_a, out_b, states);
   }
   if (tc1) {
     // first-order part on tensor cores; it adds to the second-order part when there is one

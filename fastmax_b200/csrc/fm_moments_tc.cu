@@ -35,7 +35,7 @@ using namespace sm100;
 
 constexpr int D = 64;
 constexpr int NROWS_T = 65 * 64;          // rows (c, b) of the transposed bf16 state
-constexpr int NROWS_TP = 33 * 128;        // padded to whole 128-row tiles
+constexpr int NROWS_TP = 34 * 128;        // the first-order blocks (see first_rows_to_bf16t) and padding to whole 128-row tiles
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_mtc_status, 0, code); }
 // 16 bytes from / 4 bytes to shared memory by shared-window address (keeps the access off the generic path)
@@ -70,6 +70,9 @@ struct RtArgs {
   size_t per_state;
   int dvp;
   float a0, a1;
+  // Type B does the same with one more slice: u . S1[a][0..63] from the tensor core (the copy's rows 66*64..,
+  // the u tile as the A operand) plus e * S1[a][64] from the fp32 state.
+  int first_b;
   int mode;            // 0: type A on two token tiles, 1: type B on two token tiles,
                        // 2: one token tile, group 0 type A and group 1 type B
 };
@@ -79,7 +82,8 @@ constexpr int RT_NS = 4;          // state-tile ring stages
 constexpr int RT_TILE = 128 * D * 2;
 constexpr int RT_OFF_X = 0;                         // two token tiles
 constexpr int RT_OFF_ST = 2 * RT_TILE;              // ring
-constexpr int RT_OFF_UT = RT_OFF_ST + RT_NS * RT_TILE;   // [2][128][66] fp32 (type B operand rows)
+constexpr int RT_OFF_U = RT_OFF_ST + RT_NS * RT_TILE;    // two u tiles (type B with the first-order slice)
+constexpr int RT_OFF_UT = RT_OFF_U + 2 * RT_TILE;        // [2][128][66] fp32 (type B operand rows)
 constexpr int RT_UT_LD = 66;
 constexpr int RT_OFF_BAR = RT_OFF_UT + 2 * 128 * RT_UT_LD * 4;
 constexpr int RT_NBAR = 1 + 2 * RT_NS + 8;
@@ -87,11 +91,11 @@ constexpr int RT_OFF_TMEM = RT_OFF_BAR + RT_NBAR * 8;
 constexpr int RT_OFF_VEC = RT_OFF_TMEM + 16;        // per type-A group: constant row [65] | S1 normaliser column [64]
 constexpr int RT_VEC = 132;
 constexpr int RT_SMEM = RT_OFF_VEC + 2 * RT_VEC * 4 + 1024;
-constexpr int RT_NT = NROWS_TP / 128;               // 33 slices of 128 columns of T
+constexpr int RT_NT = 33;                           // slices of 128 columns of T; slice 33 is type B's first-order one
 
 __global__ void __launch_bounds__(RT_THREADS, 1)
 readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmS,
-                  const RtArgs a) {
+                  const __grid_constant__ CUtensorMap tmU, const RtArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -113,6 +117,7 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   const int chunk = a.state_per_chunk ? tok0 / a.chunk : 0;
   const int srow = head * (a.state_per_chunk ? a.nchunk : 1) + chunk;   // index of the state matrix
   const int readers = (a.mode == 2) ? 8 : 4;                            // warps that read each T buffer
+  const int nslice = RT_NT + (a.first_b ? 1 : 0);
   if (a.state_per_chunk && chunk == a.zero_chunk) {
     // the whole CTA lies in one chunk (chunks are multiples of 256 tokens): zero rows, no products
     const int rows = min(128 * tiles_per_cta, a.n - tok0);
@@ -144,10 +149,14 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     if (lane == 0) {
       tma_prefetch_desc(&tmX);
       tma_prefetch_desc(&tmS);
-      mbar_expect_tx(BAR_X(), ntile * RT_TILE);
+      mbar_expect_tx(BAR_X(), (a.first_b ? 2 : 1) * ntile * RT_TILE);
       for (int t = 0; t < ntile; ++t) tma_load_3d(sbase + RT_OFF_X + t * RT_TILE, &tmX, BAR_X(), 0, tok0 + t * 128, head);
+      if (a.first_b) {
+        tma_prefetch_desc(&tmU);
+        for (int t = 0; t < ntile; ++t) tma_load_3d(sbase + RT_OFF_U + t * RT_TILE, &tmU, BAR_X(), 0, tok0 + t * 128, head);
+      }
     }
-    for (int n = 0; n < RT_NT; ++n) {
+    for (int n = 0; n < nslice; ++n) {
       const int s = n % RT_NS;
       if (!mbar_wait(BAR_EMPTY(s), (((n / RT_NS) & 1) ^ 1))) { report(21); break; }
       if (lane == 0) {
@@ -171,14 +180,15 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const uint32_t st0 = desc_lo(sbase + RT_OFF_ST, 16);
       const int t = one_tile ? 0 : w;
       const uint32_t x_lo = desc_lo(sbase + RT_OFF_X + t * RT_TILE, 16);
-      for (int n = one_tile ? w : 0; ok && n < RT_NT; n += one_tile ? 2 : 1) {
+      const uint32_t u_lo = desc_lo(sbase + RT_OFF_U + t * RT_TILE, 16);
+      for (int n = one_tile ? w : 0; ok && n < nslice; n += one_tile ? 2 : 1) {
         const int s = n % RT_NS, buf = n & 1;
         if (!mbar_wait_warp(BAR_FULL(s), (uint32_t)((n / RT_NS) & 1))) { report(23); break; }
         // the buffer was last used by slice n-2
         if (n >= 2 && !mbar_wait_warp(BAR_TFREE(t, buf), (uint32_t)(((n >> 1) - 1) & 1))) { report(24); break; }
         tc_fence_after();
         if (elect_one()) {
-          umma_ss_k64(tmem + t * 256 + buf * 128, x_lo, st0 + (uint32_t)s * (RT_TILE >> 4), idesc);
+          umma_ss_k64(tmem + t * 256 + buf * 128, n < RT_NT ? x_lo : u_lo, st0 + (uint32_t)s * (RT_TILE >> 4), idesc);
           umma_commit(BAR_TFULL(t, buf));
           umma_commit(BAR_EMPTY(s));
         }
@@ -231,9 +241,11 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         for (int e = 0; e < 32; ++e) xa[e] = pack2(0.f, 0.f);
       }
       const bool first_too = !type_b && a.state_f32 != nullptr;
+      const bool first_b = type_b && a.first_b != 0;
       const float A1f = a.a1 * c;
+      float k_out = 2.f * A2;                                  // type B: factor of the running sums at the end
       float* vec = (float*)(smem + RT_OFF_VEC) + g * RT_VEC;   // crow[0..64] | ncol[0..63]
-      if (first_too) {
+      if (first_too || first_b) {
         // the group's 128 threads stage the two vectors of this CTA's state (all of them reach the barrier:
         // a group is of one kind)
         const float* fs = a.state_f32 + (size_t)srow * a.per_state + (size_t)(64 * 64) * a.dvp;   // first-order rows
@@ -244,10 +256,29 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         else asm volatile("bar.sync 2, 128;" ::: "memory");
       }
       bool ok = true;
-      for (int n = 0; n < RT_NT; ++n) {
+      for (int n = 0; n < nslice; ++n) {
         const int buf = n & 1;
+        if (n == RT_NT && !type_b) break;     // the last slice is type B's alone (nothing waits for its release)
         if (!mbar_wait(BAR_TFULL(t, buf), (uint32_t)((n >> 1) & 1))) { report(25); ok = false; break; }
         tc_fence_after();
+        if (n == RT_NT) {
+          // first-order slice: T1[a] = u . S1[a][0..63] in the first 64 columns; the running sums take their
+          // final factor here and the first-order term joins them
+          uint32_t tv[64];
+          tmem_ld64(tbase + buf * 128, tv);
+          tmem_wait_ld();
+          const float ue = ut[64];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float f0, f1;
+            unpack2(xa[e], f0, f1);
+            f0 = fmaf(k_out, f0, A1f * fmaf(ue, vec[65 + 2 * e], __uint_as_float(tv[2 * e])));
+            f1 = fmaf(k_out, f1, A1f * fmaf(ue, vec[66 + 2 * e], __uint_as_float(tv[2 * e + 1])));
+            xa[e] = pack2(f0, f1);
+          }
+          k_out = 1.f;
+          break;
+        }
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const int cidx = 2 * n + hf;       // column c of the state this half belongs to
@@ -301,7 +332,7 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (a.den_a) a.den_a[grow] = ut[64];
       }
       if (ok && type_b && tok_ok) {
-        const float k2 = 2.f * A2;
+        const float k2 = k_out;
         float* dst = a.out_b + grow * D;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -331,7 +362,11 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 //   out[m][c*64 + b][a] = state[m][(b*64 + a)][c]      (S2 is symmetric in a, b)
 // one CTA per (state matrix m, b).  The 64 rows past 65*64 hold the first-order block the same way,
 //   out[m][65*64 + c][a] = state[m][64*64 + a][c],  c < 64
-// so that the read-out's last slice yields x . S1 beside the normaliser column's second-order part.
+// so that the read-out's last slice yields x . S1 beside the normaliser column's second-order part, and the
+// 64 rows after those hold it untransposed,
+//   out[m][66*64 + a][c] = state[m][64*64 + a][c],  c < 64
+// the B operand of type B's first-order slice (u . S1[a][:]).  The remaining 64 rows of the last tile are
+// never written; the columns of T they produce are never read.
 // =====================================================================================
 // rows 65*64 .. 65*64 + 63 of one copy from the (summed) first-order rows of its fp32 state
 __device__ __forceinline__ void first_rows_to_bf16t(const float* __restrict__ st, __nv_bfloat16* __restrict__ o,
@@ -342,6 +377,7 @@ __device__ __forceinline__ void first_rows_to_bf16t(const float* __restrict__ st
   uint32_t* ow = (uint32_t*)(o + (size_t)NROWS_T * 64);
   for (int w = t; w < 64 * 32; w += 256) {
     const int cc = w >> 5, ap = (w & 31) * 2;
+    ow[64 * 32 + w] = pack_bf16(blk[cc][ap], blk[cc][ap + 1]);     // rows 66*64 + a: S1[a][c], c contiguous (type B)
     ow[cc * 32 + (w & 31)] = pack_bf16(blk[ap][cc], blk[ap + 1][cc]);
   }
   __syncthreads();
@@ -1030,11 +1066,14 @@ int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int 
   if (heads == 0 || n == 0) return FASTMAX_OK;
   const fastmax_problem& p = c.p;
   const int nchunk = (n + chunk - 1) / chunk;
-  CUtensorMap tx, ts;
+  CUtensorMap tx, ts, tu;
   int rc;
+  const bool first_b = mode != 0 && state_f32 != nullptr && u != nullptr;
   if ((rc = make_map(&tx, x, heads, n))) return rc;
+  if ((rc = make_map(&tu, first_b ? u : x, heads, n))) return rc;
   if ((rc = make_map(&ts, state_bf16, (size_t)heads * (state_per_chunk ? nchunk : 1), NROWS_TP))) return rc;
   RtArgs a;
+  a.first_b = first_b ? 1 : 0;
   a.x = x; a.u = u; a.uvec = uvec; a.out_a = out_a; a.den_a = den_a; a.out_b = out_b;
   a.stat_q = p.normalize ? stats : nullptr;
   a.stat_k = p.normalize ? stats + p.bh : nullptr;
@@ -1049,7 +1088,7 @@ int moments_tc_readout(const Ctx& c, int mode, int heads, int n, int chunk, int 
   FM_CUDA_TRY(cudaFuncSetAttribute(readout_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));
   static const char* const names[3] = {"fm_moments_tc_readout_a", "fm_moments_tc_readout_b",
                                        "fm_moments_tc_readout_ab"};
-  FM_LAUNCH(names[mode], c.stream, (readout_tc_kernel<<<grid, RT_THREADS, RT_SMEM, c.stream>>>(tx, ts, a)));
+  FM_LAUNCH(names[mode], c.stream, (readout_tc_kernel<<<grid, RT_THREADS, RT_SMEM, c.stream>>>(tx, ts, tu, a)));
   FM_CUDA_TRY(cudaGetLastError());
   return FASTMAX_OK;
 }
