@@ -111,14 +111,13 @@ static bool moments_faster(const fastmax_problem& p, bool tc_ok) {
   if (!moments_supports(p)) return false;
   const double d = p.d, F = d + (p.p == 2 ? d * d : 0.0);
   // Constants fitted to this library's kernels on a B200 (bf16, d = 64, p = 2, causal): the score family takes
-  // 5.6 ns per token and head at 10^4 keys; the moment family 4.2 ns for its states and read-outs plus 2.0 ns
+  // 5.6 ns per token and head at 10^4 keys; the moment family 4.1 ns for its states and read-outs plus 2.0 ns
   // for the score kernels of a 2048-token chunk (short rows run at 0.58 of the long-row rate), the former
-  // times the share of chunks that build and read states.  The two families then break even near 9 500 keys,
-  // as measured (score against moment family for the same number of token-heads, 8192 keys: 20.3 / 23.8 ms;
-  // 9216: 22.6 / 24.0; 10000: 60.8 / 57.5; 12288: 27.7 / 25.8 and 16384: 37.8 / 28.0 before the state build
-  // halved its products).
+  // times the share of chunks that build and read states.  The two families then break even near 9 300 keys,
+  // as measured (score against moment family for the same number of token-heads, 8192 keys: 20.3 / 22.8 ms;
+  // 9216: 22.6 / 23.0; 10000: 60.9 / 54.5).
   const double rate_score = tc_ok ? 800e12 : 25e12;
-  const double rate_state = p.p == 2 ? (moments_tc_supports(p) ? 900e12 : 20e12) : (first_tc_supports(p) ? 450e12 : 20e12);
+  const double rate_state = p.p == 2 ? (moments_tc_supports(p) ? 930e12 : 20e12) : (first_tc_supports(p) ? 450e12 : 20e12);
   const double rate_chunk = tc_ok ? 0.58 * rate_score : rate_score;
   // Unmasked with nq != nk: the score form costs nq * nk pairs, the moment form one state per key and one
   // read-out per query row (and the mirror image backward), so per token of the mean length the score form
