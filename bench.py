@@ -72,8 +72,8 @@ NCU_BYTES_PER_TOKEN_HEAD = {"fm_dense_tc_fwd": 487.0, "fm_dense_tc_dq": 622.7, "
                             # per token whose chunk builds a state (profiles/moments_tc_small_case_ncu_full.md)
                             "fm_moments_tc_state": 717.5,
                             # per token that is read out (same file, section on the read-outs' traffic)
-                            "fm_moments_tc_readout_a": 611.9, "fm_moments_tc_readout_b": 734.8,
-                            "fm_moments_tc_readout_ab": 972.2}
+                            "fm_moments_tc_readout_a": 608.2, "fm_moments_tc_readout_b": 742.4,
+                            "fm_moments_tc_readout_ab": 976.1}
 # Labels that are launches of one kernel function: the roofline record is of the function with the largest share.
 KERNEL_OF_LABEL = {"fm_moments_tc_readout_a": "readout_tc_kernel", "fm_moments_tc_readout_b": "readout_tc_kernel",
                    "fm_moments_tc_readout_ab": "readout_tc_kernel"}
